@@ -1,0 +1,84 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, warp and
+// block reductions, the C calling convention of the library.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes
+// and a stream, launches on that stream and returns the cudaError_t of the
+// launch as an int (0 = success).  Element types are passed as codes:
+// 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <math.h>
+
+#define IFX_API extern "C" __attribute__((visibility("default")))
+
+enum IfxDtype : int { IFX_F32 = 0, IFX_BF16 = 1 };
+
+// Error codes above the CUDA range, returned for arguments a kernel refuses.
+enum IfxError : int {
+  IFX_ERR_UNSUPPORTED = 100001,   // a size or type the kernel does not take
+  IFX_ERR_ALIGNMENT = 100002,     // a pointer or stride that breaks an alignment rule
+};
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> struct Num;
+template <> struct Num<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct Num<bf16> {
+  static __device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ bf16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The
+// order of additions depends only on blockDim, so a row's result does not
+// depend on what else is in the batch.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : 0.0f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// Description of one layer's slice of a paged key/value pool laid out as
+// [page][layer][k|v][kv_head][slot_in_page][head_dim].
+struct PagedKV {
+  void* k;                 // this layer's keys of page 0
+  void* v;                 // this layer's values of page 0
+  long long page_stride;   // elements between consecutive pages
+  int head_stride;         // elements between kv heads = page_size * head_dim
+  int page_size;           // tokens per page (a power of two)
+  int page_shift;          // log2(page_size)
+};
+
+#define IFX_LAUNCH_CHECK() ((int)cudaGetLastError())

@@ -1,0 +1,117 @@
+// Rotary position encoding (rotate-half) fused with the q/k/v bias add and
+// the write of keys and values into the paged cache.
+//
+// Reference formulas (runtime/backends/cuda/native/cuda_kernels.cu:70-115,
+// rope_type 2 = split-half pairs): for i in [0, d/2):
+//   f = 1 / pow(theta, 2 i / d),  a = pos * f,
+//   (x_i, x_{i+d/2}) <- (x_i cos a - x_{i+d/2} sin a,  x_i sin a + x_{i+d/2} cos a)
+// applied to q and k; biases are added first (cuda_kernels.cu:694-723), then
+// the rotated k and the v row go to the cache
+// (runtime/backends/cuda/native/kernels/fused_rope_kv_append.cuh:26-166 does
+// this for decode only, with powf/cosf/sinf per element and a dense cache).
+//
+// Here the angles are computed once per step for all layers (cos/sin tables
+// per token, in double precision rounded to float32), and one kernel per layer
+// does bias + rotation + paged write for prompts and decoded tokens alike.
+#include "common.cuh"
+
+// cos/sin tables [n_tokens, half] from positions and inverse frequencies.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n_tokens, int half) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_tokens * half) return;
+  const int t = idx / half, i = idx - t * half;
+  const double a = (double)positions[t] * inv_freq[i];
+  double s, c;
+  sincos(a, &s, &c);
+  cos_t[idx] = (float)c;
+  sin_t[idx] = (float)s;
+}
+
+IFX_API int ifx_rope_table(const int* positions, const double* inv_freq, float* cos_t, float* sin_t,
+                           int n_tokens, int half, cudaStream_t stream) {
+  const int total = n_tokens * half;
+  if (total <= 0) return 0;
+  rope_table_kernel<<<(total + 127) / 128, 128, 0, stream>>>(positions, inv_freq, cos_t, sin_t, n_tokens, half);
+  return IFX_LAUNCH_CHECK();
+}
+
+// qkv: [n_tokens, (n_heads + 2 n_kv) * head_dim], q heads first, then k, then v.
+// q is rotated in place; k (rotated) and v go to the cache at slot_map[t]
+// (= page * page_size + offset; negative = do not store).  n_kv may be 0 (a
+// layer that reads another layer's cache has only q).
+template <typename T>
+__global__ void qkv_rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                         int rot_half, const int* __restrict__ slot_map, PagedKV kv,
+                                         int n_heads, int n_kv, int head_dim) {
+  const int t = blockIdx.x;
+  const int width = (n_heads + 2 * n_kv) * head_dim;
+  T* row = qkv + (size_t)t * width;
+  const float* ct = cos_t + (size_t)t * rot_half;
+  const float* st = sin_t + (size_t)t * rot_half;
+  const int slot = n_kv ? slot_map[t] : -1;
+  const long long page = slot >= 0 ? (slot >> kv.page_shift) : 0;
+  const int off = slot & (kv.page_size - 1);
+  T* kc = (T*)kv.k;
+  T* vc = (T*)kv.v;
+  const int half_dim = head_dim / 2;
+  // q and k heads: one work item per (head, i < head_dim/2): elements i and i + rot_half
+  // when i < rot_half (rotated), and the tail beyond 2*rot_half unrotated.
+  const int rot_heads = n_heads + n_kv;
+  for (int w = threadIdx.x; w < rot_heads * half_dim; w += blockDim.x) {
+    const int h = w / half_dim, i = w - h * half_dim;
+    const int base = h * head_dim;
+    int i0, i1;
+    float c = 1.0f, s = 0.0f;
+    if (i < rot_half) {
+      i0 = i; i1 = i + rot_half; c = ct[i]; s = st[i];
+    } else {             // unrotated tail: pair up the remaining dims two by two
+      i0 = 2 * rot_half + 2 * (i - rot_half); i1 = i0 + 1;
+    }
+    float x0 = Num<T>::to_f(row[base + i0]);
+    float x1 = Num<T>::to_f(row[base + i1]);
+    if (bias) { x0 += bias[base + i0]; x1 += bias[base + i1]; }
+    const T y0 = Num<T>::from_f(x0 * c - x1 * s);
+    const T y1 = Num<T>::from_f(x0 * s + x1 * c);
+    if (h < n_heads) {
+      row[base + i0] = y0; row[base + i1] = y1;
+    } else if (slot >= 0) {
+      T* dst = kc + page * kv.page_stride + (size_t)(h - n_heads) * kv.head_stride + (size_t)off * head_dim;
+      dst[i0] = y0; dst[i1] = y1;
+    }
+  }
+  if (slot >= 0) {
+    const int vbase = (n_heads + n_kv) * head_dim;
+    for (int w = threadIdx.x; w < n_kv * head_dim; w += blockDim.x) {
+      const int h = w / head_dim, d = w - h * head_dim;
+      float x = Num<T>::to_f(row[vbase + w]);
+      if (bias) x += bias[vbase + w];
+      vc[page * kv.page_stride + (size_t)h * kv.head_stride + (size_t)off * head_dim + d] = Num<T>::from_f(x);
+    }
+  }
+}
+
+IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const float* cos_t, const float* sin_t,
+                                  int rot_dim, const int* slot_map, void* k_layer, void* v_layer,
+                                  long long page_stride, int page_size, int n_tokens, int n_heads, int n_kv,
+                                  int head_dim, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (head_dim % 2 || rot_dim % 2 || rot_dim > head_dim || rot_dim < 0) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  PagedKV kv;
+  kv.k = k_layer; kv.v = v_layer; kv.page_stride = page_stride;
+  kv.head_stride = page_size * head_dim; kv.page_size = page_size;
+  kv.page_shift = 0;
+  while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
+  const int work = (n_heads + 2 * n_kv) * head_dim / 2;
+  int threads = 64;
+  while (threads < 512 && threads * 4 < work) threads <<= 1;
+  if (dtype == IFX_F32)
+    qkv_rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, bias, cos_t, sin_t, rot_dim / 2, slot_map, kv, n_heads, n_kv, head_dim);
+  else if (dtype == IFX_BF16)
+    qkv_rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, bias, cos_t, sin_t, rot_dim / 2, slot_map, kv, n_heads, n_kv, head_dim);
+  else
+    return IFX_ERR_UNSUPPORTED;
+  return IFX_LAUNCH_CHECK();
+}

@@ -1,0 +1,222 @@
+// Token selection from float32 logits: argmax, repetition / frequency /
+// presence penalties, and temperature sampling with top-k, top-p and min-p.
+//
+// Reference behaviour (runtime/backends/cuda/native/gpu_sampler.cu):
+//   greedy      argmax over the row (:124-156, one block of 256, ties by thread order)
+//   penalties   logit > 0 ? logit / rep : logit * rep;  -= freq * count;  -= pres if count > 0 (:22-48)
+//   temperature softmax(logits / T) in three passes by one block (:216-267)
+//   top-p       repeated arg-max until the cumulative probability reaches p (:273-330)
+//   draw        one thread walks the cumulative sum against one uniform (:374-401)
+// Here one block of 1024 threads serves a row, rows run in parallel, greedy
+// returns the lowest index among equal maxima, top-k/top-p/min-p become a
+// probability threshold found by bisection on the float bit pattern, and the
+// uniform comes from a counter-based generator keyed by (seed, counter) so a
+// request's draws do not depend on the batch it is in.
+//
+// Scratch: `weights` [n_rows, vocab] float32 holds exp(logit/T - max).
+#include "common.cuh"
+
+namespace {
+constexpr int ST = 1024;
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+// uniform in [0, 1) with 24 bits, from (seed, counter)
+__device__ __forceinline__ float uniform01(unsigned long long seed, unsigned long long counter) {
+  const unsigned long long x = mix64(mix64(seed) ^ (counter * 0xD1342543DE82EF95ull + 0x632BE59BD9B4E019ull));
+  return (float)(x >> 40) * (1.0f / 16777216.0f);
+}
+
+struct ArgPair { float v; int i; };
+__device__ __forceinline__ ArgPair better(ArgPair a, ArgPair b) {
+  // larger value wins; equal values: lower index wins; NaN never wins
+  if (b.i >= 0 && (a.i < 0 || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
+  return a;
+}
+__device__ ArgPair block_argmax(const float* row, int n, ArgPair* scratch) {
+  ArgPair best{-INFINITY, -1};
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = row[i];
+    if (v == v) best = better(best, ArgPair{v, i});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = best;
+  __syncthreads();
+  best = lane < nwarps ? scratch[lane] : ArgPair{-INFINITY, -1};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  return best;
+}
+
+__global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ logits, long long row_stride,
+                                                    int* __restrict__ out, int vocab) {
+  __shared__ ArgPair scratch[32];
+  const ArgPair b = block_argmax(logits + (size_t)blockIdx.x * row_stride, vocab, scratch);
+  if (threadIdx.x == 0) out[blockIdx.x] = b.i < 0 ? 0 : b.i;
+}
+
+// recent_ids / recent_counts: [n_rows, max_recent]; n_recent[row] entries are valid, ids distinct.
+__global__ void penalties_kernel(float* __restrict__ logits, long long row_stride, const int* __restrict__ recent_ids,
+                                 const int* __restrict__ recent_counts, const int* __restrict__ n_recent,
+                                 int max_recent, const float* __restrict__ rep, const float* __restrict__ freq,
+                                 const float* __restrict__ pres, int vocab) {
+  const int row = blockIdx.x;
+  float* lg = logits + (size_t)row * row_stride;
+  const int n = min(n_recent[row], max_recent);
+  for (int k = threadIdx.x; k < n; k += blockDim.x) {
+    const int id = recent_ids[(size_t)row * max_recent + k];
+    if (id < 0 || id >= vocab) continue;
+    const int count = recent_counts[(size_t)row * max_recent + k];
+    float v = lg[id];
+    const float r = rep[row];
+    v = v > 0.0f ? v / r : v * r;
+    v -= freq[row] * (float)count;
+    if (count > 0) v -= pres[row];
+    lg[id] = v;
+  }
+}
+
+// sum / count over the entries whose weight bits are >= bits
+__device__ __forceinline__ void block_sum_count_ge(const float* w, int n, unsigned bits, float* red,
+                                                   float* sum_out, int* count_out) {
+  float s = 0.0f;
+  int c = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = w[i];
+    if (__float_as_uint(v) >= bits) { s += v; ++c; }
+  }
+  *sum_out = block_sum(s, red);
+  *count_out = (int)(block_sum((float)c, red) + 0.5f);   // exact below 2^24 entries
+}
+
+__global__ void __launch_bounds__(ST)
+sample_kernel(const float* __restrict__ logits, long long row_stride, float* __restrict__ weights,
+              const float* __restrict__ temperature, const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ min_p, const unsigned long long* __restrict__ seeds,
+              const unsigned long long* __restrict__ counters, int* __restrict__ out, int vocab) {
+  __shared__ ArgPair ascratch[32];
+  __shared__ float red[32];
+  __shared__ float seg_prefix[ST];
+  __shared__ int chosen;
+  const int row = blockIdx.x;
+  const float* lg = logits + (size_t)row * row_stride;
+  const float temp = temperature[row];
+  const ArgPair top = block_argmax(lg, vocab, ascratch);
+  if (temp <= 0.0f || top.i < 0) {
+    if (threadIdx.x == 0) out[row] = top.i < 0 ? 0 : top.i;
+    return;
+  }
+  float* w = weights + (size_t)row * vocab;
+  const float inv_t = 1.0f / temp;
+  const float mx = top.v * inv_t;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = lg[i];
+    w[i] = (v == v) ? expf(v * inv_t - mx) : 0.0f;     // in [0, 1], the maximum is exactly 1
+  }
+  __syncthreads();
+  unsigned thr = 0u;                                    // keep entries with weight bits >= thr
+  float kept_sum;
+  int kept_count;
+  const int k = top_k[row];
+  if (k > 0 && k < vocab) {                             // largest threshold that keeps at least k entries
+    unsigned lo = 0u, hi = 0x3F800000u;                 // bits of 0.0 .. 1.0
+    while (lo < hi) {
+      const unsigned mid = lo + (hi - lo + 1u) / 2u;
+      block_sum_count_ge(w, vocab, mid, red, &kept_sum, &kept_count);
+      if (kept_count >= k) lo = mid; else hi = mid - 1u;
+    }
+    thr = lo;
+  }
+  const float mp = min_p[row];
+  if (mp > 0.0f) thr = max(thr, __float_as_uint(fminf(mp, 1.0f)));
+  const float p = top_p[row];
+  if (p > 0.0f && p < 1.0f) {                           // largest threshold whose kept mass is >= p of the mass kept so far
+    float base_sum;
+    block_sum_count_ge(w, vocab, thr, red, &base_sum, &kept_count);
+    const float need = p * base_sum;
+    unsigned lo = thr, hi = 0x3F800000u;
+    while (lo < hi) {
+      const unsigned mid = lo + (hi - lo + 1u) / 2u;
+      block_sum_count_ge(w, vocab, mid, red, &kept_sum, &kept_count);
+      if (kept_sum >= need) lo = mid; else hi = mid - 1u;
+    }
+    thr = lo;
+  }
+  // inverse CDF over the kept entries, in index order: thread t owns one contiguous segment
+  const int seg = (vocab + ST - 1) / ST;
+  const int begin = min(vocab, (int)threadIdx.x * seg), end = min(vocab, begin + seg);
+  float mine = 0.0f;
+  for (int i = begin; i < end; ++i) {
+    const float v = w[i];
+    if (__float_as_uint(v) >= thr) mine += v;
+  }
+  seg_prefix[threadIdx.x] = mine;
+  if (threadIdx.x == 0) chosen = -1;
+  __syncthreads();
+  if (threadIdx.x == 0) {                                // 1024 additions: exclusive prefix, fixed order
+    float run = 0.0f;
+    for (int t = 0; t < ST; ++t) { const float s = seg_prefix[t]; seg_prefix[t] = run; run += s; }
+    red[0] = run;
+  }
+  __syncthreads();
+  const float total = red[0];
+  const float target = uniform01(seeds[row], counters[row]) * total;
+  const float before = seg_prefix[threadIdx.x];
+  const bool last_seg = (threadIdx.x == ST - 1);
+  const float after = last_seg ? INFINITY : seg_prefix[threadIdx.x + 1];
+  if (mine > 0.0f && before <= target && target < after) {
+    float run = before;
+    int pick = -1, last_kept = -1;
+    for (int i = begin; i < end; ++i) {
+      const float v = w[i];
+      if (__float_as_uint(v) >= thr && v > 0.0f) {
+        run += v;
+        last_kept = i;
+        if (target < run) { pick = i; break; }
+      }
+    }
+    if (pick < 0) pick = last_kept;
+    if (pick >= 0) atomicMax(&chosen, pick);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[row] = chosen >= 0 ? chosen : top.i;
+}
+}  // namespace
+
+IFX_API int ifx_argmax(const float* logits, long long row_stride, int* out, int n_rows, int vocab, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  argmax_kernel<<<n_rows, ST, 0, stream>>>(logits, row_stride, out, vocab);
+  return IFX_LAUNCH_CHECK();
+}
+
+IFX_API int ifx_apply_penalties(float* logits, long long row_stride, const int* recent_ids, const int* recent_counts,
+                                const int* n_recent, int max_recent, const float* rep, const float* freq,
+                                const float* pres, int n_rows, int vocab, cudaStream_t stream) {
+  if (n_rows <= 0 || max_recent <= 0) return 0;
+  penalties_kernel<<<n_rows, 128, 0, stream>>>(logits, row_stride, recent_ids, recent_counts, n_recent, max_recent,
+                                               rep, freq, pres, vocab);
+  return IFX_LAUNCH_CHECK();
+}
+
+IFX_API int ifx_sample(const float* logits, long long row_stride, float* weights, const float* temperature,
+                       const int* top_k, const float* top_p, const float* min_p, const unsigned long long* seeds,
+                       const unsigned long long* counters, int* out, int n_rows, int vocab, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (vocab >= (1 << 24)) return IFX_ERR_UNSUPPORTED;
+  sample_kernel<<<n_rows, ST, 0, stream>>>(logits, row_stride, weights, temperature, top_k, top_p, min_p, seeds,
+                                           counters, out, vocab);
+  return IFX_LAUNCH_CHECK();
+}

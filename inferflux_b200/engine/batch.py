@@ -1,0 +1,97 @@
+"""One step's input: a batch of (request, its next tokens), and the device-side
+description of it that the kernels read.
+
+The reference's step input is ``UnifiedBatchInput{sequence_id, n_past,
+tokens, request_logits, ...}`` (runtime/backends/common/backend_types.h:19-28)
+and its step splits a mixed batch into one batched decode forward plus one
+forward per prompt portion
+(runtime/backends/cuda/inferflux_cuda_executor.cpp:2806-2849,3041-3099).  Here
+all entries are flattened into one token list and run as one batch; logits are
+returned at the positions each entry asks for (the reference returns them for
+the last token only, runtime/backends/cuda/native/transformer_forward.cu:2105-2112).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+QUERY_TILE = 16     # tokens per query tile of the generic attention kernel
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens (a portion of its prompt
+    or one decoded token) and the places among them whose logits are wanted."""
+
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class MetadataSlab:
+    """All int32 metadata of a step in one pinned host buffer and one device
+    buffer, so a step costs one host-to-device copy."""
+
+    def __init__(self, capacity: int, device: str):
+        self.capacity = capacity
+        self.device = device
+        pin = torch.device(device).type == "cuda"
+        self.host = torch.zeros(capacity, dtype=torch.int32, pin_memory=pin)
+        self.dev = torch.zeros(capacity, dtype=torch.int32, device=device)
+        self._used = 0
+        self._views: List[Tuple[int, int]] = []
+
+    def begin(self) -> None:
+        self._used = 0
+
+    def put(self, values, align: int = 4) -> torch.Tensor:
+        """Append values; returns the device view (valid after :meth:`upload`)."""
+        n = len(values)
+        start = (self._used + align - 1) // align * align
+        if start + n > self.capacity:
+            raise RuntimeError(f"step metadata needs {start + n} words, the slab holds {self.capacity}")
+        if n:
+            self.host[start:start + n] = torch.as_tensor(values, dtype=torch.int32)
+        self._used = start + n
+        return self.dev[start:start + n]
+
+    def upload(self) -> None:
+        if self._used:
+            self.dev[:self._used].copy_(self.host[:self._used], non_blocking=True)
+
+
+@dataclass
+class StepContext:
+    """What parts see of a step.  All tensors are int32 on the device."""
+
+    n_tokens: int
+    n_entries: int
+    entries: List[StepEntry]                  # host view, in batch order
+    ctx_starts: List[int]                     # host: tokens cached before each entry's new ones
+    slots: List[int]                          # host: state slot of each entry
+    token_ids: torch.Tensor                   # [N]
+    positions: torch.Tensor                   # [N]
+    entry_q_start: torch.Tensor               # [R] row of each entry's first new token
+    entry_q_len: torch.Tensor                 # [R]
+    entry_ctx_start: torch.Tensor             # [R]
+    entry_slot: torch.Tensor                  # [R]
+    tile_entry: torch.Tensor                  # [T] query tiles of QUERY_TILE tokens
+    tile_q0: torch.Tensor                     # [T]
+    n_tiles: int
+    block_tables: List[torch.Tensor]          # per cache group [R, max_blocks]
+    slot_maps: List[torch.Tensor]             # per cache group [N]
+    want_rows: torch.Tensor                   # [W] rows whose logits are wanted
+    n_want: int
+    max_q_len: int
+    max_ctx_len: int                          # longest context (cached + new) of any entry
+    page_size: int
+    kv: object                                # KVCacheStorage
+    dtype: torch.dtype
+    device: str
+    position_tables: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+    extras: Dict[str, object] = field(default_factory=dict)
+
+    def buffer(self, shape, dtype=None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

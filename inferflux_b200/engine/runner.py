@@ -1,0 +1,193 @@
+"""The step function: run one batch of (request, its next tokens) from the
+cache and return the logits at the wanted places.
+
+:class:`StepRunner` owns the model, the cache (pages and state slots) and the
+step metadata.  Generation (the scheduler and the Python entry point) and trace
+replay both drive this one object; nothing else runs the model.
+
+Reference counterpart: ``InferfluxCudaExecutor::ExecuteUnifiedBatch``
+(runtime/backends/cuda/inferflux_cuda_executor.cpp:2743-3226), which splits a
+mixed batch into a decode forward and one forward per prompt portion and
+returns sampled tokens; here the whole batch is one forward and the result is
+logits.
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache import OutOfPages, OutOfSlots, KVCacheManager, KVCacheStorage, StateSlotManager, StateSlotStorage, bytes_per_token
+from ..config.engine_config import EngineConfig
+from .batch import QUERY_TILE, MetadataSlab, StepContext, StepEntry
+from .model import Model
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+def torch_dtype(name: str) -> torch.dtype:
+    try:
+        return _TORCH_DTYPES[name]
+    except KeyError:
+        raise ValueError(f"dtype must be one of {sorted(_TORCH_DTYPES)}, got '{name}'") from None
+
+
+class StepRunner:
+    def __init__(self, model: Model, engine_config: EngineConfig):
+        engine_config.validate()
+        self.model = model
+        self.cfg = engine_config
+        self.device = engine_config.device
+        self.dtype = model.dtype
+        self.page_size = engine_config.page_size
+        self.max_model_len = engine_config.max_model_len or model.spec.max_position
+        needs = model.kv_needs
+        elt = torch.empty((), dtype=self.dtype).element_size()
+        per_token = max(1, bytes_per_token(needs, model.runs_per_group, elt))
+        if engine_config.kv_cache_tokens is not None:
+            tokens = engine_config.kv_cache_tokens
+        else:
+            free, _ = torch.cuda.mem_get_info(torch.device(self.device))
+            tokens = int(free * engine_config.kv_memory_ratio) // per_token
+            tokens = min(tokens, engine_config.max_seqs * self.max_model_len)
+        pages = max(1, (tokens + self.page_size - 1) // self.page_size)
+        self.num_pages = [pages for _ in needs]
+        self.kv = KVCacheManager(needs, self.num_pages, self.page_size)
+        self.kv_storage = KVCacheStorage(needs, model.runs_per_group, self.num_pages, self.page_size,
+                                         self.dtype, self.device)
+        self.slots = StateSlotManager(engine_config.max_seqs)
+        self.state_storage = StateSlotStorage(engine_config.max_seqs, model.state_needs, self.device)
+        model.attach_states(self.state_storage)
+        self.slab = MetadataSlab(1 << 16, self.device)
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------ requests
+    def has(self, rid: Hashable) -> bool:
+        return self.kv.has(rid)
+
+    def length(self, rid: Hashable) -> int:
+        return self.kv.length(rid)
+
+    def begin(self, rid: Hashable) -> None:
+        """Seat a new request: a state slot (zeroed) and empty block tables."""
+        slot = self.slots.acquire(rid)
+        self.kv.add_request(rid)
+        self.state_storage.reset(slot)
+
+    def end(self, rid: Hashable) -> None:
+        """The request is finished: its pages and its slot are given back."""
+        self.kv.free_request(rid)
+        self.slots.release(rid)
+
+    def can_run(self, rid: Optional[Hashable], n_new: int) -> bool:
+        """Whether pages (and, for an unknown request, a slot) for ``n_new`` more tokens exist."""
+        if (rid is None or not self.kv.has(rid)) and self.slots.num_free == 0:
+            return False
+        return self.kv.can_reserve(rid, n_new)
+
+    # ---------------------------------------------------------------- step
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Reserve pages for the step's tokens and describe the step on the device."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        vocab = self.model.spec.vocab_size
+        seen = set()
+        for e in entries:
+            if e.rid in seen:
+                raise ValueError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise ValueError(f"request {e.rid!r}: token id {t} is outside the vocabulary [0, {vocab})")
+            for p in e.want:
+                if not 0 <= int(p) < len(e.tokens):
+                    raise ValueError(f"request {e.rid!r}: wanted place {p} is outside its {len(e.tokens)} tokens")
+        new = [e for e in entries if not self.kv.has(e.rid)]
+        if len(new) > self.slots.num_free:
+            raise OutOfSlots(f"{len(new)} new request(s) but {self.slots.num_free} free state slot(s)")
+        total = [0] * self.kv.num_groups
+        for e in entries:
+            known = self.kv.has(e.rid)
+            have = self.kv.length(e.rid) if known else 0
+            if have + len(e.tokens) > self.max_model_len:
+                raise ValueError(f"request {e.rid!r}: {have + len(e.tokens)} tokens exceed "
+                                 f"the model length {self.max_model_len}")
+            for g, k in enumerate(self.kv.pages_needed(e.rid if known else None, len(e.tokens), 0)):
+                total[g] += k
+        for g, k in enumerate(total):
+            if k > self.kv.num_free(g):
+                raise OutOfPages(k, self.kv.num_free(g), g)
+        for e in new:
+            self.begin(e.rid)
+        for e in entries:
+            self.kv.reserve(e.rid, len(e.tokens))
+        ps = self.page_size
+        token_ids, positions, q_start, q_len, ctx_start, slots = [], [], [], [], [], []
+        tile_entry, tile_q0, want_rows = [], [], []
+        for i, e in enumerate(entries):
+            start = self.kv.length(e.rid)
+            q_start.append(len(token_ids))
+            q_len.append(len(e.tokens))
+            ctx_start.append(start)
+            slots.append(self.slots.slot(e.rid))
+            for p in e.want:
+                want_rows.append(len(token_ids) + int(p))
+            for q0 in range(0, len(e.tokens), QUERY_TILE):
+                tile_entry.append(i)
+                tile_q0.append(q0)
+            token_ids.extend(int(t) for t in e.tokens)
+            positions.extend(range(start, start + len(e.tokens)))
+        n, r = len(token_ids), len(entries)
+        groups = self.kv.num_groups
+        widths, tables, slot_maps = [], [], []
+        for g in range(groups):
+            tabs = [self.kv.block_table(e.rid, g) for e in entries]
+            width = max(1, max(len(t) for t in tabs))
+            flat = []
+            for t in tabs:
+                flat.extend(t)
+                flat.extend([-1] * (width - len(t)))
+            sm = []
+            for e, s0 in zip(entries, ctx_start):
+                tab = self.kv.block_table(e.rid, g)
+                for pos in range(s0, s0 + len(e.tokens)):
+                    sm.append(tab[pos // ps] * ps + pos % ps)
+            widths.append(width)
+            tables.append(flat)
+            slot_maps.append(sm)
+        need = 4 * (8 + groups) + 2 * n + 4 * r + 2 * len(tile_entry) + len(want_rows) \
+            + sum(len(t) for t in tables) + groups * n + 64
+        if need > self.slab.capacity:
+            self.slab = MetadataSlab(max(need, 2 * self.slab.capacity), self.device)
+        slab = self.slab
+        slab.begin()
+        d_tok, d_pos = slab.put(token_ids), slab.put(positions)
+        d_qs, d_ql, d_cs, d_sl = slab.put(q_start), slab.put(q_len), slab.put(ctx_start), slab.put(slots)
+        d_te, d_tq = slab.put(tile_entry), slab.put(tile_q0)
+        d_want = slab.put(want_rows)
+        d_tabs = [slab.put(t).view(r, w) for t, w in zip(tables, widths)]
+        d_sm = [slab.put(s) for s in slot_maps]
+        slab.upload()
+        return StepContext(
+            n_tokens=n, n_entries=r, entries=list(entries), ctx_starts=ctx_start, slots=slots,
+            token_ids=d_tok, positions=d_pos, entry_q_start=d_qs, entry_q_len=d_ql, entry_ctx_start=d_cs,
+            entry_slot=d_sl, tile_entry=d_te, tile_q0=d_tq, n_tiles=len(tile_entry),
+            block_tables=d_tabs, slot_maps=d_sm, want_rows=d_want, n_want=len(want_rows),
+            max_q_len=max(q_len), max_ctx_len=max(c + l for c, l in zip(ctx_start, q_len)),
+            page_size=ps, kv=self.kv_storage, dtype=self.dtype, device=self.device)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries' tokens as one batch; float32 logits ``[wanted, vocab]``
+        in the order of the entries and of each entry's ``want``.  Raises
+        :class:`~inferflux_b200.cache.OutOfPages` (before anything ran) when
+        the pools cannot hold the step's tokens."""
+        ctx = self.build_context(entries)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.kv.advance(e.rid, len(e.tokens))
+        self.steps += 1
+        self.tokens_run += ctx.n_tokens
+        return logits

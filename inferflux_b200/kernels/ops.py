@@ -1,0 +1,291 @@
+"""Python entry points of the hand-written CUDA kernels.
+
+Each function takes torch tensors that already live on the GPU, checks what
+the kernel cannot check itself, and launches on torch's current stream through
+the C interface of the kernel library.  There is no other implementation
+behind these functions: a tensor that is not on a CUDA device, or a library
+that cannot be built, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+#: kernels of this library launched since import (library matrix products are not counted)
+launch_count = 0
+
+_ERRORS = {100001: "unsupported size or element type", 100002: "misaligned pointer or stride"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_sigs_done = False
+
+
+def _lib():
+    global _sigs_done
+    lib = library()
+    if not _sigs_done:
+        lib.ifx_embed_gather.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_float, c_void_p,
+                                        c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_swiglu.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_convert.argtypes = [c_void_p, c_int, c_void_p, c_int, c_ll, c_void_p]
+        lib.ifx_rope_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_qkv_rope_kv_write.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                              c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.ifx_gemm_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_void_p]
+        lib.ifx_attn_paged_generic.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int,
+                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                               c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
+        lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_apply_penalties.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                            c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_sample.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_void_p]
+        for name in ("ifx_embed_gather", "ifx_add_rmsnorm", "ifx_swiglu", "ifx_convert", "ifx_rope_table",
+                     "ifx_qkv_rope_kv_write", "ifx_gemm_f32", "ifx_attn_paged_generic", "ifx_argmax",
+                     "ifx_apply_penalties", "ifx_sample"):
+            getattr(lib, name).restype = c_int
+        _sigs_done = True
+    return lib
+
+
+def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if code != 0:
+        msg = _ERRORS.get(code)
+        if msg is None:
+            msg = f"CUDA error {code}"
+            try:
+                torch.cuda.synchronize()
+            except RuntimeError as e:   # surfaces the sticky error text
+                msg += f" ({e})"
+        raise KernelError(f"{what}: {msg}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernel operands must be CUDA tensors (there is no CPU path)")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported element type {t.dtype}") from None
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+# ------------------------------------------------------------------ elementwise
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = float32(table[ids[t], :]); ids int32 [N], out float32 [N, H]."""
+    n, (vocab, hidden) = ids.numel(), table.shape
+    _need(ids.dtype == torch.int32 and out.dtype == torch.float32, "embed_gather: ids int32, out float32")
+    _need(table.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (n, hidden),
+          "embed_gather: contiguous table and out [N, H]")
+    _check(_lib().ifx_embed_gather(_ptr(table), _code(table), _ptr(ids), _ptr(out), n, hidden, vocab, _stream()),
+           "embed_gather")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+                n_partials: int = 1) -> Optional[torch.Tensor]:
+    """residual (float32 [N, H]) += delta; out = RMSNorm(residual) * weight.
+
+    With ``rows`` (int32 [R]) only those rows are normed into out [R, H] and
+    the residual is left untouched.  ``delta`` may be None; with
+    ``n_partials`` > 1 it is [P, N, H] float32 partial sums.  ``out`` may be
+    None (only the sum is stored)."""
+    n, hidden = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_rmsnorm: residual float32 contiguous")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "add_rmsnorm: weight float32 [H]")
+    n_rows = rows.numel() if rows is not None else n
+    if rows is not None:
+        _need(rows.dtype == torch.int32, "add_rmsnorm: rows int32")
+    pstride = 0
+    if delta is not None:
+        _need(delta.is_contiguous(), "add_rmsnorm: delta contiguous")
+        if n_partials > 1:
+            _need(tuple(delta.shape) == (n_partials, n, hidden), "add_rmsnorm: partials [P, N, H]")
+            pstride = n * hidden
+        else:
+            _need(tuple(delta.shape) == (n, hidden), "add_rmsnorm: delta [N, H]")
+    if out is not None:
+        _need(out.is_contiguous() and tuple(out.shape) == (n_rows, hidden), "add_rmsnorm: out [rows, H]")
+    dd = _code(delta) if delta is not None else F32
+    od = _code(out) if out is not None else F32
+    _check(_lib().ifx_add_rmsnorm(_ptr(residual), _ptr(delta), dd, n_partials, pstride, _ptr(weight), float(eps),
+                                  _ptr(out), od, _ptr(rows), n_rows, hidden, 0 if rows is not None else 1,
+                                  _stream()), "add_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i]."""
+    m, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and tuple(out.shape) == (m, two_i // 2) and out.dtype == gate_up.dtype,
+          "swiglu: gate_up [M, 2I], out [M, I] of the same type")
+    _need(gate_up.is_contiguous() and out.is_contiguous(), "swiglu: contiguous operands")
+    _check(_lib().ifx_swiglu(_ptr(gate_up), _ptr(out), _code(out), m, two_i // 2, _stream()), "swiglu")
+    return out
+
+
+def convert(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    _need(src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel(), "convert: same size, contiguous")
+    _check(_lib().ifx_convert(_ptr(src), _code(src), _ptr(dst), _code(dst), src.numel(), _stream()), "convert")
+    return dst
+
+
+# ----------------------------------------------------------------------- rotary
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+    """cos/sin [N, half] float32 of positions[t] * inv_freq[i] (inv_freq float64 [half])."""
+    n, half = positions.numel(), inv_freq.numel()
+    _need(positions.dtype == torch.int32 and inv_freq.dtype == torch.float64, "rope_table: int32 positions, float64 inv_freq")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+          and tuple(cos.shape) == (n, half) and tuple(sin.shape) == (n, half), "rope_table: cos/sin float32 [N, half]")
+    _check(_lib().ifx_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), n, half, _stream()),
+           "rope_table")
+
+
+def qkv_rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
+                      slot_map: Optional[torch.Tensor], k_layer: Optional[torch.Tensor],
+                      v_layer: Optional[torch.Tensor], page_stride: int, page_size: int,
+                      n_heads: int, n_kv: int, head_dim: int) -> None:
+    """Bias add, rotate-half rotation of q (in place) and k, and the write of k
+    and v into the paged cache at ``slot_map`` (page * page_size + offset)."""
+    n, width = qkv.shape
+    _need(qkv.is_contiguous() and width == (n_heads + 2 * n_kv) * head_dim, "qkv_rope_kv_write: qkv [N, (nh + 2 nkv) hd]")
+    rot_dim = 2 * cos.shape[1]
+    _need(tuple(cos.shape) == tuple(sin.shape) and cos.shape[0] == n and cos.dtype == torch.float32
+          and cos.is_contiguous() and sin.is_contiguous(), "qkv_rope_kv_write: cos/sin float32 [N, rot/2]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == width, "qkv_rope_kv_write: bias float32 [width]")
+    if n_kv:
+        _need(slot_map is not None and slot_map.dtype == torch.int32 and slot_map.numel() == n,
+              "qkv_rope_kv_write: slot_map int32 [N]")
+        _need(k_layer.dtype == qkv.dtype and v_layer.dtype == qkv.dtype, "qkv_rope_kv_write: cache of qkv's type")
+    _check(_lib().ifx_qkv_rope_kv_write(_ptr(qkv), _code(qkv), _ptr(bias), _ptr(cos), _ptr(sin), rot_dim,
+                                        _ptr(slot_map) if n_kv else None, _ptr(k_layer) if n_kv else None,
+                                        _ptr(v_layer) if n_kv else None, page_stride, page_size, n, n_heads, n_kv,
+                                        head_dim, _stream()), "qkv_rope_kv_write")
+
+
+# --------------------------------------------------------------- matrix product
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T + bias, all float32, plain FFMA."""
+    m, k = a.shape
+    n = w.shape[0]
+    _need(a.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32, "gemm_f32: float32")
+    _need(w.shape[1] == k and w.is_contiguous() and tuple(out.shape) == (m, n), "gemm_f32: shapes")
+    _need(a.stride(1) == 1 and out.stride(1) == 1, "gemm_f32: unit inner strides")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_f32: bias float32 [N]")
+    _check(_lib().ifx_gemm_f32(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0) if m > 1 else k,
+                               out.stride(0) if m > 1 else n, _stream()), "gemm_f32")
+    return out
+
+
+def matmul_library(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x[M, K] @ w[N, K]^T through the vendor library (cuBLAS via torch), bfloat16
+    operands, float32 accumulation, bfloat16 or float32 result.  Stands where
+    the reference calls cuBLAS (runtime/backends/cuda/native/cublas_gemm.cpp:84-102)."""
+    _need(x.is_cuda and w.is_cuda, "matmul_library: CUDA tensors (there is no CPU path)")
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "matmul_library: bfloat16 operands")
+    if out_dtype == torch.float32:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    return torch.mm(x, w.t())
+
+
+# -------------------------------------------------------------------- attention
+def attn_paged_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer: torch.Tensor,
+                       v_layer: torch.Tensor, page_stride: int, page_size: int, block_tables: torch.Tensor,
+                       tile_entry: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
+                       entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor,
+                       n_heads: int, n_kv: int, head_dim: int, scale: float, window: int) -> torch.Tensor:
+    """Causal grouped-query attention of new tokens over the paged cache.
+
+    q: first element of the query rows (row stride ``q_stride`` elements, heads
+    contiguous); out [N, n_heads * head_dim]; query tiles of 16 tokens are
+    listed by tile_entry / tile_q0."""
+    _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1,
+          "attn: block_tables int32 [R, B]")
+    for t in (tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start):
+        _need(t.dtype == torch.int32, "attn: int32 metadata")
+    _need(out.is_contiguous() and out.dtype == q.dtype and k_layer.dtype == q.dtype, "attn: types")
+    _need(1 <= head_dim <= 256, f"attention: head_dim {head_dim} is outside 1..256")
+    _need(n_heads % n_kv == 0, "attention: n_heads must be a multiple of n_kv")
+    _check(_lib().ifx_attn_paged_generic(_ptr(q), q_stride, _ptr(out), out.stride(0), _code(q), _ptr(k_layer),
+                                         _ptr(v_layer), page_stride, page_size, _ptr(block_tables),
+                                         block_tables.stride(0), _ptr(tile_entry), _ptr(tile_q0), n_tiles,
+                                         _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start),
+                                         n_heads, n_kv, head_dim, float(scale), int(window), _stream()),
+           "attn_paged_generic")
+    return out
+
+
+# --------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = lowest index of the maximum of logits[r, :] (float32 [R, V])."""
+    r, v = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32 and out.numel() >= r,
+          "argmax: float32 logits, int32 out")
+    _check(_lib().ifx_argmax(_ptr(logits), logits.stride(0), _ptr(out), r, v, _stream()), "argmax")
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, recent_ids: torch.Tensor, recent_counts: torch.Tensor,
+                    n_recent: torch.Tensor, rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> None:
+    r, v = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "penalties: float32 logits")
+    _need(recent_ids.dtype == torch.int32 and recent_counts.dtype == torch.int32 and n_recent.dtype == torch.int32
+          and recent_ids.is_contiguous() and recent_counts.is_contiguous() and recent_ids.shape[0] == r
+          and recent_ids.shape == recent_counts.shape, "penalties: int32 [R, W] ids and counts")
+    for t in (rep, freq, pres):
+        _need(t.dtype == torch.float32 and t.numel() == r, "penalties: float32 [R] parameters")
+    _check(_lib().ifx_apply_penalties(_ptr(logits), logits.stride(0), _ptr(recent_ids), _ptr(recent_counts),
+                                      _ptr(n_recent), recent_ids.shape[1], _ptr(rep), _ptr(freq), _ptr(pres), r, v,
+                                      _stream()), "apply_penalties")
+
+
+def sample(logits: torch.Tensor, weights: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, min_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
+           out: torch.Tensor) -> torch.Tensor:
+    """One token per row: argmax where temperature <= 0, else a draw from
+    softmax(logits / T) restricted by top-k / top-p / min-p.  ``weights`` is
+    float32 scratch of logits' shape; seeds / counters are int64 (read as
+    unsigned)."""
+    r, v = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: float32 logits")
+    _need(weights.dtype == torch.float32 and weights.is_contiguous() and weights.numel() >= r * v, "sample: scratch")
+    _need(temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and min_p.dtype == torch.float32
+          and top_k.dtype == torch.int32 and seeds.dtype == torch.int64 and counters.dtype == torch.int64
+          and out.dtype == torch.int32, "sample: parameter types")
+    _check(_lib().ifx_sample(_ptr(logits), logits.stride(0), _ptr(weights), _ptr(temperature), _ptr(top_k),
+                             _ptr(top_p), _ptr(min_p), _ptr(seeds), _ptr(counters), _ptr(out), r, v, _stream()),
+           "sample")
+    return out

@@ -1,0 +1,125 @@
+"""Mixers.  ``gqa_attention``: causal grouped-query attention over the paged
+cache.
+
+Per token (reference, in this order):
+  q, k, v = x Wq^T, x Wk^T, x Wv^T      runtime/backends/cuda/native/transformer_forward.cu:1479-1481,1514-1517,1550-1553
+  += biases (those that exist)          :1567-1608, runtime/backends/cuda/native/cuda_kernels.cu:694-723
+  rotate q and k by the token position  :1632-1634
+  k, v -> cache                         :1652-1653
+  head h attends with kv head h / (n_heads / n_kv); s = (q . k) / sqrt(d) after
+  the dot; causal; float32 online softmax
+                                        runtime/backends/cuda/kernels/flash_attention.cu:52-173
+  o = attn Wo^T (no bias in Qwen2)      transformer_forward.cu:1719-1727
+The reference keeps q, k, v as three products and a separate bias kernel;
+here the three weights are stacked at load, and one kernel adds the bias,
+rotates and writes the cache.  ``window`` (None = all keys) hides keys more
+than ``window - 1`` positions behind the query; the reference has no window.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from ..config.registry import register_part
+from ..kernels import ops
+from ..weights.loader import MATRIX, VECTOR, WeightSpec
+from .base import KVNeed, Part, RunInfo
+from .linear import Linear
+
+
+class GQAttention(Part):
+    """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``,
+    ``qkv_bias``, ``o_bias``, ``window`` (None or int), ``kv_shared`` (True: the
+    layer has only q and o and reads another run's cache), ``scale`` (None =
+    ``1/sqrt(head_dim)``), ``name``."""
+
+    family = "mixer"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        p = params
+        self.hidden = int(p["hidden"])
+        self.n_heads, self.n_kv, self.head_dim = int(p["n_heads"]), int(p["n_kv_heads"]), int(p["head_dim"])
+        self.window = int(p["window"]) if p.get("window") else 0
+        self.kv_shared = bool(p.get("kv_shared", False))
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"n_heads {self.n_heads} is not a multiple of n_kv_heads {self.n_kv}")
+        if self.head_dim % 2 or not 2 <= self.head_dim <= 256:
+            raise ValueError(f"head_dim {self.head_dim} must be even and within 2..256")
+        self.qkv: Linear = None
+        self.qkv_bias: Optional[torch.Tensor] = None
+        self.o: Linear = None
+
+    # -- declarations ----------------------------------------------------
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        h, nh, nkv, hd = (int(params[k]) for k in ("hidden", "n_heads", "n_kv_heads", "head_dim"))
+        n = lambda leaf: cls.full_name(prefix, params, leaf)
+        shared = bool(params.get("kv_shared", False))
+        specs = [WeightSpec(n("q_proj.weight"), (nh * hd, h), MATRIX)]
+        if not shared:
+            specs += [WeightSpec(n("k_proj.weight"), (nkv * hd, h), MATRIX),
+                      WeightSpec(n("v_proj.weight"), (nkv * hd, h), MATRIX)]
+        if params.get("qkv_bias"):
+            specs.append(WeightSpec(n("q_proj.bias"), (nh * hd,), VECTOR))
+            if not shared:
+                specs += [WeightSpec(n("k_proj.bias"), (nkv * hd,), VECTOR),
+                          WeightSpec(n("v_proj.bias"), (nkv * hd,), VECTOR)]
+        specs.append(WeightSpec(n("o_proj.weight"), (h, nh * hd), MATRIX))
+        if params.get("o_bias"):
+            specs.append(WeightSpec(n("o_proj.bias"), (h,), VECTOR))
+        return specs
+
+    @classmethod
+    def kv_need(cls, params: Dict[str, Any]) -> Optional[KVNeed]:
+        if params.get("kv_shared"):
+            return None
+        return KVNeed(int(params["n_kv_heads"]), int(params["head_dim"]),
+                      int(params["window"]) if params.get("window") else None)
+
+    # -- weights ---------------------------------------------------------
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        names = ["q_proj"] if self.kv_shared else ["q_proj", "k_proj", "v_proj"]
+        mats = [tensors.pop(n(f"{x}.weight")) for x in names]
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.float() for m in mats]
+        self.qkv = Linear(torch.cat(mats, dim=0) if len(mats) > 1 else mats[0])
+        del mats
+        if self.params.get("qkv_bias"):
+            self.qkv_bias = torch.cat([tensors.pop(n(f"{x}.bias")).float() for x in names]).contiguous()
+        o_bias = tensors.pop(n("o_proj.bias")) if self.params.get("o_bias") else None
+        self.o = Linear(tensors.pop(n("o_proj.weight")), o_bias)
+
+    # -- the step --------------------------------------------------------
+    def forward(self, x: torch.Tensor, ctx, run: RunInfo, position) -> torch.Tensor:
+        """x [N, hidden] (normed) -> [N, hidden]; writes this step's keys and
+        values into the run's cache (unless it reads another run's) and
+        attends over the cache."""
+        n = x.shape[0]
+        nkv_w = 0 if self.kv_shared else self.n_kv
+        qkv = self.qkv.forward(x)
+        if position is not None:
+            cos, sin = position
+        else:
+            cos = sin = torch.empty((n, 0), dtype=torch.float32, device=x.device)
+        g = run.kv_group
+        k_layer, v_layer, page_stride = ctx.kv.layer_views(g, run.kv_index)
+        ops.qkv_rope_kv_write(qkv, self.qkv_bias, cos, sin, ctx.slot_maps[g] if nkv_w else None,
+                              k_layer if nkv_w else None, v_layer if nkv_w else None, page_stride,
+                              ctx.page_size, self.n_heads, nkv_w, self.head_dim)
+        attn = torch.empty((n, self.n_heads * self.head_dim), dtype=qkv.dtype, device=x.device)
+        self.attend(qkv, attn, ctx, g, k_layer, v_layer, page_stride)
+        return self.o.forward(attn, out_dtype=x.dtype)
+
+    def attend(self, qkv, attn, ctx, g, k_layer, v_layer, page_stride) -> None:
+        ops.attn_paged_generic(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
+                               ctx.block_tables[g], ctx.tile_entry, ctx.tile_q0, ctx.n_tiles,
+                               ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,
+                               self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
+
+
+register_part("mixer", "gqa_attention", GQAttention)

@@ -1,0 +1,61 @@
+"""Feed-forward parts.
+
+``swiglu``: ``down( silu(gate(x)) * up(x) )`` with ``silu(g) = g / (1 + exp(-g))``
+in float32, no biases (reference:
+runtime/backends/cuda/native/transformer_forward.cu:1877-1879,1912-1914 gate
+and up, :1981-1983 activation, :2024-2026 down;
+runtime/backends/cuda/native/cuda_kernels.cu:137-149).  The reference runs
+gate and up as two products; here their weights are stacked at load so one
+product yields ``[gate | up]``.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List
+
+import torch
+
+from ..config.registry import register_part
+from ..kernels import ops
+from ..weights.loader import MATRIX, WeightSpec
+from .base import Part
+from .linear import Linear
+
+
+class SwiGLU(Part):
+    """params: ``hidden``, ``intermediate``, ``name`` (weights are
+    ``<prefix>.<name>.{gate,up,down}_proj.weight``)."""
+
+    family = "feed_forward"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden = int(params["hidden"])
+        self.intermediate = int(params["intermediate"])
+        self.gate_up: Linear = None
+        self.down: Linear = None
+
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        h, i = int(params["hidden"]), int(params["intermediate"])
+        n = lambda leaf: cls.full_name(prefix, params, leaf)
+        return [WeightSpec(n("gate_proj.weight"), (i, h), MATRIX),
+                WeightSpec(n("up_proj.weight"), (i, h), MATRIX),
+                WeightSpec(n("down_proj.weight"), (h, i), MATRIX)]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        gate, up = tensors.pop(n("gate_proj.weight")), tensors.pop(n("up_proj.weight"))
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        self.gate_up = Linear(torch.cat([gate, up], dim=0))
+        del gate, up
+        self.down = Linear(tensors.pop(n("down_proj.weight")))
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        gu = self.gate_up.forward(x)
+        act = torch.empty((x.shape[0], self.intermediate), dtype=gu.dtype, device=x.device)
+        ops.swiglu(gu, act)
+        return self.down.forward(act, out_dtype=x.dtype)
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

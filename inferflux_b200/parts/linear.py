@@ -1,0 +1,47 @@
+"""A matrix product ``y = x W^T (+ b)`` with ``W`` stored ``[out, in]``.
+
+The reference issues one cuBLAS call per projection with float32 accumulation
+(runtime/backends/cuda/native/cublas_gemm.cpp:84-102, ``C[M,N] = A[M,K] *
+B[N,K]^T``).  Here a float32 weight goes through the FFMA kernel of the 32-bit
+path; a bfloat16 weight goes through the library (cuBLAS via ``torch.mm``) for
+many rows.  This is not a registered part: mixers and feed-forwards own their
+Linears.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        if weight.dim() != 2:
+            raise ValueError("Linear wants a [out, in] matrix")
+        self.weight = weight.contiguous()
+        self.out_features, self.in_features = weight.shape
+        self.bias = None if bias is None else bias.to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x [M, in] -> [M, out] in ``out_dtype`` (default: x's type)."""
+        m = x.shape[0]
+        out_dtype = out_dtype or x.dtype
+        w = self.weight
+        if w.dtype == torch.float32:
+            # 32-bit weights: true float32 product whatever the activations are
+            if x.dtype != torch.float32:
+                x = ops.convert(x.contiguous(), torch.empty(x.shape, dtype=torch.float32, device=x.device))
+            y = torch.empty((m, self.out_features), dtype=torch.float32, device=x.device)
+            ops.gemm_f32(x, w, self.bias, y)
+            if out_dtype != torch.float32:
+                y = ops.convert(y, torch.empty(y.shape, dtype=out_dtype, device=x.device))
+            return y
+        if x.dtype != torch.bfloat16:
+            raise ops.KernelError(f"Linear: bfloat16 weights need bfloat16 activations, got {x.dtype}")
+        y = ops.matmul_library(x, w, torch.float32 if (out_dtype == torch.float32 or self.bias is not None)
+                               else torch.bfloat16)
+        if self.bias is not None:
+            y += self.bias
+        return y if y.dtype == out_dtype else y.to(out_dtype)
