@@ -1,0 +1,263 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default workload: the layer sizes of Qwen2.5-7B with random bfloat16 weights,
+8 requests decoding at a context of 4,096 tokens.  A step is one decode step.
+Prints ONE JSON line: ``value`` = decoded tokens per second at batch 8 (device
+time over K steps), ``e2e`` = the same through the Python entry point with
+host tokens in and out, ``prefill`` = one 2,048-token prompt step, ``roofline``
+= bytes the decode step must read / its time against the measured copy
+bandwidth, ``points`` = decode at batch 1 and 64.
+
+The inputs of a decode step (15 GB of weights plus the live requests' cache)
+are far larger than the 126 MB L2, so no separate L2 flush is done between
+timed steps (``config.l2`` says so).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                v = d.get(k)
+                if isinstance(v, dict):
+                    v = v.get("value")
+                if isinstance(v, (int, float)) and v > 0:
+                    out[k] = float(v)
+            return out, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def family_config():
+    """configs[2] of BASELINE.json: the Qwen2.5-7B layer sizes."""
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=3584, num_hidden_layers=28,
+                num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
+                vocab_size=152064, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=32768, use_sliding_window=False, hidden_act="silu",
+                torch_dtype="bfloat16")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                parts = [p.strip() for p in out.stdout.strip().split("\n")[0].split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except (OSError, subprocess.SubprocessError):
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=6)
+        sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the family size (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "vjsingh1984/inferflux is a C++/CMake server with no setup.py or pyproject.toml: "
+                          "pip reports 'Directory is not installable' offline"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+    from inferflux_b200 import Engine, SamplingParams, StepEntry
+    from inferflux_b200.kernels import ops
+
+    peaks, peaks_from = load_peaks()
+    cfgd = family_config()
+    full_layers = cfgd["num_hidden_layers"]
+    if args.layers:
+        cfgd["num_hidden_layers"] = args.layers
+    layers = cfgd["num_hidden_layers"]
+    ctx, batch = args.context, args.batch
+    max_b = batch if args.no_points else max(batch, 64)
+    pool_tokens = max_b * (ctx + 64)
+    eng = Engine.from_config(cfgd, seed=0, dtype="bfloat16", kv_cache_tokens=pool_tokens, max_seqs=max_b + 1,
+                             max_batch_tokens=4096, max_batch_size=max_b, chunked_prefill_tokens=2048,
+                             max_model_len=ctx + 64)
+    runner = eng.runner
+    vocab = cfgd["vocab_size"]
+    gen = torch.Generator().manual_seed(0)
+
+    h, nh, nkv, hd, inter = (cfgd[k] for k in ("hidden_size", "num_attention_heads", "num_key_value_heads",
+                                               "head_dim", "intermediate_size"))
+    per_layer_params = (nh + 2 * nkv) * hd * h + (nh + 2 * nkv) * hd + nh * hd * h + 3 * h * inter + 2 * h
+    weight_bytes = 2 * (layers * per_layer_params + vocab * h + h)          # + embedding rows (tiny)
+    kv_bytes_per_token = 2 * layers * nkv * hd * 2
+
+    def fill(rids, n_tokens):
+        """Bring requests to n_tokens cached tokens by real prompt steps of up to 2,048 tokens."""
+        for rid in rids:
+            toks = torch.randint(0, vocab, (n_tokens,), generator=gen).tolist()
+            for s in range(0, n_tokens, 2048):
+                runner.step([StepEntry(rid, toks[s:s + 2048], [])])
+        torch.cuda.synchronize()
+
+    def time_decode(b, steps, warm):
+        """Device time of `steps` decode steps at batch b, context ending at ctx."""
+        rids = [f"b{b}_{i}" for i in range(b)]
+        fill(rids, ctx - steps - warm)
+        toks = torch.randint(0, vocab, (steps + warm, b), generator=gen).tolist()
+        for w in range(warm):
+            runner.step([StepEntry(r, [toks[w][i]], [0]) for i, r in enumerate(rids)])
+        torch.cuda.synchronize()
+        l0 = ops.launch_count
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        torch.cuda.synchronize()
+        ev[0].record()
+        for s in range(steps):
+            logits = runner.step([StepEntry(r, [toks[warm + s][i]], [0]) for i, r in enumerate(rids)])
+            eng.sampler.sample(logits, [greedy] * b, [0] * b, [0] * b, [[]] * b)
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / steps
+        launches = ops.launch_count - l0
+        for r in rids:
+            runner.end(r)
+        return ms, launches
+
+    greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
+    clocks = ClockSampler()
+
+    # ---- headline: decode at `batch`, device-timed
+    clocks.start()
+    ms_step, launches = time_decode(batch, args.steps, warmup)
+    clock_rec = clocks.stop()
+    value = batch / (ms_step / 1e3)
+    step_bytes = weight_bytes + batch * (ctx - args.steps // 2) * kv_bytes_per_token
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+
+    # ---- end to end: the Python entry point, host tokens in, host tokens out
+    prompts = [torch.randint(0, vocab, (ctx - args.steps - warmup - 16,), generator=gen).tolist() for _ in range(batch)]
+    params = SamplingParams(temperature=0.0, max_tokens=args.steps + warmup + 16, ignore_eos=True)
+    for p in prompts:
+        eng.add_request(p, params)
+    while any(not r.decoding for r in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()                                   # prompt steps
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_e2e = 0
+    while eng.has_work() and n_e2e < args.steps:
+        eng.step()                                   # plan, H2D metadata, run, sample, D2H ids
+        n_e2e += 1
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / max(1, n_e2e)
+    h2d = runner.slab._used * 4
+    while eng.has_work():
+        eng.step()
+    e2e = {"value": round(batch / (e2e_ms / 1e3), 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
+
+    out = {
+        "metric": "decode tokens/s at batch 8, context 4096 (Qwen2.5-7B sizes, random bf16 weights)",
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), uniform random token ids",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-7B sizes", "layers": layers, "layers_of_family": full_layers, "hidden": h,
+                   "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": inter, "vocab": vocab,
+                   "global_batch": batch, "seq_len": ctx, "page_size": runner.page_size,
+                   "parallelism": "single GPU", "l2": "inputs (weights + cache) exceed L2; no flush",
+                   "peaks": peaks_from},
+        "e2e": e2e, "gpu_launches": launches, "clocks": clock_rec,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "bytes_per_step": step_bytes},
+    }
+
+    if not args.no_points:
+        # ---- prefill of 2,048 tokens in one step
+        T = 2048
+        toks = torch.randint(0, vocab, (T,), generator=gen).tolist()
+        for i in range(3):
+            runner.step([StepEntry(f"pw{i}", toks, [T - 1])])
+            runner.end(f"pw{i}")
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        reps = 5
+        ev[0].record()
+        for i in range(reps):
+            runner.step([StepEntry(f"p{i}", toks, [T - 1])])
+            runner.end(f"p{i}")
+        ev[1].record()
+        torch.cuda.synchronize()
+        pms = ev[0].elapsed_time(ev[1]) / reps
+        lin_flops = 2 * T * layers * ((nh + 2 * nkv) * hd * h + nh * hd * h + 3 * h * inter) + 2 * vocab * h
+        attn_flops = layers * 2 * 2 * nh * hd * (T * (T + 1) // 2)
+        pflops = lin_flops + attn_flops
+        out["prefill"] = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
+                          "frac": round(pflops / (pms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
+                          "tflop": round(pflops / 1e12, 3)}
+        points = {}
+        for b in (1, 64):
+            ms_b, _ = time_decode(b, min(args.steps, 32), 3)
+            points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 2)
+        out["points"] = points
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

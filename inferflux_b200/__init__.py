@@ -7,3 +7,10 @@ with state slots, one step function over mixed batches, a scheduler, sampling,
 hand-written sm_100a kernels, a true float32 path, and trace replay.
 """
 __version__ = "0.1.0"
+
+from .config import EngineConfig, Qwen2Config, load_config  # noqa: E402
+from .sampling import SamplingParams  # noqa: E402
+from .engine import Engine, GenerationResult, StepEntry  # noqa: E402
+
+__all__ = ["Engine", "EngineConfig", "GenerationResult", "Qwen2Config", "SamplingParams", "StepEntry",
+           "load_config"]
