@@ -1,0 +1,540 @@
+// bfloat16 paged grouped-query attention on tensor cores: one kernel for prompt
+// portions (any number of cached tokens before them) and one for single
+// decoded tokens (split over the keys, then merged).
+//
+// Same formulas as the generic kernel (attention_generic.cu): kv head = head /
+// (n_heads / n_kv), s = (q . k) * scale, causal with an optional window,
+// float32 online softmax, o = sum p v / sum p.  The reference's counterparts
+// are a scalar block-per-query kernel for ratios other than 2/4/8
+// (runtime/backends/cuda/kernels/flash_attention.cu:52-173), an mma.sync
+// kernel that converts bfloat16 q and k to float16
+// (runtime/backends/cuda/kernels/flash_attention_mma.cuh:153-379), and scalar
+// decode kernels with a fixed 8-way split (flash_attention.cu:468-570,775-973).
+//
+// Here q.k and p.v both run as m16n8k16 bfloat16 MMAs with float32
+// accumulation; keys and values come from the pages by 16-byte cp.async into
+// XOR-swizzled shared memory and are read with ldmatrix.  In the decode kernel
+// the 16 rows of an MMA tile are the query heads that share a kv head, so a
+// page is read once for all of them.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int sz = valid ? 16 : 0;    // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+// D(16x8, f32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+// A tile in shared memory: rows of HD bfloat16 = HD/8 chunks of 16 bytes; chunk c of
+// row r is stored at chunk (c ^ (r & 7)) so that ldmatrix reads are conflict-free.
+template <int HD>
+__device__ __forceinline__ bf16* tile_chunk(bf16* tile, int row, int chunk) {
+  return tile + row * HD + ((chunk ^ (row & 7)) << 3);
+}
+
+// Copy `n_rows` keys (or values) starting at absolute key index `key0` into a tile.
+// Rows outside [lo, hi) or in pages that were given back are zero-filled.
+template <int HD, int THREADS>
+__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* base, const PagedKV& kv, const int* bt,
+                                             int key0, int n_rows, int lo, int hi, int tid) {
+  constexpr int CPR = HD / 8;
+  for (int idx = tid; idx < n_rows * CPR; idx += THREADS) {
+    const int r = idx / CPR, c = idx - r * CPR;
+    const int key = key0 + r;
+    bool ok = key >= lo && key < hi;
+    const bf16* src = base;
+    if (ok) {
+      const int page = bt[key >> kv.page_shift];
+      ok = page >= 0;
+      if (ok) src = base + (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * HD + c * 8;
+    }
+    cp_async16(tile_chunk<HD>(tile, r, c), src, ok);
+  }
+}
+
+struct AttnMeta {
+  const int* block_tables; int bt_stride;
+  const int* entry_q_start; const int* entry_q_len; const int* entry_ctx_start;
+};
+
+// ------------------------------------------------------------------ prompts
+// One block: 64 consecutive new tokens of one entry (16 per warp), one head.
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
+                         PagedKV kv, AttnMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
+                         int n_heads, int n_kv, float scale, int window) {
+  constexpr int BQ = 64, BK = 64, KS = HD / 16, DT = HD / 8;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16* ks = reinterpret_cast<bf16*>(smem_raw);              // [2][BK][HD]
+  bf16* vs = ks + 2 * BK * HD;                               // [2][BK][HD]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const int e = tile_entry[blockIdx.x], q0 = tile_q0[blockIdx.x], head = blockIdx.y;
+  const int rows = min(BQ, m.entry_q_len[e] - q0);
+  if (rows <= 0) return;
+  const int tok0 = m.entry_q_start[e] + q0;
+  const int pos0 = m.entry_ctx_start[e] + q0;
+  const int kvh = head / (n_heads / n_kv);
+  const int* bt = m.block_tables + (size_t)e * m.bt_stride;
+  const bf16* kbase = (const bf16*)kv.k + (size_t)kvh * kv.head_stride;
+  const bf16* vbase = (const bf16*)kv.v + (size_t)kvh * kv.head_stride;
+
+  // this warp's 16 query rows as A fragments
+  const int wr0 = warp * 16;
+  unsigned qa[KS][4];
+  {
+    const bf16* qb = q + (size_t)head * HD;
+    const int ra = wr0 + g, rb = wr0 + g + 8;
+    const unsigned* pa = reinterpret_cast<const unsigned*>(qb + (size_t)(tok0 + ra) * q_stride);
+    const unsigned* pb = reinterpret_cast<const unsigned*>(qb + (size_t)(tok0 + rb) * q_stride);
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+      qa[k][0] = ra < rows ? pa[k * 8 + t4] : 0u;
+      qa[k][1] = rb < rows ? pb[k * 8 + t4] : 0u;
+      qa[k][2] = ra < rows ? pa[k * 8 + 4 + t4] : 0u;
+      qa[k][3] = rb < rows ? pb[k * 8 + 4 + t4] : 0u;
+    }
+  }
+  float o[DT][4];
+#pragma unroll
+  for (int d = 0; d < DT; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.0f, 0.0f};
+  const float sl2 = scale * LOG2E;
+
+  const int kend = pos0 + rows;                                  // keys [.., kend) may be seen
+  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the first row may see
+  const int t_begin = kfirst / BK, t_end = (kend - 1) / BK;
+  const int pa_row = pos0 + wr0 + g, pb_row = pa_row + 8;        // positions of this thread's two rows
+  const int warp_last = pos0 + min(wr0 + 15, rows - 1);
+
+  load_kv_tile<HD, 128>(ks, kbase, kv, bt, t_begin * BK, BK, kfirst, kend, tid);
+  load_kv_tile<HD, 128>(vs, vbase, kv, bt, t_begin * BK, BK, kfirst, kend, tid);
+  cp_async_commit();
+  for (int t = t_begin; t <= t_end; ++t) {
+    const int st = (t - t_begin) & 1;
+    if (t < t_end) {
+      load_kv_tile<HD, 128>(ks + (st ^ 1) * BK * HD, kbase, kv, bt, (t + 1) * BK, BK, kfirst, kend, tid);
+      load_kv_tile<HD, 128>(vs + (st ^ 1) * BK * HD, vbase, kv, bt, (t + 1) * BK, BK, kfirst, kend, tid);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key0 = t * BK;
+    const bool active = wr0 < rows && key0 <= warp_last &&
+                        (window <= 0 || key0 + BK > pos0 + wr0 - window + 1);
+    if (active) {
+      bf16* kt = ks + st * BK * HD;
+      bf16* vt = vs + st * BK * HD;
+      float s[BK / 8][4];
+#pragma unroll
+      for (int n = 0; n < BK / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f; }
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+#pragma unroll
+        for (int np = 0; np < BK / 16; ++np) {                   // two n-tiles (16 keys) per ldmatrix.x4
+          unsigned b[4];
+          const int j = lane >> 3, r = lane & 7;
+          ldmatrix_x4(b, tile_chunk<HD>(kt, np * 16 + (j >> 1) * 8 + r, k * 2 + (j & 1)));
+          mma_bf16(s[np * 2], qa[k], b[0], b[1]);
+          mma_bf16(s[np * 2 + 1], qa[k], b[2], b[3]);
+        }
+      }
+      // scale (after the dot), mask, row maxima
+      const bool need_mask = key0 + BK - 1 > pos0 + wr0 || window > 0 || key0 < kfirst;
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < BK / 8; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float v = s[n][c] * sl2;
+          if (need_mask) {
+            const int key = key0 + n * 8 + t4 * 2 + (c & 1);
+            const int p = (c & 2) ? pb_row : pa_row;
+            const bool vis = key <= p && key < kend && (window <= 0 || key > p - window);
+            if (!vis) v = -INFINITY;
+          }
+          s[n][c] = v;
+          mx[c >> 1] = fmaxf(mx[c >> 1], v);
+        }
+      }
+      float alpha[2], mnew[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        mnew[h] = fmaxf(mrow[h], mx[h]);
+        alpha[h] = mnew[h] == -INFINITY ? 1.0f : exp2f(mrow[h] - mnew[h]);
+        mrow[h] = mnew[h];
+      }
+      float ls[2] = {0.0f, 0.0f};
+#pragma unroll
+      for (int n = 0; n < BK / 8; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float mm = mnew[c >> 1];
+          const float p = mm == -INFINITY ? 0.0f : exp2f(s[n][c] - mm);
+          s[n][c] = p;
+          ls[c >> 1] += p;
+        }
+      }
+      lrow[0] = lrow[0] * alpha[0] + ls[0];
+      lrow[1] = lrow[1] * alpha[1] + ls[1];
+#pragma unroll
+      for (int d = 0; d < DT; ++d) { o[d][0] *= alpha[0]; o[d][1] *= alpha[0]; o[d][2] *= alpha[1]; o[d][3] *= alpha[1]; }
+#pragma unroll
+      for (int kk = 0; kk < BK / 16; ++kk) {                     // 16 keys per k-step
+        unsigned pa[4];
+        pa[0] = pack_bf16(s[kk * 2][0], s[kk * 2][1]);
+        pa[1] = pack_bf16(s[kk * 2][2], s[kk * 2][3]);
+        pa[2] = pack_bf16(s[kk * 2 + 1][0], s[kk * 2 + 1][1]);
+        pa[3] = pack_bf16(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < DT / 2; ++dp) {                    // two d-tiles (16 dims) per ldmatrix.x4.trans
+          unsigned b[4];
+          const int j = lane >> 3, r = lane & 7;
+          ldmatrix_x4_trans(b, tile_chunk<HD>(vt, kk * 16 + (j & 1) * 8 + r, dp * 2 + (j >> 1)));
+          mma_bf16(o[dp * 2], pa, b[0], b[1]);
+          mma_bf16(o[dp * 2 + 1], pa, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 1);
+    lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 2);
+  }
+  const float inv0 = lrow[0] > 0.0f ? 1.0f / lrow[0] : 0.0f;
+  const float inv1 = lrow[1] > 0.0f ? 1.0f / lrow[1] : 0.0f;
+  const int ra = wr0 + g, rb = ra + 8;
+  bf16* oa = out + (size_t)(tok0 + ra) * out_stride + (size_t)head * HD;
+  bf16* ob = out + (size_t)(tok0 + rb) * out_stride + (size_t)head * HD;
+#pragma unroll
+  for (int d = 0; d < DT; ++d) {
+    if (ra < rows) *reinterpret_cast<unsigned*>(oa + d * 8 + t4 * 2) = pack_bf16(o[d][0] * inv0, o[d][1] * inv0);
+    if (rb < rows) *reinterpret_cast<unsigned*>(ob + d * 8 + t4 * 2) = pack_bf16(o[d][2] * inv1, o[d][3] * inv1);
+  }
+}
+
+// ------------------------------------------------------------------- decode
+// One block: one decoding entry, up to 16 query heads of one kv head, one split of
+// the keys.  Each of the 4 warps takes every 4th 16-key tile of the split.
+// Partial results (max, sum, unnormalised o) go to scratch for the merge kernel;
+// with one split the block writes the final output itself.
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
+                        PagedKV kv, AttnMeta m, const int* __restrict__ dec_entries,
+                        float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits) {
+  constexpr int KS = HD / 16, DT = HD / 8, TK = 16, STAGES = 2;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);       // [4 warps][STAGES][K|V][TK][HD]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const int e = dec_entries[blockIdx.x];
+  const int kvh = blockIdx.y / head_chunks, hc = blockIdx.y - kvh * head_chunks;
+  const int split = blockIdx.z;
+  const int ratio = n_heads / n_kv;
+  const int h0 = kvh * ratio + hc * 16;
+  const int nrows = min(16, ratio - hc * 16);
+  const int tok = m.entry_q_start[e];
+  const int len = m.entry_ctx_start[e] + 1;                     // keys [0, len) exist; the query sits at len - 1
+  const int kfirst = window > 0 ? max(0, len - window) : 0;
+  const int total = len - kfirst;
+  int chunk = (total + n_splits - 1) / n_splits;
+  chunk = (chunk + TK - 1) / TK * TK;
+  const int kb = kfirst + split * chunk, ke = min(len, kb + chunk);
+  const int* bt = m.block_tables + (size_t)e * m.bt_stride;
+  const bf16* kbase = (const bf16*)kv.k + (size_t)kvh * kv.head_stride;
+  const bf16* vbase = (const bf16*)kv.v + (size_t)kvh * kv.head_stride;
+  const int dec = blockIdx.x;
+
+  float o[DT][4];
+#pragma unroll
+  for (int d = 0; d < DT; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.0f, 0.0f};
+
+  if (kb < ke) {
+    unsigned qa[KS][4];
+    {
+      const bf16* qb = q + (size_t)tok * q_stride + (size_t)h0 * HD;
+      const unsigned* pa = reinterpret_cast<const unsigned*>(qb + (size_t)g * HD);
+      const unsigned* pb = reinterpret_cast<const unsigned*>(qb + (size_t)(g + 8) * HD);
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        qa[k][0] = g < nrows ? pa[k * 8 + t4] : 0u;
+        qa[k][1] = g + 8 < nrows ? pb[k * 8 + t4] : 0u;
+        qa[k][2] = g < nrows ? pa[k * 8 + 4 + t4] : 0u;
+        qa[k][3] = g + 8 < nrows ? pb[k * 8 + 4 + t4] : 0u;
+      }
+    }
+    const float sl2 = scale * LOG2E;
+    bf16* my = stage_base + (size_t)warp * STAGES * 2 * TK * HD;
+    const int t_begin = kb / TK, t_end = (ke - 1) / TK;
+    int t = t_begin + warp;
+    if (t <= t_end) {
+      load_kv_tile<HD, 32>(my, kbase, kv, bt, t * TK, TK, kb, ke, lane);
+      load_kv_tile<HD, 32>(my + TK * HD, vbase, kv, bt, t * TK, TK, kb, ke, lane);
+    }
+    cp_async_commit();
+    int st = 0;
+    for (; t <= t_end; t += 4, st ^= 1) {
+      const int tn = t + 4;
+      if (tn <= t_end) {
+        bf16* nx = my + (size_t)(st ^ 1) * 2 * TK * HD;
+        load_kv_tile<HD, 32>(nx, kbase, kv, bt, tn * TK, TK, kb, ke, lane);
+        load_kv_tile<HD, 32>(nx + TK * HD, vbase, kv, bt, tn * TK, TK, kb, ke, lane);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncwarp();
+      bf16* kt = my + (size_t)st * 2 * TK * HD;
+      bf16* vt = kt + TK * HD;
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const int j = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        unsigned b[4];
+        ldmatrix_x4(b, tile_chunk<HD>(kt, (j >> 1) * 8 + r, k * 2 + (j & 1)));
+        mma_bf16(s[0], qa[k], b[0], b[1]);
+        mma_bf16(s[1], qa[k], b[2], b[3]);
+      }
+      const int key0 = t * TK;
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int key = key0 + n * 8 + t4 * 2 + (c & 1);
+          const float v = (key >= kb && key < ke) ? s[n][c] * sl2 : -INFINITY;
+          s[n][c] = v;
+          mx[c >> 1] = fmaxf(mx[c >> 1], v);
+        }
+      }
+      float alpha[2], mnew[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        mnew[h] = fmaxf(mrow[h], mx[h]);
+        alpha[h] = mnew[h] == -INFINITY ? 1.0f : exp2f(mrow[h] - mnew[h]);
+        mrow[h] = mnew[h];
+      }
+      float ls[2] = {0.0f, 0.0f};
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float mm = mnew[c >> 1];
+          const float p = mm == -INFINITY ? 0.0f : exp2f(s[n][c] - mm);
+          s[n][c] = p;
+          ls[c >> 1] += p;
+        }
+      }
+      lrow[0] = lrow[0] * alpha[0] + ls[0];
+      lrow[1] = lrow[1] * alpha[1] + ls[1];
+      unsigned pa[4];
+      pa[0] = pack_bf16(s[0][0], s[0][1]);
+      pa[1] = pack_bf16(s[0][2], s[0][3]);
+      pa[2] = pack_bf16(s[1][0], s[1][1]);
+      pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+      for (int dp = 0; dp < DT / 2; ++dp) {
+        unsigned b[4];
+        ldmatrix_x4_trans(b, tile_chunk<HD>(vt, (j & 1) * 8 + r, dp * 2 + (j >> 1)));
+        o[dp * 2][0] *= alpha[0]; o[dp * 2][1] *= alpha[0]; o[dp * 2][2] *= alpha[1]; o[dp * 2][3] *= alpha[1];
+        o[dp * 2 + 1][0] *= alpha[0]; o[dp * 2 + 1][1] *= alpha[0]; o[dp * 2 + 1][2] *= alpha[1]; o[dp * 2 + 1][3] *= alpha[1];
+        mma_bf16(o[dp * 2], pa, b[0], b[1]);
+        mma_bf16(o[dp * 2 + 1], pa, b[2], b[3]);
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 1);
+      lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 2);
+    }
+  }
+  // merge the four warps through shared memory (the stage buffers are free now)
+  __syncthreads();
+  float* red_o = reinterpret_cast<float*>(smem_raw);            // [4][16][HD]
+  float* red_ml = red_o + 4 * 16 * HD;                          // [4][16][2]
+#pragma unroll
+  for (int d = 0; d < DT; ++d) {
+    float* ra = red_o + ((size_t)warp * 16 + g) * HD + d * 8 + t4 * 2;
+    float* rb = red_o + ((size_t)warp * 16 + g + 8) * HD + d * 8 + t4 * 2;
+    ra[0] = o[d][0]; ra[1] = o[d][1]; rb[0] = o[d][2]; rb[1] = o[d][3];
+  }
+  if (t4 == 0) {
+    red_ml[(warp * 16 + g) * 2] = mrow[0];     red_ml[(warp * 16 + g) * 2 + 1] = lrow[0];
+    red_ml[(warp * 16 + g + 8) * 2] = mrow[1]; red_ml[(warp * 16 + g + 8) * 2 + 1] = lrow[1];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < nrows * HD; idx += 128) {
+    const int row = idx / HD, d = idx - row * HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_ml[(w * 16 + row) * 2]);
+    float l = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = red_ml[(w * 16 + row) * 2];
+      const float f = mw == -INFINITY ? 0.0f : exp2f(mw - mm);
+      l += red_ml[(w * 16 + row) * 2 + 1] * f;
+      acc += red_o[((size_t)w * 16 + row) * HD + d] * f;
+    }
+    const int head = h0 + row;
+    if (n_splits == 1) {
+      out[(size_t)tok * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    } else {
+      const size_t p = ((size_t)dec * n_heads + head) * n_splits + split;
+      part_o[p * HD + d] = acc;
+      if (d == 0) { part_ml[p * 2] = mm; part_ml[p * 2 + 1] = l; }
+    }
+  }
+}
+
+// merge the splits: grid (n_dec, n_heads), HD threads
+__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         bf16* __restrict__ out, long long out_stride, const int* __restrict__ dec_entries,
+                                         const int* __restrict__ entry_q_start, int n_heads, int head_dim, int n_splits) {
+  const int dec = blockIdx.x, head = blockIdx.y;
+  const int tok = entry_q_start[dec_entries[dec]];
+  const size_t p0 = ((size_t)dec * n_heads + head) * n_splits;
+  float mm = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(p0 + s) * 2]);
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float l = 0.0f, acc = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = part_ml[(p0 + s) * 2];
+      const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+      l += part_ml[(p0 + s) * 2 + 1] * f;
+      acc += part_o[(p0 + s) * head_dim + d] * f;
+    }
+    out[(size_t)tok * out_stride + (size_t)head * head_dim + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+  }
+}
+
+PagedKV make_kv(void* k_layer, void* v_layer, long long page_stride, int page_size, int head_dim) {
+  PagedKV kv;
+  kv.k = k_layer; kv.v = v_layer; kv.page_stride = page_stride;
+  kv.head_stride = page_size * head_dim; kv.page_size = page_size; kv.page_shift = 0;
+  while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
+  return kv;
+}
+
+template <int HD>
+int launch_prefill(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnMeta m,
+                   const int* tile_entry, const int* tile_q0, int n_tiles, int n_heads, int n_kv, float scale,
+                   int window, cudaStream_t stream) {
+  const size_t smem = (size_t)4 * 64 * HD * sizeof(bf16);
+  auto kern = attn_prefill_bf16_kernel<HD>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kern<<<dim3(n_tiles, n_heads), 128, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m,
+                                                      tile_entry, tile_q0, n_heads, n_kv, scale, window);
+  return IFX_LAUNCH_CHECK();
+}
+
+template <int HD>
+int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnMeta m,
+                  const int* dec_entries, int n_dec, float* part_o, float* part_ml, int n_heads, int n_kv,
+                  float scale, int window, int n_splits, cudaStream_t stream) {
+  const size_t stage_bytes = (size_t)4 * 2 * 2 * 16 * HD * sizeof(bf16);
+  const size_t red_bytes = (size_t)4 * 16 * HD * sizeof(float) + 4 * 16 * 2 * sizeof(float);
+  const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
+  auto kern = attn_decode_bf16_kernel<HD>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int ratio = n_heads / n_kv;
+  const int head_chunks = (ratio + 15) / 16;
+  kern<<<dim3(n_dec, n_kv * head_chunks, n_splits), 128, smem, stream>>>(
+      (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, dec_entries, part_o, part_ml, n_heads, n_kv,
+      head_chunks, scale, window, n_splits);
+  int rc = IFX_LAUNCH_CHECK();
+  if (rc || n_splits == 1) return rc;
+  attn_decode_merge_kernel<<<dim3(n_dec, n_heads), HD < 128 ? HD : 128, 0, stream>>>(
+      part_o, part_ml, (bf16*)out, out_stride, dec_entries, m.entry_q_start, n_heads, HD, n_splits);
+  return IFX_LAUNCH_CHECK();
+}
+}  // namespace
+
+// head_dim 64 or 128; page_size a power of two; q rows 4-byte aligned.
+// Query tiles are 64 tokens of one entry (tile_entry / tile_q0).
+IFX_API int ifx_attn_prefill_bf16(const void* q, long long q_stride, void* out, long long out_stride,
+                                  void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                  const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_q0,
+                                  int n_tiles, const int* entry_q_start, const int* entry_q_len,
+                                  const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
+                                  int window, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (n_kv < 1 || n_heads % n_kv || n_heads > 65535) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  if ((q_stride & 1) || (out_stride & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3)) return IFX_ERR_ALIGNMENT;
+  if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
+  PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
+  AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
+  if (head_dim == 128)
+    return launch_prefill<128>(q, q_stride, out, out_stride, kv, m, tile_entry, tile_q0, n_tiles, n_heads, n_kv, scale, window, stream);
+  if (head_dim == 64)
+    return launch_prefill<64>(q, q_stride, out, out_stride, kv, m, tile_entry, tile_q0, n_tiles, n_heads, n_kv, scale, window, stream);
+  return IFX_ERR_UNSUPPORTED;
+}
+
+// Scratch: part_o float32 [n_dec * n_heads * n_splits * head_dim], part_ml float32
+// [n_dec * n_heads * n_splits * 2] (unused when n_splits == 1).
+IFX_API int ifx_attn_decode_bf16(const void* q, long long q_stride, void* out, long long out_stride,
+                                 void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                 const int* block_tables, int bt_stride, const int* dec_entries, int n_dec,
+                                 const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
+                                 float* part_o, float* part_ml, int n_heads, int n_kv, int head_dim, float scale,
+                                 int window, int n_splits, cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (n_kv < 1 || n_heads % n_kv || n_splits < 1 || n_splits > 65535) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  if ((q_stride & 1) || ((uintptr_t)q & 3)) return IFX_ERR_ALIGNMENT;
+  if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
+  if (n_splits > 1 && (!part_o || !part_ml)) return IFX_ERR_UNSUPPORTED;
+  PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
+  AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
+  if (head_dim == 128)
+    return launch_decode<128>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, stream);
+  if (head_dim == 64)
+    return launch_decode<64>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, stream);
+  return IFX_ERR_UNSUPPORTED;
+}

@@ -18,6 +18,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import torch
 
 QUERY_TILE = 16     # tokens per query tile of the generic attention kernel
+CHUNK_TILE = 64     # tokens per query tile of the tensor-core kernel for prompt portions
 
 
 @dataclass
@@ -80,6 +81,11 @@ class StepContext:
     tile_entry: torch.Tensor                  # [T] query tiles of QUERY_TILE tokens
     tile_q0: torch.Tensor                     # [T]
     n_tiles: int
+    chunk_tile_entry: torch.Tensor            # [Tc] tiles of CHUNK_TILE tokens over entries with more than one token
+    chunk_tile_q0: torch.Tensor               # [Tc]
+    n_chunk_tiles: int
+    decode_entries: torch.Tensor              # [D] entries that bring exactly one token
+    n_decode: int
     block_tables: List[torch.Tensor]          # per cache group [R, max_blocks]
     slot_maps: List[torch.Tensor]             # per cache group [N]
     want_rows: torch.Tensor                   # [W] rows whose logits are wanted

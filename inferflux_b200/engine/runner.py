@@ -19,7 +19,7 @@ import torch
 
 from ..cache import OutOfPages, OutOfSlots, KVCacheManager, KVCacheStorage, StateSlotManager, StateSlotStorage, bytes_per_token
 from ..config.engine_config import EngineConfig
-from .batch import QUERY_TILE, MetadataSlab, StepContext, StepEntry
+from .batch import CHUNK_TILE, QUERY_TILE, MetadataSlab, StepContext, StepEntry
 from .model import Model
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -127,6 +127,7 @@ class StepRunner:
         ps = self.page_size
         token_ids, positions, q_start, q_len, ctx_start, slots = [], [], [], [], [], []
         tile_entry, tile_q0, want_rows = [], [], []
+        ctile_entry, ctile_q0, dec_entries = [], [], []
         for i, e in enumerate(entries):
             start = self.kv.length(e.rid)
             q_start.append(len(token_ids))
@@ -138,6 +139,12 @@ class StepRunner:
             for q0 in range(0, len(e.tokens), QUERY_TILE):
                 tile_entry.append(i)
                 tile_q0.append(q0)
+            if len(e.tokens) == 1:
+                dec_entries.append(i)
+            else:
+                for q0 in range(0, len(e.tokens), CHUNK_TILE):
+                    ctile_entry.append(i)
+                    ctile_q0.append(q0)
             token_ids.extend(int(t) for t in e.tokens)
             positions.extend(range(start, start + len(e.tokens)))
         n, r = len(token_ids), len(entries)
@@ -158,7 +165,7 @@ class StepRunner:
             widths.append(width)
             tables.append(flat)
             slot_maps.append(sm)
-        need = 4 * (8 + groups) + 2 * n + 4 * r + 2 * len(tile_entry) + len(want_rows) \
+        need = 4 * (12 + groups) + 2 * n + 5 * r + 2 * len(tile_entry) + 2 * len(ctile_entry) + len(want_rows) \
             + sum(len(t) for t in tables) + groups * n + 64
         if need > self.slab.capacity:
             self.slab = MetadataSlab(max(need, 2 * self.slab.capacity), self.device)
@@ -167,6 +174,7 @@ class StepRunner:
         d_tok, d_pos = slab.put(token_ids), slab.put(positions)
         d_qs, d_ql, d_cs, d_sl = slab.put(q_start), slab.put(q_len), slab.put(ctx_start), slab.put(slots)
         d_te, d_tq = slab.put(tile_entry), slab.put(tile_q0)
+        d_cte, d_ctq, d_dec = slab.put(ctile_entry), slab.put(ctile_q0), slab.put(dec_entries)
         d_want = slab.put(want_rows)
         d_tabs = [slab.put(t).view(r, w) for t, w in zip(tables, widths)]
         d_sm = [slab.put(s) for s in slot_maps]
@@ -175,6 +183,8 @@ class StepRunner:
             n_tokens=n, n_entries=r, entries=list(entries), ctx_starts=ctx_start, slots=slots,
             token_ids=d_tok, positions=d_pos, entry_q_start=d_qs, entry_q_len=d_ql, entry_ctx_start=d_cs,
             entry_slot=d_sl, tile_entry=d_te, tile_q0=d_tq, n_tiles=len(tile_entry),
+            chunk_tile_entry=d_cte, chunk_tile_q0=d_ctq, n_chunk_tiles=len(ctile_entry),
+            decode_entries=d_dec, n_decode=len(dec_entries),
             block_tables=d_tabs, slot_maps=d_sm, want_rows=d_want, n_want=len(want_rows),
             max_q_len=max(q_len), max_ctx_len=max(c + l for c, l in zip(ctx_start, q_len)),
             page_size=ps, kv=self.kv_storage, dtype=self.dtype, device=self.device)

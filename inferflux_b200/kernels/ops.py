@@ -49,6 +49,12 @@ def _lib():
         lib.ifx_attn_paged_generic.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int,
                                                c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
+        lib.ifx_attn_prefill_bf16.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
+                                              c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
+        lib.ifx_attn_decode_bf16.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
+                                             c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
         lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p]
         lib.ifx_apply_penalties.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                             c_void_p, c_int, c_int, c_void_p]
@@ -56,6 +62,7 @@ def _lib():
                                    c_void_p, c_void_p, c_int, c_int, c_void_p]
         for name in ("ifx_embed_gather", "ifx_add_rmsnorm", "ifx_swiglu", "ifx_convert", "ifx_rope_table",
                      "ifx_qkv_rope_kv_write", "ifx_gemm_f32", "ifx_attn_paged_generic", "ifx_argmax",
+                     "ifx_attn_prefill_bf16", "ifx_attn_decode_bf16",
                      "ifx_apply_penalties", "ifx_sample"):
             getattr(lib, name).restype = c_int
         _sigs_done = True
@@ -245,6 +252,58 @@ def attn_paged_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_laye
                                          _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start),
                                          n_heads, n_kv, head_dim, float(scale), int(window), _stream()),
            "attn_paged_generic")
+    return out
+
+
+FAST_ATTENTION_HEAD_DIMS = (64, 128)
+
+
+def attn_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer: torch.Tensor,
+                      v_layer: torch.Tensor, page_stride: int, page_size: int, block_tables: torch.Tensor,
+                      tile_entry: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
+                      entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor,
+                      n_heads: int, n_kv: int, head_dim: int, scale: float, window: int) -> torch.Tensor:
+    """Tensor-core attention of prompt portions over the paged cache (bfloat16,
+    head_dim 64 or 128); query tiles of 64 tokens listed by tile_entry / tile_q0."""
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16,
+          "attn_prefill_bf16: bfloat16 operands")
+    _need(head_dim in FAST_ATTENTION_HEAD_DIMS, f"attn_prefill_bf16: head_dim {head_dim} not in {FAST_ATTENTION_HEAD_DIMS}")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
+    _check(_lib().ifx_attn_prefill_bf16(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
+                                        page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
+                                        _ptr(tile_entry), _ptr(tile_q0), n_tiles, _ptr(entry_q_start),
+                                        _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, n_kv, head_dim,
+                                        float(scale), int(window), _stream()), "attn_prefill_bf16")
+    return out
+
+
+def attn_decode_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer: torch.Tensor,
+                     v_layer: torch.Tensor, page_stride: int, page_size: int, block_tables: torch.Tensor,
+                     dec_entries: torch.Tensor, n_dec: int, entry_q_start: torch.Tensor,
+                     entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor, part_o: Optional[torch.Tensor],
+                     part_ml: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int, scale: float,
+                     window: int, n_splits: int) -> torch.Tensor:
+    """Tensor-core attention of single decoded tokens (entries listed in
+    dec_entries), the keys split ``n_splits`` ways and merged.  Scratch:
+    part_o float32 [n_dec * n_heads * n_splits * head_dim], part_ml float32
+    [n_dec * n_heads * n_splits * 2]."""
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16,
+          "attn_decode_bf16: bfloat16 operands")
+    _need(head_dim in FAST_ATTENTION_HEAD_DIMS, f"attn_decode_bf16: head_dim {head_dim} not in {FAST_ATTENTION_HEAD_DIMS}")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
+    if n_splits > 1:
+        _need(part_o is not None and part_o.dtype == torch.float32
+              and part_o.numel() >= n_dec * n_heads * n_splits * head_dim
+              and part_ml is not None and part_ml.dtype == torch.float32
+              and part_ml.numel() >= n_dec * n_heads * n_splits * 2, "attn_decode_bf16: scratch too small")
+    global launch_count
+    if n_splits > 1:
+        launch_count += 1          # the merge kernel
+    _check(_lib().ifx_attn_decode_bf16(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
+                                       page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
+                                       _ptr(dec_entries), n_dec, _ptr(entry_q_start), _ptr(entry_q_len),
+                                       _ptr(entry_ctx_start), _ptr(part_o), _ptr(part_ml), n_heads, n_kv, head_dim,
+                                       float(scale), int(window), int(n_splits), _stream()), "attn_decode_bf16")
     return out
 
 

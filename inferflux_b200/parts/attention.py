@@ -116,10 +116,40 @@ class GQAttention(Part):
         return self.o.forward(attn, out_dtype=x.dtype)
 
     def attend(self, qkv, attn, ctx, g, k_layer, v_layer, page_stride) -> None:
-        ops.attn_paged_generic(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
-                               ctx.block_tables[g], ctx.tile_entry, ctx.tile_q0, ctx.n_tiles,
-                               ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,
-                               self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
+        """bfloat16 with a head size the tensor-core kernels take: prompt
+        portions and single tokens go to their own kernels; anything else
+        (float32, other head sizes) to the generic kernel."""
+        common = (ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start)
+        if qkv.dtype != torch.bfloat16 or self.head_dim not in ops.FAST_ATTENTION_HEAD_DIMS:
+            ops.attn_paged_generic(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
+                                   ctx.block_tables[g], ctx.tile_entry, ctx.tile_q0, ctx.n_tiles, *common,
+                                   self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
+            return
+        if ctx.n_chunk_tiles:
+            ops.attn_prefill_bf16(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
+                                  ctx.block_tables[g], ctx.chunk_tile_entry, ctx.chunk_tile_q0, ctx.n_chunk_tiles,
+                                  *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
+        if ctx.n_decode:
+            n_splits = decode_splits(ctx.n_decode, self.n_heads, self.n_kv,
+                                     min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len)
+            part_o = part_ml = None
+            if n_splits > 1:
+                rows = ctx.n_decode * self.n_heads * n_splits
+                part_o = torch.empty(rows * self.head_dim, dtype=torch.float32, device=qkv.device)
+                part_ml = torch.empty(rows * 2, dtype=torch.float32, device=qkv.device)
+            ops.attn_decode_bf16(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
+                                 ctx.block_tables[g], ctx.decode_entries, ctx.n_decode, *common, part_o, part_ml,
+                                 self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, n_splits)
+
+
+def decode_splits(n_decode: int, n_heads: int, n_kv: int, max_keys: int, target_blocks: int = 592) -> int:
+    """Into how many parts the decode kernel cuts the keys: enough blocks to
+    fill 148 SMs four times over, but at least 128 keys per part."""
+    ratio = n_heads // n_kv
+    base = max(1, n_decode * n_kv * ((ratio + 15) // 16))
+    by_blocks = (target_blocks + base - 1) // base
+    by_keys = max(1, max_keys // 128)
+    return max(1, min(by_blocks, by_keys, 64))
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -29,7 +29,13 @@ TINY_C = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_siz
               num_attention_heads=10, num_key_value_heads=2, head_dim=48, intermediate_size=136, vocab_size=777,
               rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=384,
               use_sliding_window=False, hidden_act="silu", torch_dtype="bfloat16")
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# head_dim 64: the size the tensor-core attention kernels take; 3 query heads per kv head, a window
+TINY_D = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=120, num_hidden_layers=2,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=200, vocab_size=600,
+              rope_theta=200000.0, rms_norm_eps=2e-6, tie_word_embeddings=True, max_position_embeddings=400,
+              use_sliding_window=True, sliding_window=70, max_window_layers=1, hidden_act="silu",
+              torch_dtype="bfloat16")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 # Largest |engine - plain| allowed, as a fraction of the largest |plain logit|.
 # float32: a few hundred float32 roundings; bfloat16: 8-bit mantissas through every layer.

@@ -1,0 +1,345 @@
+"""Each CUDA kernel alone against its plain PyTorch float32 reference
+(tests/kernel_refs.py), at sizes other than the engine's test models: row
+lengths that are no power of two, head sizes in steps of 16, odd head counts
+and group ratios, page sizes 4 to 64.  Where random inputs would hide a fault
+(one far key among hundreds, a window's edge, a page border) the inputs are
+made so that it shows."""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from inferflux_b200.kernels import ops as o
+    return o
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def _close(got, want, tol, what=""):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+    assert err <= tol, f"{what}: relative error {err:.3e} > {tol}"
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab,hidden", [(37, 24), (1000, 100), (513, 3584)])
+def test_embed_gather(ops, dtype, vocab, hidden):
+    table = _rand((vocab, hidden), dtype, 1)
+    ids = torch.tensor([0, vocab - 1, 5, 5, vocab // 2], dtype=torch.int32, device=DEV)
+    out = torch.empty((5, hidden), dtype=torch.float32, device=DEV)
+    ops.embed_gather(table, ids, out)
+    assert torch.equal(out.cpu(), table.cpu()[ids.cpu().long()].float())
+
+
+@pytest.mark.parametrize("hidden", [24, 100, 3584, 5120 + 8])
+@pytest.mark.parametrize("ddt,odt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.float32, torch.bfloat16)])
+def test_add_rmsnorm(ops, hidden, ddt, odt):
+    n = 7
+    res = _rand((n, hidden), torch.float32, 2)
+    delta = _rand((n, hidden), ddt, 3)
+    w = _rand((hidden,), torch.float32, 4) + 1.0
+    res_ref, out_ref = res.clone().cpu(), torch.empty((n, hidden), dtype=odt)
+    ref.add_rmsnorm(res_ref, delta.cpu(), w.cpu(), 1e-5, out_ref)
+    out = torch.empty((n, hidden), dtype=odt, device=DEV)
+    ops.add_rmsnorm(res, delta, w, 1e-5, out)
+    _close(res, res_ref, 1e-6, "residual")
+    _close(out, out_ref, 1e-5 if odt == torch.float32 else 8e-3, "normed")
+    # gather mode: listed rows only, a row listed twice, the residual untouched
+    rows = torch.tensor([6, 0, 6], dtype=torch.int32, device=DEV)
+    before = res.clone()
+    out2 = torch.empty((3, hidden), dtype=odt, device=DEV)
+    ops.add_rmsnorm(res, delta, w, 1e-5, out2, rows)
+    assert torch.equal(res, before)
+    out2_ref = torch.empty((3, hidden), dtype=odt)
+    ref.add_rmsnorm(before.cpu(), delta.cpu(), w.cpu(), 1e-5, out2_ref, rows.cpu())
+    _close(out2, out2_ref, 1e-5 if odt == torch.float32 else 8e-3, "gathered")
+    # no delta
+    out3 = torch.empty((n, hidden), dtype=odt, device=DEV)
+    ops.add_rmsnorm(res, None, w, 1e-5, out3)
+    out3_ref = torch.empty((n, hidden), dtype=odt)
+    ref.add_rmsnorm(before.cpu(), None, w.cpu(), 1e-5, out3_ref)
+    _close(out3, out3_ref, 1e-5 if odt == torch.float32 else 8e-3, "no delta")
+
+
+def test_add_rmsnorm_partials(ops):
+    n, hidden, parts = 5, 200, 3
+    res = _rand((n, hidden), torch.float32, 5)
+    delta = _rand((parts, n, hidden), torch.float32, 6)
+    w = torch.ones(hidden, device=DEV)
+    want = res.cpu() + delta.cpu().sum(0)
+    out = torch.empty((n, hidden), dtype=torch.float32, device=DEV)
+    ops.add_rmsnorm(res, delta, w, 1e-6, out, n_partials=parts)
+    _close(res, want, 1e-6, "partials")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,inter", [(1, 7), (5, 176), (33, 18944)])
+def test_swiglu(ops, dtype, m, inter):
+    gu = _rand((m, 2 * inter), dtype, 7, 2.0)
+    out = torch.empty((m, inter), dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    want = torch.empty((m, inter), dtype=dtype)
+    ref.swiglu(gu.cpu(), want)
+    _close(out, want, 1e-6 if dtype == torch.float32 else 8e-3, "swiglu")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 5, 3), (7, 100, 96), (65, 130, 257), (128, 64, 64), (3, 1000, 80)])
+def test_gemm_f32(ops, m, n, k):
+    a, w, b = _rand((m, k), torch.float32, 8), _rand((n, k), torch.float32, 9), _rand((n,), torch.float32, 10)
+    out = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    ops.gemm_f32(a, w, b, out)
+    want = a.double().cpu() @ w.double().cpu().T + b.double().cpu()
+    _close(out, want, 2e-6, "gemm_f32")
+    # a row's result does not depend on the other rows (bitwise)
+    one = torch.empty((1, n), dtype=torch.float32, device=DEV)
+    ops.gemm_f32(a[m - 1:m], w, b, one)
+    assert torch.equal(one[0], out[m - 1])
+
+
+def test_gemm_f32_is_true_float32(ops):
+    """Values that a reduced-precision (tf32, 10-bit mantissa) product would lose."""
+    k = 64
+    a = torch.full((1, k), 1.0 + 2.0 ** -12, device=DEV)
+    w = torch.full((1, k), 1.0 + 2.0 ** -12, device=DEV)
+    out = torch.empty((1, 1), device=DEV)
+    ops.gemm_f32(a, w, None, out)
+    want = k * (1.0 + 2.0 ** -12) ** 2
+    assert abs(float(out) - want) / want < 1e-6
+
+
+# ----------------------------------------------------------------------- rotary
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rot,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 4), (10, 2, 48, 24, 8),
+                                              (28, 4, 128, 128, 16), (5, 5, 80, 80, 64), (2, 0, 64, 64, 16)])
+def test_rope_and_kv_write(ops, dtype, nh, nkv, hd, rot, ps):
+    n, pages, layers = 19, 9, 2
+    positions = torch.tensor([0, 1, 2, 3, 500, 501, 4095, 31, 32, 33, 7, 8, 9, 10, 11, 12, 13, 14, 15],
+                             dtype=torch.int32, device=DEV)
+    inv = torch.pow(torch.tensor(1e6, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).to(DEV)
+    cos = torch.empty((n, rot // 2), dtype=torch.float32, device=DEV)
+    sin = torch.empty_like(cos)
+    ops.rope_table(positions, inv, cos, sin)
+    ang = positions.double().cpu()[:, None] * inv.cpu()[None, :]
+    _close(cos, torch.cos(ang), 1e-6, "cos")
+    _close(sin, torch.sin(ang), 1e-6, "sin")
+    width = (nh + 2 * nkv) * hd
+    qkv = _rand((n, width), dtype, 11)
+    bias = _rand((width,), torch.float32, 12)
+    pool = torch.zeros((pages, layers, 2, max(nkv, 1), ps, hd), dtype=dtype, device=DEV)
+    slots = torch.randperm(pages * ps, generator=torch.Generator().manual_seed(1))[:n].int().to(DEV)
+    slots[3] = -1                                            # not stored
+    qkv_ref, pool_ref = qkv.clone().cpu(), pool.clone().cpu()
+    ref.qkv_rope_kv_write(qkv_ref, bias.cpu(), cos.cpu(), sin.cpu(), slots.cpu(), pool_ref[0, 1, 0], pool_ref[0, 1, 1],
+                          pool_ref.stride(0), ps, nh, nkv, hd)
+    ops.qkv_rope_kv_write(qkv, bias, cos, sin, slots if nkv else None, pool[0, 1, 0] if nkv else None,
+                          pool[0, 1, 1] if nkv else None, pool.stride(0), ps, nh, nkv, hd)
+    tol = 1e-6 if dtype == torch.float32 else 8e-3
+    _close(qkv[:, :nh * hd], qkv_ref[:, :nh * hd], tol, "q")
+    if nkv:
+        _close(pool, pool_ref, tol, "cache")
+        assert float(pool[:, 0].abs().max()) == 0.0          # the other layer's pages are untouched
+
+
+# -------------------------------------------------------------------- attention
+def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, fast):
+    """entries: list of (cached tokens, new tokens).  Builds a paged cache with
+    scattered pages, runs the kernel(s) and the reference."""
+    from inferflux_b200.engine.batch import CHUNK_TILE, QUERY_TILE
+    g = torch.Generator().manual_seed(seed)
+    n = sum(q for _, q in entries)
+    total_pages = sum((c + q + ps - 1) // ps for c, q in entries) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    pool = torch.zeros((total_pages, 1, 2, nkv, ps, hd), dtype=dtype)
+    width = max((c + q + ps - 1) // ps for c, q in entries)
+    bt = torch.full((len(entries), width), -1, dtype=torch.int32)
+    q = torch.randn((n, nh * hd), generator=g)
+    q_start, q_len, ctx_start, tiles, ctiles, decs = [], [], [], [], [], []
+    row = 0
+    for e, (c, ql) in enumerate(entries):
+        nblocks = (c + ql + ps - 1) // ps
+        for b in range(nblocks):
+            bt[e, b] = perm.pop()
+        keys = torch.randn((c + ql, nkv, hd), generator=g)
+        vals = torch.randn((c + ql, nkv, hd), generator=g)
+        if peaked:
+            # one far key per (query row, kv head) dominates: the output is close to that key's value
+            for i in range(ql):
+                pos = c + i
+                lo = max(0, pos - window + 1) if window else 0
+                far = lo if i % 2 == 0 else (lo + pos) // 2
+                for h in range(nh):
+                    kh = h // (nh // nkv)
+                    if i % 3 == h % 3:
+                        q[row + i, h * hd:(h + 1) * hd] = keys[far, kh] * 3.0
+        if window:
+            first_needed = max(0, c - window + 1) // ps          # blocks before it were given back
+            for b in range(first_needed):
+                bt[e, b] = -1
+        for pos in range(c + ql):
+            page = int(bt[e, pos // ps])
+            if page >= 0:
+                pool[page, 0, 0, :, pos % ps] = keys[pos].to(dtype)
+                pool[page, 0, 1, :, pos % ps] = vals[pos].to(dtype)
+        q_start.append(row), q_len.append(ql), ctx_start.append(c)
+        tiles += [(e, q0) for q0 in range(0, ql, QUERY_TILE)]
+        if ql == 1:
+            decs.append(e)
+        else:
+            ctiles += [(e, q0) for q0 in range(0, ql, CHUNK_TILE)]
+        row += ql
+    q = q.to(dtype)
+    it = lambda v: torch.tensor(v, dtype=torch.int32)
+    meta = dict(q_start=it(q_start), q_len=it(q_len), ctx_start=it(ctx_start))
+    scale = 1.0 / math.sqrt(hd)
+    want = torch.zeros((n, nh * hd), dtype=torch.float32)
+    poolf = pool.float()
+    ref.attn_paged_generic(q.float(), nh * hd, want, poolf[0, 0, 0], poolf[0, 0, 1], poolf.stride(0), ps, bt,
+                           None, None, 0, meta["q_start"], meta["q_len"], meta["ctx_start"], nh, nkv, hd, scale,
+                           window or 0)
+    qd, poold, btd = q.to(DEV), pool.to(DEV), bt.to(DEV)
+    md = {k: v.to(DEV) for k, v in meta.items()}
+    out = torch.zeros((n, nh * hd), dtype=dtype, device=DEV)
+    args = (poold[0, 0, 0], poold[0, 0, 1], poold.stride(0), ps, btd)
+    if not fast:
+        te, tq = it([t[0] for t in tiles]).to(DEV), it([t[1] for t in tiles]).to(DEV)
+        ops.attn_paged_generic(qd, nh * hd, out, *args, te, tq, len(tiles), md["q_start"], md["q_len"], md["ctx_start"],
+                               nh, nkv, hd, scale, window or 0)
+    else:
+        if ctiles:
+            te, tq = it([t[0] for t in ctiles]).to(DEV), it([t[1] for t in ctiles]).to(DEV)
+            ops.attn_prefill_bf16(qd, nh * hd, out, *args, te, tq, len(ctiles), md["q_start"], md["q_len"],
+                                  md["ctx_start"], nh, nkv, hd, scale, window or 0)
+        if decs:
+            for splits in ([1, 3, 8] if len(entries) < 6 else [4]):
+                out_d = out.clone()
+                po = torch.empty(len(decs) * nh * splits * hd, dtype=torch.float32, device=DEV)
+                pm = torch.empty(len(decs) * nh * splits * 2, dtype=torch.float32, device=DEV)
+                ops.attn_decode_bf16(qd, nh * hd, out_d, *args, it(decs).to(DEV), len(decs), md["q_start"], md["q_len"],
+                                     md["ctx_start"], po, pm, nh, nkv, hd, scale, window or 0, splits)
+                _close(out_d, want, 1.5e-2, f"decode attention, {splits} splits")
+            out = out_d
+    _close(out, want, 2e-5 if dtype == torch.float32 else 1.5e-2, "attention")
+    return out.float().cpu(), want
+
+
+MIXED = [(0, 5), (37, 1), (100, 70), (0, 130), (255, 1), (16, 16), (15, 2), (300, 1), (63, 65)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(4, 2, 16, 16, None), (3, 1, 32, 4, 24), (10, 2, 48, 8, None),
+                                                 (7, 1, 128, 16, 100), (6, 3, 80, 64, None), (2, 2, 256, 16, 33)])
+@pytest.mark.parametrize("peaked", [False, True])
+def test_attention_generic(ops, dtype, nh, nkv, hd, ps, window, peaked):
+    _attention_case(ops, dtype, nh, nkv, hd, ps, window, MIXED, 20, peaked, fast=False)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(28, 4, 128, 16, None), (16, 2, 128, 16, None), (5, 1, 64, 8, None),
+                                                 (3, 3, 64, 32, 40), (40, 2, 128, 16, None), (14, 2, 128, 4, 129),
+                                                 (8, 8, 128, 64, None)])
+@pytest.mark.parametrize("peaked", [False, True])
+def test_attention_tensor_core(ops, nh, nkv, hd, ps, window, peaked):
+    _attention_case(ops, torch.bfloat16, nh, nkv, hd, ps, window, MIXED, 21, peaked, fast=True)
+
+
+def test_attention_long_context_far_key(ops):
+    """4,000 cached keys; the query matches key 3 only: a fault in an early page shows."""
+    for fast in (False, True):
+        _attention_case(ops, torch.bfloat16, 4, 1, 128, 16, None, [(4000, 1), (3990, 40)], 22, True, fast)
+
+
+# --------------------------------------------------------------------- sampling
+def test_argmax_lowest_index_among_equal_maxima(ops):
+    v = 152064
+    logits = _rand((5, v), torch.float32, 30)
+    logits[0, 77] = logits[0, 150000] = 50.0
+    logits[1, v - 1] = 60.0
+    logits[2, 0] = 60.0
+    logits[3, :] = 1.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    want = [77, v - 1, 0, 0, int(torch.argmax(logits[4].cpu()))]
+    assert out.tolist() == want
+    # a strided view (rows of a wider buffer)
+    wide = torch.zeros((3, 1000), device=DEV)
+    wide[:, 300] = 1.0
+    out2 = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.argmax(wide[:, :777], out2)
+    assert out2.tolist() == [300, 300, 300]
+
+
+def test_penalties(ops):
+    v = 1000
+    logits = _rand((3, v), torch.float32, 31)
+    want = logits.clone().cpu()
+    ids = torch.tensor([[5, 9, 700, 0], [1, 2, 3, 4], [0, 0, 0, 0]], dtype=torch.int32)
+    cnt = torch.tensor([[2, 1, 5, 0], [1, 1, 1, 1], [0, 0, 0, 0]], dtype=torch.int32)
+    n = torch.tensor([3, 4, 0], dtype=torch.int32)
+    rep, freq, pres = torch.tensor([1.3, 1.0, 2.0]), torch.tensor([0.1, 0.5, 0.0]), torch.tensor([0.2, 0.0, 0.0])
+    ref.apply_penalties(want, ids, cnt, n, rep, freq, pres)
+    ops.apply_penalties(logits, ids.to(DEV), cnt.to(DEV), n.to(DEV), rep.to(DEV), freq.to(DEV), pres.to(DEV))
+    _close(logits, want, 1e-6, "penalties")
+
+
+def _sample(ops, logits, temperature, top_k, top_p, min_p, seeds, counters):
+    r, v = logits.shape
+    f = lambda x, dt: torch.tensor(x, dtype=dt, device=DEV)
+    out = torch.empty(r, dtype=torch.int32, device=DEV)
+    ops.sample(logits, torch.empty(r * v, dtype=torch.float32, device=DEV), f(temperature, torch.float32),
+               f(top_k, torch.int32), f(top_p, torch.float32), f(min_p, torch.float32), f(seeds, torch.int64),
+               f(counters, torch.int64), out)
+    return out.tolist()
+
+
+def test_sample_matches_inverse_cdf(ops):
+    """For each row the drawn token is the one whose cumulative-probability
+    interval (over the kept tokens, in index order) contains the row's uniform."""
+    import plain_qwen2 as plain
+    v, r = 1000, 64
+    logits = _rand((r, v), torch.float32, 32, 3.0)
+    temps = [0.8 if i % 2 else 1.3 for i in range(r)]
+    ks = [0, 5, 50, 0][0:4] * (r // 4)
+    ps = [1.0, 1.0, 0.9, 0.5] * (r // 4)
+    mps = [0.0, 0.0, 0.0, 0.05] * (r // 4)
+    seeds, counters = [1234 + i for i in range(r)], [i * 7 for i in range(r)]
+    got = _sample(ops, logits, temps, ks, ps, mps, seeds, counters)
+    for i in range(r):
+        kept = plain.kept_probabilities(logits[i].cpu(), temps[i], ks[i], ps[i], mps[i])
+        assert kept[got[i]] > 0, f"row {i}: token {got[i]} is outside the kept set"
+        cdf = torch.cumsum(kept, 0) / kept.sum()
+        u = ref.uniform01(seeds[i], counters[i])
+        lo = float(cdf[got[i] - 1]) if got[i] > 0 else 0.0
+        assert lo - 1e-5 <= u <= float(cdf[got[i]]) + 1e-5, f"row {i}: u={u} not in [{lo}, {float(cdf[got[i]])}]"
+
+
+def test_sample_distribution_and_determinism(ops):
+    v, draws = 50, 4000
+    base = _rand((1, v), torch.float32, 33, 1.5)
+    logits = base.expand(draws, v).contiguous()
+    got = _sample(ops, logits, [1.0] * draws, [0] * draws, [1.0] * draws, [0.0] * draws, [99] * draws,
+                  list(range(draws)))
+    again = _sample(ops, logits, [1.0] * draws, [0] * draws, [1.0] * draws, [0.0] * draws, [99] * draws,
+                    list(range(draws)))
+    assert got == again
+    p = torch.softmax(base[0].double().cpu(), 0)
+    counts = torch.bincount(torch.tensor(got), minlength=v).double()
+    chi2 = float(((counts - draws * p) ** 2 / (draws * p)).sum())
+    assert chi2 < 110.0, f"chi-square {chi2:.1f} over {v - 1} degrees of freedom"   # p ~ 1e-6 under the null
+    # temperature 0 = argmax; rows are independent of their neighbours
+    mixed = _sample(ops, logits[:4], [0.0, 1.0, 0.0, 1.0], [0] * 4, [1.0] * 4, [0.0] * 4, [99] * 4, [0, 1, 2, 3])
+    am = int(torch.argmax(base[0].cpu()))
+    assert mixed[0] == am and mixed[2] == am and mixed[1] == got[1] and mixed[3] == got[3]

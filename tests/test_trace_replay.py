@@ -15,7 +15,8 @@ from helpers import TINY, TOL, TraceProcess, make_model_folder, random_tokens, r
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 33, 5, 130, 64, 97], "B": [70, 40, 9, 150, 65, 111, 1], "C": [50, 81, 17, 100]}
+LENGTHS = {"A": [70, 33, 5, 130, 64, 97], "B": [70, 40, 9, 150, 65, 111, 1], "C": [50, 81, 17, 100],
+           "D": [150, 66, 3, 129, 90]}
 MAX_LIVE_TOKENS = 4 * 192      # four live requests of at most 192 tokens (rounded up to 64)
 
 
@@ -42,7 +43,7 @@ class Case:
 _cases = {}
 
 
-@pytest.fixture(params=[(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")],
+@pytest.fixture(params=[(n, d) for n in ("A", "B", "C", "D") for d in ("float32", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}", scope="module")
 def case(request):
     key = request.param
