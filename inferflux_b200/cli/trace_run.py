@@ -51,7 +51,7 @@ def main(argv=None) -> int:
     model = Model(build_spec(config), torch_dtype(args.dtype), args.device)
     model.load_folder(args.model)
     ecfg = EngineConfig(dtype=args.dtype, device=args.device, page_size=args.page_size,
-                        kv_cache_tokens=max(args.page_size, args.max_tokens), max_seqs=64, cuda_graphs=False)
+                        kv_cache_tokens=max(args.page_size, args.max_tokens), max_seqs=64)
     runner = StepRunner(model, ecfg)
     print("trace_run: ready", file=sys.stderr, flush=True)
 

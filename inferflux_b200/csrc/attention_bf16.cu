@@ -51,6 +51,13 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 constexpr float LOG2E = 1.4426950408889634f;
 
+// 2^x by the hardware approximation (about 2 units in the last place of float32); 2^-inf = 0
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // A tile in shared memory: rows of HD bfloat16 = HD/8 chunks of 16 bytes; chunk c of
 // row r is stored at chunk (c ^ (r & 7)) so that ldmatrix reads are conflict-free.
 template <int HD>
@@ -75,6 +82,35 @@ __device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* base, const
       if (ok) src = base + (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * HD + c * 8;
     }
     cp_async16(tile_chunk<HD>(tile, r, c), src, ok);
+  }
+}
+
+// Copy 64 keys and their values (absolute key index key0 ..) into two tiles with 128 threads:
+// two threads per key, one block-table lookup per thread for both; a pair of lanes covers 32
+// contiguous bytes per instruction.  Rows outside [lo, hi) or in pages given back are zero-filled.
+template <int HD>
+__device__ __forceinline__ void load_kv_tile64(bf16* ktile, bf16* vtile, const bf16* kbase, const bf16* vbase,
+                                               const PagedKV& kv, const int* bt, int key0, int lo, int hi, int tid) {
+  constexpr int CPR = HD / 8;
+  const int r = tid >> 1, half = tid & 1;
+  const int key = key0 + r;
+  bool ok = key >= lo && key < hi;
+  size_t off = 0;
+  if (ok) {
+    const int page = bt[key >> kv.page_shift];
+    ok = page >= 0;
+    if (ok) off = (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * HD;
+  }
+  const bf16* ksrc = kbase + off;
+  const bf16* vsrc = vbase + off;
+  bf16* krow = ktile + r * HD;
+  bf16* vrow = vtile + r * HD;
+  const int sw = r & 7;
+#pragma unroll
+  for (int j = 0; j < CPR / 2; ++j) {
+    const int c = j * 2 + half;
+    cp_async16(krow + ((c ^ sw) << 3), ksrc + c * 8, ok);
+    cp_async16(vrow + ((c ^ sw) << 3), vsrc + c * 8, ok);
   }
 }
 
@@ -133,14 +169,13 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int pa_row = pos0 + wr0 + g, pb_row = pa_row + 8;        // positions of this thread's two rows
   const int warp_last = pos0 + min(wr0 + 15, rows - 1);
 
-  load_kv_tile<HD, 128>(ks, kbase, kv, bt, t_begin * BK, BK, kfirst, kend, tid);
-  load_kv_tile<HD, 128>(vs, vbase, kv, bt, t_begin * BK, BK, kfirst, kend, tid);
+  load_kv_tile64<HD>(ks, vs, kbase, vbase, kv, bt, t_begin * BK, kfirst, kend, tid);
   cp_async_commit();
   for (int t = t_begin; t <= t_end; ++t) {
     const int st = (t - t_begin) & 1;
     if (t < t_end) {
-      load_kv_tile<HD, 128>(ks + (st ^ 1) * BK * HD, kbase, kv, bt, (t + 1) * BK, BK, kfirst, kend, tid);
-      load_kv_tile<HD, 128>(vs + (st ^ 1) * BK * HD, vbase, kv, bt, (t + 1) * BK, BK, kfirst, kend, tid);
+      load_kv_tile64<HD>(ks + (st ^ 1) * BK * HD, vs + (st ^ 1) * BK * HD, kbase, vbase, kv, bt, (t + 1) * BK,
+                         kfirst, kend, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -191,7 +226,7 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
         mnew[h] = fmaxf(mrow[h], mx[h]);
-        alpha[h] = mnew[h] == -INFINITY ? 1.0f : exp2f(mrow[h] - mnew[h]);
+        alpha[h] = mnew[h] == -INFINITY ? 1.0f : fast_exp2(mrow[h] - mnew[h]);
         mrow[h] = mnew[h];
       }
       float ls[2] = {0.0f, 0.0f};
@@ -200,7 +235,7 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const float mm = mnew[c >> 1];
-          const float p = mm == -INFINITY ? 0.0f : exp2f(s[n][c] - mm);
+          const float p = mm == -INFINITY ? 0.0f : fast_exp2(s[n][c] - mm);
           s[n][c] = p;
           ls[c >> 1] += p;
         }
@@ -247,18 +282,22 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 
 // ------------------------------------------------------------------- decode
 // One block: one decoding entry, up to 16 query heads of one kv head, one split of
-// the keys.  Each of the 4 warps takes every 4th 16-key tile of the split.
-// Partial results (max, sum, unnormalised o) go to scratch for the merge kernel;
-// with one split the block writes the final output itself.
+// the keys.  The block streams its keys and values in tiles of 64 through a ring of
+// DSTAGES shared-memory stages (loads run two tiles ahead of the math); each of the
+// 4 warps takes 16 keys of a tile and keeps its own running (max, sum, o), merged at
+// the end.  Partial results go to scratch for the merge kernel; with one split the
+// block writes the final output itself.
+constexpr int DSTAGES = 3;
+
 template <int HD>
 __global__ void __launch_bounds__(128)
 attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                         PagedKV kv, AttnMeta m, const int* __restrict__ dec_entries,
                         float* __restrict__ part_o, float* __restrict__ part_ml,
                         int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits) {
-  constexpr int KS = HD / 16, DT = HD / 8, TK = 16, STAGES = 2;
+  constexpr int KS = HD / 16, DT = HD / 8, BK = 64, TK = 16;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);       // [4 warps][STAGES][K|V][TK][HD]
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw);             // [DSTAGES][K|V][BK][HD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
   const int e = dec_entries[blockIdx.x];
   const int kvh = blockIdx.y / head_chunks, hc = blockIdx.y - kvh * head_chunks;
@@ -271,7 +310,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   const int kfirst = window > 0 ? max(0, len - window) : 0;
   const int total = len - kfirst;
   int chunk = (total + n_splits - 1) / n_splits;
-  chunk = (chunk + TK - 1) / TK * TK;
+  chunk = (chunk + BK - 1) / BK * BK;
   const int kb = kfirst + split * chunk, ke = min(len, kb + chunk);
   const int* bt = m.block_tables + (size_t)e * m.bt_stride;
   const bf16* kbase = (const bf16*)kv.k + (size_t)kvh * kv.head_stride;
@@ -283,7 +322,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   for (int d = 0; d < DT; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.0f, 0.0f};
 
-  if (kb < ke) {
+  if (kb < ke) {                                                // block-uniform
     unsigned qa[KS][4];
     {
       const bf16* qb = q + (size_t)tok * q_stride + (size_t)h0 * HD;
@@ -298,39 +337,40 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       }
     }
     const float sl2 = scale * LOG2E;
-    bf16* my = stage_base + (size_t)warp * STAGES * 2 * TK * HD;
-    const int t_begin = kb / TK, t_end = (ke - 1) / TK;
-    int t = t_begin + warp;
-    if (t <= t_end) {
-      load_kv_tile<HD, 32>(my, kbase, kv, bt, t * TK, TK, kb, ke, lane);
-      load_kv_tile<HD, 32>(my + TK * HD, vbase, kv, bt, t * TK, TK, kb, ke, lane);
-    }
-    cp_async_commit();
-    int st = 0;
-    for (; t <= t_end; t += 4, st ^= 1) {
-      const int tn = t + 4;
-      if (tn <= t_end) {
-        bf16* nx = my + (size_t)(st ^ 1) * 2 * TK * HD;
-        load_kv_tile<HD, 32>(nx, kbase, kv, bt, tn * TK, TK, kb, ke, lane);
-        load_kv_tile<HD, 32>(nx + TK * HD, vbase, kv, bt, tn * TK, TK, kb, ke, lane);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
+    const int t_begin = kb / BK, t_end = (ke - 1) / BK, n_t = t_end - t_begin + 1;
+    // prologue: the first DSTAGES - 1 tiles
+#pragma unroll
+    for (int p = 0; p < DSTAGES - 1; ++p) {
+      if (p < n_t) {
+        bf16* st = ring + (size_t)p * 2 * BK * HD;
+        load_kv_tile64<HD>(st, st + BK * HD, kbase, vbase, kv, bt, (t_begin + p) * BK, kb, ke, tid);
       }
-      __syncwarp();
-      bf16* kt = my + (size_t)st * 2 * TK * HD;
-      bf16* vt = kt + TK * HD;
+      cp_async_commit();
+    }
+    for (int i = 0; i < n_t; ++i) {
+      cp_async_wait<DSTAGES - 2>();                             // tile i has landed (for this thread)
+      __syncthreads();                                          // ... for all; and tile i - 1 is no longer read
+      {
+        const int nx = i + DSTAGES - 1;
+        if (nx < n_t) {
+          bf16* st = ring + (size_t)(nx % DSTAGES) * 2 * BK * HD;
+          load_kv_tile64<HD>(st, st + BK * HD, kbase, vbase, kv, bt, (t_begin + nx) * BK, kb, ke, tid);
+        }
+        cp_async_commit();
+      }
+      const int key0 = (t_begin + i) * BK + warp * TK;          // this warp's 16 keys of the tile
+      if (key0 >= ke || key0 + TK <= kb) continue;              // warp-uniform: nothing of ours in range
+      bf16* kt = ring + (size_t)(i % DSTAGES) * 2 * BK * HD;
+      bf16* vt = kt + BK * HD;
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       const int j = lane >> 3, r = lane & 7;
 #pragma unroll
       for (int k = 0; k < KS; ++k) {
         unsigned b[4];
-        ldmatrix_x4(b, tile_chunk<HD>(kt, (j >> 1) * 8 + r, k * 2 + (j & 1)));
+        ldmatrix_x4(b, tile_chunk<HD>(kt, warp * TK + (j >> 1) * 8 + r, k * 2 + (j & 1)));
         mma_bf16(s[0], qa[k], b[0], b[1]);
         mma_bf16(s[1], qa[k], b[2], b[3]);
       }
-      const int key0 = t * TK;
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
@@ -348,7 +388,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
         mnew[h] = fmaxf(mrow[h], mx[h]);
-        alpha[h] = mnew[h] == -INFINITY ? 1.0f : exp2f(mrow[h] - mnew[h]);
+        alpha[h] = mnew[h] == -INFINITY ? 1.0f : fast_exp2(mrow[h] - mnew[h]);
         mrow[h] = mnew[h];
       }
       float ls[2] = {0.0f, 0.0f};
@@ -357,13 +397,17 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const float mm = mnew[c >> 1];
-          const float p = mm == -INFINITY ? 0.0f : exp2f(s[n][c] - mm);
+          const float p = mm == -INFINITY ? 0.0f : fast_exp2(s[n][c] - mm);
           s[n][c] = p;
           ls[c >> 1] += p;
         }
       }
       lrow[0] = lrow[0] * alpha[0] + ls[0];
       lrow[1] = lrow[1] * alpha[1] + ls[1];
+      if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {   // the maximum moved: rescale o
+#pragma unroll
+        for (int d = 0; d < DT; ++d) { o[d][0] *= alpha[0]; o[d][1] *= alpha[0]; o[d][2] *= alpha[1]; o[d][3] *= alpha[1]; }
+      }
       unsigned pa[4];
       pa[0] = pack_bf16(s[0][0], s[0][1]);
       pa[1] = pack_bf16(s[0][2], s[0][3]);
@@ -372,21 +416,19 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 #pragma unroll
       for (int dp = 0; dp < DT / 2; ++dp) {
         unsigned b[4];
-        ldmatrix_x4_trans(b, tile_chunk<HD>(vt, (j & 1) * 8 + r, dp * 2 + (j >> 1)));
-        o[dp * 2][0] *= alpha[0]; o[dp * 2][1] *= alpha[0]; o[dp * 2][2] *= alpha[1]; o[dp * 2][3] *= alpha[1];
-        o[dp * 2 + 1][0] *= alpha[0]; o[dp * 2 + 1][1] *= alpha[0]; o[dp * 2 + 1][2] *= alpha[1]; o[dp * 2 + 1][3] *= alpha[1];
+        ldmatrix_x4_trans(b, tile_chunk<HD>(vt, warp * TK + (j & 1) * 8 + r, dp * 2 + (j >> 1)));
         mma_bf16(o[dp * 2], pa, b[0], b[1]);
         mma_bf16(o[dp * 2 + 1], pa, b[2], b[3]);
       }
-      __syncwarp();
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 1);
       lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 2);
     }
   }
-  // merge the four warps through shared memory (the stage buffers are free now)
+  // merge the four warps through shared memory (the ring is free now)
   __syncthreads();
   float* red_o = reinterpret_cast<float*>(smem_raw);            // [4][16][HD]
   float* red_ml = red_o + 4 * 16 * HD;                          // [4][16][2]
@@ -410,7 +452,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = red_ml[(w * 16 + row) * 2];
-      const float f = mw == -INFINITY ? 0.0f : exp2f(mw - mm);
+      const float f = mw == -INFINITY ? 0.0f : fast_exp2(mw - mm);
       l += red_ml[(w * 16 + row) * 2 + 1] * f;
       acc += red_o[((size_t)w * 16 + row) * HD + d] * f;
     }
@@ -438,7 +480,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
     float l = 0.0f, acc = 0.0f;
     for (int s = 0; s < n_splits; ++s) {
       const float ms = part_ml[(p0 + s) * 2];
-      const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+      const float f = ms == -INFINITY ? 0.0f : fast_exp2(ms - mm);
       l += part_ml[(p0 + s) * 2 + 1] * f;
       acc += part_o[(p0 + s) * head_dim + d] * f;
     }
@@ -473,7 +515,7 @@ template <int HD>
 int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnMeta m,
                   const int* dec_entries, int n_dec, float* part_o, float* part_ml, int n_heads, int n_kv,
                   float scale, int window, int n_splits, cudaStream_t stream) {
-  const size_t stage_bytes = (size_t)4 * 2 * 2 * 16 * HD * sizeof(bf16);
+  const size_t stage_bytes = (size_t)DSTAGES * 2 * 64 * HD * sizeof(bf16);
   const size_t red_bytes = (size_t)4 * 16 * HD * sizeof(float) + 4 * 16 * 2 * sizeof(float);
   const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
   auto kern = attn_decode_bf16_kernel<HD>;

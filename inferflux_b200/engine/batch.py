@@ -40,6 +40,7 @@ class MetadataSlab:
         self.device = device
         pin = torch.device(device).type == "cuda"
         self.host = torch.zeros(capacity, dtype=torch.int32, pin_memory=pin)
+        self._np = self.host.numpy()
         self.dev = torch.zeros(capacity, dtype=torch.int32, device=device)
         self._used = 0
         self._views: List[Tuple[int, int]] = []
@@ -54,7 +55,7 @@ class MetadataSlab:
         if start + n > self.capacity:
             raise RuntimeError(f"step metadata needs {start + n} words, the slab holds {self.capacity}")
         if n:
-            self.host[start:start + n] = torch.as_tensor(values, dtype=torch.int32)
+            self._np[start:start + n] = values
         self._used = start + n
         return self.dev[start:start + n]
 

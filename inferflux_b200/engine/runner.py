@@ -15,11 +15,13 @@ from __future__ import annotations
 
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import OutOfPages, OutOfSlots, KVCacheManager, KVCacheStorage, StateSlotManager, StateSlotStorage, bytes_per_token
 from ..config.engine_config import EngineConfig
 from .batch import CHUNK_TILE, QUERY_TILE, MetadataSlab, StepContext, StepEntry
+from ..kernels import ops
 from .model import Model
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -59,6 +61,8 @@ class StepRunner:
         self.state_storage = StateSlotStorage(engine_config.max_seqs, model.state_needs, self.device)
         model.attach_states(self.state_storage)
         self.slab = MetadataSlab(1 << 16, self.device)
+        self._graphs = {}
+        self.graph_replays = 0
         self.steps = 0
         self.tokens_run = 0
 
@@ -87,8 +91,9 @@ class StepRunner:
         return self.kv.can_reserve(rid, n_new)
 
     # ---------------------------------------------------------------- step
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Reserve pages for the step's tokens and describe the step on the device."""
+    def _admit(self, entries: Sequence[StepEntry]) -> None:
+        """Check the entries, seat new requests and hold pages for the step's
+        tokens; raises before anything is taken when they do not fit."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         vocab = self.model.spec.vocab_size
@@ -99,9 +104,8 @@ class StepRunner:
             seen.add(e.rid)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab:
-                    raise ValueError(f"request {e.rid!r}: token id {t} is outside the vocabulary [0, {vocab})")
+            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                raise ValueError(f"request {e.rid!r}: a token id is outside the vocabulary [0, {vocab})")
             for p in e.want:
                 if not 0 <= int(p) < len(e.tokens):
                     raise ValueError(f"request {e.rid!r}: wanted place {p} is outside its {len(e.tokens)} tokens")
@@ -124,80 +128,138 @@ class StepRunner:
             self.begin(e.rid)
         for e in entries:
             self.kv.reserve(e.rid, len(e.tokens))
+
+    def _describe(self, entries: Sequence[StepEntry], slab: Optional[MetadataSlab] = None,
+                  widths: Optional[Sequence[int]] = None) -> StepContext:
+        """Write the step's metadata into a slab (the runner's own unless one is
+        given) and return the context whose tensors are views of it.  With
+        ``widths`` the block tables are padded to those widths, so that steps
+        of the same shape have the same layout."""
         ps = self.page_size
-        token_ids, positions, q_start, q_len, ctx_start, slots = [], [], [], [], [], []
-        tile_entry, tile_q0, want_rows = [], [], []
-        ctile_entry, ctile_q0, dec_entries = [], [], []
-        for i, e in enumerate(entries):
-            start = self.kv.length(e.rid)
-            q_start.append(len(token_ids))
-            q_len.append(len(e.tokens))
-            ctx_start.append(start)
-            slots.append(self.slots.slot(e.rid))
-            for p in e.want:
-                want_rows.append(len(token_ids) + int(p))
-            for q0 in range(0, len(e.tokens), QUERY_TILE):
-                tile_entry.append(i)
-                tile_q0.append(q0)
-            if len(e.tokens) == 1:
-                dec_entries.append(i)
-            else:
-                for q0 in range(0, len(e.tokens), CHUNK_TILE):
-                    ctile_entry.append(i)
-                    ctile_q0.append(q0)
-            token_ids.extend(int(t) for t in e.tokens)
-            positions.extend(range(start, start + len(e.tokens)))
-        n, r = len(token_ids), len(entries)
+        r = len(entries)
+        lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=r)
+        starts = np.fromiter((self.kv.length(e.rid) for e in entries), dtype=np.int64, count=r)
+        q_start = np.zeros(r, dtype=np.int64)
+        np.cumsum(lens[:-1], out=q_start[1:])
+        n = int(lens.sum())
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        entry_of_token = np.repeat(np.arange(r), lens)
+        offs = np.arange(n) - q_start[entry_of_token]
+        positions = starts[entry_of_token] + offs
+        slots = [self.slots.slot(e.rid) for e in entries]
+        want_rows = [int(q_start[i]) + int(p) for i, e in enumerate(entries) for p in e.want]
+        tile_entry, tile_q0, ctile_entry, ctile_q0, dec_entries = [], [], [], [], []
+        for i in range(r):
+            ln = int(lens[i])
+            if ln == 1:
+                tile_entry.append(i), tile_q0.append(0), dec_entries.append(i)
+                continue
+            for q0 in range(0, ln, QUERY_TILE):
+                tile_entry.append(i), tile_q0.append(q0)
+            for q0 in range(0, ln, CHUNK_TILE):
+                ctile_entry.append(i), ctile_q0.append(q0)
         groups = self.kv.num_groups
-        widths, tables, slot_maps = [], [], []
+        tables, slot_maps, out_widths = [], [], []
         for g in range(groups):
             tabs = [self.kv.block_table(e.rid, g) for e in entries]
             width = max(1, max(len(t) for t in tabs))
-            flat = []
-            for t in tabs:
-                flat.extend(t)
-                flat.extend([-1] * (width - len(t)))
-            sm = []
-            for e, s0 in zip(entries, ctx_start):
-                tab = self.kv.block_table(e.rid, g)
-                for pos in range(s0, s0 + len(e.tokens)):
-                    sm.append(tab[pos // ps] * ps + pos % ps)
-            widths.append(width)
-            tables.append(flat)
-            slot_maps.append(sm)
+            if widths is not None:
+                if widths[g] < width:
+                    raise RuntimeError("block tables are wider than the layout they are written into")
+                width = widths[g]
+            arr = np.full((r, width), -1, dtype=np.int32)
+            for i, t in enumerate(tabs):
+                arr[i, :len(t)] = t
+            pages = arr[entry_of_token, positions // ps]
+            slot_maps.append(pages.astype(np.int64) * ps + positions % ps)
+            tables.append(arr.reshape(-1))
+            out_widths.append(width)
         need = 4 * (12 + groups) + 2 * n + 5 * r + 2 * len(tile_entry) + 2 * len(ctile_entry) + len(want_rows) \
-            + sum(len(t) for t in tables) + groups * n + 64
-        if need > self.slab.capacity:
-            self.slab = MetadataSlab(max(need, 2 * self.slab.capacity), self.device)
-        slab = self.slab
+            + sum(t.size for t in tables) + groups * n + 64
+        if slab is None:
+            if need > self.slab.capacity:
+                self.slab = MetadataSlab(max(need, 2 * self.slab.capacity), self.device)
+            slab = self.slab
         slab.begin()
         d_tok, d_pos = slab.put(token_ids), slab.put(positions)
-        d_qs, d_ql, d_cs, d_sl = slab.put(q_start), slab.put(q_len), slab.put(ctx_start), slab.put(slots)
+        d_qs, d_ql, d_cs, d_sl = slab.put(q_start), slab.put(lens), slab.put(starts), slab.put(slots)
         d_te, d_tq = slab.put(tile_entry), slab.put(tile_q0)
         d_cte, d_ctq, d_dec = slab.put(ctile_entry), slab.put(ctile_q0), slab.put(dec_entries)
         d_want = slab.put(want_rows)
-        d_tabs = [slab.put(t).view(r, w) for t, w in zip(tables, widths)]
-        d_sm = [slab.put(s) for s in slot_maps]
+        d_tabs = [slab.put(t).view(r, w) for t, w in zip(tables, out_widths)]
+        d_sm = [slab.put(sm) for sm in slot_maps]
         slab.upload()
         return StepContext(
-            n_tokens=n, n_entries=r, entries=list(entries), ctx_starts=ctx_start, slots=slots,
+            n_tokens=n, n_entries=r, entries=list(entries), ctx_starts=starts.tolist(), slots=slots,
             token_ids=d_tok, positions=d_pos, entry_q_start=d_qs, entry_q_len=d_ql, entry_ctx_start=d_cs,
             entry_slot=d_sl, tile_entry=d_te, tile_q0=d_tq, n_tiles=len(tile_entry),
             chunk_tile_entry=d_cte, chunk_tile_q0=d_ctq, n_chunk_tiles=len(ctile_entry),
             decode_entries=d_dec, n_decode=len(dec_entries),
             block_tables=d_tabs, slot_maps=d_sm, want_rows=d_want, n_want=len(want_rows),
-            max_q_len=max(q_len), max_ctx_len=max(c + l for c, l in zip(ctx_start, q_len)),
+            max_q_len=int(lens.max()),
+            max_ctx_len=int((starts + lens).max()) if widths is None else max(out_widths) * ps,
             page_size=ps, kv=self.kv_storage, dtype=self.dtype, device=self.device)
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Reserve pages for the step's tokens and describe the step on the device."""
+        self._admit(entries)
+        return self._describe(entries)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens as one batch; float32 logits ``[wanted, vocab]``
         in the order of the entries and of each entry's ``want``.  Raises
         :class:`~inferflux_b200.cache.OutOfPages` (before anything ran) when
-        the pools cannot hold the step's tokens."""
-        ctx = self.build_context(entries)
-        logits = self.model.forward(ctx)
+        the pools cannot hold the step's tokens.  The logits of a decode-only
+        step live in a buffer that the next such step overwrites."""
+        self._admit(entries)
+        if self._graphable(entries):
+            logits = self._step_graph(entries)
+        else:
+            logits = self.model.forward(self._describe(entries))
+        n = 0
         for e in entries:
             self.kv.advance(e.rid, len(e.tokens))
+            n += len(e.tokens)
         self.steps += 1
-        self.tokens_run += ctx.n_tokens
+        self.tokens_run += n
         return logits
+
+    # ------------------------------------------------------- captured decode
+    GRAPH_WIDTH_STEP = 32      # block-table widths of captured steps are multiples of this many pages
+    MAX_GRAPHS = 48
+
+    def _graphable(self, entries: Sequence[StepEntry]) -> bool:
+        """A step of single decoded tokens, each wanting its logits, runs as a
+        captured CUDA graph (the same kernels, launched by one replay)."""
+        if not self.cfg.cuda_graphs or torch.device(self.device).type != "cuda":
+            return False
+        return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
+    def _step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        step = self.GRAPH_WIDTH_STEP
+        widths = tuple((max(len(self.kv.block_table(e.rid, g)) for e in entries) + step - 1) // step * step
+                       for g in range(self.kv.num_groups))
+        key = (len(entries), widths)
+        rec = self._graphs.get(key)
+        if rec is None:
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            r = len(entries)
+            slab = MetadataSlab(64 + 16 * r + sum(r * w for w in widths) + 8 * (12 + len(widths)), self.device)
+            ctx = self._describe(entries, slab, widths)
+            logits = self.model.forward(ctx)                 # this step runs eagerly (and warms the libraries up)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            launches = ops.launch_count
+            with torch.cuda.graph(graph):                    # records the same launches; nothing runs
+                static_logits = self.model.forward(ctx)
+            self._graphs[key] = dict(slab=slab, graph=graph, logits=static_logits, used=slab._used,
+                                     launches=ops.launch_count - launches)
+            return logits
+        ctx = self._describe(entries, rec["slab"], widths)
+        if rec["slab"]._used != rec["used"]:
+            raise RuntimeError("a captured step's metadata layout changed")
+        rec["graph"].replay()
+        ops.launch_count += rec["launches"]
+        self.graph_replays += 1
+        return rec["logits"]

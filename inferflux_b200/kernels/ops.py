@@ -55,6 +55,8 @@ def _lib():
         lib.ifx_attn_decode_bf16.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
                                              c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
+        lib.ifx_gemv_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll,
+                                      c_int, c_int, c_void_p]
         lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p]
         lib.ifx_apply_penalties.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                             c_void_p, c_int, c_int, c_void_p]
@@ -62,7 +64,7 @@ def _lib():
                                    c_void_p, c_void_p, c_int, c_int, c_void_p]
         for name in ("ifx_embed_gather", "ifx_add_rmsnorm", "ifx_swiglu", "ifx_convert", "ifx_rope_table",
                      "ifx_qkv_rope_kv_write", "ifx_gemm_f32", "ifx_attn_paged_generic", "ifx_argmax",
-                     "ifx_attn_prefill_bf16", "ifx_attn_decode_bf16",
+                     "ifx_attn_prefill_bf16", "ifx_attn_decode_bf16", "ifx_gemv_bf16",
                      "ifx_apply_penalties", "ifx_sample"):
             getattr(lib, name).restype = c_int
         _sigs_done = True
@@ -214,6 +216,37 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_f32: bias float32 [N]")
     _check(_lib().ifx_gemm_f32(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0) if m > 1 else k,
                                out.stride(0) if m > 1 else n, _stream()), "gemm_f32")
+    return out
+
+
+GEMV_MAX_ROWS = 32
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+              swiglu: bool = False, k_splits: int = 1) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) for M <= 32, bfloat16 operands,
+    float32 accumulation, bfloat16 or float32 result.  With ``swiglu`` w is
+    [2N, K] = [gate; up] and out = silu(x gate^T) * (x up^T).  With
+    ``k_splits`` > 1 out is float32 [k_splits, M, N]: slice s is the sum over the
+    s-th part of K and the caller adds the slices."""
+    m, k = x.shape
+    n = out.shape[-1]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous(), "gemv_bf16: bfloat16 operands")
+    _need(w.shape == ((2 * n if swiglu else n), k), "gemv_bf16: shapes")
+    _need(m <= GEMV_MAX_ROWS and k % 8 == 0, f"gemv_bf16: at most {GEMV_MAX_ROWS} rows and K a multiple of 8")
+    if k_splits > 1:
+        _need(tuple(out.shape) == (k_splits, m, n) and out.is_contiguous() and out.dtype == torch.float32
+              and not swiglu, "gemv_bf16: partial sums are float32 [k_splits, M, N]")
+        ldo = n
+    else:
+        _need(out.dim() == 2 and out.shape[0] == m and out.stride(1) == 1, "gemv_bf16: out [M, N]")
+        ldo = out.stride(0) if m > 1 else n
+    _need(x.stride(1) == 1, "gemv_bf16: unit inner strides")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n and not swiglu, "gemv_bf16: bias float32 [N]")
+    _check(_lib().ifx_gemv_bf16(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), m, n, k,
+                                x.stride(0) if m > 1 else k, ldo, 1 if swiglu else 0, int(k_splits),
+                                _stream()), "gemv_bf16")
     return out
 
 

@@ -113,7 +113,7 @@ class GQAttention(Part):
                               ctx.page_size, self.n_heads, nkv_w, self.head_dim)
         attn = torch.empty((n, self.n_heads * self.head_dim), dtype=qkv.dtype, device=x.device)
         self.attend(qkv, attn, ctx, g, k_layer, v_layer, page_stride)
-        return self.o.forward(attn, out_dtype=x.dtype)
+        return self.o.forward(attn, out_dtype=x.dtype, allow_partials=True)
 
     def attend(self, qkv, attn, ctx, g, k_layer, v_layer, page_stride) -> None:
         """bfloat16 with a head size the tensor-core kernels take: prompt
@@ -142,13 +142,13 @@ class GQAttention(Part):
                                  self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, n_splits)
 
 
-def decode_splits(n_decode: int, n_heads: int, n_kv: int, max_keys: int, target_blocks: int = 592) -> int:
-    """Into how many parts the decode kernel cuts the keys: enough blocks to
-    fill 148 SMs four times over, but at least 128 keys per part."""
+def decode_splits(n_decode: int, n_heads: int, n_kv: int, max_keys: int, target_blocks: int = 296) -> int:
+    """Into how many parts the decode kernel cuts the keys: enough blocks for
+    two per SM (148 SMs), each part at least 256 keys (four 64-key tiles)."""
     ratio = n_heads // n_kv
     base = max(1, n_decode * n_kv * ((ratio + 15) // 16))
     by_blocks = (target_blocks + base - 1) // base
-    by_keys = max(1, max_keys // 128)
+    by_keys = max(1, max_keys // 256)
     return max(1, min(by_blocks, by_keys, 64))
 
 

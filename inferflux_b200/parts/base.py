@@ -35,6 +35,16 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+class PartialSums:
+    """A value given as float32 slices ``[S, N, H]`` whose sum it is.  A mixer
+    or feed-forward may return one instead of a tensor; the norm that follows
+    adds the slices (in index order) while it adds the residual."""
+
+    def __init__(self, tensor: torch.Tensor):
+        self.tensor = tensor
+        self.count = tensor.shape[0]
+
+
 class Part:
     """Base of all parts.  ``params`` are the PartSpec's parameters, ``prefix``
     the weight-name prefix of the enclosing layer ("" at model level)."""

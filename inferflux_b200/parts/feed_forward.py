@@ -52,10 +52,14 @@ class SwiGLU(Part):
         self.down = Linear(tensors.pop(n("down_proj.weight")))
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        gu = self.gate_up.forward(x)
-        act = torch.empty((x.shape[0], self.intermediate), dtype=gu.dtype, device=x.device)
-        ops.swiglu(gu, act)
-        return self.down.forward(act, out_dtype=x.dtype)
+        w = self.gate_up.weight
+        act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+        if w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and x.shape[0] <= ops.GEMV_MAX_ROWS \
+                and self.hidden % 8 == 0:
+            ops.gemv_bf16(x, w, None, act, swiglu=True)       # product and activation in one kernel
+        else:
+            ops.swiglu(self.gate_up.forward(x), act)
+        return self.down.forward(act, out_dtype=x.dtype, allow_partials=True)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

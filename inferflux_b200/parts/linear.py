@@ -4,7 +4,8 @@ The reference issues one cuBLAS call per projection with float32 accumulation
 (runtime/backends/cuda/native/cublas_gemm.cpp:84-102, ``C[M,N] = A[M,K] *
 B[N,K]^T``).  Here a float32 weight goes through the FFMA kernel of the 32-bit
 path; a bfloat16 weight goes through the library (cuBLAS via ``torch.mm``) for
-many rows.  This is not a registered part: mixers and feed-forwards own their
+many rows and through the weight-streaming kernel (gemv_bf16.cu) for up to 32
+rows.  This is not a registered part: mixers and feed-forwards own their
 Linears.
 """
 from __future__ import annotations
@@ -14,6 +15,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+from .base import PartialSums
 
 
 class Linear:
@@ -24,8 +26,11 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         self.bias = None if bias is None else bias.to(torch.float32).contiguous()
 
-    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """x [M, in] -> [M, out] in ``out_dtype`` (default: x's type)."""
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False):
+        """x [M, in] -> [M, out] in ``out_dtype`` (default: x's type).  With
+        ``allow_partials`` the result may be a :class:`PartialSums` (the
+        weight-streaming kernel cuts K between blocks when a matrix has too few
+        rows to fill the GPU)."""
         m = x.shape[0]
         out_dtype = out_dtype or x.dtype
         w = self.weight
@@ -40,8 +45,24 @@ class Linear:
             return y
         if x.dtype != torch.bfloat16:
             raise ops.KernelError(f"Linear: bfloat16 weights need bfloat16 activations, got {x.dtype}")
+        if m <= ops.GEMV_MAX_ROWS and self.in_features % 8 == 0:
+            # a few rows: bound by reading the weights once -> the weight-streaming kernel
+            splits = self._k_splits() if allow_partials else 1
+            if splits > 1:
+                y = torch.empty((splits, m, self.out_features), dtype=torch.float32, device=x.device)
+                return PartialSums(ops.gemv_bf16(x, w, self.bias, y, k_splits=splits))
+            y = torch.empty((m, self.out_features), dtype=out_dtype, device=x.device)
+            return ops.gemv_bf16(x, w, self.bias, y)
         y = ops.matmul_library(x, w, torch.float32 if (out_dtype == torch.float32 or self.bias is not None)
                                else torch.bfloat16)
         if self.bias is not None:
             y += self.bias
         return y if y.dtype == out_dtype else y.to(out_dtype)
+
+    def _k_splits(self, target_blocks: int = 592, min_chunks: int = 32, max_splits: int = 4) -> int:
+        """Into how many parts the weight-streaming kernel cuts K: enough blocks
+        (one per 16 rows and part) for four per SM, each part at least 32
+        chunks of 32."""
+        tiles = (self.out_features + 15) // 16
+        chunks = (self.in_features + 31) // 32
+        return max(1, min(max_splits, (target_blocks + tiles - 1) // tiles, chunks // min_chunks))

@@ -15,7 +15,7 @@ import torch
 from ..config.registry import register_part
 from ..kernels import ops
 from ..weights.loader import VECTOR, WeightSpec
-from .base import Part
+from .base import Part, PartialSums
 
 
 class RMSNorm(Part):
@@ -37,11 +37,14 @@ class RMSNorm(Part):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.full_name(self.prefix, self.params, "weight")].to(torch.float32).contiguous()
 
-    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
-                rows: Optional[torch.Tensor] = None, n_partials: int = 1) -> torch.Tensor:
-        """Adds ``delta`` into the float32 ``residual`` (unless ``rows`` picks
-        rows, which leaves it untouched) and returns the normed rows in the
-        engine's type."""
+    def forward(self, residual: torch.Tensor, delta, out: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Adds ``delta`` (a tensor, a :class:`PartialSums` or None) into the
+        float32 ``residual`` (unless ``rows`` picks rows, which leaves it
+        untouched) and returns the normed rows in the engine's type."""
+        n_partials = 1
+        if isinstance(delta, PartialSums):
+            delta, n_partials = delta.tensor, delta.count
         n_rows = rows.numel() if rows is not None else residual.shape[0]
         if out is None:
             out = torch.empty((n_rows, self.hidden), dtype=self.dtype, device=residual.device)

@@ -97,6 +97,28 @@ def gemm_f32(a, w, bias, out):
     return out
 
 
+def gemv_bf16(x, w, bias, out, swiglu=False, k_splits=1):
+    if k_splits > 1:
+        k = x.shape[1]
+        chunks = (k + 31) // 32
+        per = (chunks + k_splits - 1) // k_splits
+        for s in range(k_splits):
+            lo, hi = min(k, s * per * 32), min(k, (s + 1) * per * 32)
+            out[s] = x[:, lo:hi].float() @ w[:, lo:hi].float().T
+        if bias is not None:
+            out[0] += bias
+        return out
+    y = x.float() @ w.float().T
+    if swiglu:
+        n = out.shape[1]
+        g, u = y[:, :n], y[:, n:]
+        y = g / (1.0 + torch.exp(-g)) * u
+    elif bias is not None:
+        y = y + bias
+    out.copy_(y.to(out.dtype))
+    return out
+
+
 def attn_paged_generic(q, q_stride, out, k_layer, v_layer, page_stride, page_size, block_tables,
                        tile_entry, tile_q0, n_tiles, entry_q_start, entry_q_len, entry_ctx_start,
                        n_heads, n_kv, head_dim, scale, window):
