@@ -88,16 +88,19 @@ __device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* base, const
 // Copy 64 keys and their values (absolute key index key0 ..) into two tiles with 128 threads:
 // two threads per key, one block-table lookup per thread for both; a pair of lanes covers 32
 // contiguous bytes per instruction.  Rows outside [lo, hi) or in pages given back are zero-filled.
+// `bt` may point to a copy of the block table in shared memory that starts at logical block
+// `bt_first` (the copy removes a global load from the path between two tiles).
 template <int HD>
 __device__ __forceinline__ void load_kv_tile64(bf16* ktile, bf16* vtile, const bf16* kbase, const bf16* vbase,
-                                               const PagedKV& kv, const int* bt, int key0, int lo, int hi, int tid) {
+                                               const PagedKV& kv, const int* bt, int key0, int lo, int hi, int tid,
+                                               int bt_first = 0) {
   constexpr int CPR = HD / 8;
   const int r = tid >> 1, half = tid & 1;
   const int key = key0 + r;
   bool ok = key >= lo && key < hi;
   size_t off = 0;
   if (ok) {
-    const int page = bt[key >> kv.page_shift];
+    const int page = bt[(key >> kv.page_shift) - bt_first];
     ok = page >= 0;
     if (ok) off = (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * HD;
   }
@@ -113,6 +116,8 @@ __device__ __forceinline__ void load_kv_tile64(bf16* ktile, bf16* vtile, const b
     cp_async16(vrow + ((c ^ sw) << 3), vsrc + c * 8, ok);
   }
 }
+
+constexpr int BT_CACHE = 1024;      // block-table entries a block keeps in shared memory
 
 struct AttnMeta {
   const int* block_tables; int bt_stride;
@@ -131,7 +136,10 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);              // [2][BK][HD]
   bf16* vs = ks + 2 * BK * HD;                               // [2][BK][HD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
-  const int e = tile_entry[blockIdx.x], q0 = tile_q0[blockIdx.x], head = blockIdx.y;
+  // tiles run last to first: within a request the later tiles see more keys, and the
+  // longest blocks should start first
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int e = tile_entry[tile], q0 = tile_q0[tile], head = blockIdx.y;
   const int rows = min(BQ, m.entry_q_len[e] - q0);
   if (rows <= 0) return;
   const int tok0 = m.entry_q_start[e] + q0;
@@ -166,16 +174,27 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int kend = pos0 + rows;                                  // keys [.., kend) may be seen
   const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the first row may see
   const int t_begin = kfirst / BK, t_end = (kend - 1) / BK;
+  __shared__ int bt_s[BT_CACHE];                                 // this block's slice of the block table
+  int bt_first = 0;
+  {
+    const int b0 = kfirst >> kv.page_shift, b1 = (kend - 1) >> kv.page_shift;
+    if (b1 - b0 < BT_CACHE) {
+      for (int i = tid; i <= b1 - b0; i += 128) bt_s[i] = bt[b0 + i];
+      bt = bt_s;
+      bt_first = b0;
+      __syncthreads();
+    }
+  }
   const int pa_row = pos0 + wr0 + g, pb_row = pa_row + 8;        // positions of this thread's two rows
   const int warp_last = pos0 + min(wr0 + 15, rows - 1);
 
-  load_kv_tile64<HD>(ks, vs, kbase, vbase, kv, bt, t_begin * BK, kfirst, kend, tid);
+  load_kv_tile64<HD>(ks, vs, kbase, vbase, kv, bt, t_begin * BK, kfirst, kend, tid, bt_first);
   cp_async_commit();
   for (int t = t_begin; t <= t_end; ++t) {
     const int st = (t - t_begin) & 1;
     if (t < t_end) {
       load_kv_tile64<HD>(ks + (st ^ 1) * BK * HD, vs + (st ^ 1) * BK * HD, kbase, vbase, kv, bt, (t + 1) * BK,
-                         kfirst, kend, tid);
+                         kfirst, kend, tid, bt_first);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -281,13 +300,22 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 }
 
 // ------------------------------------------------------------------- decode
-// One block: one decoding entry, up to 16 query heads of one kv head, one split of
-// the keys.  The block streams its keys and values in tiles of 64 through a ring of
-// DSTAGES shared-memory stages (loads run two tiles ahead of the math); each of the
-// 4 warps takes 16 keys of a tile and keeps its own running (max, sum, o), merged at
-// the end.  Partial results go to scratch for the merge kernel; with one split the
-// block writes the final output itself.
+// One block: one decoding entry, up to 8 query heads of one kv head, one split of the keys.
+// The product is laid out transposed, S^T = K Q^T and O^T = V^T P^T: the 16 rows of an MMA
+// tile are 16 keys (or 16 head dims) and its 8 columns are the query heads that share the kv
+// head, so with 7 heads per kv head 7/8 of every MMA is useful work and the accumulator is
+// [head_dim x 8] (32 registers).  P^T goes from accumulator layout to operand layout by one
+// movmatrix per 8 keys.  The block streams keys and values in tiles of 64 through a ring of
+// DSTAGES shared-memory stages (loads run ahead of the math); each of the 4 warps takes 16
+// keys of a tile and keeps its own running (max, sum, o), merged at the end.  Partial
+// results go to scratch for the merge kernel; with one split the block writes the output.
 constexpr int DSTAGES = 3;
+
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned x) {
+  unsigned y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(128)
@@ -295,7 +323,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
                         PagedKV kv, AttnMeta m, const int* __restrict__ dec_entries,
                         float* __restrict__ part_o, float* __restrict__ part_ml,
                         int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits) {
-  constexpr int KS = HD / 16, DT = HD / 8, BK = 64, TK = 16;
+  constexpr int KS = HD / 16, BK = 64, TK = 16;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16* ring = reinterpret_cast<bf16*>(smem_raw);             // [DSTAGES][K|V][BK][HD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
@@ -303,8 +331,8 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   const int kvh = blockIdx.y / head_chunks, hc = blockIdx.y - kvh * head_chunks;
   const int split = blockIdx.z;
   const int ratio = n_heads / n_kv;
-  const int h0 = kvh * ratio + hc * 16;
-  const int nrows = min(16, ratio - hc * 16);
+  const int h0 = kvh * ratio + hc * 8;
+  const int nrows = min(8, ratio - hc * 8);                     // query heads of this block
   const int tok = m.entry_q_start[e];
   const int len = m.entry_ctx_start[e] + 1;                     // keys [0, len) exist; the query sits at len - 1
   const int kfirst = window > 0 ? max(0, len - window) : 0;
@@ -316,37 +344,46 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   const bf16* kbase = (const bf16*)kv.k + (size_t)kvh * kv.head_stride;
   const bf16* vbase = (const bf16*)kv.v + (size_t)kvh * kv.head_stride;
   const int dec = blockIdx.x;
+  // this block's slice of the block table, copied to shared memory once
+  __shared__ int bt_s[BT_CACHE];
+  int bt_first = 0;
+  if (kb < ke) {
+    const int b0 = kb >> kv.page_shift, b1 = (ke - 1) >> kv.page_shift;
+    if (b1 - b0 < BT_CACHE) {
+      for (int i = tid; i <= b1 - b0; i += 128) bt_s[i] = bt[b0 + i];
+      bt = bt_s;
+      bt_first = b0;
+      __syncthreads();
+    }
+  }
 
-  float o[DT][4];
+  // o[dd]: rows d = dd*16 + g (regs 0,1) and + 8 (regs 2,3); columns heads 2*t4 (regs 0,2) and 2*t4+1 (regs 1,3)
+  float o[KS][4];
 #pragma unroll
-  for (int d = 0; d < DT; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
-  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.0f, 0.0f};
+  for (int d = 0; d < KS; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
+  float mcol[2] = {-INFINITY, -INFINITY}, lcol[2] = {0.0f, 0.0f};   // heads 2*t4, 2*t4+1
 
   if (kb < ke) {                                                // block-uniform
-    unsigned qa[KS][4];
+    unsigned qb[KS][2];                                         // Q^T as the B operand: k = d, n = head g
     {
-      const bf16* qb = q + (size_t)tok * q_stride + (size_t)h0 * HD;
-      const unsigned* pa = reinterpret_cast<const unsigned*>(qb + (size_t)g * HD);
-      const unsigned* pb = reinterpret_cast<const unsigned*>(qb + (size_t)(g + 8) * HD);
+      const unsigned* pq = reinterpret_cast<const unsigned*>(q + (size_t)tok * q_stride + (size_t)(h0 + g) * HD);
 #pragma unroll
       for (int k = 0; k < KS; ++k) {
-        qa[k][0] = g < nrows ? pa[k * 8 + t4] : 0u;
-        qa[k][1] = g + 8 < nrows ? pb[k * 8 + t4] : 0u;
-        qa[k][2] = g < nrows ? pa[k * 8 + 4 + t4] : 0u;
-        qa[k][3] = g + 8 < nrows ? pb[k * 8 + 4 + t4] : 0u;
+        qb[k][0] = g < nrows ? pq[k * 8 + t4] : 0u;
+        qb[k][1] = g < nrows ? pq[k * 8 + 4 + t4] : 0u;
       }
     }
     const float sl2 = scale * LOG2E;
     const int t_begin = kb / BK, t_end = (ke - 1) / BK, n_t = t_end - t_begin + 1;
-    // prologue: the first DSTAGES - 1 tiles
 #pragma unroll
     for (int p = 0; p < DSTAGES - 1; ++p) {
       if (p < n_t) {
         bf16* st = ring + (size_t)p * 2 * BK * HD;
-        load_kv_tile64<HD>(st, st + BK * HD, kbase, vbase, kv, bt, (t_begin + p) * BK, kb, ke, tid);
+        load_kv_tile64<HD>(st, st + BK * HD, kbase, vbase, kv, bt, (t_begin + p) * BK, kb, ke, tid, bt_first);
       }
       cp_async_commit();
     }
+    const int j = lane >> 3, r = lane & 7;
     for (int i = 0; i < n_t; ++i) {
       cp_async_wait<DSTAGES - 2>();                             // tile i has landed (for this thread)
       __syncthreads();                                          // ... for all; and tile i - 1 is no longer read
@@ -354,7 +391,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
         const int nx = i + DSTAGES - 1;
         if (nx < n_t) {
           bf16* st = ring + (size_t)(nx % DSTAGES) * 2 * BK * HD;
-          load_kv_tile64<HD>(st, st + BK * HD, kbase, vbase, kv, bt, (t_begin + nx) * BK, kb, ke, tid);
+          load_kv_tile64<HD>(st, st + BK * HD, kbase, vbase, kv, bt, (t_begin + nx) * BK, kb, ke, tid, bt_first);
         }
         cp_async_commit();
       }
@@ -362,99 +399,82 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       if (key0 >= ke || key0 + TK <= kb) continue;              // warp-uniform: nothing of ours in range
       bf16* kt = ring + (size_t)(i % DSTAGES) * 2 * BK * HD;
       bf16* vt = kt + BK * HD;
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      const int j = lane >> 3, r = lane & 7;
+      float s[4] = {0.f, 0.f, 0.f, 0.f};                        // (key g | g+8) x (head 2*t4 | 2*t4+1)
 #pragma unroll
       for (int k = 0; k < KS; ++k) {
-        unsigned b[4];
-        ldmatrix_x4(b, tile_chunk<HD>(kt, warp * TK + (j >> 1) * 8 + r, k * 2 + (j & 1)));
-        mma_bf16(s[0], qa[k], b[0], b[1]);
-        mma_bf16(s[1], qa[k], b[2], b[3]);
+        unsigned a[4];
+        ldmatrix_x4(a, tile_chunk<HD>(kt, warp * TK + (j & 1) * 8 + r, k * 2 + (j >> 1)));
+        mma_bf16(s, a, qb[k][0], qb[k][1]);
       }
-      float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int key = key0 + n * 8 + t4 * 2 + (c & 1);
-          const float v = (key >= kb && key < ke) ? s[n][c] * sl2 : -INFINITY;
-          s[n][c] = v;
-          mx[c >> 1] = fmaxf(mx[c >> 1], v);
-        }
-      }
+      const bool in0 = key0 + g >= kb && key0 + g < ke, in1 = key0 + g + 8 >= kb && key0 + g + 8 < ke;
+      s[0] = in0 ? s[0] * sl2 : -INFINITY;
+      s[1] = in0 ? s[1] * sl2 : -INFINITY;
+      s[2] = in1 ? s[2] * sl2 : -INFINITY;
+      s[3] = in1 ? s[3] * sl2 : -INFINITY;
+      float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
       float alpha[2], mnew[2];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        mnew[h] = fmaxf(mrow[h], mx[h]);
-        alpha[h] = mnew[h] == -INFINITY ? 1.0f : fast_exp2(mrow[h] - mnew[h]);
-        mrow[h] = mnew[h];
+      for (int h = 0; h < 2; ++h) {                             // over the 8 lanes that hold the other keys
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+        mnew[h] = fmaxf(mcol[h], mx[h]);
+        alpha[h] = mnew[h] == -INFINITY ? 1.0f : fast_exp2(mcol[h] - mnew[h]);
+        mcol[h] = mnew[h];
       }
-      float ls[2] = {0.0f, 0.0f};
+      float p[4];
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int c = 0; c < 4; ++c) p[c] = mnew[c & 1] == -INFINITY ? 0.0f : fast_exp2(s[c] - mnew[c & 1]);
+      lcol[0] = lcol[0] * alpha[0] + p[0] + p[2];
+      lcol[1] = lcol[1] * alpha[1] + p[1] + p[3];
+      if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {   // a maximum moved: rescale o
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float mm = mnew[c >> 1];
-          const float p = mm == -INFINITY ? 0.0f : fast_exp2(s[n][c] - mm);
-          s[n][c] = p;
-          ls[c >> 1] += p;
-        }
+        for (int d = 0; d < KS; ++d) { o[d][0] *= alpha[0]; o[d][1] *= alpha[1]; o[d][2] *= alpha[0]; o[d][3] *= alpha[1]; }
       }
-      lrow[0] = lrow[0] * alpha[0] + ls[0];
-      lrow[1] = lrow[1] * alpha[1] + ls[1];
-      if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {   // the maximum moved: rescale o
+      // P^T as the B operand (k = key, n = head): transpose the two 8x8 blocks
+      const unsigned pb0 = movmatrix_trans(pack_bf16(p[0], p[1]));
+      const unsigned pb1 = movmatrix_trans(pack_bf16(p[2], p[3]));
 #pragma unroll
-        for (int d = 0; d < DT; ++d) { o[d][0] *= alpha[0]; o[d][1] *= alpha[0]; o[d][2] *= alpha[1]; o[d][3] *= alpha[1]; }
-      }
-      unsigned pa[4];
-      pa[0] = pack_bf16(s[0][0], s[0][1]);
-      pa[1] = pack_bf16(s[0][2], s[0][3]);
-      pa[2] = pack_bf16(s[1][0], s[1][1]);
-      pa[3] = pack_bf16(s[1][2], s[1][3]);
-#pragma unroll
-      for (int dp = 0; dp < DT / 2; ++dp) {
-        unsigned b[4];
-        ldmatrix_x4_trans(b, tile_chunk<HD>(vt, warp * TK + (j & 1) * 8 + r, dp * 2 + (j >> 1)));
-        mma_bf16(o[dp * 2], pa, b[0], b[1]);
-        mma_bf16(o[dp * 2 + 1], pa, b[2], b[3]);
+      for (int d = 0; d < KS; ++d) {                             // V^T as the A operand: rows d, columns keys
+        unsigned a[4];
+        ldmatrix_x4_trans(a, tile_chunk<HD>(vt, warp * TK + (j >> 1) * 8 + r, d * 2 + (j & 1)));
+        mma_bf16(o[d], a, pb0, pb1);
       }
     }
     cp_async_wait<0>();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 1);
-      lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 2);
+      lcol[h] += __shfl_xor_sync(0xffffffffu, lcol[h], 4);
+      lcol[h] += __shfl_xor_sync(0xffffffffu, lcol[h], 8);
+      lcol[h] += __shfl_xor_sync(0xffffffffu, lcol[h], 16);
     }
   }
   // merge the four warps through shared memory (the ring is free now)
   __syncthreads();
-  float* red_o = reinterpret_cast<float*>(smem_raw);            // [4][16][HD]
-  float* red_ml = red_o + 4 * 16 * HD;                          // [4][16][2]
+  float* red_o = reinterpret_cast<float*>(smem_raw);            // [4][8 heads][HD]
+  float* red_ml = red_o + 4 * 8 * HD;                           // [4][8][2]
 #pragma unroll
-  for (int d = 0; d < DT; ++d) {
-    float* ra = red_o + ((size_t)warp * 16 + g) * HD + d * 8 + t4 * 2;
-    float* rb = red_o + ((size_t)warp * 16 + g + 8) * HD + d * 8 + t4 * 2;
-    ra[0] = o[d][0]; ra[1] = o[d][1]; rb[0] = o[d][2]; rb[1] = o[d][3];
+  for (int d = 0; d < KS; ++d) {
+    float* r0 = red_o + ((size_t)warp * 8 + t4 * 2) * HD + d * 16 + g;
+    r0[0] = o[d][0]; r0[HD] = o[d][1]; r0[8] = o[d][2]; r0[HD + 8] = o[d][3];
   }
-  if (t4 == 0) {
-    red_ml[(warp * 16 + g) * 2] = mrow[0];     red_ml[(warp * 16 + g) * 2 + 1] = lrow[0];
-    red_ml[(warp * 16 + g + 8) * 2] = mrow[1]; red_ml[(warp * 16 + g + 8) * 2 + 1] = lrow[1];
+  if (g == 0) {
+    red_ml[(warp * 8 + t4 * 2) * 2] = mcol[0];     red_ml[(warp * 8 + t4 * 2) * 2 + 1] = lcol[0];
+    red_ml[(warp * 8 + t4 * 2 + 1) * 2] = mcol[1]; red_ml[(warp * 8 + t4 * 2 + 1) * 2 + 1] = lcol[1];
   }
   __syncthreads();
   for (int idx = tid; idx < nrows * HD; idx += 128) {
     const int row = idx / HD, d = idx - row * HD;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_ml[(w * 16 + row) * 2]);
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_ml[(w * 8 + row) * 2]);
     float l = 0.0f, acc = 0.0f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float mw = red_ml[(w * 16 + row) * 2];
+      const float mw = red_ml[(w * 8 + row) * 2];
       const float f = mw == -INFINITY ? 0.0f : fast_exp2(mw - mm);
-      l += red_ml[(w * 16 + row) * 2 + 1] * f;
-      acc += red_o[((size_t)w * 16 + row) * HD + d] * f;
+      l += red_ml[(w * 8 + row) * 2 + 1] * f;
+      acc += red_o[((size_t)w * 8 + row) * HD + d] * f;
     }
     const int head = h0 + row;
     if (n_splits == 1) {
@@ -516,7 +536,7 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
                   const int* dec_entries, int n_dec, float* part_o, float* part_ml, int n_heads, int n_kv,
                   float scale, int window, int n_splits, cudaStream_t stream) {
   const size_t stage_bytes = (size_t)DSTAGES * 2 * 64 * HD * sizeof(bf16);
-  const size_t red_bytes = (size_t)4 * 16 * HD * sizeof(float) + 4 * 16 * 2 * sizeof(float);
+  const size_t red_bytes = (size_t)4 * 8 * HD * sizeof(float) + 4 * 8 * 2 * sizeof(float);
   const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
   auto kern = attn_decode_bf16_kernel<HD>;
   if (smem > 48 * 1024) {
@@ -524,7 +544,7 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
     if (e != cudaSuccess) return (int)e;
   }
   const int ratio = n_heads / n_kv;
-  const int head_chunks = (ratio + 15) / 16;
+  const int head_chunks = (ratio + 7) / 8;
   kern<<<dim3(n_dec, n_kv * head_chunks, n_splits), 128, smem, stream>>>(
       (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, dec_entries, part_o, part_ml, n_heads, n_kv,
       head_chunks, scale, window, n_splits);

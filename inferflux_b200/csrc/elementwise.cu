@@ -26,12 +26,32 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = Num<T>::to_f(row[i]);
 }
 
+// 8 bfloat16 (16 bytes) per thread per step; hidden a multiple of 8
+__global__ void embed_gather_bf16x8_kernel(const bf16* __restrict__ table, const int* __restrict__ ids,
+                                           float* __restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)(ok ? id : 0) * hidden);
+  float4* o = reinterpret_cast<float4*>(out + (size_t)t * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) {
+    uint4 v = ok ? row[i] : make_uint4(0u, 0u, 0u, 0u);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    const float2 c = __bfloat1622float2(h[2]), d = __bfloat1622float2(h[3]);
+    o[2 * i] = make_float4(a.x, a.y, b.x, b.y);
+    o[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+  }
+}
+
 IFX_API int ifx_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
                              int n_tokens, int hidden, int vocab, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
   if (table_dtype == IFX_F32)
     embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+  else if (table_dtype == IFX_BF16 && hidden % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0)
+    embed_gather_bf16x8_kernel<<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, hidden, vocab);
   else if (table_dtype == IFX_BF16)
     embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, hidden, vocab);
   else
@@ -75,10 +95,90 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   }
 }
 
+// Vector path: hidden a multiple of 4 and at most 4 * VT * blockDim.  Each thread keeps its
+// (up to VT) groups of 4 consecutive values in registers between the sum of squares and the
+// scaling, so a row is read once and written once.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ float4 load(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&a);
+    u.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+
+template <typename TD, typename TO, int VT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
+                       long long partial_stride, const float* __restrict__ weight, float eps,
+                       TO* __restrict__ out, const int* __restrict__ rows, int hidden, int write_residual) {
+  __shared__ float red[32];
+  const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* r = residual + (size_t)src * hidden;
+  const int groups = hidden >> 2;
+  float4 v[VT];
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < VT; ++j) {
+    const int gidx = threadIdx.x + j * 256;
+    if (gidx < groups) {
+      float4 x = Vec4<float>::load(r + 4 * gidx);
+      if (delta) {
+        const TD* d = delta + (size_t)src * hidden + 4 * gidx;
+        for (int p = 0; p < n_partials; ++p) {
+          const float4 y = Vec4<TD>::load(d + (size_t)p * partial_stride);
+          x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+        }
+      }
+      v[j] = x;
+      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+  TO* o = out ? out + (size_t)blockIdx.x * hidden : nullptr;
+#pragma unroll
+  for (int j = 0; j < VT; ++j) {
+    const int gidx = threadIdx.x + j * 256;
+    if (gidx < groups) {
+      if (write_residual) Vec4<float>::store(r + 4 * gidx, v[j]);
+      if (o) {
+        const float4 w = Vec4<float>::load(weight + 4 * gidx);
+        Vec4<TO>::store(o + 4 * gidx, make_float4(v[j].x * rstd * w.x, v[j].y * rstd * w.y,
+                                                  v[j].z * rstd * w.z, v[j].w * rstd * w.w));
+      }
+    }
+  }
+}
+
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* residual, const void* delta, int n_partials, long long partial_stride,
                               const float* weight, float eps, void* out, const int* rows, int n_rows,
                               int hidden, int write_residual, cudaStream_t stream) {
+  const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0
+                       && (partial_stride & 3) == 0;
+  if (hidden % 4 == 0 && aligned && hidden <= 4 * 8 * 256) {
+    const int groups = hidden / 4;
+    if (groups <= 4 * 256)
+      add_rmsnorm_vec_kernel<TD, TO, 4><<<n_rows, 256, 0, stream>>>(residual, (const TD*)delta, n_partials, partial_stride,
+                                                                    weight, eps, (TO*)out, rows, hidden, write_residual);
+    else
+      add_rmsnorm_vec_kernel<TD, TO, 8><<<n_rows, 256, 0, stream>>>(residual, (const TD*)delta, n_partials, partial_stride,
+                                                                    weight, eps, (TO*)out, rows, hidden, write_residual);
+    return IFX_LAUNCH_CHECK();
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return IFX_ERR_UNSUPPORTED;
   auto kern = add_rmsnorm_kernel<TD, TO>;
@@ -127,12 +227,41 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   }
 }
 
+// 8 outputs per thread per step: 16-byte loads of gate and up, one 16-byte store; inter a multiple of 8
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, long long total8, int inter8) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; idx < total8; idx += stride) {
+    const long long m = idx / inter8;
+    const int i = (int)(idx - m * inter8);
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + (m * 2 * inter8 + i) * 8);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + (m * 2 * inter8 + inter8 + i) * 8);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = ov;
+  }
+}
+
 IFX_API int ifx_swiglu(const void* gate_up, void* out, int dtype, int m, int inter, cudaStream_t stream) {
   const long long total = (long long)m * inter;
   if (total <= 0) return 0;
   const int threads = 256;
   long long blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == IFX_BF16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+    const long long total8 = total / 8;
+    long long b8 = (total8 + threads - 1) / threads;
+    if (b8 > 148 * 16) b8 = 148 * 16;
+    swiglu_bf16x8_kernel<<<(int)b8, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total8, inter / 8);
+    return IFX_LAUNCH_CHECK();
+  }
   if (dtype == IFX_F32)
     swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, inter);
   else if (dtype == IFX_BF16)

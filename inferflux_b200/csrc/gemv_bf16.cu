@@ -1,20 +1,21 @@
 // Weight-streaming matrix product for a few rows of activations (decode):
-// out[M, N] = X[M, K] * W[N, K]^T, bfloat16 in, float32 accumulation, M <= 32.
+// out[M, N] = X[M, K] * W[N, K]^T, bfloat16 in, float32 accumulation, M <= 16.
 //
 // The reference sends every dense projection to cuBLAS whatever M is
 // (runtime/backends/cuda/native/cublas_gemm.cpp:84-102; its hand-written GEMV
-// kernels are for quantized weights only).  At M of 1 to 32 the product is bound
+// kernels are for quantized weights only).  At M of 1 to 16 the product is bound
 // by reading W once, so this kernel is laid out around that read: the weights
 // are the 16-row "A" operand of an m16n8k16 MMA and the tokens the 8-column "B"
 // operand.  Each lane reads 16 contiguous bytes of two weight rows and 16 bytes
 // of one token's activations per 32-wide K chunk; because a dot product does
 // not care about the order of K, those 8 consecutive values feed two MMAs
-// directly from registers, without shared memory or shuffles.  When there are
-// many row tiles each warp owns one over the whole of K; when there are few, the
-// warps of a block take interleaved K chunks of one tile and add their partial
-// sums in shared memory in a fixed order, and K may also be cut between blocks,
-// whose float32 partial results the consumer adds (the fused residual-add +
-// norm kernel does).
+// as they are, without shuffles.  To keep the read of W in flight each thread
+// copies its 16-byte pieces with cp.async into a shared-memory ring of its own,
+// six chunks deep (it reads back only what it copied, so no barrier is needed).
+// The warps of a block take interleaved K chunks of the same row tiles and add
+// their partial sums in shared memory in warp order; K may also be cut between
+// blocks, whose float32 partial results the consumer adds (the fused
+// residual-add + norm kernel does).
 //
 // SwiGLU mode: rows 0-7 of the tile come from the gate half of a stacked
 // [gate; up] weight and rows 8-15 from the up half at the same index, so each
@@ -25,11 +26,21 @@
 
 namespace {
 
-// Loads are plain (always from a valid, clamped address) and masked afterwards, so that the
-// compiler can issue the loads of an unrolled group together and keep them all in flight.
 __device__ __forceinline__ uint4 mask16(uint4 v, bool keep) {
   return keep ? v : make_uint4(0u, 0u, 0u, 0u);
 }
+
+// Weights go from global to shared memory with 16-byte cp.async, each thread into a ring of
+// its own (it reads back only what it copied, so no barrier is needed): the copies of the next
+// NST - 1 chunks stay in flight while a chunk is multiplied.  A copy whose source is out of range
+// has source size 0 and fills zeros.
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -41,30 +52,37 @@ template <typename T> __device__ __forceinline__ T to_out(float v);
 template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 to_out<bf16>(float v) { return __float2bfloat16_rn(v); }
 
-constexpr int KCHUNK = 32, UNROLL = 8;
+constexpr int KCHUNK = 32, NST = 6;
 
-// A block has RW x KW warps: warp (rw, kw) owns row tile `blockIdx.x * RW + rw` (16 weight
-// rows, or 8 gate + 8 up rows in SwiGLU mode) and the K chunks kw, kw + KW, ... of the
-// block's K range; the KW partial sums of a row tile are added in shared memory in warp
-// order.  gridDim.y > 1 cuts K between blocks: block y writes float32 partial sums to
-// out + y * M * ldo... (partial_stride elements apart), to be added by the consumer.
+// A block has KW warps that share RT row tiles (tiles blockIdx.x * RT ..; a tile is 16 weight rows,
+// or 8 gate + 8 up rows in SwiGLU mode).  Warp kw takes the K chunks kw, kw + KW, ... of the block's
+// K range for all RT tiles, so one 16-byte read of a token's activations feeds 2 * RT MMAs; the KW
+// partial sums are added in shared memory in warp order.  gridDim.y > 1 cuts K between blocks:
+// block y writes float32 partial sums partial_stride elements apart, to be added by the consumer.
 // NT: token tiles of 8 (M <= 8 * NT).
-template <int NT, bool SWIGLU, typename TOut, int RW, int KW>
-__global__ void __launch_bounds__(RW * KW * 32)
+template <int NT, bool SWIGLU, typename TOut, int RT, int KW>
+__global__ void __launch_bounds__(KW * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias,
                  TOut* __restrict__ out, int M, int n_out, int K, long long ldx, long long ldo,
                  long long partial_stride) {
-  __shared__ float red[KW > 1 ? RW * KW : 1][NT][32][4];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
-  const int rw = warp / KW, kw = warp - rw * KW;
-  const int tile = blockIdx.x * RW + rw;
+  constexpr int THREADS = KW * 32;
+  extern __shared__ __align__(16) uint4 ring[];                 // [NST][2 * RT][threads]: a thread's slots are [..][..][tid]
+  __shared__ float red[KW][RT][NT][32][4];
+  const int tid = threadIdx.x, lane = tid & 31, kw = tid >> 5, g = lane >> 2, t4 = lane & 3;
   const int n_rows = SWIGLU ? 2 * n_out : n_out;                // rows of W
-  int row_a, row_b;
-  if (SWIGLU) { row_a = tile * 8 + g; row_b = n_out + row_a; if (row_a >= n_out) row_a = row_b = n_rows; }
-  else { row_a = tile * 16 + g; row_b = row_a + 8; }
-  const bool ok_a = row_a < n_rows, ok_b = row_b < n_rows;
-  const bf16* wa = W + (size_t)(ok_a ? row_a : 0) * K;
-  const bf16* wb = W + (size_t)(ok_b ? row_b : 0) * K;
+  const bf16* wrow[2 * RT];
+  bool ok_row[2 * RT];
+#pragma unroll
+  for (int r = 0; r < RT; ++r) {
+    const int tile = blockIdx.x * RT + r;
+    int row_a, row_b;
+    if (SWIGLU) { row_a = tile * 8 + g; row_b = n_out + row_a; if (row_a >= n_out) row_a = row_b = n_rows; }
+    else { row_a = tile * 16 + g; row_b = row_a + 8; }
+    ok_row[2 * r] = row_a < n_rows;
+    ok_row[2 * r + 1] = row_b < n_rows;
+    wrow[2 * r] = W + (size_t)(ok_row[2 * r] ? row_a : 0) * K;
+    wrow[2 * r + 1] = W + (size_t)(ok_row[2 * r + 1] ? row_b : 0) * K;
+  }
   const bf16* xr[NT];
   bool ok_x[NT];
 #pragma unroll
@@ -72,66 +90,92 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
     ok_x[t] = t * 8 + g < M;
     xr[t] = X + (size_t)(ok_x[t] ? t * 8 + g : 0) * ldx;
   }
-  float acc[NT][4];
+  float acc[RT][NT][4];
 #pragma unroll
-  for (int t = 0; t < NT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f; }
+  for (int r = 0; r < RT; ++r)
+#pragma unroll
+    for (int t = 0; t < NT; ++t) { acc[r][t][0] = acc[r][t][1] = acc[r][t][2] = acc[r][t][3] = 0.0f; }
 
   const int n_chunks = (K + KCHUNK - 1) / KCHUNK;
   const int per_split = (n_chunks + gridDim.y - 1) / gridDim.y;
   const int c_begin = blockIdx.y * per_split, c_end = min(n_chunks, c_begin + per_split);
+  // this warp's chunks: c_begin + kw, + KW, ...
+  const int n_my = c_begin + kw < c_end ? (c_end - c_begin - kw + KW - 1) / KW : 0;
   const int k_last = K - 8;                                      // the last 16-byte piece of a row
-  for (int c0 = c_begin + kw; c0 < c_end; c0 += KW * UNROLL) {
-    uint4 a[UNROLL], b[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {                           // all weight loads first: many bytes in flight
-      const int kk = min((c0 + u * KW) * KCHUNK + t4 * 8, k_last);
-      a[u] = __ldcs(reinterpret_cast<const uint4*>(wa + kk));
-      b[u] = __ldcs(reinterpret_cast<const uint4*>(wb + kk));
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int c = c0 + u * KW;
-      const int kraw = c * KCHUNK + t4 * 8;
-      const bool in = c < c_end && kraw < K;
+  auto issue = [&](int j) {
+    if (j < n_my) {
+      const int kraw = (c_begin + kw + j * KW) * KCHUNK + t4 * 8;
+      const bool in = kraw < K;
       const int kk = min(kraw, k_last);
-      const uint4 av = mask16(a[u], in && ok_a), bv = mask16(b[u], in && ok_b);
+      uint4* slot = ring + (size_t)((j % NST) * 2 * RT) * THREADS + tid;
+#pragma unroll
+      for (int r = 0; r < 2 * RT; ++r) cp_async16_zfill(slot + r * THREADS, wrow[r] + kk, in && ok_row[r]);
+    }
+    cp_async_commit_group();
+  };
+#pragma unroll
+  for (int j = 0; j < NST - 1; ++j) issue(j);
+  // activations come from L1/L2 with plain loads, one chunk ahead of their use
+  uint4 xn[NT];
+  {
+    const int kk = min((c_begin + kw) * KCHUNK + t4 * 8, k_last);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) xn[t] = __ldg(reinterpret_cast<const uint4*>(xr[t] + kk));
+  }
+  for (int j = 0; j < n_my; ++j) {
+    uint4 x[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) x[t] = mask16(xn[t], ok_x[t]);
+    {
+      const int kk = min((c_begin + kw + (j + 1) * KW) * KCHUNK + t4 * 8, k_last);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) xn[t] = __ldg(reinterpret_cast<const uint4*>(xr[t] + kk));
+    }
+    cp_async_wait_group<NST - 2>();                              // chunk j has landed
+    const uint4* slot = ring + (size_t)((j % NST) * 2 * RT) * THREADS + tid;
+    uint4 w[2 * RT];
+#pragma unroll
+    for (int r = 0; r < 2 * RT; ++r) w[r] = slot[r * THREADS];
+    issue(j + NST - 1);                                          // reuses the slot of chunk j - 1
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint4 x = mask16(__ldg(reinterpret_cast<const uint4*>(xr[t] + kk)), ok_x[t]);
-        mma16816(acc[t], av.x, bv.x, av.y, bv.y, x.x, x.y);
-        mma16816(acc[t], av.z, bv.z, av.w, bv.w, x.z, x.w);
+        mma16816(acc[r][t], w[2 * r].x, w[2 * r + 1].x, w[2 * r].y, w[2 * r + 1].y, x[t].x, x[t].y);
+        mma16816(acc[r][t], w[2 * r].z, w[2 * r + 1].z, w[2 * r].w, w[2 * r + 1].w, x[t].z, x[t].w);
       }
     }
   }
-  if (KW > 1) {
+  cp_async_wait_group<0>();
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
+  for (int r = 0; r < RT; ++r)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) red[warp][t][lane][c] = acc[t][c];
-    }
-    __syncthreads();
-    if (kw != 0) return;
+    for (int t = 0; t < NT; ++t)
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < KW; ++w) v += red[rw * KW + w][t][lane][c];
-        acc[t][c] = v;
-      }
-    }
-  }
-  // this lane holds, per token tile: rows g (c = 0, 1) and g + 8 (c = 2, 3) of tokens t4*2, t4*2 + 1
+      for (int c = 0; c < 4; ++c) red[kw][r][t][lane][c] = acc[r][t][c];
+  __syncthreads();
+  // warp r (< RT) finishes row tile r: this lane holds, per token tile, rows g (c = 0, 1) and
+  // g + 8 (c = 2, 3) of tokens t4*2, t4*2 + 1
+  if (kw >= RT) return;
+  const int r = kw;
+  const int tile = blockIdx.x * RT + r;
   TOut* dst = out + (size_t)blockIdx.y * partial_stride;
   const bool add_bias = bias && blockIdx.y == 0;
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
+    float v[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int w = 0; w < KW; ++w) sum += red[w][r][t][lane][c];
+      v[c] = sum;
+    }
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
       const int token = t * 8 + t4 * 2 + cc;
       if (token >= M) continue;
-      const float lo = acc[t][cc], hi = acc[t][cc + 2];
+      const float lo = v[cc], hi = v[cc + 2];
       if (SWIGLU) {
         const int o = tile * 8 + g;
         if (o < n_out) dst[(size_t)token * ldo + o] = to_out<TOut>(lo / (1.0f + expf(-lo)) * hi);
@@ -144,25 +188,32 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
   }
 }
 
-template <int NT, bool SWIGLU, typename TOut, int RW, int KW>
+template <int NT, bool SWIGLU, typename TOut, int RT, int KW>
 int launch(const void* X, const void* W, const float* bias, void* out, int M, int n_out, int K, long long ldx,
            long long ldo, int k_splits, long long partial_stride, cudaStream_t stream) {
   const int tiles = SWIGLU ? (n_out + 7) / 8 : (n_out + 15) / 16;
-  dim3 grid((tiles + RW - 1) / RW, k_splits);
-  gemv_bf16_kernel<NT, SWIGLU, TOut, RW, KW><<<grid, RW * KW * 32, 0, stream>>>(
-      (const bf16*)X, (const bf16*)W, bias, (TOut*)out, M, n_out, K, ldx, ldo, partial_stride);
+  dim3 grid((tiles + RT - 1) / RT, k_splits);
+  const size_t smem = (size_t)NST * 2 * RT * KW * 32 * sizeof(uint4);
+  auto kern = gemv_bf16_kernel<NT, SWIGLU, TOut, RT, KW>;
+  {  // dynamic plus static shared memory passes 48 KB
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kern<<<grid, KW * 32, smem, stream>>>((const bf16*)X, (const bf16*)W, bias, (TOut*)out, M, n_out, K, ldx, ldo,
+                                        partial_stride);
   return IFX_LAUNCH_CHECK();
 }
 
-// Block shape by the amount of work: many row tiles -> each warp owns its rows over the whole K
-// (no shared-memory sum); few row tiles -> the warps of a block share one row tile and cut K.
+// Block shape by the amount of work: with plenty of row tiles a block takes two (the activations
+// are read half as often); short K ranges get 4 warps instead of 8.
 template <int NT, bool SWIGLU, typename TOut>
 int by_shape(const void* X, const void* W, const float* bias, void* out, int M, int n_out, int K, long long ldx,
              long long ldo, int k_splits, long long partial_stride, cudaStream_t stream) {
   const int tiles = SWIGLU ? (n_out + 7) / 8 : (n_out + 15) / 16;
   const int chunks = (K + KCHUNK - 1) / KCHUNK / k_splits;
-  if (tiles >= 1184) return launch<NT, SWIGLU, TOut, 4, 1>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
-  if (chunks >= 128) return launch<NT, SWIGLU, TOut, 1, 8>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
+  if (tiles * k_splits >= 1184 && chunks >= 64)
+    return launch<NT, SWIGLU, TOut, 2, 8>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
+  if (chunks >= 64) return launch<NT, SWIGLU, TOut, 1, 8>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
   return launch<NT, SWIGLU, TOut, 1, 4>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
 }
 
@@ -170,20 +221,19 @@ template <bool SWIGLU, typename TOut>
 int by_tiles(const void* X, const void* W, const float* bias, void* out, int M, int n_out, int K, long long ldx,
              long long ldo, int k_splits, long long partial_stride, cudaStream_t stream) {
   if (M <= 8) return by_shape<1, SWIGLU, TOut>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
-  if (M <= 16) return by_shape<2, SWIGLU, TOut>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
-  return by_shape<4, SWIGLU, TOut>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
+  return by_shape<2, SWIGLU, TOut>(X, W, bias, out, M, n_out, K, ldx, ldo, k_splits, partial_stride, stream);
 }
 }  // namespace
 
 // out[M, n_out] = X[M, K] * W^T (+ bias), W [n_out, K]; or, with swiglu != 0, W [2 * n_out, K] = [gate; up]
-// and out = silu(X gate^T) * (X up^T).  M <= 32; K a multiple of 8; X rows and W 16-byte aligned.
+// and out = silu(X gate^T) * (X up^T).  M <= 16; K a multiple of 8; X rows and W 16-byte aligned.
 // k_splits > 1 (float32 output, no swiglu): out is [k_splits, M, n_out], slice s holding the sum over
 // the s-th part of K; the caller adds the slices (the fused residual-add + norm kernel does).
 IFX_API int ifx_gemv_bf16(const void* X, const void* W, const float* bias, void* out, int out_dtype, int M,
                           int n_out, int K, long long ldx, long long ldo, int swiglu, int k_splits,
                           cudaStream_t stream) {
   if (M <= 0 || n_out <= 0) return 0;
-  if (M > 32 || K <= 0 || (K & 7)) return IFX_ERR_UNSUPPORTED;
+  if (M > 16 || K <= 0 || (K & 7)) return IFX_ERR_UNSUPPORTED;
   if (((uintptr_t)X & 15) || ((uintptr_t)W & 15) || (ldx & 7)) return IFX_ERR_ALIGNMENT;
   if (swiglu && bias) return IFX_ERR_UNSUPPORTED;
   if (k_splits < 1 || k_splits > 64) return IFX_ERR_UNSUPPORTED;

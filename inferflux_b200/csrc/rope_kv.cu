@@ -92,6 +92,80 @@ __global__ void qkv_rope_kv_write_kernel(T* __restrict__ qkv, const float* __res
   }
 }
 
+// Vector path (bfloat16, whole head rotated, head_dim a multiple of 16): a work item is 8
+// consecutive pairs (i .. i+7, i+half .. i+half+7) of one head: two 16-byte loads, two 16-byte stores.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { const float2 t = __bfloat1622float2(h[k]); f[2 * k] = t.x; f[2 * k + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+  return v;
+}
+
+__global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
+                                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                const int* __restrict__ slot_map, PagedKV kv,
+                                                int n_heads, int n_kv, int head_dim) {
+  const int t = blockIdx.x;
+  const int half = head_dim / 2, hv = half / 8;               // 8-wide groups per half head
+  const int width = (n_heads + 2 * n_kv) * head_dim;
+  bf16* row = qkv + (size_t)t * width;
+  const float* ct = cos_t + (size_t)t * half;
+  const float* st = sin_t + (size_t)t * half;
+  const int slot = n_kv ? slot_map[t] : -1;
+  const long long page = slot >= 0 ? (slot >> kv.page_shift) : 0;
+  const int off = slot & (kv.page_size - 1);
+  bf16* kc = (bf16*)kv.k + page * kv.page_stride + (size_t)off * head_dim;
+  bf16* vc = (bf16*)kv.v + page * kv.page_stride + (size_t)off * head_dim;
+  const int rot_heads = n_heads + n_kv;
+  for (int w = threadIdx.x; w < rot_heads * hv; w += blockDim.x) {
+    const int h = w / hv, i = (w - h * hv) * 8;
+    const int base = h * head_dim;
+    float x0[8], x1[8], c[8], s[8];
+    unpack8(*reinterpret_cast<const uint4*>(row + base + i), x0);
+    unpack8(*reinterpret_cast<const uint4*>(row + base + half + i), x1);
+    *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(ct + i);
+    *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(ct + i + 4);
+    *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(st + i);
+    *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(st + i + 4);
+    float y0[8], y1[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float a = x0[k], b = x1[k];
+      if (bias) { a += bias[base + i + k]; b += bias[base + half + i + k]; }
+      y0[k] = a * c[k] - b * s[k];
+      y1[k] = a * s[k] + b * c[k];
+    }
+    const uint4 p0 = pack8(y0), p1 = pack8(y1);
+    if (h < n_heads) {
+      *reinterpret_cast<uint4*>(row + base + i) = p0;
+      *reinterpret_cast<uint4*>(row + base + half + i) = p1;
+    } else if (slot >= 0) {
+      bf16* dst = kc + (size_t)(h - n_heads) * kv.head_stride;
+      *reinterpret_cast<uint4*>(dst + i) = p0;
+      *reinterpret_cast<uint4*>(dst + half + i) = p1;
+    }
+  }
+  if (slot >= 0) {
+    const int vbase = (n_heads + n_kv) * head_dim;
+    for (int w = threadIdx.x; w < n_kv * head_dim / 8; w += blockDim.x) {
+      const int e0 = w * 8, h = e0 / head_dim, d = e0 - h * head_dim;
+      float x[8];
+      unpack8(*reinterpret_cast<const uint4*>(row + vbase + e0), x);
+      if (bias) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[k] += bias[vbase + e0 + k];
+      }
+      *reinterpret_cast<uint4*>(vc + (size_t)h * kv.head_stride + d) = pack8(x);
+    }
+  }
+}
+
 IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const float* cos_t, const float* sin_t,
                                   int rot_dim, const int* slot_map, void* k_layer, void* v_layer,
                                   long long page_stride, int page_size, int n_tokens, int n_heads, int n_kv,
@@ -107,6 +181,16 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
   const int work = (n_heads + 2 * n_kv) * head_dim / 2;
   int threads = 64;
   while (threads < 512 && threads * 4 < work) threads <<= 1;
+  const bool aligned = (((uintptr_t)qkv | (uintptr_t)k_layer | (uintptr_t)v_layer | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0
+                       && (page_stride & 7) == 0;
+  if (dtype == IFX_BF16 && rot_dim == head_dim && head_dim % 16 == 0 && aligned) {
+    const int work8 = (n_heads + n_kv) * head_dim / 16;
+    int th = 32;
+    while (th < 256 && th < work8) th <<= 1;
+    qkv_rope_kv_write_bf16x8_kernel<<<n_tokens, th, 0, stream>>>((bf16*)qkv, bias, cos_t, sin_t, slot_map, kv,
+                                                                 n_heads, n_kv, head_dim);
+    return IFX_LAUNCH_CHECK();
+  }
   if (dtype == IFX_F32)
     qkv_rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, bias, cos_t, sin_t, rot_dim / 2, slot_map, kv, n_heads, n_kv, head_dim);
   else if (dtype == IFX_BF16)

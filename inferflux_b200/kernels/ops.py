@@ -219,12 +219,12 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
     return out
 
 
-GEMV_MAX_ROWS = 32
+GEMV_MAX_ROWS = 16
 
 
 def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
               swiglu: bool = False, k_splits: int = 1) -> torch.Tensor:
-    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) for M <= 32, bfloat16 operands,
+    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) for M <= 16, bfloat16 operands,
     float32 accumulation, bfloat16 or float32 result.  With ``swiglu`` w is
     [2N, K] = [gate; up] and out = silu(x gate^T) * (x up^T).  With
     ``k_splits`` > 1 out is float32 [k_splits, M, N]: slice s is the sum over the
@@ -248,6 +248,27 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
                                 x.stride(0) if m > 1 else k, ldo, 1 if swiglu else 0, int(k_splits),
                                 _stream()), "gemv_bf16")
     return out
+
+
+_error_flags = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """The device word that kernels with bounded waits set when a wait runs out."""
+    key = torch.device(device).index or 0
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+def check_device_errors(device) -> None:
+    """Raise if a kernel reported that one of its bounded waits ran out (this
+    reads one word back from the device, so it synchronises)."""
+    key = torch.device(device).index or 0
+    flag = _error_flags.get(key)
+    if flag is not None and int(flag.item()) != 0:
+        flag.zero_()
+        raise KernelError("a kernel gave up waiting on a barrier (bounded wait ran out); its output is invalid")
 
 
 def matmul_library(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:

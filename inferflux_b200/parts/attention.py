@@ -146,7 +146,7 @@ def decode_splits(n_decode: int, n_heads: int, n_kv: int, max_keys: int, target_
     """Into how many parts the decode kernel cuts the keys: enough blocks for
     two per SM (148 SMs), each part at least 256 keys (four 64-key tiles)."""
     ratio = n_heads // n_kv
-    base = max(1, n_decode * n_kv * ((ratio + 15) // 16))
+    base = max(1, n_decode * n_kv * ((ratio + 7) // 8))
     by_blocks = (target_blocks + base - 1) // base
     by_keys = max(1, max_keys // 256)
     return max(1, min(by_blocks, by_keys, 64))

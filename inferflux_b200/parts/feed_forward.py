@@ -18,7 +18,7 @@ from ..config.registry import register_part
 from ..kernels import ops
 from ..weights.loader import MATRIX, WeightSpec
 from .base import Part
-from .linear import Linear
+from .linear import GEMV_ROWS, Linear
 
 
 class SwiGLU(Part):
@@ -54,7 +54,7 @@ class SwiGLU(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         w = self.gate_up.weight
         act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
-        if w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and x.shape[0] <= ops.GEMV_MAX_ROWS \
+        if w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and x.shape[0] <= GEMV_ROWS \
                 and self.hidden % 8 == 0:
             ops.gemv_bf16(x, w, None, act, swiglu=True)       # product and activation in one kernel
         else:

@@ -18,6 +18,9 @@ from ..kernels import ops
 from .base import PartialSums
 
 
+GEMV_ROWS = 8     # up to this many rows go to the weight-streaming kernel (it matches the library there)
+
+
 class Linear:
     def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
         if weight.dim() != 2:
@@ -45,7 +48,7 @@ class Linear:
             return y
         if x.dtype != torch.bfloat16:
             raise ops.KernelError(f"Linear: bfloat16 weights need bfloat16 activations, got {x.dtype}")
-        if m <= ops.GEMV_MAX_ROWS and self.in_features % 8 == 0:
+        if m <= GEMV_ROWS and self.in_features % 8 == 0:
             # a few rows: bound by reading the weights once -> the weight-streaming kernel
             splits = self._k_splits() if allow_partials else 1
             if splits > 1:
@@ -59,10 +62,19 @@ class Linear:
             y += self.bias
         return y if y.dtype == out_dtype else y.to(out_dtype)
 
-    def _k_splits(self, target_blocks: int = 592, min_chunks: int = 32, max_splits: int = 4) -> int:
-        """Into how many parts the weight-streaming kernel cuts K: enough blocks
-        (one per 16 rows and part) for four per SM, each part at least 32
-        chunks of 32."""
+    def _k_splits(self, slots: int = 592, min_chunks: int = 16, max_splits: int = 8) -> int:
+        """Into how many parts the weight-streaming kernel cuts K.  A block
+        takes 16 rows of one part and 4 blocks fit an SM (592 on 148 SMs); the
+        number of parts is the one whose last wave of blocks is fullest, the
+        smallest such number within 3 percent."""
         tiles = (self.out_features + 15) // 16
         chunks = (self.in_features + 31) // 32
-        return max(1, min(max_splits, (target_blocks + tiles - 1) // tiles, chunks // min_chunks))
+        best, best_use = 1, 0.0
+        for s in range(1, max_splits + 1):
+            if s > 1 and chunks // s < min_chunks:
+                break
+            blocks = tiles * s
+            use = blocks / (-(-blocks // slots) * slots)
+            if use > best_use * 1.03:
+                best, best_use = s, use
+        return best
