@@ -522,7 +522,7 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
                    int window, cudaStream_t stream) {
   const size_t smem = (size_t)4 * 64 * HD * sizeof(bf16);
   auto kern = attn_prefill_bf16_kernel<HD>;
-  if (smem > 48 * 1024) {
+  {  // dynamic plus static shared memory may pass 48 KB
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
@@ -539,7 +539,7 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
   const size_t red_bytes = (size_t)4 * 8 * HD * sizeof(float) + 4 * 8 * 2 * sizeof(float);
   const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
   auto kern = attn_decode_bf16_kernel<HD>;
-  if (smem > 48 * 1024) {
+  {  // dynamic plus static shared memory may pass 48 KB
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
