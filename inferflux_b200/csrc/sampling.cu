@@ -220,3 +220,51 @@ IFX_API int ifx_sample(const float* logits, long long row_stride, float* weights
                                            counters, out, vocab);
   return IFX_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------- no allocation
+// ifx_sample_static: ifx_sample for callers that cannot allocate (see sample_static.h).
+// The scratch that ifx_sample takes from its caller lives here instead.
+#include "sample_static.h"
+
+namespace {
+// exp(logit / T - max) of the rows of the call in progress; shared by all calls on the device
+static __device__ __align__(256) float g_sample_static_weights[(size_t)IFX_SAMPLE_STATIC_MAX_ROWS *
+                                                               IFX_SAMPLE_STATIC_MAX_VOCAB];
+constexpr int kMaxDevices = 64;
+float* g_sample_static_ptr[kMaxDevices] = {};   // device address of the array, per device, once looked up
+}  // namespace
+
+extern "C" const char* ifx_sample_static_message(int code) {
+  switch (code) {
+    case 0: return "success";
+    case IFX_ERR_STATIC_TOO_LARGE:
+      return "ifx_sample_static: n_rows or vocab is beyond the built-in scratch "
+             "(at most 8 rows of at most 262144 logits); use ifx_sample with a buffer of your own";
+    case IFX_ERR_UNSUPPORTED: return "ifx_sample_static: unsupported argument (vocab must be below 2^24, device index below 64)";
+    default: return cudaGetErrorString((cudaError_t)code);
+  }
+}
+
+extern "C" int ifx_sample_static(const float* logits, long long row_stride, const float* temperature,
+                                 const int* top_k, const float* top_p, const float* min_p,
+                                 const unsigned long long* seeds, const unsigned long long* counters, int* out,
+                                 int n_rows, int vocab, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (n_rows > IFX_SAMPLE_STATIC_MAX_ROWS || vocab > IFX_SAMPLE_STATIC_MAX_VOCAB) return IFX_ERR_STATIC_TOO_LARGE;
+  if (vocab < 1) return IFX_ERR_UNSUPPORTED;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return IFX_ERR_UNSUPPORTED;
+  float* scratch = g_sample_static_ptr[dev];
+  if (!scratch) {
+    // In host code the array's name is only a handle; the kernel needs its address on this device.
+    e = cudaGetSymbolAddress((void**)&scratch, g_sample_static_weights);
+    if (e != cudaSuccess) return (int)e;
+    g_sample_static_ptr[dev] = scratch;
+  }
+  // rows are packed [n_rows, vocab]; every element a row reads is written first, so nothing is cleared
+  sample_kernel<<<n_rows, ST, 0, stream>>>(logits, row_stride, scratch, temperature, top_k, top_p, min_p, seeds,
+                                           counters, out, vocab);
+  return IFX_LAUNCH_CHECK();
+}
