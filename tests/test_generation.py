@@ -1,0 +1,159 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy continuations, long decoding token by token (captured decode steps),
+the first tokens of a sequence, temperature sampling that does not depend on
+the batch, preemption when pages run out, penalties."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+from helpers import TINY, TOL, make_model_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders():
+    out = {}
+    for name in ("A", "B", "D"):
+        folder = make_model_folder(TINY[name], seed=40 + ord(name), sharpen=4.0)
+        out[name] = (folder, *plain.load_folder(folder))
+    return out
+
+
+def _engine(folder, dtype, **kw):
+    from inferflux_b200 import Engine
+    opts = dict(kv_cache_tokens=1024, max_seqs=8)
+    opts.update(kw)
+    return Engine.from_pretrained(folder, dtype=dtype, **opts)
+
+
+def _check_greedy(cfg, w, prompt, tokens, dtype):
+    """Every generated token is the plain implementation's argmax given the
+    tokens before it (bfloat16: within the tolerance of the largest logit)."""
+    seq = list(prompt)
+    for t in tokens:
+        logits = plain.forward(cfg, w, seq)[-1]
+        if dtype == "float32":
+            assert t == int(torch.argmax(logits)), (len(seq), t)
+        else:
+            assert float(logits.max() - logits[t]) <= 2 * TOL[dtype] * float(logits.abs().max()), (len(seq), t)
+        seq.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_greedy_generation_through_the_entry_point(folders, name, dtype):
+    from inferflux_b200 import SamplingParams
+    folder, cfg, w = folders[name]
+    lengths = [5, 17, 33] if name == "A" else [1, 9, 40, 70]
+    prompts = [random_tokens(cfg["vocab_size"], n, 60 + n) for n in lengths]
+    eng = _engine(folder, dtype, chunked_prefill_tokens=16, max_batch_tokens=48)
+    res = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    assert [r.finish_reason for r in res] == ["length"] * len(prompts)
+    for p, r in zip(prompts, res):
+        assert len(r.tokens) == 16 and r.prompt_tokens == len(p)
+        _check_greedy(cfg, w, p, r.tokens, dtype)
+    assert eng.stats["pages_free"] == eng.stats["pages_total"]
+    if dtype == "bfloat16":
+        assert eng.runner.graph_replays > 0          # decode-only steps ran as captured graphs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_long_decoding_token_by_token(folders, name, dtype):
+    """Two prompt tokens, then 200 tokens one at a time (three requests side by
+    side, crossing a dozen page borders and, in D, the window); the logits of
+    every step are compared."""
+    from inferflux_b200 import StepEntry
+    folder, cfg, w = folders[name]
+    n = 200
+    seqs = [random_tokens(cfg["vocab_size"], n, 70 + i) for i in range(3)]
+    refs = [plain.forward(cfg, w, s).numpy() for s in seqs]
+    eng = _engine(folder, dtype)
+    got = [[] for _ in seqs]
+    first = eng.run_step([StepEntry(f"r{i}", s[:2], [0, 1]) for i, s in enumerate(seqs)]).cpu().numpy()
+    for i in range(3):
+        got[i] += [first[2 * i], first[2 * i + 1]]
+    for p in range(2, n):
+        logits = eng.run_step([StepEntry(f"r{i}", [s[p]], [0]) for i, s in enumerate(seqs)]).cpu().numpy()
+        for i in range(3):
+            got[i].append(logits[i])
+    for i in range(3):
+        err = np.abs(np.stack(got[i]).astype(np.float64) - refs[i]).max() / np.abs(refs[i]).max()
+        assert err <= TOL[dtype], f"request {i}: {err:.3e}"
+    assert eng.runner.graph_replays >= n - 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(folders, dtype):
+    """Position 0 alone, positions 0-1, and a one-token prompt beside longer ones."""
+    from inferflux_b200 import StepEntry
+    folder, cfg, w = folders["B"]
+    a, b, c = (random_tokens(cfg["vocab_size"], n, 80 + n) for n in (1, 2, 19))
+    eng = _engine(folder, dtype)
+    logits = eng.run_step([StepEntry("a", a, [0]), StepEntry("b", b, [0, 1]), StepEntry("c", c, [0, 18])]).cpu().double()
+    want = torch.cat([plain.forward(cfg, w, a), plain.forward(cfg, w, b), plain.forward(cfg, w, c)[[0, 18]]])
+    assert float((logits - want).abs().max() / want.abs().max()) <= TOL[dtype]
+    # the first token's logits do not depend on what follows it
+    assert float((logits[1] - plain.forward(cfg, w, b[:1])[0]).abs().max() / want.abs().max()) <= TOL[dtype]
+
+
+def test_sampling_does_not_depend_on_the_batch(folders):
+    from inferflux_b200 import SamplingParams
+    folder, cfg, w = folders["A"]
+    prompts = [random_tokens(cfg["vocab_size"], n, 90 + n) for n in (4, 11, 26)]
+    params = [SamplingParams(temperature=0.8, seed=7 + i, max_tokens=24, ignore_eos=True, top_p=0.95) for i in range(3)]
+    together = _engine(folder, "float32").generate(prompts, params)
+    for i in range(3):
+        alone = _engine(folder, "float32", chunked_prefill_tokens=5).generate([prompts[i]], [params[i]])
+        assert alone[0].tokens == together[i].tokens
+    # another seed gives another continuation; the same seed the same one
+    other = _engine(folder, "float32").generate([prompts[0]], SamplingParams(temperature=0.8, seed=1234, max_tokens=24,
+                                                                            ignore_eos=True, top_p=0.95))
+    assert other[0].tokens != together[0].tokens
+    # every sampled token lies in the plain implementation's nucleus
+    seq = list(prompts[0])
+    for t in together[0].tokens:
+        kept = plain.kept_probabilities(plain.forward(cfg, w, seq)[-1], 0.8, 0, 0.95, 0.0)
+        assert kept[t] > 0
+        seq.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_when_pages_run_out_keeps_the_output(folders, dtype):
+    from inferflux_b200 import SamplingParams
+    folder, cfg, w = folders["A"]
+    prompts = [random_tokens(cfg["vocab_size"], n, 100 + n) for n in (30, 28, 9, 33)]
+    sp = SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)
+    roomy = _engine(folder, dtype).generate(prompts, sp)
+    tight_engine = _engine(folder, dtype, kv_cache_tokens=112, max_seqs=4, chunked_prefill_tokens=16, max_batch_tokens=40)
+    tight = tight_engine.generate(prompts, sp)
+    assert tight_engine.stats["preemptions"] > 0 and sum(r.preemptions for r in tight) > 0
+    for p, a, b in zip(prompts, roomy, tight):
+        assert b.finish_reason == "length" and len(b.tokens) == 30
+        if dtype == "float32":
+            assert a.tokens == b.tokens
+        _check_greedy(cfg, w, p, b.tokens, dtype)
+    assert tight_engine.stats["pages_free"] == tight_engine.stats["pages_total"]
+    assert sum(tight_engine.stats["page_reuses"]) > 0
+
+
+def test_penalties_and_stop(folders):
+    from inferflux_b200 import SamplingParams
+    folder, cfg, w = folders["A"]
+    prompt = random_tokens(cfg["vocab_size"], 12, 111)
+    plain_logits = plain.forward(cfg, w, prompt)[-1]
+    first = int(torch.argmax(plain_logits))
+    # a presence penalty on a prompt made of the would-be winner pushes it out
+    pen = SamplingParams(temperature=0.0, max_tokens=1, presence_penalty=100.0, repetition_penalty=1.3, ignore_eos=True)
+    prompt2 = prompt[:-1] + [first]
+    want = plain.apply_penalties(plain.forward(cfg, w, prompt2)[-1], prompt2[-pen.penalty_last_n:], 1.3, 0.0, 100.0)
+    got = _engine(folder, "float32").generate([prompt2], pen)[0].tokens
+    assert got == [int(torch.argmax(want))] and got[0] not in prompt2
+    # stop tokens end a request early
+    stop = SamplingParams(temperature=0.0, max_tokens=20, stop_token_ids=[first], ignore_eos=True)
+    r = _engine(folder, "float32").generate([prompt], stop)[0]
+    assert r.tokens == [first] and r.finish_reason == "stop"

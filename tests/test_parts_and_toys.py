@@ -1,0 +1,290 @@
+"""Each part alone against the plain implementation, and the generality of
+the layer description: a toy mixer with per-request state of its own that is
+defined here, registered, built into a model and stepped without any change to
+the package; a layer that runs twice; a layer that reads another run's cache."""
+from __future__ import annotations
+
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+
+
+def _rel(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def _rand(shape, seed, scale=1.0):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def _load(part, tensors, dtype):
+    """Give a part its tensors the way the loader would: matrices in the engine's type, vectors float32."""
+    part.load({k: (v.to(dtype) if v.dim() > 1 else v.float()).to(DEV) for k, v in tensors.items()})
+
+
+# ------------------------------------------------------------------ parts alone
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_alone(dtype):
+    from inferflux_b200.parts import RMSNorm
+    h = 100
+    part = RMSNorm(dict(name="n", hidden=h, eps=3e-6), "l", dtype, DEV)
+    assert [w.name for w in RMSNorm.weight_specs(part.params, "l")] == ["l.n.weight"]
+    w = 1 + _rand((h,), 1, 0.1)
+    _load(part, {"l.n.weight": w}, dtype)
+    res, delta = _rand((9, h), 2).to(DEV), _rand((9, h), 3).to(dtype).to(DEV)
+    want_res = res.cpu().double() + delta.cpu().double()
+    out = part.forward(res, delta)
+    assert out.dtype == dtype
+    assert _rel(res, want_res) < 1e-6
+    assert _rel(out, plain.rms_norm(want_res, w.double(), 3e-6)) < TOL[dtype]
+
+
+def test_rotary_alone():
+    from inferflux_b200.parts import RotaryHalf
+    part = RotaryHalf(dict(rotary_dim=48, theta=50000.0), "", torch.float32, DEV)
+    pos = torch.tensor([0, 1, 17, 300, 4095], dtype=torch.int32, device=DEV)
+    cos, sin = part.prepare(SimpleNamespace(n_tokens=5, positions=pos, device=DEV))
+    wc, ws = plain.rope_angles(pos.cpu(), 48, 50000.0, torch.float64)
+    assert cos.shape == (5, 24) and _rel(cos, wc) < 1e-6 and _rel(sin, ws) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [3, 40])           # the weight-streaming kernel and the library product
+def test_swiglu_alone(dtype, rows):
+    from inferflux_b200.parts import SwiGLU
+    h, inter = 96, 136
+    part = SwiGLU(dict(name="mlp", hidden=h, intermediate=inter), "l", dtype, DEV)
+    w = {"l.mlp.gate_proj.weight": _rand((inter, h), 4, 0.2), "l.mlp.up_proj.weight": _rand((inter, h), 5, 0.2),
+         "l.mlp.down_proj.weight": _rand((h, inter), 6, 0.2)}
+    w = {k: v.to(dtype).float() for k, v in w.items()}          # what the engine will really hold
+    _load(part, dict(w), dtype)
+    x = _rand((rows, h), 7).to(dtype)
+    out = part.forward(x.to(DEV), None)
+    from inferflux_b200.parts.base import PartialSums
+    if isinstance(out, PartialSums):
+        out = out.tensor.sum(0)
+    want = plain.mlp_block(x.double(), {k: v.double() for k, v in w.items()}, "l.mlp")
+    assert _rel(out, want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_alone(dtype):
+    from inferflux_b200.parts import LinearHead, TokenEmbedding
+    v, h = 77, 40
+    table = _rand((v, h), 8).to(dtype).float()
+    emb = TokenEmbedding(dict(name="emb", vocab=v, hidden=h), "", dtype, DEV)
+    _load(emb, {"emb.weight": table}, dtype)
+    ids = torch.tensor([0, 76, 5, 5], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids).cpu(), table[ids.cpu().long()])
+    head = LinearHead(dict(name="head", vocab=v, hidden=h, tied_to="emb.weight"), "", dtype, DEV)
+    assert LinearHead.weight_specs(head.params, "")[0].kind == "ignored"
+    head.load({"emb.weight": table.to(dtype).to(DEV)})
+    x = _rand((6, h), 9).to(dtype)
+    logits = head.forward(x.to(DEV))
+    assert logits.dtype == torch.float32 and _rel(logits, x.double() @ table.double().T) < TOL[dtype]
+
+
+def _one_layer_spec(hidden, nh, nkv, hd, window=None, extra_layers=(), schedule=None):
+    from inferflux_b200.config.spec import LayerSpec, ModelSpec, PartSpec, Run
+    norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
+    attn = LayerSpec("layers.0", "prenorm",
+                     PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                                                    qkv_bias=True, o_bias=False, window=window)),
+                     norm("n1"), PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=2 * hidden)), norm("n2"),
+                     position="rope")
+    layers = [attn, *extra_layers]
+    return ModelSpec("Toy", hidden, 50, 512, PartSpec("token_embedding", dict(name="emb", vocab=50, hidden=hidden)),
+                     norm("final"), PartSpec("linear_head", dict(name="head", vocab=50, hidden=hidden, tied_to=None)),
+                     {"rope": PartSpec("rotary_half", dict(rotary_dim=hd, theta=10000.0))}, layers,
+                     schedule or [Run(i) for i in range(len(layers))])
+
+
+def _build(spec, dtype, seed, tokens=256, sharpen=4.0):
+    from inferflux_b200.config import EngineConfig
+    from inferflux_b200.engine import Model, StepRunner
+    from inferflux_b200.weights.random_init import random_tensors
+    model = Model(spec, dtype, DEV)
+    tensors = random_tensors(model.weight_specs(), seed, torch.bfloat16, torch.float32, "cpu")
+    for k in tensors:
+        if k.endswith(("q_proj.weight", "k_proj.weight")):
+            tensors[k] = (tensors[k].float() * sharpen).to(tensors[k].dtype)
+    plain_w = {k: v.double() for k, v in tensors.items()}
+    model.load({k: (v.to(dtype) if v.dim() > 1 else v.float()).to(DEV) for k, v in tensors.items()})
+    runner = StepRunner(model, EngineConfig(dtype="float32" if dtype == torch.float32 else "bfloat16",
+                                            kv_cache_tokens=tokens, max_seqs=4, cuda_graphs=False))
+    return model, runner, plain_w
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, None), (6, 2, 64, 20)])
+def test_attention_mixer_alone(dtype, nh, nkv, hd, window):
+    """Only the mixer is called: normed input in, attention output out, first for a
+    portion of 21 tokens, then for 12 more that attend over the cache."""
+    from inferflux_b200.engine import StepEntry
+    from inferflux_b200.parts.base import PartialSums
+    hidden = 72
+    model, runner, w = _build(_one_layer_spec(hidden, nh, nkv, hd, window), dtype, 11)
+    mixer = model.blocks[0].mixer
+    x = _rand((33, hidden), 12).to(dtype)
+    want = plain.attention_block(x.double(), {k.replace("layers.0.attn", "a"): v for k, v in w.items()}, "a",
+                                 torch.arange(33), nh, nkv, hd, 10000.0, window)
+    outs = []
+    for lo, hi in ((0, 21), (21, 33)):
+        ctx = runner.build_context([StepEntry("r", [1] * (hi - lo), [])])
+        ctx.position_tables["rope"] = model.positions["rope"].prepare(ctx)
+        out = mixer.forward(x[lo:hi].to(DEV), ctx, model.runs[0], ctx.position_tables["rope"])
+        outs.append(out.tensor.sum(0) if isinstance(out, PartialSums) else out.float())
+        runner.kv.advance("r", hi - lo)
+    assert _rel(torch.cat(outs), want) < TOL[dtype]
+
+
+# ------------------------------------------------------- a toy mixer with state
+def _register_running_mean():
+    """out[t] = W * mean(x[0..t]): a mixer whose only memory is a running sum
+    per request, kept in the request's state slot.  Defined in this test."""
+    from inferflux_b200.config import register_part
+    from inferflux_b200.parts.base import Part, StateNeed
+    from inferflux_b200.weights.loader import MATRIX, WeightSpec
+
+    class RunningMean(Part):
+        family = "mixer"
+
+        @classmethod
+        def weight_specs(cls, params, prefix):
+            h = int(params["hidden"])
+            return [WeightSpec(cls.full_name(prefix, params, "mix.weight"), (h, h), MATRIX)]
+
+        @classmethod
+        def state_needs(cls, params):
+            return [StateNeed("sum", (int(params["hidden"]),), torch.float32)]
+
+        def load(self, tensors):
+            self.w = tensors[self.full_name(self.prefix, self.params, "mix.weight")].float()
+
+        def forward(self, x, ctx, run, position):
+            out = torch.empty_like(x)
+            state = run.states["sum"]
+            for e, slot, start in zip(ctx.entries, ctx.slots, ctx.ctx_starts):
+                q0 = ctx.entries.index(e)
+                lo = sum(len(p.tokens) for p in ctx.entries[:q0])
+                n = len(e.tokens)
+                sums = state[slot] + torch.cumsum(x[lo:lo + n].float(), 0)
+                counts = torch.arange(start + 1, start + n + 1, device=x.device, dtype=torch.float32)[:, None]
+                out[lo:lo + n] = ((sums / counts) @ self.w.T).to(x.dtype)
+                state[slot] = sums[-1]
+            return out
+
+    register_part("mixer", "running_mean", RunningMean)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
+    from inferflux_b200.config.spec import LayerSpec, PartSpec
+    from inferflux_b200.engine import StepEntry
+    _register_running_mean()
+    hidden = 48
+    norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
+    toy = LayerSpec("layers.1", "prenorm", PartSpec("running_mean", dict(name="rm", hidden=hidden)), norm("n1"),
+                    PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=80)), norm("n2"), position=None)
+    spec = _one_layer_spec(hidden, 3, 1, 16, extra_layers=[toy])
+    model, runner, w = _build(spec, dtype, 21)
+    assert model.state_needs[1][0].name == "sum" and model.kv_needs[0].n_kv_heads == 1
+    assert runner.state_storage.of_run(1)["sum"].shape == (4, hidden)
+
+    def plain_forward(tokens):
+        x = plain.embed(w["emb.weight"], tokens)
+        h = plain.rms_norm(x, w["layers.0.n1.weight"], 1e-6)
+        x = x + plain.attention_block(h, {k.replace("layers.0.attn", "a"): v for k, v in w.items()}, "a",
+                                      torch.arange(len(tokens)), 3, 1, 16, 10000.0, None)
+        x = x + plain.mlp_block(plain.rms_norm(x, w["layers.0.n2.weight"], 1e-6), w, "layers.0.mlp")
+        h = plain.rms_norm(x, w["layers.1.n1.weight"], 1e-6)
+        means = torch.cumsum(h, 0) / torch.arange(1, len(tokens) + 1, dtype=torch.float64)[:, None]
+        x = x + means @ w["layers.1.rm.mix.weight"].T
+        x = x + plain.mlp_block(plain.rms_norm(x, w["layers.1.n2.weight"], 1e-6), w, "layers.1.mlp")
+        return plain.rms_norm(x, w["final.weight"], 1e-6) @ w["head.weight"].T
+
+    toks_a = torch.randint(0, 50, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+    toks_b = torch.randint(0, 50, (23,), generator=torch.Generator().manual_seed(2)).tolist()
+    want_a, want_b = plain_forward(toks_a), plain_forward(toks_b)
+    # whole
+    got = runner.step([StepEntry("a", toks_a, list(range(40)))])
+    runner.end("a")
+    assert _rel(got, want_a) < TOL[dtype]
+    # two requests in portions and single tokens, mixed; the slot of "a" is used again (and must start from zero)
+    outs = {"a": [], "b": []}
+    plan = [[("a", 0, 7), ("b", 0, 2)], [("a", 7, 1), ("b", 2, 20)], [("a", 8, 31)], [("a", 39, 1), ("b", 22, 1)]]
+    for step in plan:
+        entries = [StepEntry(r, (toks_a if r == "a" else toks_b)[lo:lo + n], list(range(n))) for r, lo, n in step]
+        logits = runner.step(entries)
+        row = 0
+        for r, lo, n in step:
+            outs[r].append(logits[row:row + n].clone())
+            row += n
+    assert _rel(torch.cat(outs["a"]), want_a) < TOL[dtype]
+    assert _rel(torch.cat(outs["b"]), want_b) < TOL[dtype]
+    runner.end("a"), runner.end("b")
+    runner.kv.check(), runner.slots.check()
+
+
+# ------------------------------------ a layer twice, and a layer reading another run's cache
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layer_runs_twice_and_shared_cache(dtype):
+    from inferflux_b200.config.spec import LayerSpec, PartSpec, Run
+    from inferflux_b200.engine import StepEntry
+    hidden, nh, nkv, hd = 64, 4, 2, 16
+    norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
+    shared = LayerSpec("layers.1", "prenorm",
+                       PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                                                      qkv_bias=False, o_bias=False, window=None, kv_shared=True)),
+                       norm("n1"), PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=96)), norm("n2"),
+                       position="rope")
+    # run 0: layer 0; run 1: layer 1 reading run 0's keys and values; run 2: layer 0 again (a cache of its own)
+    spec = _one_layer_spec(hidden, nh, nkv, hd, extra_layers=[shared], schedule=[Run(0), Run(1, cache_of=0), Run(0)])
+    model, runner, w = _build(spec, dtype, 31)
+    assert model.runs_per_group == [2] and [r.writes_kv for r in model.runs] == [True, False, True]
+    assert "layers.1.attn.k_proj.weight" not in w and "layers.1.attn.q_proj.weight" in w
+
+    def layer0(x, positions):
+        h = plain.rms_norm(x, w["layers.0.n1.weight"], 1e-6)
+        x = x + plain.attention_block(h, {k.replace("layers.0.attn", "a"): v for k, v in w.items()}, "a", positions,
+                                      nh, nkv, hd, 10000.0, None)
+        return x + plain.mlp_block(plain.rms_norm(x, w["layers.0.n2.weight"], 1e-6), w, "layers.0.mlp"), h
+
+    def plain_forward(tokens):
+        t = len(tokens)
+        pos = torch.arange(t)
+        x0 = plain.embed(w["emb.weight"], tokens)
+        x, h0 = layer0(x0, pos)
+        # run 0's keys and values, as they lie in its cache
+        k = (h0 @ w["layers.0.attn.k_proj.weight"].T + w["layers.0.attn.k_proj.bias"]).view(t, nkv, hd)
+        v = (h0 @ w["layers.0.attn.v_proj.weight"].T + w["layers.0.attn.v_proj.bias"]).view(t, nkv, hd)
+        cos, sin = plain.rope_angles(pos, hd, 10000.0, torch.float64)
+        k = plain.apply_rope_half(k, cos, sin)
+        h = plain.rms_norm(x, w["layers.1.n1.weight"], 1e-6)
+        q = plain.apply_rope_half((h @ w["layers.1.attn.q_proj.weight"].T).view(t, nh, hd), cos, sin)
+        a = plain.causal_gqa_attention(q, k, v, 1.0 / math.sqrt(hd))
+        x = x + a.reshape(t, nh * hd) @ w["layers.1.attn.o_proj.weight"].T
+        x = x + plain.mlp_block(plain.rms_norm(x, w["layers.1.n2.weight"], 1e-6), w, "layers.1.mlp")
+        x, _ = layer0(x, pos)
+        return plain.rms_norm(x, w["final.weight"], 1e-6) @ w["head.weight"].T
+
+    toks = torch.randint(0, 50, (45,), generator=torch.Generator().manual_seed(3)).tolist()
+    want = plain_forward(toks)
+    got = runner.step([StepEntry("w", toks, list(range(45)))])
+    runner.end("w")
+    assert _rel(got, want) < TOL[dtype]
+    outs, pos = [], 0
+    for n in (9, 2, 17, 1, 1, 15):
+        outs.append(runner.step([StepEntry("c", toks[pos:pos + n], list(range(n)))]).clone())
+        pos += n
+    assert _rel(torch.cat(outs), want) < TOL[dtype]
