@@ -1,0 +1,173 @@
+"""Time (or just launch, for a profiler) single kernels at a model family's sizes.
+
+    python -m inferflux_b200.cli.kernel_bench list
+    python -m inferflux_b200.cli.kernel_bench time  [--rows 1 8 64] [--context 4096] [--kernels gemv attn_decode ...]
+    python -m inferflux_b200.cli.kernel_bench launch KERNEL [--rows 8] [--context 4096] [--repeat 5]
+
+``time`` captures each kernel 20 times into a CUDA graph and times the replay with CUDA events (so the
+host's launch cost is not in the number); operands rotate between buffers larger than L2.  ``launch`` runs
+one kernel a few times eagerly, which is what ``ncu -k regex:... -s 2 -c 1`` wants.  Sizes default to the
+Qwen2.5-7B layer sizes; ``--sizes hidden,heads,kv_heads,head_dim,intermediate,vocab`` changes them.
+The library product (cuBLAS through torch) is timed beside the weight-streaming kernel for comparison.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+from ..kernels import ops
+from ..parts.attention import decode_splits
+
+DEV = "cuda:0"
+KERNELS = ["gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_lm_head", "attn_decode", "attn_prefill",
+           "add_rmsnorm", "rope_kv", "swiglu", "argmax"]
+
+
+def _timeit(fn, n_rot, reps=20):
+    for i in range(3):
+        fn(i % n_rot)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(reps):
+            fn(i % n_rot)
+    g.replay()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    g.replay()
+    ev[1].record()
+    torch.cuda.synchronize()
+    return ev[0].elapsed_time(ev[1]) / reps * 1e3      # microseconds
+
+
+class Case:
+    """Builds operands for one kernel at the given sizes; ``run(i)`` launches it on buffer set i."""
+
+    def __init__(self, name, sizes, rows, context):
+        h, nh, nkv, hd, inter, vocab = sizes
+        self.name, self.bytes, self.flops, self.extra = name, 0, 0, []
+        bf = dict(device=DEV, dtype=torch.bfloat16)
+        it = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        if name.startswith("gemv_"):
+            n, k, sw = {"qkv": ((nh + 2 * nkv) * hd, h, False), "o": (h, nh * hd, False), "gate_up": (inter, h, True),
+                        "down": (h, inter, False), "lm_head": (vocab, h, False)}[name[5:]]
+            wrows = 2 * n if sw else n
+            self.n_rot = max(2, int(300e6 // (wrows * k * 2)) + 1)
+            ws = [torch.randn(wrows, k, **bf) * 0.02 for _ in range(self.n_rot)]
+            x = torch.randn(rows, k, **bf)
+            self.bytes = wrows * k * 2
+            if rows <= ops.GEMV_MAX_ROWS:
+                out = torch.empty(rows, n, **bf)
+                self.run = lambda i: ops.gemv_bf16(x, ws[i], None, out, swiglu=sw)
+                if not sw and n < 10000:
+                    for s in (2, 3, 4, 5):
+                        outp = torch.empty(s, rows, n, device=DEV, dtype=torch.float32)
+                        self.extra.append((f"k_splits={s}", lambda i, s=s, outp=outp: ops.gemv_bf16(x, ws[i], None, outp, k_splits=s)))
+            else:
+                self.run = None
+            self.extra.append(("library", lambda i: torch.mm(x, ws[i].t())))
+        elif name in ("attn_decode", "attn_prefill"):
+            ps = 16
+            decode = name == "attn_decode"
+            b = rows if decode else 1
+            q_len = 1 if decode else rows
+            ctx = context
+            nblk = (ctx + ps - 1) // ps
+            pages = b * nblk
+            self.n_rot = max(2, int(300e6 // (pages * 2 * nkv * ps * hd * 2)) + 1)
+            pools = [torch.randn(pages, 1, 2, nkv, ps, hd, **bf) for _ in range(self.n_rot)]
+            bt = torch.randperm(pages, device=DEV).int().view(b, nblk).contiguous()
+            n = b * q_len
+            q = torch.randn(n, (nh + 2 * nkv) * hd, **bf)
+            out = torch.empty(n, nh * hd, **bf)
+            qs, ql, cs = it([i * q_len for i in range(b)]), it([q_len] * b), it([ctx - q_len] * b)
+            scale = hd ** -0.5
+            if decode:
+                dec = it(list(range(b)))
+                splits = decode_splits(b, nh, nkv, ctx)
+                po = torch.empty(b * nh * splits * hd, device=DEV)
+                pm = torch.empty(b * nh * splits * 2, device=DEV)
+                self.bytes = b * ctx * nkv * hd * 2 * 2
+                self.note = f"splits={splits}"
+                self.run = lambda i: ops.attn_decode_bf16(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
+                                                          pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, po, pm, nh, nkv,
+                                                          hd, scale, 0, splits)
+            else:
+                tiles = [(0, q0) for q0 in range(0, q_len, 64)]
+                te, tq = it([t[0] for t in tiles]), it([t[1] for t in tiles])
+                # causal: query i sees ctx - q_len + i + 1 keys
+                keys = sum(ctx - q_len + i + 1 for i in range(q_len))
+                self.flops = 2 * 2 * nh * hd * keys
+                self.run = lambda i: ops.attn_prefill_bf16(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
+                                                           pools[i].stride(0), ps, bt, te, tq, len(tiles), qs, ql, cs, nh,
+                                                           nkv, hd, scale, 0)
+        elif name == "add_rmsnorm":
+            res, delta = torch.randn(rows, h, device=DEV), torch.randn(rows, h, **bf)
+            w, o = torch.ones(h, device=DEV), torch.empty(rows, h, **bf)
+            self.n_rot, self.bytes = 1, rows * h * (4 + 4 + 2 + 2)
+            self.run = lambda i: ops.add_rmsnorm(res, delta, w, 1e-6, o)
+        elif name == "swiglu":
+            gu, o = torch.randn(rows, 2 * inter, **bf), torch.empty(rows, inter, **bf)
+            self.n_rot, self.bytes = 1, rows * inter * 6
+            self.run = lambda i: ops.swiglu(gu, o)
+        elif name == "rope_kv":
+            ps = 16
+            width = (nh + 2 * nkv) * hd
+            qkv, bias = torch.randn(rows, width, **bf), torch.randn(width, device=DEV)
+            cos, sin = torch.randn(rows, hd // 2, device=DEV), torch.randn(rows, hd // 2, device=DEV)
+            pool = torch.zeros((rows + ps - 1) // ps + 1, 1, 2, nkv, ps, hd, **bf)
+            slots = torch.arange(rows, dtype=torch.int32, device=DEV)
+            self.n_rot, self.bytes = 1, rows * width * 2 * 2
+            self.run = lambda i: ops.qkv_rope_kv_write(qkv, bias, cos, sin, slots, pool[0, 0, 0], pool[0, 0, 1],
+                                                       pool.stride(0), ps, nh, nkv, hd)
+        elif name == "argmax":
+            lg, oi = torch.randn(rows, vocab, device=DEV), torch.empty(rows, dtype=torch.int32, device=DEV)
+            self.n_rot, self.bytes = 1, rows * vocab * 4
+            self.run = lambda i: ops.argmax(lg, oi)
+        else:
+            raise SystemExit(f"unknown kernel '{name}'; one of {KERNELS}")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="kernel_bench", description=__doc__.split("\n\n")[0])
+    ap.add_argument("mode", choices=["list", "time", "launch"])
+    ap.add_argument("kernel", nargs="?")
+    ap.add_argument("--kernels", nargs="*", default=None)
+    ap.add_argument("--rows", nargs="*", type=int, default=[1, 8, 64])
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--repeat", type=int, default=5)
+    ap.add_argument("--sizes", default="3584,28,4,128,18944,152064",
+                    help="hidden,heads,kv_heads,head_dim,intermediate,vocab")
+    args = ap.parse_args(argv)
+    if args.mode == "list":
+        print("\n".join(KERNELS))
+        return 0
+    sizes = tuple(int(v) for v in args.sizes.split(","))
+    if args.mode == "launch":
+        case = Case(args.kernel, sizes, args.rows[0], args.context)
+        if case.run is None:
+            case.run = case.extra[-1][1]
+        for i in range(args.repeat):
+            case.run(i % case.n_rot)
+        torch.cuda.synchronize()
+        print(f"launched {args.kernel} {args.repeat} times at rows={args.rows[0]} context={args.context}")
+        return 0
+    for rows in args.rows:
+        print(f"--- rows={rows} context={args.context}")
+        for name in args.kernels or KERNELS:
+            case = Case(name, sizes, rows, args.context)
+            runs = ([("", case.run)] if case.run else []) + case.extra
+            for label, fn in runs:
+                t = _timeit(fn, case.n_rot)
+                what = f"{name} {label} {getattr(case, 'note', '')}".strip()
+                rate = f"{case.bytes / t / 1e3:8.0f} GB/s" if case.bytes else f"{case.flops / t / 1e6:8.1f} TFLOP/s"
+                print(f"{what:34s} {t:9.1f} us {rate}")
+            del case
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -28,15 +28,13 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+__device__ __forceinline__ void ldmatrix_x4_at(unsigned (&r)[4], unsigned saddr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+__device__ __forceinline__ void ldmatrix_x4_trans_at(unsigned (&r)[4], unsigned saddr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
 }
 // D(16x8, f32) += A(16x16, bf16, row) * B(16x8, bf16, col)
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -136,10 +134,10 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);              // [2][BK][HD]
   bf16* vs = ks + 2 * BK * HD;                               // [2][BK][HD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
-  // tiles run last to first: within a request the later tiles see more keys, and the
-  // longest blocks should start first
-  const int tile = gridDim.x - 1 - blockIdx.x;
-  const int e = tile_entry[tile], q0 = tile_q0[tile], head = blockIdx.y;
+  // tiles run last to first and heads fastest: within a request the later tiles see more
+  // keys, and the longest blocks (of every head) should start first
+  const int tile = gridDim.y - 1 - blockIdx.y;
+  const int e = tile_entry[tile], q0 = tile_q0[tile], head = blockIdx.x;
   const int rows = min(BQ, m.entry_q_len[e] - q0);
   if (rows <= 0) return;
   const int tok0 = m.entry_q_start[e] + q0;
@@ -188,6 +186,16 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int pa_row = pos0 + wr0 + g, pb_row = pa_row + 8;        // positions of this thread's two rows
   const int warp_last = pos0 + min(wr0 + 15, rows - 1);
 
+  // shared-memory byte offsets of this lane's ldmatrix rows, swizzle included (they do not depend on the tile)
+  const unsigned ks_addr = (unsigned)__cvta_generic_to_shared(ks), vs_addr = (unsigned)__cvta_generic_to_shared(vs);
+  unsigned koff[KS], voff[DT / 2];
+  {
+    const int j = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) koff[k] = (unsigned)((((j >> 1) * 8 + r) * HD + (((k * 2 + (j & 1)) ^ r) << 3)) * 2);
+#pragma unroll
+    for (int dp = 0; dp < DT / 2; ++dp) voff[dp] = (unsigned)((((j & 1) * 8 + r) * HD + (((dp * 2 + (j >> 1)) ^ r) << 3)) * 2);
+  }
   load_kv_tile64<HD>(ks, vs, kbase, vbase, kv, bt, t_begin * BK, kfirst, kend, tid, bt_first);
   cp_async_commit();
   for (int t = t_begin; t <= t_end; ++t) {
@@ -205,78 +213,91 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     const bool active = wr0 < rows && key0 <= warp_last &&
                         (window <= 0 || key0 + BK > pos0 + wr0 - window + 1);
     if (active) {
-      bf16* kt = ks + st * BK * HD;
-      bf16* vt = vs + st * BK * HD;
+      const unsigned kt = ks_addr + (unsigned)(st * BK * HD * 2);
+      const unsigned vt = vs_addr + (unsigned)(st * BK * HD * 2);
       float s[BK / 8][4];
 #pragma unroll
       for (int n = 0; n < BK / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f; }
 #pragma unroll
       for (int k = 0; k < KS; ++k) {
+        unsigned kb[BK / 16][4];                                 // the step's four fragments first, then its MMAs
+#pragma unroll
+        for (int np = 0; np < BK / 16; ++np) ldmatrix_x4_at(kb[np], kt + (unsigned)(np * 16 * HD * 2) + koff[k]);
 #pragma unroll
         for (int np = 0; np < BK / 16; ++np) {                   // two n-tiles (16 keys) per ldmatrix.x4
-          unsigned b[4];
-          const int j = lane >> 3, r = lane & 7;
-          ldmatrix_x4(b, tile_chunk<HD>(kt, np * 16 + (j >> 1) * 8 + r, k * 2 + (j & 1)));
-          mma_bf16(s[np * 2], qa[k], b[0], b[1]);
-          mma_bf16(s[np * 2 + 1], qa[k], b[2], b[3]);
+          mma_bf16(s[np * 2], qa[k], kb[np][0], kb[np][1]);
+          mma_bf16(s[np * 2 + 1], qa[k], kb[np][2], kb[np][3]);
         }
       }
-      // scale (after the dot), mask, row maxima
+      // mask (diagonal, window and edge tiles only), row maxima of the raw scores
       const bool need_mask = key0 + BK - 1 > pos0 + wr0 || window > 0 || key0 < kfirst;
-      float mx[2] = {-INFINITY, -INFINITY};
+      if (need_mask) {
 #pragma unroll
-      for (int n = 0; n < BK / 8; ++n) {
+        for (int n = 0; n < BK / 8; ++n) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float v = s[n][c] * sl2;
-          if (need_mask) {
+          for (int c = 0; c < 4; ++c) {
             const int key = key0 + n * 8 + t4 * 2 + (c & 1);
             const int p = (c & 2) ? pb_row : pa_row;
             const bool vis = key <= p && key < kend && (window <= 0 || key > p - window);
-            if (!vis) v = -INFINITY;
+            if (!vis) s[n][c] = -INFINITY;
           }
-          s[n][c] = v;
-          mx[c >> 1] = fmaxf(mx[c >> 1], v);
         }
       }
-      float alpha[2], mnew[2];
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < BK / 8; ++n) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
+      }
+      // running maxima are kept in raw-score units; exponents are taken of (s - m) * scale * log2(e)
+      float alpha[2], msc[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        mnew[h] = fmaxf(mrow[h], mx[h]);
-        alpha[h] = mnew[h] == -INFINITY ? 1.0f : fast_exp2(mrow[h] - mnew[h]);
-        mrow[h] = mnew[h];
+        const float mnew = fmaxf(mrow[h], mx[h]);
+        msc[h] = mnew == -INFINITY ? 0.0f : mnew * sl2;          // a row that has seen nothing yet
+        alpha[h] = fast_exp2(mrow[h] * sl2 - msc[h]);            // 2^-inf = 0 on the first visible tile
+        mrow[h] = mnew;
       }
       float ls[2] = {0.0f, 0.0f};
 #pragma unroll
       for (int n = 0; n < BK / 8; ++n) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float mm = mnew[c >> 1];
-          const float p = mm == -INFINITY ? 0.0f : fast_exp2(s[n][c] - mm);
-          s[n][c] = p;
-          ls[c >> 1] += p;
-        }
+        s[n][0] = fast_exp2(fmaf(s[n][0], sl2, -msc[0]));
+        s[n][1] = fast_exp2(fmaf(s[n][1], sl2, -msc[0]));
+        s[n][2] = fast_exp2(fmaf(s[n][2], sl2, -msc[1]));
+        s[n][3] = fast_exp2(fmaf(s[n][3], sl2, -msc[1]));
+        ls[0] += s[n][0] + s[n][1];
+        ls[1] += s[n][2] + s[n][3];
       }
       lrow[0] = lrow[0] * alpha[0] + ls[0];
       lrow[1] = lrow[1] * alpha[1] + ls[1];
+      if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {   // a maximum moved: rescale o
 #pragma unroll
-      for (int d = 0; d < DT; ++d) { o[d][0] *= alpha[0]; o[d][1] *= alpha[0]; o[d][2] *= alpha[1]; o[d][3] *= alpha[1]; }
-#pragma unroll
-      for (int kk = 0; kk < BK / 16; ++kk) {                     // 16 keys per k-step
+        for (int d = 0; d < DT; ++d) { o[d][0] *= alpha[0]; o[d][1] *= alpha[0]; o[d][2] *= alpha[1]; o[d][3] *= alpha[1]; }
+      }
+      {
+        // value fragments run two ldmatrix ahead of the MMAs that use them
+        constexpr int NV = (BK / 16) * (DT / 2);                  // (key step, d pair) in order
+        unsigned vb[3][4];
+        ldmatrix_x4_trans_at(vb[0], vt + voff[0]);
+        if (NV > 1) ldmatrix_x4_trans_at(vb[1], vt + (unsigned)((1 / (DT / 2)) * 16 * HD * 2) + voff[1 % (DT / 2)]);
         unsigned pa[4];
-        pa[0] = pack_bf16(s[kk * 2][0], s[kk * 2][1]);
-        pa[1] = pack_bf16(s[kk * 2][2], s[kk * 2][3]);
-        pa[2] = pack_bf16(s[kk * 2 + 1][0], s[kk * 2 + 1][1]);
-        pa[3] = pack_bf16(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
 #pragma unroll
-        for (int dp = 0; dp < DT / 2; ++dp) {                    // two d-tiles (16 dims) per ldmatrix.x4.trans
-          unsigned b[4];
-          const int j = lane >> 3, r = lane & 7;
-          ldmatrix_x4_trans(b, tile_chunk<HD>(vt, kk * 16 + (j & 1) * 8 + r, dp * 2 + (j >> 1)));
-          mma_bf16(o[dp * 2], pa, b[0], b[1]);
-          mma_bf16(o[dp * 2 + 1], pa, b[2], b[3]);
+        for (int i = 0; i < NV; ++i) {
+          const int kk = i / (DT / 2), dp = i % (DT / 2);
+          if (dp == 0) {                                          // 16 keys per k-step
+            pa[0] = pack_bf16(s[kk * 2][0], s[kk * 2][1]);
+            pa[1] = pack_bf16(s[kk * 2][2], s[kk * 2][3]);
+            pa[2] = pack_bf16(s[kk * 2 + 1][0], s[kk * 2 + 1][1]);
+            pa[3] = pack_bf16(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
+          }
+          if (i + 2 < NV) {
+            const int k2 = (i + 2) / (DT / 2), d2 = (i + 2) % (DT / 2);
+            ldmatrix_x4_trans_at(vb[(i + 2) % 3], vt + (unsigned)(k2 * 16 * HD * 2) + voff[d2]);
+          }
+          mma_bf16(o[dp * 2], pa, vb[i % 3][0], vb[i % 3][1]);   // two d-tiles (16 dims) per ldmatrix.x4.trans
+          mma_bf16(o[dp * 2 + 1], pa, vb[i % 3][2], vb[i % 3][3]);
         }
       }
     }
@@ -383,7 +404,16 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       }
       cp_async_commit();
     }
-    const int j = lane >> 3, r = lane & 7;
+    const unsigned ring_addr = (unsigned)__cvta_generic_to_shared(ring);
+    unsigned koff[KS], voff[KS];                                // this lane's ldmatrix rows within a stage, swizzle included
+    {
+      const int j = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        koff[k] = (unsigned)(((warp * TK + (j & 1) * 8 + r) * HD + (((k * 2 + (j >> 1)) ^ r) << 3)) * 2);
+        voff[k] = (unsigned)(((BK + warp * TK + (j >> 1) * 8 + r) * HD + (((k * 2 + (j & 1)) ^ r) << 3)) * 2);
+      }
+    }
     for (int i = 0; i < n_t; ++i) {
       cp_async_wait<DSTAGES - 2>();                             // tile i has landed (for this thread)
       __syncthreads();                                          // ... for all; and tile i - 1 is no longer read
@@ -397,34 +427,34 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       }
       const int key0 = (t_begin + i) * BK + warp * TK;          // this warp's 16 keys of the tile
       if (key0 >= ke || key0 + TK <= kb) continue;              // warp-uniform: nothing of ours in range
-      bf16* kt = ring + (size_t)(i % DSTAGES) * 2 * BK * HD;
-      bf16* vt = kt + BK * HD;
+      const unsigned stage = ring_addr + (unsigned)((i % DSTAGES) * 2 * BK * HD * 2);
       float s[4] = {0.f, 0.f, 0.f, 0.f};                        // (key g | g+8) x (head 2*t4 | 2*t4+1)
+      {
+        unsigned ka[KS][4];                                     // all key fragments first, then the MMAs
 #pragma unroll
-      for (int k = 0; k < KS; ++k) {
-        unsigned a[4];
-        ldmatrix_x4(a, tile_chunk<HD>(kt, warp * TK + (j & 1) * 8 + r, k * 2 + (j >> 1)));
-        mma_bf16(s, a, qb[k][0], qb[k][1]);
+        for (int k = 0; k < KS; ++k) ldmatrix_x4_at(ka[k], stage + koff[k]);
+#pragma unroll
+        for (int k = 0; k < KS; ++k) mma_bf16(s, ka[k], qb[k][0], qb[k][1]);
       }
       const bool in0 = key0 + g >= kb && key0 + g < ke, in1 = key0 + g + 8 >= kb && key0 + g + 8 < ke;
-      s[0] = in0 ? s[0] * sl2 : -INFINITY;
-      s[1] = in0 ? s[1] * sl2 : -INFINITY;
-      s[2] = in1 ? s[2] * sl2 : -INFINITY;
-      s[3] = in1 ? s[3] * sl2 : -INFINITY;
+      if (!in0) { s[0] = -INFINITY; s[1] = -INFINITY; }
+      if (!in1) { s[2] = -INFINITY; s[3] = -INFINITY; }
       float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
-      float alpha[2], mnew[2];
+      // maxima are kept in raw-score units (and, scaled, in the partial results)
+      float alpha[2], msc[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {                             // over the 8 lanes that hold the other keys
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
-        mnew[h] = fmaxf(mcol[h], mx[h]);
-        alpha[h] = mnew[h] == -INFINITY ? 1.0f : fast_exp2(mcol[h] - mnew[h]);
-        mcol[h] = mnew[h];
+        const float mnew = fmaxf(mcol[h], mx[h]);
+        msc[h] = mnew == -INFINITY ? 0.0f : mnew * sl2;
+        alpha[h] = fast_exp2(mcol[h] * sl2 - msc[h]);
+        mcol[h] = mnew;
       }
       float p[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) p[c] = mnew[c & 1] == -INFINITY ? 0.0f : fast_exp2(s[c] - mnew[c & 1]);
+      for (int c = 0; c < 4; ++c) p[c] = fast_exp2(fmaf(s[c], sl2, -msc[c & 1]));
       lcol[0] = lcol[0] * alpha[0] + p[0] + p[2];
       lcol[1] = lcol[1] * alpha[1] + p[1] + p[3];
       if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {   // a maximum moved: rescale o
@@ -434,16 +464,18 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       // P^T as the B operand (k = key, n = head): transpose the two 8x8 blocks
       const unsigned pb0 = movmatrix_trans(pack_bf16(p[0], p[1]));
       const unsigned pb1 = movmatrix_trans(pack_bf16(p[2], p[3]));
+      {
+        unsigned va[KS][4];                                     // V^T as the A operand: rows d, columns keys
 #pragma unroll
-      for (int d = 0; d < KS; ++d) {                             // V^T as the A operand: rows d, columns keys
-        unsigned a[4];
-        ldmatrix_x4_trans(a, tile_chunk<HD>(vt, warp * TK + (j >> 1) * 8 + r, d * 2 + (j & 1)));
-        mma_bf16(o[d], a, pb0, pb1);
+        for (int d = 0; d < KS; ++d) ldmatrix_x4_trans_at(va[d], stage + voff[d]);
+#pragma unroll
+        for (int d = 0; d < KS; ++d) mma_bf16(o[d], va[d], pb0, pb1);
       }
     }
     cp_async_wait<0>();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
+      mcol[h] = mcol[h] == -INFINITY ? -INFINITY : mcol[h] * sl2;   // to exponent units for the merges
       lcol[h] += __shfl_xor_sync(0xffffffffu, lcol[h], 4);
       lcol[h] += __shfl_xor_sync(0xffffffffu, lcol[h], 8);
       lcol[h] += __shfl_xor_sync(0xffffffffu, lcol[h], 16);
@@ -526,7 +558,7 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<dim3(n_tiles, n_heads), 128, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m,
+  kern<<<dim3(n_heads, n_tiles), 128, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m,
                                                       tile_entry, tile_q0, n_heads, n_kv, scale, window);
   return IFX_LAUNCH_CHECK();
 }
@@ -565,7 +597,7 @@ IFX_API int ifx_attn_prefill_bf16(const void* q, long long q_stride, void* out, 
                                   const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
                                   int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (n_kv < 1 || n_heads % n_kv || n_heads > 65535) return IFX_ERR_UNSUPPORTED;
+  if (n_kv < 1 || n_heads % n_kv || n_tiles > 65535) return IFX_ERR_UNSUPPORTED;
   if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
   if ((q_stride & 1) || (out_stride & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3)) return IFX_ERR_ALIGNMENT;
   if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
