@@ -22,6 +22,7 @@ from ..parts.attention import decode_splits
 
 DEV = "cuda:0"
 KERNELS = ["gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_lm_head", "attn_decode", "attn_prefill",
+           "attn_prefill_umma",
            "add_rmsnorm", "rope_kv", "swiglu", "argmax"]
 
 
@@ -69,7 +70,7 @@ class Case:
             else:
                 self.run = None
             self.extra.append(("library", lambda i: torch.mm(x, ws[i].t())))
-        elif name in ("attn_decode", "attn_prefill"):
+        elif name in ("attn_decode", "attn_prefill", "attn_prefill_umma"):
             ps = 16
             decode = name == "attn_decode"
             b = rows if decode else 1
@@ -96,12 +97,14 @@ class Case:
                                                           pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, po, pm, nh, nkv,
                                                           hd, scale, 0, splits)
             else:
-                tiles = [(0, q0) for q0 in range(0, q_len, 64)]
+                umma = name.endswith("umma")
+                tiles = [(0, q0) for q0 in range(0, q_len, 128 if umma else 64)]
                 te, tq = it([t[0] for t in tiles]), it([t[1] for t in tiles])
+                kernel = ops.attn_prefill_umma if umma else ops.attn_prefill_bf16
                 # causal: query i sees ctx - q_len + i + 1 keys
                 keys = sum(ctx - q_len + i + 1 for i in range(q_len))
                 self.flops = 2 * 2 * nh * hd * keys
-                self.run = lambda i: ops.attn_prefill_bf16(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
+                self.run = lambda i: kernel(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
                                                            pools[i].stride(0), ps, bt, te, tq, len(tiles), qs, ql, cs, nh,
                                                            nkv, hd, scale, 0)
         elif name == "add_rmsnorm":

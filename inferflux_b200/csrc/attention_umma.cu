@@ -1,0 +1,350 @@
+// Attention of prompt portions on the fifth-generation tensor cores:
+// tcgen05.mma with accumulators in tensor memory, for head size 128.
+//
+// Same formulas as the other attention kernels (attention_generic.cu): kv head
+// = head / (n_heads / n_kv), s = (q . k) * scale, causal with an optional
+// window, float32 softmax, o = sum p v / sum p.  The reference's kernel for this
+// case is scalar or mma.sync with fp16 operands
+// (runtime/backends/cuda/kernels/flash_attention.cu:52-173,
+// runtime/backends/cuda/kernels/flash_attention_mma.cuh:153-379).
+//
+// One block takes 128 consecutive new tokens of one request and one head.
+//   * Q (128 x 128), and per step a tile of 64 keys and 64 values, lie in shared
+//     memory in the 128-byte-swizzle layouts the tensor core reads (written with
+//     16-byte cp.async from the paged cache; two stages, the next tile loads
+//     while this one is used).
+//   * S = Q K^T is one chain of 8 tcgen05.mma (M 128, N 64, K 16) into 64
+//     columns of tensor memory.  Thread r then owns row r: it reads its 64
+//     scores with tcgen05.ld, masks, keeps the running maximum and sum, and
+//     writes P = exp(s - max) as bfloat16 into shared memory as the next MMA's
+//     A operand.
+//   * O_tile = P V is 4 tcgen05.mma (M 128, N 128, K 16) with V read in its
+//     natural [key][dim] layout (MN-major B operand) into 128 more columns; the
+//     thread folds it into its float32 row: o = o * alpha + O_tile.
+// One thread issues the MMAs; tcgen05.commit arrives on an mbarrier that the
+// others wait on.  Every such wait is bounded: if one runs out the block sets
+// *error_flag, waits for its copies in flight, frees its tensor memory and
+// returns.
+#include "common.cuh"
+
+namespace {
+
+constexpr int UM = 128;          // query rows per block
+constexpr int UN = 64;           // keys per tile
+constexpr int UD = 128;          // head size
+constexpr int WAIT_LIMIT = 1 << 22;
+constexpr int BT_CACHE_U = 512;  // block-table entries a block keeps in shared memory
+constexpr float LOG2E_U = 1.4426950408889634f;
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16_u(unsigned dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ bool mbar_try_wait_u(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_u(unsigned bar, unsigned parity) {
+  for (int i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait_u(bar, parity)) return true;
+  return false;
+}
+// shared-memory matrix descriptor: start address, leading / stride byte offsets (in 16-byte units),
+// descriptor version 1, 128-byte swizzle
+__device__ __forceinline__ unsigned long long umma_desc(unsigned saddr, unsigned lbo_bytes, unsigned sbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((saddr & 0x3FFFF) >> 4);
+  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+// instruction descriptor, kind::f16: D float32, A and B bfloat16, A K-major; B K-major or MN-major
+__host__ __device__ constexpr unsigned umma_idesc(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)b_mn_major << 16) | ((unsigned)(n >> 3) << 17) |
+         ((unsigned)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                         unsigned accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// 32 consecutive columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct UmmaMeta {
+  const int* block_tables; int bt_stride;
+  const int* entry_q_start; const int* entry_q_len; const int* entry_ctx_start;
+};
+
+// Shared memory (1024-byte aligned): Q 32 KB | K 2 x 16 KB | V 2 x 16 KB | P 16 KB
+constexpr int SQ_BYTES = 2 * UM * 128, SKV_BYTES = 2 * UN * 128, SP_BYTES = UM * 128;
+constexpr int SMEM_UMMA = SQ_BYTES + 4 * SKV_BYTES + SP_BYTES + 1024;
+
+// 64 keys and values (absolute key index key0 ..) into one stage: row = key, two panels of 64 dims,
+// 16-byte chunk c of a 128-byte row stored at c ^ (row & 7)
+__device__ __forceinline__ void load_kv64(unsigned sk, unsigned sv, const bf16* kbase, const bf16* vbase,
+                                          const PagedKV& kv, const int* bt, int bt_first, int key0, int lo, int hi,
+                                          int tid) {
+  const int r = tid >> 1, half = tid & 1;
+  const int key = key0 + r;
+  bool ok = key >= lo && key < hi;
+  size_t off = 0;
+  if (ok) {
+    const int page = bt[(key >> kv.page_shift) - bt_first];
+    ok = page >= 0;
+    if (ok) off = (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * UD;
+  }
+  const bf16* ksrc = kbase + off;
+  const bf16* vsrc = vbase + off;
+  const unsigned row = (unsigned)r * 128u;
+  const int sw = r & 7;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = j * 2 + half;                                 // 16-byte chunk of the 256-byte row
+    const unsigned dst = (unsigned)(c >> 3) * (UN * 128) + row + (unsigned)(((c & 7) ^ sw) << 4);
+    cp_async16_u(sk + dst, ksrc + c * 8, ok);
+    cp_async16_u(sv + dst, vsrc + c * 8, ok);
+  }
+}
+
+__global__ void __launch_bounds__(128)
+attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
+                         PagedKV kv, UmmaMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
+                         int n_heads, int n_kv, float scale, int window, int* __restrict__ error_flag) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bar_s, bar_o;
+  __shared__ unsigned tmem_slot;
+  __shared__ int bt_s[BT_CACHE_U];
+  const unsigned sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  const unsigned sq = sbase, sk0 = sq + SQ_BYTES, sv0 = sk0 + 2 * SKV_BYTES, sp = sv0 + 2 * SKV_BYTES;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  // tiles run last to first and heads fastest: the longest blocks (of every head) start first
+  const int tile = gridDim.y - 1 - blockIdx.y;
+  const int e = tile_entry[tile], q0 = tile_q0[tile], head = blockIdx.x;
+  const int rows = min(UM, m.entry_q_len[e] - q0);
+  if (rows <= 0) return;
+  const int tok0 = m.entry_q_start[e] + q0;
+  const int pos0 = m.entry_ctx_start[e] + q0;
+  const int kvh = head / (n_heads / n_kv);
+  const int* bt = m.block_tables + (size_t)e * m.bt_stride;
+  const bf16* kbase = (const bf16*)kv.k + (size_t)kvh * kv.head_stride;
+  const bf16* vbase = (const bf16*)kv.v + (size_t)kvh * kv.head_stride;
+  const int kend = pos0 + rows;                                  // keys [.., kend) may be seen
+  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the first row may see
+  const int t_begin = kfirst / UN, t_end = (kend - 1) / UN, n_t = t_end - t_begin + 1;
+
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s)));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_o)));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 0) {                                               // 256 columns: 64 for S, 128 for O
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;\n" ::"r"(smem_addr(&tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  int bt_first = 0;
+  {
+    const int b0 = kfirst >> kv.page_shift, b1 = (kend - 1) >> kv.page_shift;
+    if (b1 - b0 < BT_CACHE_U) {
+      for (int i = tid; i <= b1 - b0; i += 128) bt_s[i] = bt[b0 + i];
+      bt = bt_s;
+      bt_first = b0;
+    }
+  }
+  // Q: row r (token tok0 + r), two panels of 64 dims; rows beyond the portion are zero
+  for (int idx = tid; idx < UM * 16; idx += 128) {
+    const int r = idx >> 4, c = idx & 15;
+    const bool ok = r < rows;
+    const bf16* src = q + (size_t)(tok0 + (ok ? r : 0)) * q_stride + (size_t)head * UD + c * 8;
+    cp_async16_u(sq + (unsigned)(c >> 3) * (UM * 128) + (unsigned)r * 128u + (unsigned)(((c & 7) ^ (r & 7)) << 4), src, ok);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();                                               // bt_s, barriers, tensor-memory address
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem = tmem_slot;
+  const unsigned tmem_s = tmem, tmem_o = tmem + 64;
+  const unsigned lane_base = (unsigned)(warp * 32) << 16;        // this warp's quarter of the 128 lanes
+
+  load_kv64(sk0, sv0, kbase, vbase, kv, bt, bt_first, t_begin * UN, kfirst, kend, tid);
+  asm volatile("cp.async.commit_group;\n" ::);
+
+  float o[UD];
+#pragma unroll
+  for (int d = 0; d < UD; ++d) o[d] = 0.0f;
+  float mrow = -INFINITY, lrow = 0.0f;
+  const float sl2 = scale * LOG2E_U;
+  const int p_row = pos0 + tid;                                   // this thread's query position
+  constexpr unsigned IDESC_QK = umma_idesc(UM, UN, 0), IDESC_PV = umma_idesc(UM, UD, 1);
+  bool failed = false;
+
+  for (int i = 0; i < n_t; ++i) {
+    const int st = i & 1;
+    const unsigned sk = sk0 + st * SKV_BYTES, sv = sv0 + st * SKV_BYTES;
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");         // tile i (and Q) have landed
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); // ... and are visible to the tensor core
+    if (__syncthreads_or(failed)) { failed = true; break; }        // (a wait ran out somewhere: all leave together)
+    if (i + 1 < n_t) {                                             // the other stage is free: tile i - 1 is done with
+      load_kv64(sk0 + (st ^ 1) * SKV_BYTES, sv0 + (st ^ 1) * SKV_BYTES, kbase, vbase, kv, bt, bt_first,
+                (t_begin + i + 1) * UN, kfirst, kend, tid);
+      asm volatile("cp.async.commit_group;\n" ::);
+    }
+    if (tid == 0) {                                                // S = Q K^T, 8 steps of 16 dims
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const unsigned long long da = umma_desc(sq + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
+        const unsigned long long db = umma_desc(sk + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
+        umma_f16(tmem_s, da, db, IDESC_QK, k > 0);
+      }
+      umma_commit(smem_addr(&bar_s));
+    }
+    float alpha = 1.0f;
+    if (mbar_wait_u(smem_addr(&bar_s), (unsigned)(i & 1))) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      // this thread's row of scores
+      const int key0 = (t_begin + i) * UN;
+      float s[UN];
+      {
+        float v[32];
+        tmem_ld32(tmem_s + lane_base, v);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) s[c] = v[c];
+        tmem_ld32(tmem_s + lane_base + 32, v);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) s[32 + c] = v[c];
+      }
+      const bool need_mask = key0 + UN - 1 > pos0 || window > 0 || key0 < kfirst || key0 + UN > kend;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < UN; ++c) {
+          const int key = key0 + c;
+          const bool vis = key <= p_row && key < kend && (window <= 0 || key > p_row - window);
+          if (!vis) s[c] = -INFINITY;
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < UN; ++c) mx = fmaxf(mx, s[c]);
+      // the running maximum is kept in raw-score units; exponents are taken of (s - m) * scale * log2(e)
+      const float mnew = fmaxf(mrow, mx);
+      const float msc = mnew == -INFINITY ? 0.0f : mnew * sl2;     // a row that has seen nothing yet
+      alpha = ex2(mrow * sl2 - msc);                               // 2^-inf = 0 on the first visible tile
+      mrow = mnew;
+      float ls = 0.0f;
+#pragma unroll
+      for (int c = 0; c < UN; ++c) { s[c] = ex2(fmaf(s[c], sl2, -msc)); ls += s[c]; }
+      lrow = lrow * alpha + ls;
+      // P as the next A operand: row = this thread, 64 keys = one 128-byte swizzled row
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const unsigned x = pack2(s[c * 8], s[c * 8 + 1]), y = pack2(s[c * 8 + 2], s[c * 8 + 3]);
+        const unsigned z = pack2(s[c * 8 + 4], s[c * 8 + 5]), w = pack2(s[c * 8 + 6], s[c * 8 + 7]);
+        const unsigned dst = sp + (unsigned)tid * 128u + (unsigned)((c ^ (tid & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+      }
+    } else {
+      failed = true;
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    if (__syncthreads_or(failed)) { failed = true; break; }        // P is complete; everyone has read S
+    if (tid == 0) {                                                // O_tile = P V, 4 steps of 16 keys
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const unsigned long long da = umma_desc(sp + kk * 32, 16, 1024);
+        const unsigned long long db = umma_desc(sv + kk * 16 * 128, UN * 128, 1024);   // leading offset = panel stride
+        umma_f16(tmem_o, da, db, IDESC_PV, kk > 0);
+      }
+      umma_commit(smem_addr(&bar_o));
+    }
+    if (mbar_wait_u(smem_addr(&bar_o), (unsigned)(i & 1))) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+      for (int j = 0; j < UD / 32; ++j) {
+        float v[32];
+        tmem_ld32(tmem_o + lane_base + j * 32, v);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[j * 32 + c] = fmaf(o[j * 32 + c], alpha, v[c]);
+      }
+    } else {
+      failed = true;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");             // nothing of ours is still in flight
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  const int any_failed = __syncthreads_or(failed);
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;\n" ::"r"(tmem) : "memory");
+  if (any_failed) {
+    if (tid == 0) atomicExch(error_flag, 1);
+    return;
+  }
+  if (tid < rows) {
+    const float inv = lrow > 0.0f ? 1.0f / lrow : 0.0f;
+    bf16* dst = out + (size_t)(tok0 + tid) * out_stride + (size_t)head * UD;
+#pragma unroll
+    for (int c = 0; c < UD / 8; ++c) {
+      uint4 v;
+      v.x = pack2(o[c * 8] * inv, o[c * 8 + 1] * inv);     v.y = pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+      v.z = pack2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); v.w = pack2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+      *reinterpret_cast<uint4*>(dst + c * 8) = v;
+    }
+  }
+}
+}  // namespace
+
+// Prompt portions, head_dim 128, query tiles of 128 tokens of one entry (tile_entry / tile_q0).
+// q rows, out rows, k_layer and v_layer 16-byte aligned.  error_flag: a device int set to 1 if a bounded
+// wait inside the kernel ran out (the output is then invalid).
+IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, long long out_stride,
+                                  void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                  const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_q0,
+                                  int n_tiles, const int* entry_q_start, const int* entry_q_len,
+                                  const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
+                                  int window, int* error_flag, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (head_dim != UD || n_kv < 1 || n_heads % n_kv || n_tiles > 65535 || !error_flag) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return IFX_ERR_ALIGNMENT;
+  if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
+  PagedKV kv;
+  kv.k = k_layer; kv.v = v_layer; kv.page_stride = page_stride;
+  kv.head_stride = page_size * head_dim; kv.page_size = page_size; kv.page_shift = 0;
+  while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
+  UmmaMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
+  cudaError_t e = cudaFuncSetAttribute(attn_prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_UMMA);
+  if (e != cudaSuccess) return (int)e;
+  attn_prefill_umma_kernel<<<dim3(n_heads, n_tiles), 128, SMEM_UMMA, stream>>>(
+      (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, tile_entry, tile_q0, n_heads, n_kv, scale, window,
+      error_flag);
+  return IFX_LAUNCH_CHECK();
+}

@@ -18,7 +18,8 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import torch
 
 QUERY_TILE = 16     # tokens per query tile of the generic attention kernel
-CHUNK_TILE = 64     # tokens per query tile of the tensor-core kernel for prompt portions
+CHUNK_TILE = 64     # tokens per query tile of the mma.sync kernel for prompt portions
+UMMA_TILE = 128     # tokens per query tile of the tcgen05 kernel for prompt portions
 
 
 @dataclass
@@ -85,6 +86,9 @@ class StepContext:
     chunk_tile_entry: torch.Tensor            # [Tc] tiles of CHUNK_TILE tokens over entries with more than one token
     chunk_tile_q0: torch.Tensor               # [Tc]
     n_chunk_tiles: int
+    umma_tile_entry: torch.Tensor             # [Tu] tiles of UMMA_TILE tokens over the same entries
+    umma_tile_q0: torch.Tensor                # [Tu]
+    n_umma_tiles: int
     decode_entries: torch.Tensor              # [D] entries that bring exactly one token
     n_decode: int
     block_tables: List[torch.Tensor]          # per cache group [R, max_blocks]

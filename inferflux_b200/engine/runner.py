@@ -20,7 +20,7 @@ import torch
 
 from ..cache import OutOfPages, OutOfSlots, KVCacheManager, KVCacheStorage, StateSlotManager, StateSlotStorage, bytes_per_token
 from ..config.engine_config import EngineConfig
-from .batch import CHUNK_TILE, QUERY_TILE, MetadataSlab, StepContext, StepEntry
+from .batch import CHUNK_TILE, QUERY_TILE, UMMA_TILE, MetadataSlab, StepContext, StepEntry
 from ..kernels import ops
 from .model import Model
 
@@ -149,6 +149,7 @@ class StepRunner:
         slots = [self.slots.slot(e.rid) for e in entries]
         want_rows = [int(q_start[i]) + int(p) for i, e in enumerate(entries) for p in e.want]
         tile_entry, tile_q0, ctile_entry, ctile_q0, dec_entries = [], [], [], [], []
+        utile_entry, utile_q0 = [], []
         for i in range(r):
             ln = int(lens[i])
             if ln == 1:
@@ -158,6 +159,8 @@ class StepRunner:
                 tile_entry.append(i), tile_q0.append(q0)
             for q0 in range(0, ln, CHUNK_TILE):
                 ctile_entry.append(i), ctile_q0.append(q0)
+            for q0 in range(0, ln, UMMA_TILE):
+                utile_entry.append(i), utile_q0.append(q0)
         groups = self.kv.num_groups
         tables, slot_maps, out_widths = [], [], []
         for g in range(groups):
@@ -174,7 +177,7 @@ class StepRunner:
             slot_maps.append(pages.astype(np.int64) * ps + positions % ps)
             tables.append(arr.reshape(-1))
             out_widths.append(width)
-        need = 4 * (12 + groups) + 2 * n + 5 * r + 2 * len(tile_entry) + 2 * len(ctile_entry) + len(want_rows) \
+        need = 4 * (14 + groups) + 2 * n + 5 * r + 2 * len(tile_entry) + 3 * len(ctile_entry) + len(want_rows) \
             + sum(t.size for t in tables) + groups * n + 64
         if slab is None:
             if need > self.slab.capacity:
@@ -185,6 +188,7 @@ class StepRunner:
         d_qs, d_ql, d_cs, d_sl = slab.put(q_start), slab.put(lens), slab.put(starts), slab.put(slots)
         d_te, d_tq = slab.put(tile_entry), slab.put(tile_q0)
         d_cte, d_ctq, d_dec = slab.put(ctile_entry), slab.put(ctile_q0), slab.put(dec_entries)
+        d_ute, d_utq = slab.put(utile_entry), slab.put(utile_q0)
         d_want = slab.put(want_rows)
         d_tabs = [slab.put(t).view(r, w) for t, w in zip(tables, out_widths)]
         d_sm = [slab.put(sm) for sm in slot_maps]
@@ -194,6 +198,7 @@ class StepRunner:
             token_ids=d_tok, positions=d_pos, entry_q_start=d_qs, entry_q_len=d_ql, entry_ctx_start=d_cs,
             entry_slot=d_sl, tile_entry=d_te, tile_q0=d_tq, n_tiles=len(tile_entry),
             chunk_tile_entry=d_cte, chunk_tile_q0=d_ctq, n_chunk_tiles=len(ctile_entry),
+            umma_tile_entry=d_ute, umma_tile_q0=d_utq, n_umma_tiles=len(utile_entry),
             decode_entries=d_dec, n_decode=len(dec_entries),
             block_tables=d_tabs, slot_maps=d_sm, want_rows=d_want, n_want=len(want_rows),
             max_q_len=int(lens.max()),
@@ -245,7 +250,7 @@ class StepRunner:
             if len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
             r = len(entries)
-            slab = MetadataSlab(64 + 16 * r + sum(r * w for w in widths) + 8 * (12 + len(widths)), self.device)
+            slab = MetadataSlab(64 + 16 * r + sum(r * w for w in widths) + 8 * (14 + len(widths)), self.device)
             ctx = self._describe(entries, slab, widths)
             logits = self.model.forward(ctx)                 # this step runs eagerly (and warms the libraries up)
             torch.cuda.synchronize()

@@ -57,6 +57,9 @@ def _lib():
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
         lib.ifx_gemv_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll,
                                       c_int, c_int, c_void_p]
+        lib.ifx_attn_prefill_umma.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
+                                              c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
         lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p]
         lib.ifx_apply_penalties.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                             c_void_p, c_int, c_int, c_void_p]
@@ -64,7 +67,7 @@ def _lib():
                                    c_void_p, c_void_p, c_int, c_int, c_void_p]
         for name in ("ifx_embed_gather", "ifx_add_rmsnorm", "ifx_swiglu", "ifx_convert", "ifx_rope_table",
                      "ifx_qkv_rope_kv_write", "ifx_gemm_f32", "ifx_attn_paged_generic", "ifx_argmax",
-                     "ifx_attn_prefill_bf16", "ifx_attn_decode_bf16", "ifx_gemv_bf16",
+                     "ifx_attn_prefill_bf16", "ifx_attn_decode_bf16", "ifx_gemv_bf16", "ifx_attn_prefill_umma",
                      "ifx_apply_penalties", "ifx_sample"):
             getattr(lib, name).restype = c_int
         _sigs_done = True
@@ -328,6 +331,32 @@ def attn_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
                                         _ptr(tile_entry), _ptr(tile_q0), n_tiles, _ptr(entry_q_start),
                                         _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, n_kv, head_dim,
                                         float(scale), int(window), _stream()), "attn_prefill_bf16")
+    return out
+
+
+UMMA_ATTENTION_HEAD_DIM = 128
+UMMA_TILE = 128
+
+
+def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer: torch.Tensor,
+                      v_layer: torch.Tensor, page_stride: int, page_size: int, block_tables: torch.Tensor,
+                      tile_entry: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
+                      entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor,
+                      n_heads: int, n_kv: int, head_dim: int, scale: float, window: int) -> torch.Tensor:
+    """Attention of prompt portions with tcgen05.mma and tensor-memory
+    accumulators (bfloat16, head_dim 128); query tiles of 128 tokens listed by
+    tile_entry / tile_q0.  A bounded wait that runs out sets the device error
+    flag (see :func:`check_device_errors`)."""
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16,
+          "attn_prefill_umma: bfloat16 operands")
+    _need(head_dim == UMMA_ATTENTION_HEAD_DIM, f"attn_prefill_umma: head_dim {head_dim} is not 128")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
+    _check(_lib().ifx_attn_prefill_umma(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
+                                        page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
+                                        _ptr(tile_entry), _ptr(tile_q0), n_tiles, _ptr(entry_q_start),
+                                        _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, n_kv, head_dim,
+                                        float(scale), int(window), _ptr(error_flag(q.device)), _stream()),
+           "attn_prefill_umma")
     return out
 
 

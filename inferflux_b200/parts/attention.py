@@ -117,15 +117,20 @@ class GQAttention(Part):
 
     def attend(self, qkv, attn, ctx, g, k_layer, v_layer, page_stride) -> None:
         """bfloat16 with a head size the tensor-core kernels take: prompt
-        portions and single tokens go to their own kernels; anything else
-        (float32, other head sizes) to the generic kernel."""
+        portions go to the tcgen05 kernel (head size 128) or the mma.sync kernel
+        (64), single tokens to the split decode kernel; anything else (float32,
+        other head sizes) to the generic kernel."""
         common = (ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start)
         if qkv.dtype != torch.bfloat16 or self.head_dim not in ops.FAST_ATTENTION_HEAD_DIMS:
             ops.attn_paged_generic(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
                                    ctx.block_tables[g], ctx.tile_entry, ctx.tile_q0, ctx.n_tiles, *common,
                                    self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
             return
-        if ctx.n_chunk_tiles:
+        if ctx.n_chunk_tiles and self.head_dim == ops.UMMA_ATTENTION_HEAD_DIM:
+            ops.attn_prefill_umma(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
+                                  ctx.block_tables[g], ctx.umma_tile_entry, ctx.umma_tile_q0, ctx.n_umma_tiles,
+                                  *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
+        elif ctx.n_chunk_tiles:
             ops.attn_prefill_bf16(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
                                   ctx.block_tables[g], ctx.chunk_tile_entry, ctx.chunk_tile_q0, ctx.n_chunk_tiles,
                                   *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)

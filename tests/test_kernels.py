@@ -200,7 +200,7 @@ def test_rope_and_kv_write(ops, dtype, nh, nkv, hd, rot, ps):
 
 
 # -------------------------------------------------------------------- attention
-def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, fast):
+def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, fast, umma=False):
     """entries: list of (cached tokens, new tokens).  Builds a paged cache with
     scattered pages, runs the kernel(s) and the reference."""
     from inferflux_b200.engine.batch import CHUNK_TILE, QUERY_TILE
@@ -264,7 +264,13 @@ def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, 
         ops.attn_paged_generic(qd, nh * hd, out, *args, te, tq, len(tiles), md["q_start"], md["q_len"], md["ctx_start"],
                                nh, nkv, hd, scale, window or 0)
     else:
-        if ctiles:
+        if ctiles and umma:
+            utiles = [(e, q0) for e, (c, ql) in enumerate(entries) if ql > 1 for q0 in range(0, ql, 128)]
+            te, tq = it([t[0] for t in utiles]).to(DEV), it([t[1] for t in utiles]).to(DEV)
+            ops.attn_prefill_umma(qd, nh * hd, out, *args, te, tq, len(utiles), md["q_start"], md["q_len"],
+                                  md["ctx_start"], nh, nkv, hd, scale, window or 0)
+            ops.check_device_errors(DEV)
+        elif ctiles:
             te, tq = it([t[0] for t in ctiles]).to(DEV), it([t[1] for t in ctiles]).to(DEV)
             ops.attn_prefill_bf16(qd, nh * hd, out, *args, te, tq, len(ctiles), md["q_start"], md["q_len"],
                                   md["ctx_start"], nh, nkv, hd, scale, window or 0)
@@ -300,10 +306,18 @@ def test_attention_tensor_core(ops, nh, nkv, hd, ps, window, peaked):
     _attention_case(ops, torch.bfloat16, nh, nkv, hd, ps, window, MIXED, 21, peaked, fast=True)
 
 
+@pytest.mark.parametrize("nh,nkv,ps,window", [(28, 4, 16, None), (3, 1, 4, 129), (8, 8, 64, None), (2, 1, 16, 40)])
+@pytest.mark.parametrize("peaked", [False, True])
+def test_attention_tcgen05_prompt_portions(ops, nh, nkv, ps, window, peaked):
+    """The tcgen05 / tensor-memory kernel for prompt portions (head size 128), beside the decode kernel."""
+    entries = MIXED + [(0, 300), (200, 129), (5, 128)]
+    _attention_case(ops, torch.bfloat16, nh, nkv, 128, ps, window, entries, 23, peaked, fast=True, umma=True)
+
+
 def test_attention_long_context_far_key(ops):
     """4,000 cached keys; the query matches key 3 only: a fault in an early page shows."""
-    for fast in (False, True):
-        _attention_case(ops, torch.bfloat16, 4, 1, 128, 16, None, [(4000, 1), (3990, 40)], 22, True, fast)
+    for fast, umma in ((False, False), (True, False), (True, True)):
+        _attention_case(ops, torch.bfloat16, 4, 1, 128, 16, None, [(4000, 1), (3990, 40)], 22, True, fast, umma)
 
 
 # --------------------------------------------------------------------- sampling
