@@ -11,20 +11,23 @@
 // One block takes 128 consecutive new tokens of one request and one head.
 //   * Q (128 x 128), and per step a tile of 64 keys and 64 values, lie in shared
 //     memory in the 128-byte-swizzle layouts the tensor core reads (written with
-//     16-byte cp.async from the paged cache; two stages, the next tile loads
-//     while this one is used).
+//     16-byte cp.async from the paged cache; two stages, loads run a tile ahead).
 //   * S = Q K^T is one chain of 8 tcgen05.mma (M 128, N 64, K 16) into 64
-//     columns of tensor memory.  Thread r then owns row r: it reads its 64
-//     scores with tcgen05.ld, masks, keeps the running maximum and sum, and
-//     writes P = exp(s - max) as bfloat16 into shared memory as the next MMA's
-//     A operand.
+//     columns of tensor memory.  Thread r then owns row r: it reads its scores
+//     with tcgen05.ld (once for the maximum, once more for the exponentials, 32
+//     at a time, so few registers are live), keeps the running maximum and sum,
+//     and writes P = exp(s - max) as packed bfloat16 back into tensor memory
+//     (tcgen05.st), from where the next MMA takes it as its A operand.
 //   * O_tile = P V is 4 tcgen05.mma (M 128, N 128, K 16) with V read in its
 //     natural [key][dim] layout (MN-major B operand) into 128 more columns; the
-//     thread folds it into its float32 row: o = o * alpha + O_tile.
+//     thread folds it into its float32 row: o = o * alpha + O_tile.  The MMAs of
+//     the next tile's scores are issued together with this tile's P V, so they
+//     run while the threads fold O.
 // One thread issues the MMAs; tcgen05.commit arrives on an mbarrier that the
-// others wait on.  Every such wait is bounded: if one runs out the block sets
-// *error_flag, waits for its copies in flight, frees its tensor memory and
-// returns.
+// others wait on.  Two blocks fit an SM (96 KB of shared memory, 256 columns of
+// tensor memory each), so one block's softmax overlaps the other's MMAs.  Every
+// mbarrier wait is bounded: if one runs out the block sets *error_flag, waits
+// for its copies in flight, frees its tensor memory and returns.
 #include "common.cuh"
 
 namespace {
@@ -76,18 +79,15 @@ __device__ __forceinline__ void umma_f16(unsigned tmem_d, unsigned long long da,
 __device__ __forceinline__ void umma_commit(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
-// 32 consecutive columns of this thread's tensor-memory lane
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
-  unsigned r[32];
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+// 32 consecutive columns of this thread's tensor-memory lane; the values are valid after tmem_ld_wait()
+__device__ __forceinline__ void tmem_ld32_nowait(unsigned taddr, unsigned (&r)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -104,15 +104,17 @@ struct UmmaMeta {
   const int* entry_q_start; const int* entry_q_len; const int* entry_ctx_start;
 };
 
-// Shared memory (1024-byte aligned): Q 32 KB | K 2 x 16 KB | V 2 x 16 KB | P 16 KB
-constexpr int SQ_BYTES = 2 * UM * 128, SKV_BYTES = 2 * UN * 128, SP_BYTES = UM * 128;
-constexpr int SMEM_UMMA = SQ_BYTES + 4 * SKV_BYTES + SP_BYTES + 1024;
+// Shared memory (1024-byte aligned): Q 32 KB | K 2 x 16 KB | V 2 x 16 KB
+constexpr int SQ_BYTES = 2 * UM * 128, SKV_BYTES = 2 * UN * 128;
+constexpr int SMEM_UMMA = SQ_BYTES + 4 * SKV_BYTES + 1024;
+// Tensor memory columns: S 64 | P 32 (64 packed bfloat16) | - | O 128
+constexpr unsigned TM_S = 0, TM_P = 64, TM_O = 128;
 
-// 64 keys and values (absolute key index key0 ..) into one stage: row = key, two panels of 64 dims,
-// 16-byte chunk c of a 128-byte row stored at c ^ (row & 7)
-__device__ __forceinline__ void load_kv64(unsigned sk, unsigned sv, const bf16* kbase, const bf16* vbase,
-                                          const PagedKV& kv, const int* bt, int bt_first, int key0, int lo, int hi,
-                                          int tid) {
+// 64 keys (or values) starting at absolute key index key0 into one stage: row = key, two panels of 64
+// dims, 16-byte chunk c of a 128-byte row stored at c ^ (row & 7).  Keys and values of a tile are loaded
+// at different times (a key stage is free as soon as its scores are done), so each has its own call.
+__device__ __forceinline__ void load_rows64(unsigned sdst, const bf16* base, const PagedKV& kv, const int* bt,
+                                            int bt_first, int key0, int lo, int hi, int tid) {
   const int r = tid >> 1, half = tid & 1;
   const int key = key0 + r;
   bool ok = key >= lo && key < hi;
@@ -122,16 +124,13 @@ __device__ __forceinline__ void load_kv64(unsigned sk, unsigned sv, const bf16* 
     ok = page >= 0;
     if (ok) off = (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * UD;
   }
-  const bf16* ksrc = kbase + off;
-  const bf16* vsrc = vbase + off;
+  const bf16* src = base + off;
   const unsigned row = (unsigned)r * 128u;
   const int sw = r & 7;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int c = j * 2 + half;                                 // 16-byte chunk of the 256-byte row
-    const unsigned dst = (unsigned)(c >> 3) * (UN * 128) + row + (unsigned)(((c & 7) ^ sw) << 4);
-    cp_async16_u(sk + dst, ksrc + c * 8, ok);
-    cp_async16_u(sv + dst, vsrc + c * 8, ok);
+    cp_async16_u(sdst + (unsigned)(c >> 3) * (UN * 128) + row + (unsigned)(((c & 7) ^ sw) << 4), src + c * 8, ok);
   }
 }
 
@@ -144,7 +143,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   __shared__ unsigned tmem_slot;
   __shared__ int bt_s[BT_CACHE_U];
   const unsigned sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
-  const unsigned sq = sbase, sk0 = sq + SQ_BYTES, sv0 = sk0 + 2 * SKV_BYTES, sp = sv0 + 2 * SKV_BYTES;
+  const unsigned sq = sbase, sk0 = sq + SQ_BYTES, sv0 = sk0 + 2 * SKV_BYTES;
   const int tid = threadIdx.x, warp = tid >> 5;
   // tiles run last to first and heads fastest: the longest blocks (of every head) start first
   const int tile = gridDim.y - 1 - blockIdx.y;
@@ -166,7 +165,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_o)));
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 0) {                                               // 256 columns: 64 for S, 128 for O
+  if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;\n" ::"r"(smem_addr(&tmem_slot)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -190,11 +189,42 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   __syncthreads();                                               // bt_s, barriers, tensor-memory address
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem = tmem_slot;
-  const unsigned tmem_s = tmem, tmem_o = tmem + 64;
   const unsigned lane_base = (unsigned)(warp * 32) << 16;        // this warp's quarter of the 128 lanes
+  const unsigned tm_s = tmem + TM_S + lane_base, tm_p = tmem + TM_P + lane_base, tm_o = tmem + TM_O + lane_base;
 
-  load_kv64(sk0, sv0, kbase, vbase, kv, bt, bt_first, t_begin * UN, kfirst, kend, tid);
-  asm volatile("cp.async.commit_group;\n" ::);
+  constexpr unsigned IDESC_QK = umma_idesc(UM, UN, 0), IDESC_PV = umma_idesc(UM, UD, 1);
+  auto issue_qk = [&](int st) {                                   // S = Q K^T, 8 steps of 16 dims (one thread)
+    const unsigned sk = sk0 + st * SKV_BYTES;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const unsigned long long da = umma_desc(sq + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
+      const unsigned long long db = umma_desc(sk + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
+      umma_f16(tmem + TM_S, da, db, IDESC_QK, k > 0);
+    }
+    umma_commit(smem_addr(&bar_s));
+  };
+
+  // copy groups, in this order: [Q, K0] [V0] [K1] [V1], then K(i+2) after the scores of tile i are done and
+  // V(i+2) after its P V is done; "all but the newest two groups" therefore covers K(i+1) and V(i)
+  auto load_k = [&](int t) {
+    if (t < n_t) load_rows64(sk0 + (t & 1) * SKV_BYTES, kbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  auto load_v = [&](int t) {
+    if (t < n_t) load_rows64(sv0 + (t & 1) * SKV_BYTES, vbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  load_k(0);
+  load_v(0);
+  load_k(1);
+  load_v(1);
+  asm volatile("cp.async.wait_group 3;\n" ::: "memory");           // Q and K0 have landed
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // ... and are visible to the tensor core
+  __syncthreads();
+  if (tid == 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    issue_qk(0);
+  }
 
   float o[UD];
 #pragma unroll
@@ -202,47 +232,26 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   float mrow = -INFINITY, lrow = 0.0f;
   const float sl2 = scale * LOG2E_U;
   const int p_row = pos0 + tid;                                   // this thread's query position
-  constexpr unsigned IDESC_QK = umma_idesc(UM, UN, 0), IDESC_PV = umma_idesc(UM, UD, 1);
   bool failed = false;
 
   for (int i = 0; i < n_t; ++i) {
     const int st = i & 1;
-    const unsigned sk = sk0 + st * SKV_BYTES, sv = sv0 + st * SKV_BYTES;
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");         // tile i (and Q) have landed
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); // ... and are visible to the tensor core
-    if (__syncthreads_or(failed)) { failed = true; break; }        // (a wait ran out somewhere: all leave together)
-    if (i + 1 < n_t) {                                             // the other stage is free: tile i - 1 is done with
-      load_kv64(sk0 + (st ^ 1) * SKV_BYTES, sv0 + (st ^ 1) * SKV_BYTES, kbase, vbase, kv, bt, bt_first,
-                (t_begin + i + 1) * UN, kfirst, kend, tid);
-      asm volatile("cp.async.commit_group;\n" ::);
-    }
-    if (tid == 0) {                                                // S = Q K^T, 8 steps of 16 dims
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const unsigned long long da = umma_desc(sq + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
-        const unsigned long long db = umma_desc(sk + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
-        umma_f16(tmem_s, da, db, IDESC_QK, k > 0);
-      }
-      umma_commit(smem_addr(&bar_s));
-    }
     float alpha = 1.0f;
     if (mbar_wait_u(smem_addr(&bar_s), (unsigned)(i & 1))) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      // this thread's row of scores
+      load_k(i + 2);                                               // the scores are done: this key stage is free
       const int key0 = (t_begin + i) * UN;
+      // this thread's row of scores
       float s[UN];
       {
-        float v[32];
-        tmem_ld32(tmem_s + lane_base, v);
+        unsigned r0[32], r1[32];
+        tmem_ld32_nowait(tm_s, r0);
+        tmem_ld32_nowait(tm_s + 32, r1);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) s[c] = v[c];
-        tmem_ld32(tmem_s + lane_base + 32, v);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) s[32 + c] = v[c];
+        for (int c = 0; c < 32; ++c) { s[c] = __uint_as_float(r0[c]); s[32 + c] = __uint_as_float(r1[c]); }
       }
-      const bool need_mask = key0 + UN - 1 > pos0 || window > 0 || key0 < kfirst || key0 + UN > kend;
-      if (need_mask) {
+      if (key0 + UN - 1 > pos0 || window > 0 || key0 < kfirst || key0 + UN > kend) {   // diagonal, window, edges
 #pragma unroll
         for (int c = 0; c < UN; ++c) {
           const int key = key0 + c;
@@ -258,42 +267,58 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       const float msc = mnew == -INFINITY ? 0.0f : mnew * sl2;     // a row that has seen nothing yet
       alpha = ex2(mrow * sl2 - msc);                               // 2^-inf = 0 on the first visible tile
       mrow = mnew;
+      // P = 2^(s * sl2 - msc) as packed bfloat16 into tensor memory
       float ls = 0.0f;
 #pragma unroll
-      for (int c = 0; c < UN; ++c) { s[c] = ex2(fmaf(s[c], sl2, -msc)); ls += s[c]; }
-      lrow = lrow * alpha + ls;
-      // P as the next A operand: row = this thread, 64 keys = one 128-byte swizzled row
+      for (int h = 0; h < 4; ++h) {
+        unsigned pk[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const unsigned x = pack2(s[c * 8], s[c * 8 + 1]), y = pack2(s[c * 8 + 2], s[c * 8 + 3]);
-        const unsigned z = pack2(s[c * 8 + 4], s[c * 8 + 5]), w = pack2(s[c * 8 + 6], s[c * 8 + 7]);
-        const unsigned dst = sp + (unsigned)tid * 128u + (unsigned)((c ^ (tid & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+        for (int c = 0; c < 8; ++c) {
+          const float p0 = ex2(fmaf(s[h * 16 + 2 * c], sl2, -msc)), p1 = ex2(fmaf(s[h * 16 + 2 * c + 1], sl2, -msc));
+          ls += p0 + p1;
+          pk[c] = pack2(p0, p1);
+        }
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+                     ::"r"(tm_p + h * 8), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
+                       "r"(pk[6]), "r"(pk[7]) : "memory");
       }
+      lrow = lrow * alpha + ls;
+      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
     } else {
       failed = true;
     }
+    asm volatile("cp.async.wait_group 2;\n" ::: "memory");         // K(i+1) and V(i) have landed
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     if (__syncthreads_or(failed)) { failed = true; break; }        // P is complete; everyone has read S
-    if (tid == 0) {                                                // O_tile = P V, 4 steps of 16 keys
+    if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const unsigned sv = sv0 + st * SKV_BYTES;
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const unsigned long long da = umma_desc(sp + kk * 32, 16, 1024);
+      for (int kk = 0; kk < 4; ++kk) {                             // O_tile = P V, 4 steps of 16 keys; P from tensor memory
         const unsigned long long db = umma_desc(sv + kk * 16 * 128, UN * 128, 1024);   // leading offset = panel stride
-        umma_f16(tmem_o, da, db, IDESC_PV, kk > 0);
+        const unsigned a_t = tmem + TM_P + kk * 8;
+        const unsigned acc = kk > 0;
+        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                     ::"r"(tmem + TM_O), "r"(a_t), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
       }
       umma_commit(smem_addr(&bar_o));
+      if (i + 1 < n_t) issue_qk(st ^ 1);                           // the next tile's scores run while O is folded
     }
     if (mbar_wait_u(smem_addr(&bar_o), (unsigned)(i & 1))) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      load_v(i + 2);                                               // P V is done: this value stage is free
 #pragma unroll
-      for (int j = 0; j < UD / 32; ++j) {
-        float v[32];
-        tmem_ld32(tmem_o + lane_base + j * 32, v);
+      for (int j = 0; j < UD / 64; ++j) {
+        unsigned r0[32], r1[32];
+        tmem_ld32_nowait(tm_o + j * 64, r0);
+        tmem_ld32_nowait(tm_o + j * 64 + 32, r1);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) o[j * 32 + c] = fmaf(o[j * 32 + c], alpha, v[c]);
+        for (int c = 0; c < 32; ++c) {
+          o[j * 64 + c] = fmaf(o[j * 64 + c], alpha, __uint_as_float(r0[c]));
+          o[j * 64 + 32 + c] = fmaf(o[j * 64 + 32 + c], alpha, __uint_as_float(r1[c]));
+        }
       }
     } else {
       failed = true;
