@@ -34,19 +34,35 @@ class StepEntry:
 
 class MetadataSlab:
     """All int32 metadata of a step in one pinned host buffer and one device
-    buffer, so a step costs one host-to-device copy."""
+    buffer, so a step costs one host-to-device copy.
+
+    The copy is asynchronous and the GPU may run several steps behind the
+    host, so the host side is a small ring of pinned buffers: a buffer is
+    written again only after the copy that last read it has completed (an
+    event per buffer tells)."""
+
+    RING = 4
 
     def __init__(self, capacity: int, device: str):
         self.capacity = capacity
         self.device = device
-        pin = torch.device(device).type == "cuda"
-        self.host = torch.zeros(capacity, dtype=torch.int32, pin_memory=pin)
+        self._cuda = torch.device(device).type == "cuda"
+        n = self.RING if self._cuda else 1
+        self._hosts = [torch.zeros(capacity, dtype=torch.int32, pin_memory=self._cuda) for _ in range(n)]
+        self._events = [None] * n
+        self._turn = -1
+        self.host = self._hosts[0]
         self._np = self.host.numpy()
         self.dev = torch.zeros(capacity, dtype=torch.int32, device=device)
         self._used = 0
-        self._views: List[Tuple[int, int]] = []
 
     def begin(self) -> None:
+        self._turn = (self._turn + 1) % len(self._hosts)
+        ev = self._events[self._turn]
+        if ev is not None:
+            ev.synchronize()            # the copy that read this buffer last has finished
+        self.host = self._hosts[self._turn]
+        self._np = self.host.numpy()
         self._used = 0
 
     def put(self, values, align: int = 4) -> torch.Tensor:
@@ -63,6 +79,11 @@ class MetadataSlab:
     def upload(self) -> None:
         if self._used:
             self.dev[:self._used].copy_(self.host[:self._used], non_blocking=True)
+            if self._cuda:
+                ev = self._events[self._turn]
+                if ev is None:
+                    ev = self._events[self._turn] = torch.cuda.Event()
+                ev.record()
 
 
 @dataclass

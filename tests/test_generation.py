@@ -157,3 +157,30 @@ def test_penalties_and_stop(folders):
     stop = SamplingParams(temperature=0.0, max_tokens=20, stop_token_ids=[first], ignore_eos=True)
     r = _engine(folder, "float32").generate([prompt], stop)[0]
     assert r.tokens == [first] and r.finish_reason == "stop"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_queued_behind_a_busy_gpu(folders, dtype):
+    """The host may prepare several steps while the GPU still works on an
+    earlier one: each step's metadata must survive until its kernels have read
+    it.  A long library product keeps the GPU busy while six different steps
+    are queued without any synchronisation."""
+    from inferflux_b200 import StepEntry
+    folder, cfg, w = folders["A"]
+    eng = _engine(folder, dtype, cuda_graphs=False)
+    seqs = [random_tokens(cfg["vocab_size"], n, 120 + n) for n in (90, 37, 64, 130, 5, 71)]
+    busy = torch.randn(8192, 8192, device="cuda:0")
+    for _ in range(40):
+        busy = (busy @ busy).clamp_(-1, 1)
+    outs = []
+    for i, s in enumerate(seqs):                    # no synchronisation between these steps
+        half = max(1, len(s) // 2)
+        eng.run_step([StepEntry(f"q{i}", s[:half], [])])
+        outs.append(eng.run_step([StepEntry(f"q{i}", s[half:], [len(s) - half - 1])]).clone() if len(s) > half else None)
+    torch.cuda.synchronize()
+    for i, s in enumerate(seqs):
+        if outs[i] is None:
+            continue
+        want = plain.forward(cfg, w, s)[-1]
+        err = float((outs[i][0].cpu().double() - want).abs().max() / want.abs().max())
+        assert err <= TOL[dtype], f"request {i}: {err:.3e}"
