@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(128)
 attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                          PagedKV kv, AttnMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
                          int n_heads, int n_kv, float scale, int window) {
+  pdl_enter();
   constexpr int BQ = 64, BK = 64, KS = HD / 16, DT = HD / 8;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);              // [2][BK][HD]
@@ -344,6 +345,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
                         PagedKV kv, AttnMeta m, const int* __restrict__ dec_entries,
                         float* __restrict__ part_o, float* __restrict__ part_ml,
                         int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits) {
+  pdl_enter();
   constexpr int KS = HD / 16, BK = 64, TK = 16;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16* ring = reinterpret_cast<bf16*>(smem_raw);             // [DSTAGES][K|V][BK][HD]
@@ -523,6 +525,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, long long out_stride, const int* __restrict__ dec_entries,
                                          const int* __restrict__ entry_q_start, int n_heads, int head_dim, int n_splits) {
+  pdl_enter();
   const int dec = blockIdx.x, head = blockIdx.y;
   const int tok = entry_q_start[dec_entries[dec]];
   const size_t p0 = ((size_t)dec * n_heads + head) * n_splits;
@@ -558,9 +561,9 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<dim3(n_heads, n_tiles), 128, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m,
+  const int ifx_rc = launch_pdl(kern, dim3(n_heads, n_tiles), dim3(128), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m,
                                                       tile_entry, tile_q0, n_heads, n_kv, scale, window);
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 template <int HD>
@@ -577,14 +580,12 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
   }
   const int ratio = n_heads / n_kv;
   const int head_chunks = (ratio + 7) / 8;
-  kern<<<dim3(n_dec, n_kv * head_chunks, n_splits), 128, smem, stream>>>(
-      (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, dec_entries, part_o, part_ml, n_heads, n_kv,
+  int rc = launch_pdl(kern, dim3(n_dec, n_kv * head_chunks, n_splits), dim3(128), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, dec_entries, part_o, part_ml, n_heads, n_kv,
       head_chunks, scale, window, n_splits);
-  int rc = IFX_LAUNCH_CHECK();
+  if (!rc) rc = IFX_LAUNCH_CHECK();
   if (rc || n_splits == 1) return rc;
-  attn_decode_merge_kernel<<<dim3(n_dec, n_heads), HD < 128 ? HD : 128, 0, stream>>>(
-      part_o, part_ml, (bf16*)out, out_stride, dec_entries, m.entry_q_start, n_heads, HD, n_splits);
-  return IFX_LAUNCH_CHECK();
+  rc = launch_pdl(attn_decode_merge_kernel, dim3(n_dec, n_heads), dim3(HD < 128 ? HD : 128), 0, stream, part_o, part_ml, (bf16*)out, out_stride, dec_entries, m.entry_q_start, n_heads, HD, n_splits);
+  return rc ? rc : IFX_LAUNCH_CHECK();
 }
 }  // namespace
 

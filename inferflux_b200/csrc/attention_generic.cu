@@ -33,6 +33,7 @@ template <typename T, int NACC>
 __global__ void __launch_bounds__(256)
 attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
                           PagedKV kv, AttnBatch b, int n_heads, int n_kv, int head_dim, float scale, int window) {
+  pdl_enter();
   extern __shared__ float smem[];
   float* qs = smem;                               // [BQ][head_dim]
   float* ks = qs + BQ * head_dim;                 // [BKEYS][head_dim + 1]
@@ -145,8 +146,9 @@ int launch_generic(const void* q, long long q_stride, void* out, long long out_s
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_tiles, n_heads);
-  kern<<<grid, 256, smem, stream>>>((const T*)q, q_stride, (T*)out, out_stride, kv, b, n_heads, n_kv, head_dim, scale, window);
-  return IFX_LAUNCH_CHECK();
+  const int ifx_rc = launch_pdl(kern, grid, dim3(256), smem, stream, (const T*)q, q_stride, (T*)out, out_stride, kv, b, n_heads, n_kv,
+                                head_dim, scale, window);
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 template <typename T>

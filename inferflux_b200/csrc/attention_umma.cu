@@ -138,6 +138,7 @@ __global__ void __launch_bounds__(128)
 attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                          PagedKV kv, UmmaMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
                          int n_heads, int n_kv, float scale, int window, int* __restrict__ error_flag) {
+  pdl_enter();
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bar_s, bar_o;
   __shared__ unsigned tmem_slot;
@@ -368,8 +369,7 @@ IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, 
   UmmaMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_UMMA);
   if (e != cudaSuccess) return (int)e;
-  attn_prefill_umma_kernel<<<dim3(n_heads, n_tiles), 128, SMEM_UMMA, stream>>>(
-      (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, tile_entry, tile_q0, n_heads, n_kv, scale, window,
+  const int ifx_rc = launch_pdl(attn_prefill_umma_kernel, dim3(n_heads, n_tiles), dim3(128), SMEM_UMMA, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, tile_entry, tile_q0, n_heads, n_kv, scale, window,
       error_flag);
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }

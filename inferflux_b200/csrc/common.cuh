@@ -82,3 +82,27 @@ struct PagedKV {
 };
 
 #define IFX_LAUNCH_CHECK() ((int)cudaGetLastError())
+
+// Programmatic dependent launch.  Every kernel of the library starts with pdl_enter(): it waits until the
+// kernel before it in the stream has finished (and its writes are visible), then lets the kernel after it
+// be launched, so that one's launch latency and set-up overlap this kernel's work; the next kernel in turn
+// waits at its own pdl_enter().  Kernels are launched with launch_pdl(), which sets the attribute that
+// allows this; after a kernel that never signals (a library kernel) the launch behaves like a plain one.
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+template <typename Kern, typename... Args>
+inline int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, args...);
+}

@@ -15,6 +15,7 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int hidden, int vocab) {
+  pdl_enter();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * hidden;
@@ -29,6 +30,7 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
 // 8 bfloat16 (16 bytes) per thread per step; hidden a multiple of 8
 __global__ void embed_gather_bf16x8_kernel(const bf16* __restrict__ table, const int* __restrict__ ids,
                                            float* __restrict__ out, int hidden, int vocab) {
+  pdl_enter();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -47,16 +49,17 @@ __global__ void embed_gather_bf16x8_kernel(const bf16* __restrict__ table, const
 IFX_API int ifx_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
                              int n_tokens, int hidden, int vocab, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  int ifx_rc = 0;
   const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
   if (table_dtype == IFX_F32)
-    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    ifx_rc = launch_pdl(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, hidden, vocab);
   else if (table_dtype == IFX_BF16 && hidden % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0)
-    embed_gather_bf16x8_kernel<<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, hidden, vocab);
+    ifx_rc = launch_pdl(embed_gather_bf16x8_kernel, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, hidden, vocab);
   else if (table_dtype == IFX_BF16)
-    embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, hidden, vocab);
+    ifx_rc = launch_pdl(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, hidden, vocab);
   else
     return IFX_ERR_UNSUPPORTED;
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 // ------------------------------------------------------ residual add + RMSNorm
@@ -71,6 +74,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    const float* __restrict__ weight, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows,
                                    int hidden, int write_residual) {
+  pdl_enter();
   extern __shared__ float row_buf[];
   __shared__ float red[32];
   const int src = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -124,6 +128,7 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
                        long long partial_stride, const float* __restrict__ weight, float eps,
                        TO* __restrict__ out, const int* __restrict__ rows, int hidden, int write_residual) {
+  pdl_enter();
   __shared__ float red[32];
   const int src = rows ? rows[blockIdx.x] : blockIdx.x;
   float* r = residual + (size_t)src * hidden;
@@ -167,17 +172,18 @@ template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* residual, const void* delta, int n_partials, long long partial_stride,
                               const float* weight, float eps, void* out, const int* rows, int n_rows,
                               int hidden, int write_residual, cudaStream_t stream) {
+  int ifx_rc = 0;
   const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0
                        && (partial_stride & 3) == 0;
   if (hidden % 4 == 0 && aligned && hidden <= 4 * 8 * 256) {
     const int groups = hidden / 4;
     if (groups <= 4 * 256)
-      add_rmsnorm_vec_kernel<TD, TO, 4><<<n_rows, 256, 0, stream>>>(residual, (const TD*)delta, n_partials, partial_stride,
+      ifx_rc = launch_pdl(add_rmsnorm_vec_kernel<TD, TO, 4>, dim3(n_rows), dim3(256), 0, stream, residual, (const TD*)delta, n_partials, partial_stride,
                                                                     weight, eps, (TO*)out, rows, hidden, write_residual);
     else
-      add_rmsnorm_vec_kernel<TD, TO, 8><<<n_rows, 256, 0, stream>>>(residual, (const TD*)delta, n_partials, partial_stride,
+      ifx_rc = launch_pdl(add_rmsnorm_vec_kernel<TD, TO, 8>, dim3(n_rows), dim3(256), 0, stream, residual, (const TD*)delta, n_partials, partial_stride,
                                                                     weight, eps, (TO*)out, rows, hidden, write_residual);
-    return IFX_LAUNCH_CHECK();
+    return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
   }
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return IFX_ERR_UNSUPPORTED;
@@ -188,9 +194,9 @@ static int launch_add_rmsnorm(float* residual, const void* delta, int n_partials
   }
   int threads = 128;
   while (threads < 1024 && threads * 4 < hidden) threads <<= 1;
-  kern<<<n_rows, threads, smem, stream>>>(residual, (const TD*)delta, n_partials, partial_stride, weight, eps,
+  ifx_rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, residual, (const TD*)delta, n_partials, partial_stride, weight, eps,
                                           (TO*)out, rows, hidden, write_residual);
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 // delta_dtype / out_dtype: IFX_F32 or IFX_BF16.  delta and out may be null.
@@ -216,6 +222,7 @@ IFX_API int ifx_add_rmsnorm(float* residual, const void* delta, int delta_dtype,
 // gate_up [M, 2*I] (gate columns first) -> out [M, I]
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter) {
+  pdl_enter();
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) {
@@ -229,6 +236,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 
 // 8 outputs per thread per step: 16-byte loads of gate and up, one 16-byte store; inter a multiple of 8
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, long long total8, int inter8) {
+  pdl_enter();
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (; idx < total8; idx += stride) {
@@ -252,6 +260,7 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* __r
 IFX_API int ifx_swiglu(const void* gate_up, void* out, int dtype, int m, int inter, cudaStream_t stream) {
   const long long total = (long long)m * inter;
   if (total <= 0) return 0;
+  int ifx_rc = 0;
   const int threads = 256;
   long long blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
@@ -259,21 +268,22 @@ IFX_API int ifx_swiglu(const void* gate_up, void* out, int dtype, int m, int int
     const long long total8 = total / 8;
     long long b8 = (total8 + threads - 1) / threads;
     if (b8 > 148 * 16) b8 = 148 * 16;
-    swiglu_bf16x8_kernel<<<(int)b8, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total8, inter / 8);
-    return IFX_LAUNCH_CHECK();
+    ifx_rc = launch_pdl(swiglu_bf16x8_kernel, dim3((int)b8), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, total8, inter / 8);
+    return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
   }
   if (dtype == IFX_F32)
-    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, inter);
+    ifx_rc = launch_pdl(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, total, inter);
   else if (dtype == IFX_BF16)
-    swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, inter);
+    ifx_rc = launch_pdl(swiglu_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, total, inter);
   else
     return IFX_ERR_UNSUPPORTED;
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------- conversion
 template <typename TS, typename TD>
 __global__ void convert_kernel(const TS* __restrict__ src, TD* __restrict__ dst, long long n) {
+  pdl_enter();
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (; idx < n; idx += stride) dst[idx] = Num<TD>::from_f(Num<TS>::to_f(src[idx]));
@@ -281,14 +291,15 @@ __global__ void convert_kernel(const TS* __restrict__ src, TD* __restrict__ dst,
 
 IFX_API int ifx_convert(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
+  int ifx_rc = 0;
   const int threads = 256;
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (src_dtype == IFX_BF16 && dst_dtype == IFX_F32)
-    convert_kernel<bf16, float><<<(int)blocks, threads, 0, stream>>>((const bf16*)src, (float*)dst, n);
+    ifx_rc = launch_pdl(convert_kernel<bf16, float>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)src, (float*)dst, n);
   else if (src_dtype == IFX_F32 && dst_dtype == IFX_BF16)
-    convert_kernel<float, bf16><<<(int)blocks, threads, 0, stream>>>((const float*)src, (bf16*)dst, n);
+    ifx_rc = launch_pdl(convert_kernel<float, bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)src, (bf16*)dst, n);
   else
     return IFX_ERR_UNSUPPORTED;
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }

@@ -15,6 +15,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;   // 256 threads, 4x4 o
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
                 float* __restrict__ C, int M, int N, int K, long long lda, long long ldc) {
+  pdl_enter();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -68,7 +69,8 @@ IFX_API int ifx_gemm_f32(const float* A, const float* W, const float* bias, floa
                          long long lda, long long ldc, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return IFX_ERR_UNSUPPORTED;
+  int ifx_rc = 0;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldc);
-  return IFX_LAUNCH_CHECK();
+  ifx_rc = launch_pdl(gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, A, W, bias, C, M, N, K, lda, ldc);
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }

@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(KW * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias,
                  TOut* __restrict__ out, int M, int n_out, int K, long long ldx, long long ldo,
                  long long partial_stride) {
+  pdl_enter();
   constexpr int THREADS = KW * 32;
   extern __shared__ __align__(16) uint4 ring[];                 // [NST][2 * RT][threads]: a thread's slots are [..][..][tid]
   __shared__ float red[KW][RT][NT][32][4];
@@ -199,9 +200,9 @@ int launch(const void* X, const void* W, const float* bias, void* out, int M, in
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<grid, KW * 32, smem, stream>>>((const bf16*)X, (const bf16*)W, bias, (TOut*)out, M, n_out, K, ldx, ldo,
+  int ifx_rc = launch_pdl(kern, dim3(grid), dim3(KW * 32), smem, stream, (const bf16*)X, (const bf16*)W, bias, (TOut*)out, M, n_out, K, ldx, ldo,
                                         partial_stride);
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 // Block shape by the amount of work: with plenty of row tiles a block takes two (the activations

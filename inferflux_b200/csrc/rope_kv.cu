@@ -18,6 +18,7 @@
 // cos/sin tables [n_tokens, half] from positions and inverse frequencies.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                   float* __restrict__ cos_t, float* __restrict__ sin_t, int n_tokens, int half) {
+  pdl_enter();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_tokens * half) return;
   const int t = idx / half, i = idx - t * half;
@@ -32,8 +33,8 @@ IFX_API int ifx_rope_table(const int* positions, const double* inv_freq, float* 
                            int n_tokens, int half, cudaStream_t stream) {
   const int total = n_tokens * half;
   if (total <= 0) return 0;
-  rope_table_kernel<<<(total + 127) / 128, 128, 0, stream>>>(positions, inv_freq, cos_t, sin_t, n_tokens, half);
-  return IFX_LAUNCH_CHECK();
+  int ifx_rc = launch_pdl(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, positions, inv_freq, cos_t, sin_t, n_tokens, half);
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 // qkv: [n_tokens, (n_heads + 2 n_kv) * head_dim], q heads first, then k, then v.
@@ -45,6 +46,7 @@ __global__ void qkv_rope_kv_write_kernel(T* __restrict__ qkv, const float* __res
                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                          int rot_half, const int* __restrict__ slot_map, PagedKV kv,
                                          int n_heads, int n_kv, int head_dim) {
+  pdl_enter();
   const int t = blockIdx.x;
   const int width = (n_heads + 2 * n_kv) * head_dim;
   T* row = qkv + (size_t)t * width;
@@ -111,6 +113,7 @@ __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const fl
                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                 const int* __restrict__ slot_map, PagedKV kv,
                                                 int n_heads, int n_kv, int head_dim) {
+  pdl_enter();
   const int t = blockIdx.x;
   const int half = head_dim / 2, hv = half / 8;               // 8-wide groups per half head
   const int width = (n_heads + 2 * n_kv) * head_dim;
@@ -171,6 +174,7 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
                                   long long page_stride, int page_size, int n_tokens, int n_heads, int n_kv,
                                   int head_dim, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  int ifx_rc = 0;
   if (head_dim % 2 || rot_dim % 2 || rot_dim > head_dim || rot_dim < 0) return IFX_ERR_UNSUPPORTED;
   if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
   PagedKV kv;
@@ -187,15 +191,15 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
     const int work8 = (n_heads + n_kv) * head_dim / 16;
     int th = 32;
     while (th < 256 && th < work8) th <<= 1;
-    qkv_rope_kv_write_bf16x8_kernel<<<n_tokens, th, 0, stream>>>((bf16*)qkv, bias, cos_t, sin_t, slot_map, kv,
+    ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t, sin_t, slot_map, kv,
                                                                  n_heads, n_kv, head_dim);
-    return IFX_LAUNCH_CHECK();
+    return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
   }
   if (dtype == IFX_F32)
-    qkv_rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, bias, cos_t, sin_t, rot_dim / 2, slot_map, kv, n_heads, n_kv, head_dim);
+    ifx_rc = launch_pdl(qkv_rope_kv_write_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (float*)qkv, bias, cos_t, sin_t, rot_dim / 2, slot_map, kv, n_heads, n_kv, head_dim);
   else if (dtype == IFX_BF16)
-    qkv_rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, bias, cos_t, sin_t, rot_dim / 2, slot_map, kv, n_heads, n_kv, head_dim);
+    ifx_rc = launch_pdl(qkv_rope_kv_write_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (bf16*)qkv, bias, cos_t, sin_t, rot_dim / 2, slot_map, kv, n_heads, n_kv, head_dim);
   else
     return IFX_ERR_UNSUPPORTED;
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }

@@ -63,6 +63,7 @@ __device__ ArgPair block_argmax(const float* row, int n, ArgPair* scratch) {
 
 __global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ logits, long long row_stride,
                                                     int* __restrict__ out, int vocab) {
+  pdl_enter();
   __shared__ ArgPair scratch[32];
   const ArgPair b = block_argmax(logits + (size_t)blockIdx.x * row_stride, vocab, scratch);
   if (threadIdx.x == 0) out[blockIdx.x] = b.i < 0 ? 0 : b.i;
@@ -73,6 +74,7 @@ __global__ void penalties_kernel(float* __restrict__ logits, long long row_strid
                                  const int* __restrict__ recent_counts, const int* __restrict__ n_recent,
                                  int max_recent, const float* __restrict__ rep, const float* __restrict__ freq,
                                  const float* __restrict__ pres, int vocab) {
+  pdl_enter();
   const int row = blockIdx.x;
   float* lg = logits + (size_t)row * row_stride;
   const int n = min(n_recent[row], max_recent);
@@ -107,6 +109,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, float* __r
               const float* __restrict__ temperature, const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ min_p, const unsigned long long* __restrict__ seeds,
               const unsigned long long* __restrict__ counters, int* __restrict__ out, int vocab) {
+  pdl_enter();
   __shared__ ArgPair ascratch[32];
   __shared__ float red[32];
   __shared__ float seg_prefix[ST];
@@ -198,17 +201,17 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, float* __r
 
 IFX_API int ifx_argmax(const float* logits, long long row_stride, int* out, int n_rows, int vocab, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  argmax_kernel<<<n_rows, ST, 0, stream>>>(logits, row_stride, out, vocab);
-  return IFX_LAUNCH_CHECK();
+  const int ifx_rc = launch_pdl(argmax_kernel, dim3(n_rows), dim3(ST), 0, stream, logits, row_stride, out, vocab);
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 IFX_API int ifx_apply_penalties(float* logits, long long row_stride, const int* recent_ids, const int* recent_counts,
                                 const int* n_recent, int max_recent, const float* rep, const float* freq,
                                 const float* pres, int n_rows, int vocab, cudaStream_t stream) {
   if (n_rows <= 0 || max_recent <= 0) return 0;
-  penalties_kernel<<<n_rows, 128, 0, stream>>>(logits, row_stride, recent_ids, recent_counts, n_recent, max_recent,
+  const int ifx_rc = launch_pdl(penalties_kernel, dim3(n_rows), dim3(128), 0, stream, logits, row_stride, recent_ids, recent_counts, n_recent, max_recent,
                                                rep, freq, pres, vocab);
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 IFX_API int ifx_sample(const float* logits, long long row_stride, float* weights, const float* temperature,
@@ -216,9 +219,9 @@ IFX_API int ifx_sample(const float* logits, long long row_stride, float* weights
                        const unsigned long long* counters, int* out, int n_rows, int vocab, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (vocab >= (1 << 24)) return IFX_ERR_UNSUPPORTED;
-  sample_kernel<<<n_rows, ST, 0, stream>>>(logits, row_stride, weights, temperature, top_k, top_p, min_p, seeds,
+  const int ifx_rc = launch_pdl(sample_kernel, dim3(n_rows), dim3(ST), 0, stream, logits, row_stride, weights, temperature, top_k, top_p, min_p, seeds,
                                            counters, out, vocab);
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------- no allocation
@@ -264,7 +267,7 @@ extern "C" int ifx_sample_static(const float* logits, long long row_stride, cons
     g_sample_static_ptr[dev] = scratch;
   }
   // rows are packed [n_rows, vocab]; every element a row reads is written first, so nothing is cleared
-  sample_kernel<<<n_rows, ST, 0, stream>>>(logits, row_stride, scratch, temperature, top_k, top_p, min_p, seeds,
+  const int ifx_rc = launch_pdl(sample_kernel, dim3(n_rows), dim3(ST), 0, stream, logits, row_stride, scratch, temperature, top_k, top_p, min_p, seeds,
                                            counters, out, vocab);
-  return IFX_LAUNCH_CHECK();
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
