@@ -88,9 +88,11 @@ struct PagedKV {
 // be launched, so that one's launch latency and set-up overlap this kernel's work; the next kernel in turn
 // waits at its own pdl_enter().  Kernels are launched with launch_pdl(), which sets the attribute that
 // allows this; after a kernel that never signals (a library kernel) the launch behaves like a plain one.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_enter() {
-  asm volatile("griddepcontrol.wait;\n" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  pdl_wait();
+  pdl_launch_dependents();
 }
 template <typename Kern, typename... Args>
 inline int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {

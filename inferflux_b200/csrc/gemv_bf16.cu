@@ -65,7 +65,6 @@ __global__ void __launch_bounds__(KW * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias,
                  TOut* __restrict__ out, int M, int n_out, int K, long long ldx, long long ldo,
                  long long partial_stride) {
-  pdl_enter();
   constexpr int THREADS = KW * 32;
   extern __shared__ __align__(16) uint4 ring[];                 // [NST][2 * RT][threads]: a thread's slots are [..][..][tid]
   __shared__ float red[KW][RT][NT][32][4];
@@ -116,6 +115,9 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
   };
 #pragma unroll
   for (int j = 0; j < NST - 1; ++j) issue(j);
+  // The weights are parameters, which no kernel of a step writes, so their first copies are issued before
+  // this kernel waits for the one before it: the ring fills while that kernel drains.
+  pdl_enter();
   // activations come from L1/L2 with plain loads, one chunk ahead of their use
   uint4 xn[NT];
   {
@@ -230,6 +232,8 @@ int by_tiles(const void* X, const void* W, const float* bias, void* out, int M, 
 // and out = silu(X gate^T) * (X up^T).  M <= 16; K a multiple of 8; X rows and W 16-byte aligned.
 // k_splits > 1 (float32 output, no swiglu): out is [k_splits, M, n_out], slice s holding the sum over
 // the s-th part of K; the caller adds the slices (the fused residual-add + norm kernel does).
+// W is read before the kernel has waited for the kernel launched before it in the stream, so W must
+// not be the output of a kernel of this library launched directly before (weights are parameters).
 IFX_API int ifx_gemv_bf16(const void* X, const void* W, const float* bias, void* out, int out_dtype, int M,
                           int n_out, int K, long long ldx, long long ldo, int swiglu, int k_splits,
                           cudaStream_t stream) {

@@ -231,7 +231,9 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     float32 accumulation, bfloat16 or float32 result.  With ``swiglu`` w is
     [2N, K] = [gate; up] and out = silu(x gate^T) * (x up^T).  With
     ``k_splits`` > 1 out is float32 [k_splits, M, N]: slice s is the sum over the
-    s-th part of K and the caller adds the slices."""
+    s-th part of K and the caller adds the slices.  ``w`` is a parameter: the
+    kernel starts to read it before the kernel launched before it has finished,
+    so it must not be that kernel's output."""
     m, k = x.shape
     n = out.shape[-1]
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous(), "gemv_bf16: bfloat16 operands")
