@@ -33,6 +33,8 @@ class _Sequence:
     length: int = 0                    # tokens whose keys and values are in the cache
     reserved: int = 0                  # tokens for which pages are held (>= length)
     tables: List[List[int]] = field(default_factory=list)   # per group: page of each logical block, -1 = given back
+    serial: int = 0                    # unique among all sequences the manager ever held
+    version: int = 0                   # counts the changes of the block tables
 
 
 class KVCacheManager:
@@ -45,6 +47,7 @@ class KVCacheManager:
         self.page_size = page_size
         self.pools = [PagePool(n, g) for g, n in enumerate(num_pages)]
         self._seqs: Dict[Hashable, _Sequence] = {}
+        self._serials = 0
 
     # ------------------------------------------------------------ queries
     @property
@@ -62,6 +65,13 @@ class KVCacheManager:
 
     def block_table(self, rid: Hashable, group: int) -> List[int]:
         return self._seqs[rid].tables[group]
+
+    def table_stamp(self, rid: Hashable):
+        """Changes whenever the request's block tables do (a page taken or given
+        back, or the request ended and begun again), so a copy of the tables
+        made under the same stamp is still right."""
+        seq = self._seqs[rid]
+        return (seq.serial, seq.version)
 
     def _first_needed_block(self, group: int, length: int) -> int:
         """Blocks below this one lie wholly behind the window of every token at
@@ -92,7 +102,8 @@ class KVCacheManager:
     def add_request(self, rid: Hashable) -> None:
         if rid in self._seqs:
             raise KeyError(f"request {rid!r} is already in the cache")
-        self._seqs[rid] = _Sequence(tables=[[] for _ in self.needs])
+        self._serials += 1
+        self._seqs[rid] = _Sequence(tables=[[] for _ in self.needs], serial=self._serials)
 
     def reserve(self, rid: Hashable, n_new: int) -> None:
         """Hold pages for positions [length, length + n_new) in every group, or
@@ -103,7 +114,9 @@ class KVCacheManager:
             if n > self.pools[g].num_free:
                 raise OutOfPages(n, self.pools[g].num_free, g)
         for g, n in enumerate(need):
-            seq.tables[g].extend(self.pools[g].alloc(n))
+            if n:
+                seq.tables[g].extend(self.pools[g].alloc(n))
+                seq.version += 1
         seq.reserved = max(seq.reserved, seq.length + n_new)
 
     def advance(self, rid: Hashable, n_new: int) -> None:
@@ -121,6 +134,7 @@ class KVCacheManager:
                 for b in range(min(first, len(table))):
                     table[b] = -1
                 self.pools[g].free(gone)
+                seq.version += 1
 
     def free_request(self, rid: Hashable) -> None:
         seq = self._seqs.pop(rid)

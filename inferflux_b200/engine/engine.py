@@ -133,7 +133,7 @@ class Engine:
             self.scheduler.begin_step(plan)
             entries = []
             for it in plan.items:
-                toks = it.request.tokens[it.start:it.start + it.count]
+                toks = it.request.token_slice(it.start, it.count)
                 entries.append(StepEntry(it.request.rid, toks, [it.count - 1] if it.samples else []))
             logits = self.runner.step(entries)
             sampling = [it.request for it in plan.items if it.samples]
@@ -141,7 +141,8 @@ class Engine:
             if sampling:
                 ids = self.sampler.sample(
                     logits, [r.params for r in sampling], [r.seed for r in sampling],
-                    [len(r.output) for r in sampling], [r.tokens for r in sampling])
+                    [len(r.output) for r in sampling],
+                    [r.tokens if r.params.has_penalties else () for r in sampling])
                 for r, t in zip(sampling, ids.tolist()):
                     sampled[r.rid] = t
             finished += self.scheduler.finish_step(plan, sampled)

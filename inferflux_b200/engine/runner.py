@@ -258,13 +258,50 @@ class StepRunner:
             launches = ops.launch_count
             with torch.cuda.graph(graph):                    # records the same launches; nothing runs
                 static_logits = self.model.forward(ctx)
+            off = lambda t: int(t.storage_offset())
             self._graphs[key] = dict(slab=slab, graph=graph, logits=static_logits, used=slab._used,
-                                     launches=ops.launch_count - launches)
+                                     launches=ops.launch_count - launches,
+                                     image=slab._np[:slab._used].copy(), stamps=[None] * r, widths=widths,
+                                     at=dict(tok=off(ctx.token_ids), pos=off(ctx.positions),
+                                             cs=off(ctx.entry_ctx_start), sl=off(ctx.entry_slot),
+                                             tab=[off(t) for t in ctx.block_tables],
+                                             sm=[off(t) for t in ctx.slot_maps]))
             return logits
-        ctx = self._describe(entries, rec["slab"], widths)
-        if rec["slab"]._used != rec["used"]:
-            raise RuntimeError("a captured step's metadata layout changed")
+        self._refresh_decode(entries, rec)
         rec["graph"].replay()
         ops.launch_count += rec["launches"]
         self.graph_replays += 1
         return rec["logits"]
+
+    def _refresh_decode(self, entries: Sequence[StepEntry], rec: dict) -> None:
+        """The metadata of a captured decode step, brought up to date in the
+        host image that the record keeps and sent to the device.  Per entry
+        only the token, the position and the cache slot of the new token
+        change from step to step; a row of a block table is written again only
+        when its request's tables have changed (the stamp tells)."""
+        img, at, widths, stamps = rec["image"], rec["at"], rec["widths"], rec["stamps"]
+        kv, ps = self.kv, self.page_size
+        for i, e in enumerate(entries):
+            rid = e.rid
+            length = kv.length(rid)
+            img[at["tok"] + i] = e.tokens[0]
+            img[at["pos"] + i] = length
+            img[at["cs"] + i] = length
+            stamp = (rid, kv.table_stamp(rid))
+            fresh = stamps[i] != stamp
+            if fresh:
+                stamps[i] = stamp
+                img[at["sl"] + i] = self.slots.slot(rid)
+            for g, w in enumerate(widths):
+                base = at["tab"][g] + i * w
+                if fresh:
+                    table = kv.block_table(rid, g)
+                    if len(table) > w:
+                        raise RuntimeError("block tables are wider than the layout they are written into")
+                    img[base:base + len(table)] = table
+                    img[base + len(table):base + w] = -1
+                img[at["sm"][g] + i] = int(img[base + length // ps]) * ps + length % ps
+        slab = rec["slab"]
+        slab.begin()
+        slab.put(img)
+        slab.upload()

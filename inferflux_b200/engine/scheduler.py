@@ -92,6 +92,15 @@ class Request:
         """Everything the cache must hold before the next token can be sampled."""
         return self.prompt + self.output
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """``tokens[start:start + count]`` without joining the two lists."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - n]
+
     @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed

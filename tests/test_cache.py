@@ -132,3 +132,26 @@ def test_state_slots():
     s.release("a")
     assert s.acquire("c") == a                  # the seat is used again
     s.check()
+
+
+def test_table_stamp_changes_with_the_tables():
+    """The stamp tells a holder of a copy of the block tables whether it is still right."""
+    kv = KVCacheManager([KVNeed(2, 16), KVNeed(2, 16, window=20)], [8, 8], 16)
+    kv.add_request("a")
+    s0 = kv.table_stamp("a")
+    kv.reserve("a", 10)
+    s1 = kv.table_stamp("a")
+    assert s1 != s0                                  # a page was taken
+    kv.advance("a", 10)
+    kv.reserve("a", 3)
+    kv.advance("a", 3)
+    assert kv.table_stamp("a") == s1                 # tokens within the page: the tables stand
+    kv.reserve("a", 30)
+    s2 = kv.table_stamp("a")
+    kv.advance("a", 30)                              # 43 tokens: the window has passed block 0
+    assert kv.block_table("a", 1)[0] == -1 and kv.table_stamp("a") not in (s1, s2)
+    kv.free_request("a")
+    kv.add_request("a")
+    kv.reserve("a", 10)
+    assert kv.table_stamp("a") not in (s0, s1, s2)   # the same name, another sequence
+    kv.check()

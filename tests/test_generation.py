@@ -184,3 +184,46 @@ def test_steps_queued_behind_a_busy_gpu(folders, dtype):
         want = plain.forward(cfg, w, s)[-1]
         err = float((outs[i][0].cpu().double() - want).abs().max() / want.abs().max())
         assert err <= TOL[dtype], f"request {i}: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_steps_follow_changes_of_the_batch(folders, dtype):
+    """A captured decode step keeps a host copy of its metadata and rewrites
+    only what changed.  Here the batch of a captured shape changes under it: a
+    request ends and another takes its row, one is ended and begun again under
+    the same name, and the order of the rows changes."""
+    from inferflux_b200 import StepEntry
+    folder, cfg, w = folders["D"]
+    seqs = {k: random_tokens(cfg["vocab_size"], 60, 130 + i) for i, k in enumerate("abcd")}
+    refs = {k: plain.forward(cfg, w, s).numpy() for k, s in seqs.items()}
+    eng = _engine(folder, dtype)
+    pos = {}
+
+    def prompt(k, n):
+        eng.run_step([StepEntry(k, seqs[k][:n], [])])
+        pos[k] = n
+
+    def decode(keys):
+        logits = eng.run_step([StepEntry(k, [seqs[k][pos[k]]], [0]) for k in keys]).cpu().numpy()
+        for i, k in enumerate(keys):
+            err = np.abs(logits[i].astype(np.float64) - refs[k][pos[k]]).max() / np.abs(refs[k]).max()
+            assert err <= TOL[dtype], f"request {k} at {pos[k]}: {err:.3e}"
+            pos[k] += 1
+
+    for k, n in (("a", 5), ("b", 17), ("c", 30)):
+        prompt(k, n)
+    for _ in range(4):
+        decode("abc")
+    replays = eng.runner.graph_replays
+    assert replays >= 3
+    eng.end_request("b")
+    prompt("d", 9)
+    for _ in range(3):
+        decode("adc")                    # d sits in b's row
+    eng.end_request("a")
+    prompt("a", 21)                      # the same name, other pages and another length
+    for _ in range(3):
+        decode("adc")
+    for _ in range(3):
+        decode("cad")                    # rows in another order
+    assert eng.runner.graph_replays >= replays + 9

@@ -211,3 +211,12 @@ def test_random_workloads_finish_and_free_everything():
             else:
                 assert r.finish_reason in ("cache_full", "prompt_too_long")
         assert cache.free_pages() == [pages] and cache.free_slots() == s.cfg.max_seqs
+
+
+def test_token_slice_equals_the_slice_of_all_tokens():
+    from inferflux_b200.engine.scheduler import Request
+    from inferflux_b200.sampling.params import SamplingParams
+    r = Request(rid="x", prompt=[1, 2, 3, 4, 5], params=SamplingParams(), output=[6, 7, 8])
+    for start in range(0, 8):
+        for count in range(1, 9 - start):
+            assert r.token_slice(start, count) == r.tokens[start:start + count]
