@@ -47,7 +47,7 @@ def _timeit(fn, n_rot, reps=20):
 class Case:
     """Builds operands for one kernel at the given sizes; ``run(i)`` launches it on buffer set i."""
 
-    def __init__(self, name, sizes, rows, context):
+    def __init__(self, name, sizes, rows, context, sweep=False):
         h, nh, nkv, hd, inter, vocab = sizes
         self.name, self.bytes, self.flops, self.extra = name, 0, 0, []
         bf = dict(device=DEV, dtype=torch.bfloat16)
@@ -64,9 +64,15 @@ class Case:
                 out = torch.empty(rows, n, **bf)
                 self.run = lambda i: ops.gemv_bf16(x, ws[i], None, out, swiglu=sw)
                 if not sw and n < 10000:
-                    for s in (2, 3, 4, 5):
-                        outp = torch.empty(s, rows, n, device=DEV, dtype=torch.float32)
-                        self.extra.append((f"k_splits={s}", lambda i, s=s, outp=outp: ops.gemv_bf16(x, ws[i], None, outp, k_splits=s)))
+                    # projections whose consumer adds float32 partial sums run with the planned number of K parts
+                    planned = ops.gemv_k_splits(n, k)
+                    self.note = f"k_splits={planned} (planned)"
+                    outp = torch.empty(planned, rows, n, device=DEV, dtype=torch.float32)
+                    self.run = lambda i: ops.gemv_bf16(x, ws[i], None, outp, k_splits=planned)
+                    if sweep:
+                        for s in range(1, 9):
+                            outs = torch.empty(s, rows, n, device=DEV, dtype=torch.float32)
+                            self.extra.append((f"k_splits={s}", lambda i, s=s, outs=outs: ops.gemv_bf16(x, ws[i], None, outs, k_splits=s)))
             else:
                 self.run = None
             self.extra.append(("library", lambda i: torch.mm(x, ws[i].t())))
@@ -142,6 +148,7 @@ def main(argv=None) -> int:
     ap.add_argument("--rows", nargs="*", type=int, default=[1, 8, 64])
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--repeat", type=int, default=5)
+    ap.add_argument("--sweep", action="store_true", help="time: also every number of K parts of the small products")
     ap.add_argument("--sizes", default="3584,28,4,128,18944,152064",
                     help="hidden,heads,kv_heads,head_dim,intermediate,vocab")
     args = ap.parse_args(argv)
@@ -161,7 +168,7 @@ def main(argv=None) -> int:
     for rows in args.rows:
         print(f"--- rows={rows} context={args.context}")
         for name in args.kernels or KERNELS:
-            case = Case(name, sizes, rows, args.context)
+            case = Case(name, sizes, rows, args.context, args.sweep)
             runs = ([("", case.run)] if case.run else []) + case.extra
             for label, fn in runs:
                 t = _timeit(fn, case.n_rot)

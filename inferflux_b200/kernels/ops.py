@@ -57,6 +57,8 @@ def _lib():
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
         lib.ifx_gemv_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll,
                                       c_int, c_int, c_void_p]
+        lib.ifx_gemv_bf16_plan.argtypes = [c_int, c_int, c_int]
+        lib.ifx_gemv_bf16_plan.restype = c_int
         lib.ifx_attn_prefill_umma.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                               c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
@@ -253,6 +255,22 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
                                 x.stride(0) if m > 1 else k, ldo, 1 if swiglu else 0, int(k_splits),
                                 _stream()), "gemv_bf16")
     return out
+
+
+_gemv_plans = {}
+
+
+def gemv_k_splits(n: int, k: int, max_splits: int = 8) -> int:
+    """Into how many parts of K the weight-streaming kernel is best told to cut
+    an [n, k] matrix when float32 partial sums are welcome: the kernel's own
+    count of what keeps the GPU fullest.  It depends on the matrix only."""
+    key = (n, k, max_splits)
+    if key not in _gemv_plans:
+        s = int(_lib().ifx_gemv_bf16_plan(n, k, max_splits))
+        if s < 1:
+            raise KernelError(f"gemv_k_splits: CUDA error {-s}")
+        _gemv_plans[key] = s
+    return _gemv_plans[key]
 
 
 _error_flags = {}

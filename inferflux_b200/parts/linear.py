@@ -62,19 +62,8 @@ class Linear:
             y += self.bias
         return y if y.dtype == out_dtype else y.to(out_dtype)
 
-    def _k_splits(self, slots: int = 592, min_chunks: int = 16, max_splits: int = 8) -> int:
-        """Into how many parts the weight-streaming kernel cuts K.  A block
-        takes 16 rows of one part and 4 blocks fit an SM (592 on 148 SMs); the
-        number of parts is the one whose last wave of blocks is fullest, the
-        smallest such number within 3 percent."""
-        tiles = (self.out_features + 15) // 16
-        chunks = (self.in_features + 31) // 32
-        best, best_use = 1, 0.0
-        for s in range(1, max_splits + 1):
-            if s > 1 and chunks // s < min_chunks:
-                break
-            blocks = tiles * s
-            use = blocks / (-(-blocks // slots) * slots)
-            if use > best_use * 1.03:
-                best, best_use = s, use
-        return best
+    def _k_splits(self) -> int:
+        """Into how many parts the weight-streaming kernel cuts K (it knows its
+        block shapes and how many blocks the GPU holds; the number depends on
+        the matrix only, never on the batch)."""
+        return ops.gemv_k_splits(self.out_features, self.in_features)

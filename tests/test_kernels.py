@@ -401,3 +401,13 @@ def test_sample_distribution_and_determinism(ops):
     mixed = _sample(ops, logits[:4], [0.0, 1.0, 0.0, 1.0], [0] * 4, [1.0] * 4, [0.0] * 4, [99] * 4, [0, 1, 2, 3])
     am = int(torch.argmax(base[0].cpu()))
     assert mixed[0] == am and mixed[2] == am and mixed[1] == got[1] and mixed[3] == got[3]
+
+
+def test_gemv_plan_depends_on_the_matrix_only(ops):
+    """The number of K parts is the kernel's own choice from the matrix sizes; it
+    is within bounds, repeatable, and 1 where K is too short to cut."""
+    for n, k in ((3584, 3584), (4608, 3584), (3584, 18944), (48, 64), (1000, 520)):
+        s = ops.gemv_k_splits(n, k)
+        assert 1 <= s <= 8 and s == ops.gemv_k_splits(n, k)
+        assert s == 1 or (k + 31) // 32 // s >= 16
+    assert ops.gemv_k_splits(48, 64) == 1
