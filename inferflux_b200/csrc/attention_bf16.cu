@@ -345,7 +345,9 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
                         PagedKV kv, AttnMeta m, const int* __restrict__ dec_entries,
                         float* __restrict__ part_o, float* __restrict__ part_ml,
                         int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits) {
-  pdl_enter();
+  // Up to pdl_wait() below the block reads only what no kernel of the step writes (the step's
+  // metadata) and keys and values of tokens older than the one being decoded.
+  pdl_launch_dependents();
   constexpr int KS = HD / 16, BK = 64, TK = 16;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16* ring = reinterpret_cast<bf16*>(smem_raw);             // [DSTAGES][K|V][BK][HD]
@@ -386,6 +388,23 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   for (int d = 0; d < KS; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
   float mcol[2] = {-INFINITY, -INFINITY}, lcol[2] = {0.0f, 0.0f};   // heads 2*t4, 2*t4+1
 
+  const int t_begin = kb / BK, t_end = kb < ke ? (ke - 1) / BK : t_begin - 1, n_t = t_end - t_begin + 1;
+  auto first_tiles = [&]() {
+#pragma unroll
+    for (int p = 0; p < DSTAGES - 1; ++p) {
+      if (p < n_t) {
+        bf16* st = ring + (size_t)p * 2 * BK * HD;
+        load_kv_tile64<HD>(st, st + BK * HD, kbase, vbase, kv, bt, (t_begin + p) * BK, kb, ke, tid, bt_first);
+      }
+      cp_async_commit();
+    }
+  };
+  // The kernel before this one writes the newest token's key and value (position len - 1).  If none
+  // of the first tiles holds it, their copies start before this kernel waits for that one.
+  const bool early = kb < ke && min(ke, (t_begin + DSTAGES - 1) * BK) <= len - 1;
+  if (early) first_tiles();
+  pdl_wait();
+
   if (kb < ke) {                                                // block-uniform
     unsigned qb[KS][2];                                         // Q^T as the B operand: k = d, n = head g
     {
@@ -397,15 +416,7 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       }
     }
     const float sl2 = scale * LOG2E;
-    const int t_begin = kb / BK, t_end = (ke - 1) / BK, n_t = t_end - t_begin + 1;
-#pragma unroll
-    for (int p = 0; p < DSTAGES - 1; ++p) {
-      if (p < n_t) {
-        bf16* st = ring + (size_t)p * 2 * BK * HD;
-        load_kv_tile64<HD>(st, st + BK * HD, kbase, vbase, kv, bt, (t_begin + p) * BK, kb, ke, tid, bt_first);
-      }
-      cp_async_commit();
-    }
+    if (!early) first_tiles();
     const unsigned ring_addr = (unsigned)__cvta_generic_to_shared(ring);
     unsigned koff[KS], voff[KS];                                // this lane's ldmatrix rows within a stage, swizzle included
     {
@@ -530,9 +541,11 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
   const int tok = entry_q_start[dec_entries[dec]];
   const size_t p0 = ((size_t)dec * n_heads + head) * n_splits;
   float mm = -INFINITY;
+#pragma unroll 8
   for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(p0 + s) * 2]);
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float l = 0.0f, acc = 0.0f;
+#pragma unroll 8
     for (int s = 0; s < n_splits; ++s) {
       const float ms = part_ml[(p0 + s) * 2];
       const float f = ms == -INFINITY ? 0.0f : fast_exp2(ms - mm);

@@ -83,16 +83,18 @@ struct PagedKV {
 
 #define IFX_LAUNCH_CHECK() ((int)cudaGetLastError())
 
-// Programmatic dependent launch.  Every kernel of the library starts with pdl_enter(): it waits until the
-// kernel before it in the stream has finished (and its writes are visible), then lets the kernel after it
-// be launched, so that one's launch latency and set-up overlap this kernel's work; the next kernel in turn
-// waits at its own pdl_enter().  Kernels are launched with launch_pdl(), which sets the attribute that
-// allows this; after a kernel that never signals (a library kernel) the launch behaves like a plain one.
+// Programmatic dependent launch.  Every kernel of the library starts with pdl_enter(): it lets the kernel
+// after it in the stream be launched at once (that kernel's launch latency and set-up then overlap this
+// kernel's work; it waits at its own pdl_wait), and waits until the kernel before it has finished and
+// its writes are visible.  A kernel may do work that does not depend on the kernels before it (reading
+// parameters or a step's metadata) between pdl_launch_dependents() and pdl_wait(); it must not write
+// anything there.  Kernels are launched with launch_pdl(), which sets the attribute that allows this;
+// after a kernel that never signals (a library kernel) the launch behaves like a plain one.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_enter() {
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
 }
 template <typename Kern, typename... Args>
 inline int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {

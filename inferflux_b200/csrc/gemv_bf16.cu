@@ -68,6 +68,7 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
                  TOut* __restrict__ out, int M, int n_out, int K, long long ldx, long long ldo,
                  long long partial_stride, int n_groups) {
   constexpr int THREADS = KW * 32;
+  pdl_launch_dependents();
   extern __shared__ __align__(16) uint4 ring[];                 // [NST][2 * RT][threads]: a thread's slots are [..][..][tid]
   constexpr int NBUF = RT * NT >= 4 ? 1 : 2;                    // two buffers (if they fit): a group's sums are read while the next runs
   __shared__ float red[NBUF][KW][RT][NT][32][4];
@@ -120,7 +121,7 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
   for (int j = 0; j < NST - 1; ++j) issue();
   // The weights are parameters, which no kernel of a step writes, so their first copies are issued before
   // this kernel waits for the one before it: the ring fills while that kernel drains.
-  pdl_enter();
+  pdl_wait();
 
   const bf16* xr[NT];
   bool ok_x[NT];
