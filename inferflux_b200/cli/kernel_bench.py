@@ -18,7 +18,6 @@ import sys
 import torch
 
 from ..kernels import ops
-from ..parts.attention import decode_splits
 
 DEV = "cuda:0"
 KERNELS = ["gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_lm_head", "attn_decode", "attn_prefill",
@@ -94,7 +93,7 @@ class Case:
             scale = hd ** -0.5
             if decode:
                 dec = it(list(range(b)))
-                splits = decode_splits(b, nh, nkv, ctx)
+                splits = ops.attn_decode_splits(b, nh, nkv, hd, ctx)
                 po = torch.empty(b * nh * splits * hd, device=DEV)
                 pm = torch.empty(b * nh * splits * 2, device=DEV)
                 self.bytes = b * ctx * nkv * hd * 2 * 2
@@ -102,6 +101,15 @@ class Case:
                 self.run = lambda i: ops.attn_decode_bf16(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
                                                           pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, po, pm, nh, nkv,
                                                           hd, scale, 0, splits)
+                if sweep:
+                    for s in (1, 2, 3, 4, 5, 6, 7, 8, 10, 11, 13, 16, 22, 32):
+                        if s * 64 > ctx:
+                            break
+                        pos = torch.empty(b * nh * s * hd, device=DEV)
+                        pms = torch.empty(b * nh * s * 2, device=DEV)
+                        self.extra.append((f"splits={s}", lambda i, s=s, pos=pos, pms=pms: ops.attn_decode_bf16(
+                            q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1], pools[i].stride(0), ps, bt, dec, b,
+                            qs, ql, cs, pos, pms, nh, nkv, hd, scale, 0, s)))
             else:
                 umma = name.endswith("umma")
                 tiles = [(0, q0) for q0 in range(0, q_len, 128 if umma else 64)]
@@ -148,7 +156,7 @@ def main(argv=None) -> int:
     ap.add_argument("--rows", nargs="*", type=int, default=[1, 8, 64])
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--repeat", type=int, default=5)
-    ap.add_argument("--sweep", action="store_true", help="time: also every number of K parts of the small products")
+    ap.add_argument("--sweep", action="store_true", help="time: also other numbers of K parts (small products) and of key splits (decode attention)")
     ap.add_argument("--sizes", default="3584,28,4,128,18944,152064",
                     help="hidden,heads,kv_heads,head_dim,intermediate,vocab")
     args = ap.parse_args(argv)

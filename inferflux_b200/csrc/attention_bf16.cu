@@ -646,3 +646,42 @@ IFX_API int ifx_attn_decode_bf16(const void* q, long long q_stride, void* out, l
     return launch_decode<64>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, stream);
   return IFX_ERR_UNSUPPORTED;
 }
+
+namespace {
+// Blocks of the decode kernel that the GPU holds at once (asked once per head size); negative: a CUDA error.
+template <int HD>
+int decode_resident_blocks() {
+  static int resident = 0;
+  if (!resident) {
+    const size_t stage_bytes = (size_t)DSTAGES * 2 * 64 * HD * sizeof(bf16);
+    const size_t red_bytes = (size_t)4 * 8 * HD * sizeof(float) + 4 * 8 * 2 * sizeof(float);
+    const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
+    auto kern = attn_decode_bf16_kernel<HD>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return -(int)e;
+    int per_sm = 0, dev = 0, sms = 0;
+    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 128, smem)) != cudaSuccess) return -(int)e;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return -(int)e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return -(int)e;
+    resident = per_sm * sms > 0 ? per_sm * sms : 1;
+  }
+  return resident;
+}
+}  // namespace
+
+// Into how many parts the decode kernel is best told to cut the keys of n_dec entries whose longest
+// context is max_keys: as many as give every block a place on the GPU at once (a second round of
+// blocks costs more than longer parts), each part at least four 64-key tiles.  Negative: a CUDA error.
+IFX_API int ifx_attn_decode_plan(int n_dec, int n_heads, int n_kv, int head_dim, int max_keys) {
+  if (n_dec < 1 || n_kv < 1 || n_heads < n_kv || max_keys < 1) return 1;
+  const int resident = head_dim == 128 ? decode_resident_blocks<128>() : head_dim == 64 ? decode_resident_blocks<64>() : 1;
+  if (resident < 0) return resident;
+  const int base = n_dec * n_kv * ((n_heads / n_kv + 7) / 8);
+  int s = resident / base;
+  const int by_keys = max_keys / 256;
+  if (s > by_keys) s = by_keys;
+  if (s > 64) s = 64;
+  if (s < 1) s = 1;
+  const int tiles = (max_keys + 63) / 64, per = (tiles + s - 1) / s;
+  return (tiles + per - 1) / per;                              // no part without a tile
+}

@@ -37,12 +37,8 @@ __device__ __forceinline__ ArgPair better(ArgPair a, ArgPair b) {
   if (b.i >= 0 && (a.i < 0 || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
   return a;
 }
-__device__ ArgPair block_argmax(const float* row, int n, ArgPair* scratch) {
-  ArgPair best{-INFINITY, -1};
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = row[i];
-    if (v == v) best = better(best, ArgPair{v, i});
-  }
+// The best pair of the block; every thread of warp 0 gets it.  `scratch` holds 32 pairs.
+__device__ ArgPair block_best(ArgPair best, ArgPair* scratch) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
@@ -60,6 +56,14 @@ __device__ ArgPair block_argmax(const float* row, int n, ArgPair* scratch) {
   }
   return best;
 }
+__device__ ArgPair block_argmax(const float* row, int n, ArgPair* scratch) {
+  ArgPair best{-INFINITY, -1};
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = row[i];
+    if (v == v) best = better(best, ArgPair{v, i});
+  }
+  return block_best(best, scratch);
+}
 
 __global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ logits, long long row_stride,
                                                     int* __restrict__ out, int vocab) {
@@ -67,6 +71,55 @@ __global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ lo
   __shared__ ArgPair scratch[32];
   const ArgPair b = block_argmax(logits + (size_t)blockIdx.x * row_stride, vocab, scratch);
   if (threadIdx.x == 0) out[blockIdx.x] = b.i < 0 ? 0 : b.i;
+}
+
+// A wide row in two steps: blocks (part, row) each find the best of a slice of the row, then one
+// warp per row picks among the parts.  `slice` is a multiple of 4; with `vec` rows are 16-byte aligned.
+constexpr int AP = 256;
+__global__ void __launch_bounds__(AP) argmax_part_kernel(const float* __restrict__ logits, long long row_stride,
+                                                         int2* __restrict__ part, int vocab, int slice, int vec) {
+  pdl_enter();
+  __shared__ ArgPair scratch[32];
+  const float* row = logits + (size_t)blockIdx.y * row_stride;
+  const int lo = blockIdx.x * slice, hi = min(vocab, lo + slice);
+  ArgPair best{-INFINITY, -1};
+  if (vec) {
+    for (int i = lo + threadIdx.x * 4; i < hi; i += AP * 4) {
+      if (i + 3 < hi) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        if (v.x == v.x) best = better(best, ArgPair{v.x, i});
+        if (v.y == v.y) best = better(best, ArgPair{v.y, i + 1});
+        if (v.z == v.z) best = better(best, ArgPair{v.z, i + 2});
+        if (v.w == v.w) best = better(best, ArgPair{v.w, i + 3});
+      } else {
+        for (int j = i; j < hi; ++j) {
+          const float v = row[j];
+          if (v == v) best = better(best, ArgPair{v, j});
+        }
+      }
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += AP) {
+      const float v = row[i];
+      if (v == v) best = better(best, ArgPair{v, i});
+    }
+  }
+  best = block_best(best, scratch);
+  if (threadIdx.x == 0) part[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = make_int2(__float_as_int(best.v), best.i);
+}
+__global__ void __launch_bounds__(32) argmax_final_kernel(const int2* __restrict__ part, int* __restrict__ out, int parts) {
+  pdl_enter();
+  ArgPair best{-INFINITY, -1};
+  for (int p = threadIdx.x; p < parts; p += 32) {
+    const int2 v = part[(size_t)blockIdx.x * parts + p];
+    best = better(best, ArgPair{__int_as_float(v.x), v.y});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) out[blockIdx.x] = best.i < 0 ? 0 : best.i;
 }
 
 // recent_ids / recent_counts: [n_rows, max_recent]; n_recent[row] entries are valid, ids distinct.
@@ -199,9 +252,24 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, float* __r
 }
 }  // namespace
 
-IFX_API int ifx_argmax(const float* logits, long long row_stride, int* out, int n_rows, int vocab, cudaStream_t stream) {
+// out[row] = lowest index of the largest value of the row (0 for a row of NaNs).  `part` is scratch of
+// n_rows * parts pairs of ints (8-byte aligned) for rows cut into `parts` slices, or null with parts <= 1.
+IFX_API int ifx_argmax(const float* logits, long long row_stride, int* out, int n_rows, int vocab, void* part, int parts,
+                       cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  const int ifx_rc = launch_pdl(argmax_kernel, dim3(n_rows), dim3(ST), 0, stream, logits, row_stride, out, vocab);
+  if (vocab <= 0) return IFX_ERR_UNSUPPORTED;
+  int ifx_rc;
+  if (parts <= 1 || !part) {
+    ifx_rc = launch_pdl(argmax_kernel, dim3(n_rows), dim3(ST), 0, stream, logits, row_stride, out, vocab);
+    return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
+  }
+  if (((uintptr_t)part & 7) || n_rows > 65535) return IFX_ERR_ALIGNMENT;
+  const int slice = ((vocab + parts - 1) / parts + 3) / 4 * 4;
+  const int vec = ((uintptr_t)logits & 15) == 0 && (row_stride & 3) == 0;
+  ifx_rc = launch_pdl(argmax_part_kernel, dim3(parts, n_rows), dim3(AP), 0, stream, logits, row_stride, (int2*)part, vocab, slice, vec);
+  if (!ifx_rc) ifx_rc = IFX_LAUNCH_CHECK();
+  if (ifx_rc) return ifx_rc;
+  ifx_rc = launch_pdl(argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, (const int2*)part, out, parts);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 

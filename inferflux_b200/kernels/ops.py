@@ -59,10 +59,12 @@ def _lib():
                                       c_int, c_int, c_void_p]
         lib.ifx_gemv_bf16_plan.argtypes = [c_int, c_int, c_int]
         lib.ifx_gemv_bf16_plan.restype = c_int
+        lib.ifx_attn_decode_plan.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        lib.ifx_attn_decode_plan.restype = c_int
         lib.ifx_attn_prefill_umma.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                               c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
-        lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.ifx_apply_penalties.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                             c_void_p, c_int, c_int, c_void_p]
         lib.ifx_sample.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -410,13 +412,37 @@ def attn_decode_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer:
     return out
 
 
+_decode_plans = {}
+
+
+def attn_decode_splits(n_dec: int, n_heads: int, n_kv: int, head_dim: int, max_keys: int) -> int:
+    """Into how many parts :func:`attn_decode_bf16` is best told to cut the keys
+    (the kernel's own count: every block has a place on the GPU at once)."""
+    key = (n_dec, n_heads, n_kv, head_dim, (max_keys + 63) // 64)
+    if key not in _decode_plans:
+        if len(_decode_plans) > 65536:
+            _decode_plans.clear()
+        s = int(_lib().ifx_attn_decode_plan(n_dec, n_heads, n_kv, head_dim, max_keys))
+        if s < 1:
+            raise KernelError(f"attn_decode_splits: CUDA error {-s}")
+        _decode_plans[key] = s
+    return _decode_plans[key]
+
+
 # --------------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[r] = lowest index of the maximum of logits[r, :] (float32 [R, V])."""
     r, v = logits.shape
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32 and out.numel() >= r,
           "argmax: float32 logits, int32 out")
-    _check(_lib().ifx_argmax(_ptr(logits), logits.stride(0), _ptr(out), r, v, _stream()), "argmax")
+    # a wide row is cut into slices with a block each (then a second launch picks among them)
+    parts = min(64, v // 2048) if r <= 65535 else 1
+    part = None
+    global launch_count
+    if parts > 1:
+        part = torch.empty((r, parts, 2), dtype=torch.int32, device=logits.device)
+        launch_count += 1
+    _check(_lib().ifx_argmax(_ptr(logits), logits.stride(0), _ptr(out), r, v, _ptr(part), parts, _stream()), "argmax")
     return out
 
 

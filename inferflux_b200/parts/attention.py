@@ -135,8 +135,8 @@ class GQAttention(Part):
                                   ctx.block_tables[g], ctx.chunk_tile_entry, ctx.chunk_tile_q0, ctx.n_chunk_tiles,
                                   *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
         if ctx.n_decode:
-            n_splits = decode_splits(ctx.n_decode, self.n_heads, self.n_kv,
-                                     min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len)
+            n_splits = ops.attn_decode_splits(ctx.n_decode, self.n_heads, self.n_kv, self.head_dim,
+                                              min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len)
             part_o = part_ml = None
             if n_splits > 1:
                 rows = ctx.n_decode * self.n_heads * n_splits
@@ -145,16 +145,6 @@ class GQAttention(Part):
             ops.attn_decode_bf16(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
                                  ctx.block_tables[g], ctx.decode_entries, ctx.n_decode, *common, part_o, part_ml,
                                  self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, n_splits)
-
-
-def decode_splits(n_decode: int, n_heads: int, n_kv: int, max_keys: int, target_blocks: int = 296) -> int:
-    """Into how many parts the decode kernel cuts the keys: enough blocks for
-    two per SM (148 SMs), each part at least 256 keys (four 64-key tiles)."""
-    ratio = n_heads // n_kv
-    base = max(1, n_decode * n_kv * ((ratio + 7) // 8))
-    by_blocks = (target_blocks + base - 1) // base
-    by_keys = max(1, max_keys // 256)
-    return max(1, min(by_blocks, by_keys, 64))
 
 
 register_part("mixer", "gqa_attention", GQAttention)

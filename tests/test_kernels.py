@@ -340,6 +340,29 @@ def test_argmax_lowest_index_among_equal_maxima(ops):
     assert out2.tolist() == [300, 300, 300]
 
 
+@pytest.mark.parametrize("v", [4096, 10007, 33333, 152064])
+def test_argmax_of_wide_rows_in_slices(ops, v):
+    """Wide rows are cut into slices (one block each): maxima on the borders of
+    slices, equal maxima in different slices, NaNs, rows that are not 16-byte
+    aligned (an odd row stride)."""
+    parts = min(64, v // 2048)
+    slice_len = ((v + parts - 1) // parts + 3) // 4 * 4
+    for stride in (v, v + 1):
+        buf = _rand((6, stride), torch.float32, 32 + v % 7)
+        logits = buf[:, :v]
+        logits[0, slice_len - 1] = 70.0                      # last element of the first slice
+        logits[1, slice_len] = 70.0                          # first element of the second
+        logits[2, v - 1] = logits[2, slice_len + 5] = 70.0   # equal maxima in two slices: the lower index
+        logits[3, :] = float("nan")
+        logits[3, v - 3] = -5.0                              # the only number of the row
+        logits[4, 17] = float("nan")
+        logits[4, v // 2] = 80.0
+        out = torch.empty(6, dtype=torch.int32, device=DEV)
+        ops.argmax(logits, out)
+        assert out.tolist() == [slice_len - 1, slice_len, slice_len + 5, v - 3, v // 2,
+                                int(torch.argmax(logits[5].cpu()))], (v, stride)
+
+
 def test_penalties(ops):
     v = 1000
     logits = _rand((3, v), torch.float32, 31)
