@@ -41,6 +41,7 @@ def main(argv=None) -> int:
     import torch
     from ..config import EngineConfig, build_spec, load_config
     from ..engine import Model, StepEntry, StepRunner, torch_dtype
+    from ..kernels import ops
 
     os.makedirs(args.out, exist_ok=True)
     if not torch.cuda.is_available():
@@ -72,6 +73,7 @@ def main(argv=None) -> int:
                 os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
             else:
                 torch.cuda.synchronize()
+            ops.check_device_errors(args.device)          # raises if a kernel's bounded wait ran out
         for rid in rec.get("end", []):
             rid = str(rid)
             if runner.has(rid):

@@ -19,6 +19,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Union
 import torch
 
 from ..config import EngineConfig, ModelConfig, build_spec, load_config
+from ..kernels import ops
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .model import Model
@@ -146,6 +147,8 @@ class Engine:
                 for r, t in zip(sampling, ids.tolist()):
                     sampled[r.rid] = t
             finished += self.scheduler.finish_step(plan, sampled)
+        if finished:
+            ops.check_device_errors(self.engine_config.device)    # a kernel's bounded wait ran out: do not hand out its tokens
         return [self._result(r) for r in finished]
 
     def _result(self, r: Request) -> GenerationResult:
@@ -177,6 +180,7 @@ class Engine:
 
     @property
     def stats(self) -> dict:
+        ops.check_device_errors(self.engine_config.device)
         s = dict(self.scheduler.stats)
         s.update(pages_free=[p.num_free for p in self.runner.kv.pools],
                  pages_total=[p.num_pages for p in self.runner.kv.pools],
