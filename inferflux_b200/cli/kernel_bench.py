@@ -74,6 +74,14 @@ class Case:
                             self.extra.append((f"k_splits={s}", lambda i, s=s, outs=outs: ops.gemv_bf16(x, ws[i], None, outs, k_splits=s)))
             else:
                 self.run = None
+                if rows >= 256:
+                    # many rows: the tcgen05 product beside the library's (SwiGLU: against library product + SwiGLU kernel)
+                    outg = torch.empty(rows, n, **bf)
+                    self.flops, self.bytes = 2 * rows * wrows * k, 0
+                    self.extra.append(("tcgen05", lambda i: ops.gemm_umma(x, ws[i], None, outg, swiglu=sw)))
+                    if sw:
+                        gu = torch.empty(rows, wrows, **bf)
+                        self.extra.append(("library + swiglu", lambda i: ops.swiglu(torch.mm(x, ws[i].t(), out=gu), outg)))
             self.extra.append(("library", lambda i: torch.mm(x, ws[i].t())))
         elif name in ("attn_decode", "attn_prefill", "attn_prefill_umma"):
             ps = 16

@@ -110,3 +110,24 @@ inline int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_
   cfg.numAttrs = 1;
   return (int)cudaLaunchKernelEx(&cfg, kern, args...);
 }
+
+// The same with the blocks grouped into thread-block clusters of `cluster` blocks (grid dimensions are
+// multiples of it).
+template <typename Kern, typename... Args>
+inline int launch_pdl_cluster(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, dim3 cluster, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster.x;
+  attr[1].val.clusterDim.y = cluster.y;
+  attr[1].val.clusterDim.z = cluster.z;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, kern, args...);
+}

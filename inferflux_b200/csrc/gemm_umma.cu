@@ -1,0 +1,353 @@
+// Matrix product for many rows of activations (prompt portions) on the fifth-generation tensor
+// cores: out[M, N] = A[M, K] * W[N, K]^T (+ bias), or with a stacked [gate; up] weight
+// out[M, I] = silu(A gate^T) * (A up^T), bfloat16 operands, float32 accumulation in tensor memory.
+//
+// The reference sends every dense projection to cuBLAS and runs SwiGLU as a kernel of its own over
+// the [M, 2I] result (runtime/backends/cuda/native/cublas_gemm.cpp:84-102,
+// runtime/backends/cuda/native/cuda_kernels.cu:137-149).  Here the product is written out so that the
+// activation can sit in its epilogue: the [M, 2I] intermediate never goes to memory.
+//
+// Two blocks on neighbouring SMs form a cluster and share one output tile of 256 rows x 256
+// accumulator columns (cta_group::2); clusters are persistent over the tiles.  Per step of 64 along K
+// each block brings 128 rows of A and 128 of the tile's 256 rows of W into its shared memory by TMA
+// (32 KB, six stages, the 128-byte-swizzle layout the tensor core reads).  Warp 0 of each block issues
+// its TMA loads; warp 1 of the leader (cluster rank 0) issues the MMAs, four tcgen05.mma of M 256, N 256,
+// K 16 per step, which read A and the two halves of W from both blocks' shared memory; each block's
+// tensor memory gets its 128 rows of the result.  A tile takes 256 of the 512 columns, so the epilogue
+// of one tile (warps 2-5: each reads its quarter of the 128 lanes, 32 columns at a time, applies bias or
+// SwiGLU and stores its row's 32 values) runs while the MMAs of the next fill the other 256.  With
+// SwiGLU the leader's half of W is the gate rows and the other block's the up rows of the same 128
+// outputs, so a thread finds gate and up of an output in its own lane.
+//
+// Barriers (same offsets in both blocks): full[s] counts the bytes of both blocks' copies and lives in
+// the leader (the other block's TMA completes on it; no multicast); empty[s] and acc_full[a] are
+// arrived on in both blocks by one tcgen05.commit; acc_empty[a] in the leader counts the 256 epilogue
+// threads of both blocks.  The pair synchronises as a cluster after set-up and before it frees tensor
+// memory, so neither block leaves while the other may still signal it.
+//
+// Every mbarrier wait is bounded: if one runs out the thread sets *error_flag and the block's abort
+// word, the other warps leave their loops, the block waits a moment for TMA copies in flight, and the
+// pair frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace {
+
+constexpr int TK = 64;                  // K per stage: one 128-byte swizzled row of bfloat16
+constexpr int G_WAIT_LIMIT = 1 << 20;   // tries of at most 2 microseconds each
+
+__device__ __forceinline__ unsigned g_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+// false: the wait ran out, or (abort_flag given) another warp of the block gave up
+__device__ __forceinline__ bool g_wait(unsigned bar, unsigned parity, const volatile int* abort_flag) {
+  for (int i = 0; i < G_WAIT_LIMIT; ++i) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");   // a try sleeps 2 microseconds at most
+    if (ok) return true;
+    if (abort_flag && (i & 255) == 255 && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void g_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long g_desc(unsigned saddr) {      // K-major, 128-byte swizzle, 8-row groups of 1024 bytes
+  unsigned long long d = 0;
+  d |= (unsigned long long)((saddr & 0x3FFFF) >> 4);
+  d |= (unsigned long long)(16 >> 4) << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+__device__ __forceinline__ void g_tmem_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename T> __device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int n_valid, bool vec);
+template <> __device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[32], int n_valid, bool vec) {
+  if (vec && n_valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (i < n_valid) dst[i] = v[i];
+  }
+}
+template <> __device__ __forceinline__ void store_row32<bf16>(bf16* dst, const float (&v)[32], int n_valid, bool vec) {
+  if (vec && n_valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 p;
+      __nv_bfloat162 a = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]), b = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+      __nv_bfloat162 c = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]), d = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+      p.x = *reinterpret_cast<unsigned*>(&a); p.y = *reinterpret_cast<unsigned*>(&b);
+      p.z = *reinterpret_cast<unsigned*>(&c); p.w = *reinterpret_cast<unsigned*>(&d);
+      reinterpret_cast<uint4*>(dst)[i] = p;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (i < n_valid) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+constexpr int P_STAGES = 6;
+constexpr int P_HALF_BYTES = 128 * TK * 2;            // 16 KB: 128 rows of 128 bytes
+constexpr int P_STAGE_BYTES = 2 * P_HALF_BYTES;       // this block's rows of A, then its rows of W
+constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + 1024;
+constexpr int P_THREADS = 192;                        // producer warp, MMA warp, 4 epilogue warps
+constexpr unsigned LEADER_MASK = 0xFEFFFFFFu;         // a shared-memory address of this block -> the same place in the pair's leader
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M 256 (over the pair), N 256
+constexpr unsigned P_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(256 >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+
+__device__ __forceinline__ unsigned p_cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void p_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// One TMA box (64 elements along K x 128 rows) whose first element is (k, row), into this block's shared
+// memory; its bytes are counted by the leader's barrier.  The coordinate along K is a multiple of 64
+// elements, so the copy starts on a 128-byte boundary.  No multicast.
+__device__ __forceinline__ void p_tma_load(unsigned dst, const CUtensorMap* map, int k, int row, unsigned leader_bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+               ::"r"(dst), "l"(map), "r"(k), "r"(row), "r"(leader_bar) : "memory");
+}
+__device__ __forceinline__ void p_mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(P_IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void p_commit_both(unsigned bar) {      // arrives on this barrier in both blocks of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+               ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void p_arrive_leader(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(bar & LEADER_MASK) : "memory");
+}
+
+template <bool SWIGLU, typename TOut>
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      TOut* __restrict__ out, long long ldo, const float* __restrict__ bias, int M, int n_out, int K,
+                      int* __restrict__ error_flag) {
+  pdl_enter();
+  extern __shared__ unsigned char g_smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[2 * P_STAGES + 4];    // full[s], empty[s], acc_full[2], acc_empty[2]
+  __shared__ unsigned tmem_slot;
+  __shared__ int abort_s;
+  const unsigned sbase = (g_smem_addr(g_smem_raw) + 1023u) & ~1023u;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const unsigned rank = p_cluster_rank();
+  const bool leader = rank == 0;
+  const unsigned bar_full = g_smem_addr(&bars[0]), bar_empty = g_smem_addr(&bars[P_STAGES]);
+  const unsigned bar_acc_full = g_smem_addr(&bars[2 * P_STAGES]), bar_acc_empty = g_smem_addr(&bars[2 * P_STAGES + 2]);
+  volatile int* abort_flag = &abort_s;
+
+  if (tid == 0) {
+    abort_s = 0;
+    for (int s = 0; s < P_STAGES; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar_full + 8 * s));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar_empty + 8 * s));
+    }
+    for (int a = 0; a < 2; ++a) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar_acc_full + 8 * a));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 256;\n" ::"r"(bar_acc_empty + 8 * a));   // epilogue threads of both blocks
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(g_smem_addr(&tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  p_cluster_sync();                                              // the other block's barriers exist before anything signals them
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem = tmem_slot;
+
+  const int out_cols = SWIGLU ? 128 : 256;
+  const int m_tiles = (M + 255) / 256, n_tiles = (n_out + out_cols - 1) / out_cols;
+  const int tiles = m_tiles * n_tiles, k_steps = (K + TK - 1) / TK;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  bool gave_up = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      unsigned phase = 0;
+      for (int t = pair; t < tiles && !gave_up; t += n_pairs) {
+        const int m0 = (t % m_tiles) * 256 + (int)rank * 128;
+        const int n0 = (t / m_tiles) * out_cols;
+        const int w_row = SWIGLU ? (int)rank * n_out + n0 : n0 + (int)rank * 128;
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!g_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { gave_up = true; break; }
+          const unsigned sa = sbase + stage * P_STAGE_BYTES, sw = sa + P_HALF_BYTES;
+          const unsigned full = (bar_full + 8 * stage) & LEADER_MASK;
+          if (leader) g_expect_tx(bar_full + 8 * stage, 2 * P_STAGE_BYTES);
+          p_tma_load(sa, &map_a, ks * TK, m0, full);
+          p_tma_load(sw, &map_w, ks * TK, w_row, full);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      int stage = 0, count = 0;
+      unsigned phase = 0;
+      for (int t = pair; t < tiles && !gave_up; t += n_pairs, ++count) {
+        const int acc = count & 1;
+        const unsigned acc_parity = (unsigned)(count >> 1) & 1u;
+        if (!g_wait(bar_acc_empty + 8 * acc, acc_parity ^ 1u, abort_flag)) { gave_up = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned d = tmem + (unsigned)(acc * 256);
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!g_wait(bar_full + 8 * stage, phase, abort_flag)) { gave_up = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const unsigned sa = sbase + stage * P_STAGE_BYTES, sw = sa + P_HALF_BYTES;
+#pragma unroll
+          for (int k = 0; k < TK / 16; ++k) p_mma(d, g_desc(sa + k * 32), g_desc(sw + k * 32), (ks | k) != 0);
+          p_commit_both(bar_empty + 8 * stage);                  // both blocks' stage is free once these MMAs have read it
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!gave_up) p_commit_both(bar_acc_full + 8 * acc);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row_in_tile = (int)rank * 128 + quarter * 32 + lane;
+    const bool vec = (ldo % 8 == 0) && ((uintptr_t)out % 16 == 0);
+    int count = 0;
+    for (int t = pair; t < tiles; t += n_pairs, ++count) {
+      const int acc = count & 1;
+      const unsigned acc_parity = (unsigned)(count >> 1) & 1u;
+      const int m0 = (t % m_tiles) * 256, n0 = (t / m_tiles) * out_cols;
+      if (!g_wait(bar_acc_full + 8 * acc, acc_parity, abort_flag)) { gave_up = true; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const unsigned taddr = tmem + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * 256);
+      const int row = m0 + row_in_tile;
+      TOut* orow = out + (size_t)(row < M ? row : 0) * ldo;
+      if (SWIGLU) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float gate[32], up[32];
+          g_tmem_ld32(taddr + c * 32, gate);
+          g_tmem_ld32(taddr + 128 + c * 32, up);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) gate[i] = gate[i] / (1.0f + __expf(-gate[i])) * up[i];
+          const int col = n0 + c * 32;
+          if (row < M && col < n_out) store_row32<TOut>(orow + col, gate, min(32, n_out - col), vec && (col % 8 == 0));
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          float v[32];
+          g_tmem_ld32(taddr + c * 32, v);
+          const int col = n0 + c * 32;
+          if (row < M && col < n_out) {
+            if (bias) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] += col + i < n_out ? bias[col + i] : 0.0f;
+            }
+            store_row32<TOut>(orow + col, v, min(32, n_out - col), vec && (col % 8 == 0));
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      p_arrive_leader(bar_acc_empty + 8 * acc);                  // this thread has read its part of the accumulator
+    }
+  }
+  if (gave_up) {                                                 // a wait ran out: tell everyone, let copies in flight land
+    atomicExch(error_flag, 1);
+    abort_s = 1;
+    __nanosleep(2000000);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  p_cluster_sync();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  }
+  return fn;
+}
+
+// [rows, K] bfloat16, row stride ld elements; boxes of box_rows rows x 64 elements, 128-byte swizzle, zeros outside
+int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+  PFN_cuTensorMapEncodeTiled_v12000 enc = tensor_map_encoder();
+  if (!enc) return IFX_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : IFX_ERR_UNSUPPORTED;
+}
+
+template <bool SWIGLU, typename TOut>
+int launch_gemm_pair(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int n_out,
+                     int K, int* error_flag, cudaStream_t stream) {
+  CUtensorMap map_a, map_w;
+  int rc = make_map(&map_a, A, M, K, lda, 128);
+  if (!rc) rc = make_map(&map_w, W, SWIGLU ? 2ll * n_out : n_out, K, K, 128);
+  if (rc) return rc;
+  auto kern = gemm_umma_pair_kernel<SWIGLU, TOut>;
+  static int sms = 0;
+  if (!sms) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    int dev = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+  }
+  const int out_cols = SWIGLU ? 128 : 256;
+  const int tiles = ((M + 255) / 256) * ((n_out + out_cols - 1) / out_cols);
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_a, map_w, (TOut*)out,
+                          ldo, bias, M, n_out, K, error_flag);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+}  // namespace
+
+// out[M, n_out] = A[M, K] * W^T (+ bias), W [n_out, K] contiguous; or, with swiglu != 0, W [2 * n_out, K] =
+// [gate; up] and out = silu(A gate^T) * (A up^T).  A rows lda elements apart; K and lda multiples of 8;
+// A and W 16-byte aligned.  out_dtype: float32 or bfloat16.  error_flag: a device word set if a bounded
+// wait inside the kernel runs out.
+IFX_API int ifx_gemm_umma(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo,
+                          int out_dtype, int M, int n_out, int K, int swiglu, int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || n_out <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || !error_flag) return IFX_ERR_UNSUPPORTED;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return IFX_ERR_ALIGNMENT;
+  if (swiglu && bias) return IFX_ERR_UNSUPPORTED;
+  if (out_dtype == IFX_BF16)
+    return swiglu ? launch_gemm_pair<true, bf16>(A, lda, W, bias, out, ldo, M, n_out, K, error_flag, stream)
+                  : launch_gemm_pair<false, bf16>(A, lda, W, bias, out, ldo, M, n_out, K, error_flag, stream);
+  if (out_dtype == IFX_F32)
+    return swiglu ? launch_gemm_pair<true, float>(A, lda, W, bias, out, ldo, M, n_out, K, error_flag, stream)
+                  : launch_gemm_pair<false, float>(A, lda, W, bias, out, ldo, M, n_out, K, error_flag, stream);
+  return IFX_ERR_UNSUPPORTED;
+}

@@ -57,6 +57,9 @@ def _lib():
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
         lib.ifx_gemv_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll,
                                       c_int, c_int, c_void_p]
+        lib.ifx_gemm_umma.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
+                                      c_void_p, c_void_p]
+        lib.ifx_gemm_umma.restype = c_int
         lib.ifx_gemv_bf16_plan.argtypes = [c_int, c_int, c_int]
         lib.ifx_gemv_bf16_plan.restype = c_int
         lib.ifx_attn_decode_plan.argtypes = [c_int, c_int, c_int, c_int, c_int]
@@ -256,6 +259,29 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     _check(_lib().ifx_gemv_bf16(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), m, n, k,
                                 x.stride(0) if m > 1 else k, ldo, 1 if swiglu else 0, int(k_splits),
                                 _stream()), "gemv_bf16")
+    return out
+
+
+def gemm_umma(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+              swiglu: bool = False) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) for many rows, on the tcgen05 tensor
+    cores (TMA operands, accumulators in tensor memory), bfloat16 operands, float32
+    accumulation, bfloat16 or float32 result.  With ``swiglu`` w is [2N, K] =
+    [gate; up] and out = silu(x gate^T) * (x up^T), the activation applied in the
+    product's epilogue.  Two SMs share each tile (cta_group::2).  A bounded wait
+    that runs out sets the device's error flag (see :func:`check_device_errors`)."""
+    m, k = x.shape
+    n = out.shape[-1]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous(), "gemm_umma: bfloat16 operands")
+    _need(w.shape == ((2 * n if swiglu else n), k), "gemm_umma: shapes")
+    _need(out.dim() == 2 and out.shape[0] == m and out.stride(1) == 1 and x.stride(1) == 1,
+          "gemm_umma: out [M, N], unit inner strides")
+    _need(k % 8 == 0 and (m == 1 or x.stride(0) % 8 == 0), "gemm_umma: K and the row stride of x must be multiples of 8")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n and not swiglu, "gemm_umma: bias float32 [N]")
+    _check(_lib().ifx_gemm_umma(_ptr(x), x.stride(0) if m > 1 else k, _ptr(w), _ptr(bias), _ptr(out), out.stride(0),
+                                _code(out), m, n, k, 1 if swiglu else 0, _ptr(error_flag(x.device)), _stream()),
+           "gemm_umma")
     return out
 
 

@@ -426,6 +426,51 @@ def test_sample_distribution_and_determinism(ops):
     assert mixed[0] == am and mixed[2] == am and mixed[1] == got[1] and mixed[3] == got[3]
 
 
+@pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 200), (2048, 4608, 3584), (17, 40, 72), (513, 1000, 1096)])
+def test_gemm_umma(ops, m, n, k, odt):
+    """The tcgen05 product against float64, with tiles cut by M, N and K (TMA fills
+    the missing rows and the K tail with zeros), with and without bias."""
+    x, w, b = _rand((m, k), torch.bfloat16, 50), _rand((n, k), torch.bfloat16, 51, 0.1), _rand((n,), torch.float32, 52)
+    want = x.double().cpu() @ w.double().cpu().T
+    for bias in (None, b):
+        out = torch.full((m, n), float("nan"), dtype=odt, device=DEV)
+        ops.gemm_umma(x, w, bias, out)
+        ops.check_device_errors(DEV)
+        _close(out, want + (0 if bias is None else b.double().cpu()), 1e-5 if odt == torch.float32 else 6e-3, "gemm_umma")
+    # rows of a wider buffer as input (a row stride that is not K)
+    wide = _rand((m, k + 24), torch.bfloat16, 53)
+    out = torch.empty((m, n), dtype=odt, device=DEV)
+    ops.gemm_umma(wide[:, 8:8 + k], w, None, out)
+    _close(out, wide[:, 8:8 + k].double().cpu() @ w.double().cpu().T, 1e-5 if odt == torch.float32 else 6e-3, "strided rows")
+
+
+def test_gemm_umma_one_hot(ops):
+    """Each output picks one product: a wrong row, column or K slice of a tile shows as a wrong value."""
+    m, n, k = 512, 768, 256
+    x = torch.zeros((m, k), dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((n, k), dtype=torch.bfloat16, device=DEV)
+    rows = torch.arange(m, device=DEV)
+    x[rows, rows % k] = (1 + rows % 7).to(torch.bfloat16)
+    cols = torch.arange(n, device=DEV)
+    w[cols, (cols * 5) % k] = (1 + cols % 5).to(torch.bfloat16)
+    out = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    ops.gemm_umma(x, w, None, out)
+    ops.check_device_errors(DEV)
+    assert torch.equal(out, x.float() @ w.float().T)
+
+
+@pytest.mark.parametrize("m,inter,k", [(256, 128, 64), (700, 1000, 328), (2048, 18944, 3584)])
+def test_gemm_umma_swiglu(ops, m, inter, k):
+    x, w = _rand((m, k), torch.bfloat16, 54), _rand((2 * inter, k), torch.bfloat16, 55, 0.2)
+    out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_umma(x, w, None, out, swiglu=True)
+    ops.check_device_errors(DEV)
+    gu = x.double().cpu() @ w.double().cpu().T
+    gate, up = gu[:, :inter], gu[:, inter:]
+    _close(out, gate / (1 + torch.exp(-gate)) * up, 6e-3, "gemm_umma swiglu")
+
+
 def test_gemv_plan_depends_on_the_matrix_only(ops):
     """The number of K parts is the kernel's own choice from the matrix sizes; it
     is within bounds, repeatable, and 1 where K is too short to cut."""
