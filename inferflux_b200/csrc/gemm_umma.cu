@@ -109,7 +109,7 @@ constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + 1024;
 constexpr int P_THREADS = 192;                        // producer warp, MMA warp, 4 epilogue warps
 constexpr unsigned LEADER_MASK = 0xFEFFFFFFu;         // a shared-memory address of this block -> the same place in the pair's leader
 // kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M 256 (over the pair), N 256
-constexpr unsigned P_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(256 >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+constexpr unsigned P_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(256 >> 4) << 24);   // N (in eighths) goes to bits 17-22
 
 __device__ __forceinline__ unsigned p_cluster_rank() {
   unsigned r;
@@ -127,9 +127,21 @@ __device__ __forceinline__ void p_tma_load(unsigned dst, const CUtensorMap* map,
   asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                ::"r"(dst), "l"(map), "r"(k), "r"(row), "r"(leader_bar) : "memory");
 }
-__device__ __forceinline__ void p_mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned accumulate) {
+__device__ __forceinline__ void p_mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                      unsigned accumulate) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-               ::"r"(tmem_d), "l"(da), "l"(db), "r"(P_IDESC), "r"(accumulate) : "memory");
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive columns of this thread's lane (the narrow last piece of a tile whose width is not a multiple of 32)
+__device__ __forceinline__ void g_tmem_ld16(unsigned taddr, float (&v)[32]) {
+  unsigned r[16];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { v[i] = __uint_as_float(r[i]); v[16 + i] = 0.0f; }
 }
 __device__ __forceinline__ void p_commit_both(unsigned bar) {      // arrives on this barrier in both blocks of the pair
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
@@ -143,7 +155,7 @@ template <bool SWIGLU, typename TOut>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       TOut* __restrict__ out, long long ldo, const float* __restrict__ bias, int M, int n_out, int K,
-                      int* __restrict__ error_flag) {
+                      int tile_n, int* __restrict__ error_flag) {
   pdl_enter();
   extern __shared__ unsigned char g_smem_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * P_STAGES + 4];    // full[s], empty[s], acc_full[2], acc_empty[2]
@@ -180,10 +192,12 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem = tmem_slot;
 
-  const int out_cols = SWIGLU ? 128 : 256;
+  // tile_n: accumulator columns of a tile (a multiple of 16 up to 256; SwiGLU: 256 = 128 gate + 128 up)
+  const int out_cols = SWIGLU ? 128 : tile_n;
   const int m_tiles = (M + 255) / 256, n_tiles = (n_out + out_cols - 1) / out_cols;
   const int tiles = m_tiles * n_tiles, k_steps = (K + TK - 1) / TK;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int w_half_rows = tile_n / 2;                            // rows of W this block loads per step
   bool gave_up = false;
 
   if (warp == 0) {
@@ -193,12 +207,12 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       for (int t = pair; t < tiles && !gave_up; t += n_pairs) {
         const int m0 = (t % m_tiles) * 256 + (int)rank * 128;
         const int n0 = (t / m_tiles) * out_cols;
-        const int w_row = SWIGLU ? (int)rank * n_out + n0 : n0 + (int)rank * 128;
+        const int w_row = SWIGLU ? (int)rank * n_out + n0 : n0 + (int)rank * w_half_rows;
         for (int ks = 0; ks < k_steps; ++ks) {
           if (!g_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { gave_up = true; break; }
           const unsigned sa = sbase + stage * P_STAGE_BYTES, sw = sa + P_HALF_BYTES;
           const unsigned full = (bar_full + 8 * stage) & LEADER_MASK;
-          if (leader) g_expect_tx(bar_full + 8 * stage, 2 * P_STAGE_BYTES);
+          if (leader) g_expect_tx(bar_full + 8 * stage, 2 * (P_HALF_BYTES + w_half_rows * 128));
           p_tma_load(sa, &map_a, ks * TK, m0, full);
           p_tma_load(sw, &map_w, ks * TK, w_row, full);
           if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
@@ -209,6 +223,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (lane == 0 && leader) {
       int stage = 0, count = 0;
       unsigned phase = 0;
+      const unsigned idesc = P_IDESC | ((unsigned)(tile_n >> 3) << 17);
       for (int t = pair; t < tiles && !gave_up; t += n_pairs, ++count) {
         const int acc = count & 1;
         const unsigned acc_parity = (unsigned)(count >> 1) & 1u;
@@ -220,7 +235,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const unsigned sa = sbase + stage * P_STAGE_BYTES, sw = sa + P_HALF_BYTES;
 #pragma unroll
-          for (int k = 0; k < TK / 16; ++k) p_mma(d, g_desc(sa + k * 32), g_desc(sw + k * 32), (ks | k) != 0);
+          for (int k = 0; k < TK / 16; ++k) p_mma(d, g_desc(sa + k * 32), g_desc(sw + k * 32), idesc, (ks | k) != 0);
           p_commit_both(bar_empty + 8 * stage);                  // both blocks' stage is free once these MMAs have read it
           if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -254,16 +269,17 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c * 32 < tile_n; ++c) {
           float v[32];
-          g_tmem_ld32(taddr + c * 32, v);
+          if (tile_n - c * 32 >= 32) g_tmem_ld32(taddr + c * 32, v);
+          else g_tmem_ld16(taddr + c * 32, v);                   // warp-uniform: the tile's last 16 columns
           const int col = n0 + c * 32;
           if (row < M && col < n_out) {
             if (bias) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] += col + i < n_out ? bias[col + i] : 0.0f;
             }
-            store_row32<TOut>(orow + col, v, min(32, n_out - col), vec && (col % 8 == 0));
+            store_row32<TOut>(orow + col, v, min(min(32, tile_n - c * 32), n_out - col), vec && (col % 8 == 0));
           }
         }
       }
@@ -308,13 +324,24 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
   return r == CUDA_SUCCESS ? 0 : IFX_ERR_UNSUPPORTED;
 }
 
+// Accumulator columns per tile for a plain product: the multiple of 16 (128 to 256) with which the pairs
+// of SMs finish soonest.  The kernel runs at the rate at which shared memory is fed from L2 (about 83 GB/s
+// per SM measured), so a tile costs its 256 rows of A plus its rows of W; wider wins a tie.
+int pick_tile_n(int M, int n_out, int pairs) {
+  const int m_tiles = (M + 255) / 256;
+  int best = 256;
+  long long best_cost = -1;
+  for (int tn = 256; tn >= 128; tn -= 16) {
+    const long long tiles = (long long)m_tiles * ((n_out + tn - 1) / tn);
+    const long long cost = ((tiles + pairs - 1) / pairs) * (256 + tn);
+    if (best_cost < 0 || cost < best_cost) { best = tn; best_cost = cost; }
+  }
+  return best;
+}
+
 template <bool SWIGLU, typename TOut>
 int launch_gemm_pair(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int n_out,
                      int K, int* error_flag, cudaStream_t stream) {
-  CUtensorMap map_a, map_w;
-  int rc = make_map(&map_a, A, M, K, lda, 128);
-  if (!rc) rc = make_map(&map_w, W, SWIGLU ? 2ll * n_out : n_out, K, K, 128);
-  if (rc) return rc;
   auto kern = gemm_umma_pair_kernel<SWIGLU, TOut>;
   static int sms = 0;
   if (!sms) {
@@ -324,11 +351,16 @@ int launch_gemm_pair(const void* A, long long lda, const void* W, const float* b
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
   }
-  const int out_cols = SWIGLU ? 128 : 256;
+  const int tile_n = SWIGLU ? 256 : pick_tile_n(M, n_out, sms / 2);
+  const int out_cols = SWIGLU ? 128 : tile_n;
+  CUtensorMap map_a, map_w;
+  int rc = make_map(&map_a, A, M, K, lda, 128);
+  if (!rc) rc = make_map(&map_w, W, SWIGLU ? 2ll * n_out : n_out, K, K, tile_n / 2);
+  if (rc) return rc;
   const int tiles = ((M + 255) / 256) * ((n_out + out_cols - 1) / out_cols);
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_a, map_w, (TOut*)out,
-                          ldo, bias, M, n_out, K, error_flag);
+                          ldo, bias, M, n_out, K, tile_n, error_flag);
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 }  // namespace

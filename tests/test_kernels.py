@@ -427,7 +427,8 @@ def test_sample_distribution_and_determinism(ops):
 
 
 @pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 200), (2048, 4608, 3584), (17, 40, 72), (513, 1000, 1096)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 200), (2048, 4608, 3584), (17, 40, 72), (513, 1000, 1096),
+                                   (1024, 3584, 512), (2048, 3584, 256)])
 def test_gemm_umma(ops, m, n, k, odt):
     """The tcgen05 product against float64, with tiles cut by M, N and K (TMA fills
     the missing rows and the K tail with zeros), with and without bias."""
