@@ -126,43 +126,53 @@ __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const fl
   bf16* kc = (bf16*)kv.k + page * kv.page_stride + (size_t)off * head_dim;
   bf16* vc = (bf16*)kv.v + page * kv.page_stride + (size_t)off * head_dim;
   const int rot_heads = n_heads + n_kv;
-  for (int w = threadIdx.x; w < rot_heads * hv; w += blockDim.x) {
-    const int h = w / hv, i = (w - h * hv) * 8;
-    const int base = h * head_dim;
-    float x0[8], x1[8], c[8], s[8];
-    unpack8(*reinterpret_cast<const uint4*>(row + base + i), x0);
-    unpack8(*reinterpret_cast<const uint4*>(row + base + half + i), x1);
-    *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(ct + i);
-    *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(ct + i + 4);
-    *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(st + i);
-    *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(st + i + 4);
-    float y0[8], y1[8];
+  const int rot_items = rot_heads * hv, v_items = slot >= 0 ? n_kv * head_dim / 8 : 0;
+  const int vbase = (n_heads + n_kv) * head_dim;
+  // one list of 8-wide items, rotated pairs first and values after them, so that a thread's loads of both
+  // kinds are in flight together
+  for (int w = threadIdx.x; w < rot_items + v_items; w += blockDim.x) {
+    if (w < rot_items) {
+      const int h = w / hv, i = (w - h * hv) * 8;
+      const int base = h * head_dim;
+      float x0[8], x1[8], c[8], s[8], b0[8], b1[8];
+      unpack8(*reinterpret_cast<const uint4*>(row + base + i), x0);
+      unpack8(*reinterpret_cast<const uint4*>(row + base + half + i), x1);
+      *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(ct + i);
+      *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(ct + i + 4);
+      *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(st + i);
+      *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(st + i + 4);
+      if (bias) {                                               // 16-byte aligned: head_dim is a multiple of 16
+        *reinterpret_cast<float4*>(b0) = *reinterpret_cast<const float4*>(bias + base + i);
+        *reinterpret_cast<float4*>(b0 + 4) = *reinterpret_cast<const float4*>(bias + base + i + 4);
+        *reinterpret_cast<float4*>(b1) = *reinterpret_cast<const float4*>(bias + base + half + i);
+        *reinterpret_cast<float4*>(b1 + 4) = *reinterpret_cast<const float4*>(bias + base + half + i + 4);
+      }
+      float y0[8], y1[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float a = x0[k], b = x1[k];
-      if (bias) { a += bias[base + i + k]; b += bias[base + half + i + k]; }
-      y0[k] = a * c[k] - b * s[k];
-      y1[k] = a * s[k] + b * c[k];
-    }
-    const uint4 p0 = pack8(y0), p1 = pack8(y1);
-    if (h < n_heads) {
-      *reinterpret_cast<uint4*>(row + base + i) = p0;
-      *reinterpret_cast<uint4*>(row + base + half + i) = p1;
-    } else if (slot >= 0) {
-      bf16* dst = kc + (size_t)(h - n_heads) * kv.head_stride;
-      *reinterpret_cast<uint4*>(dst + i) = p0;
-      *reinterpret_cast<uint4*>(dst + half + i) = p1;
-    }
-  }
-  if (slot >= 0) {
-    const int vbase = (n_heads + n_kv) * head_dim;
-    for (int w = threadIdx.x; w < n_kv * head_dim / 8; w += blockDim.x) {
-      const int e0 = w * 8, h = e0 / head_dim, d = e0 - h * head_dim;
-      float x[8];
+      for (int k = 0; k < 8; ++k) {
+        float a = x0[k], b = x1[k];
+        if (bias) { a += b0[k]; b += b1[k]; }
+        y0[k] = a * c[k] - b * s[k];
+        y1[k] = a * s[k] + b * c[k];
+      }
+      const uint4 p0 = pack8(y0), p1 = pack8(y1);
+      if (h < n_heads) {
+        *reinterpret_cast<uint4*>(row + base + i) = p0;
+        *reinterpret_cast<uint4*>(row + base + half + i) = p1;
+      } else if (slot >= 0) {
+        bf16* dst = kc + (size_t)(h - n_heads) * kv.head_stride;
+        *reinterpret_cast<uint4*>(dst + i) = p0;
+        *reinterpret_cast<uint4*>(dst + half + i) = p1;
+      }
+    } else {
+      const int e0 = (w - rot_items) * 8, h = e0 / head_dim, d = e0 - h * head_dim;
+      float x[8], bv[8];
       unpack8(*reinterpret_cast<const uint4*>(row + vbase + e0), x);
       if (bias) {
+        *reinterpret_cast<float4*>(bv) = *reinterpret_cast<const float4*>(bias + vbase + e0);
+        *reinterpret_cast<float4*>(bv + 4) = *reinterpret_cast<const float4*>(bias + vbase + e0 + 4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) x[k] += bias[vbase + e0 + k];
+        for (int k = 0; k < 8; ++k) x[k] += bv[k];
       }
       *reinterpret_cast<uint4*>(vc + (size_t)h * kv.head_stride + d) = pack8(x);
     }
@@ -185,12 +195,13 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
   const int work = (n_heads + 2 * n_kv) * head_dim / 2;
   int threads = 64;
   while (threads < 512 && threads * 4 < work) threads <<= 1;
-  const bool aligned = (((uintptr_t)qkv | (uintptr_t)k_layer | (uintptr_t)v_layer | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0
+  const bool aligned = (((uintptr_t)qkv | (uintptr_t)k_layer | (uintptr_t)v_layer | (uintptr_t)cos_t | (uintptr_t)sin_t |
+                         (uintptr_t)bias) & 15) == 0
                        && (page_stride & 7) == 0;
   if (dtype == IFX_BF16 && rot_dim == head_dim && head_dim % 16 == 0 && aligned) {
-    const int work8 = (n_heads + n_kv) * head_dim / 16;
+    const int work8 = (n_heads + n_kv) * head_dim / 16 + n_kv * head_dim / 8;
     int th = 32;
-    while (th < 256 && th < work8) th <<= 1;
+    while (th < 512 && th < work8) th <<= 1;
     ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t, sin_t, slot_map, kv,
                                                                  n_heads, n_kv, head_dim);
     return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
