@@ -109,15 +109,31 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return v;
 }
 
+// 8 values of a row: from the bfloat16 row itself, or the sum (in slice order) of float32 partial sums
+// [n_partials][n_tokens][width] of the product that made it
+__device__ __forceinline__ void load8(const bf16* row, const float* part, int n_partials, long long part_stride, int e,
+                                      float (&f)[8]) {
+  if (!part) { unpack8(*reinterpret_cast<const uint4*>(row + e), f); return; }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) f[k] = 0.0f;
+  for (int p = 0; p < n_partials; ++p) {
+    const float4 a = *reinterpret_cast<const float4*>(part + p * part_stride + e);
+    const float4 b = *reinterpret_cast<const float4*>(part + p * part_stride + e + 4);
+    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w; f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+  }
+}
+
 __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                 const int* __restrict__ slot_map, PagedKV kv,
-                                                int n_heads, int n_kv, int head_dim) {
+                                                int n_heads, int n_kv, int head_dim,
+                                                const float* __restrict__ partials, int n_partials, long long part_stride) {
   pdl_enter();
   const int t = blockIdx.x;
   const int half = head_dim / 2, hv = half / 8;               // 8-wide groups per half head
   const int width = (n_heads + 2 * n_kv) * head_dim;
   bf16* row = qkv + (size_t)t * width;
+  const float* part = partials ? partials + (size_t)t * width : nullptr;
   const float* ct = cos_t + (size_t)t * half;
   const float* st = sin_t + (size_t)t * half;
   const int slot = n_kv ? slot_map[t] : -1;
@@ -135,8 +151,8 @@ __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const fl
       const int h = w / hv, i = (w - h * hv) * 8;
       const int base = h * head_dim;
       float x0[8], x1[8], c[8], s[8], b0[8], b1[8];
-      unpack8(*reinterpret_cast<const uint4*>(row + base + i), x0);
-      unpack8(*reinterpret_cast<const uint4*>(row + base + half + i), x1);
+      load8(row, part, n_partials, part_stride, base + i, x0);
+      load8(row, part, n_partials, part_stride, base + half + i, x1);
       *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(ct + i);
       *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(ct + i + 4);
       *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(st + i);
@@ -167,7 +183,7 @@ __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const fl
     } else {
       const int e0 = (w - rot_items) * 8, h = e0 / head_dim, d = e0 - h * head_dim;
       float x[8], bv[8];
-      unpack8(*reinterpret_cast<const uint4*>(row + vbase + e0), x);
+      load8(row, part, n_partials, part_stride, vbase + e0, x);
       if (bias) {
         *reinterpret_cast<float4*>(bv) = *reinterpret_cast<const float4*>(bias + vbase + e0);
         *reinterpret_cast<float4*>(bv + 4) = *reinterpret_cast<const float4*>(bias + vbase + e0 + 4);
@@ -182,7 +198,7 @@ __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const fl
 IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const float* cos_t, const float* sin_t,
                                   int rot_dim, const int* slot_map, void* k_layer, void* v_layer,
                                   long long page_stride, int page_size, int n_tokens, int n_heads, int n_kv,
-                                  int head_dim, cudaStream_t stream) {
+                                  int head_dim, const float* partials, int n_partials, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   int ifx_rc = 0;
   if (head_dim % 2 || rot_dim % 2 || rot_dim > head_dim || rot_dim < 0) return IFX_ERR_UNSUPPORTED;
@@ -202,10 +218,13 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
     const int work8 = (n_heads + n_kv) * head_dim / 16 + n_kv * head_dim / 8;
     int th = 32;
     while (th < 512 && th < work8) th <<= 1;
+    if (partials && (((uintptr_t)partials & 15) || n_partials < 1)) return IFX_ERR_ALIGNMENT;
     ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t, sin_t, slot_map, kv,
-                                                                 n_heads, n_kv, head_dim);
+                        n_heads, n_kv, head_dim, partials, n_partials,
+                        (long long)n_tokens * (n_heads + 2 * n_kv) * head_dim);
     return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
   }
+  if (partials) return IFX_ERR_UNSUPPORTED;                      // partial sums only on the bfloat16 vector path
   if (dtype == IFX_F32)
     ifx_rc = launch_pdl(qkv_rope_kv_write_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (float*)qkv, bias, cos_t, sin_t, rot_dim / 2, slot_map, kv, n_heads, n_kv, head_dim);
   else if (dtype == IFX_BF16)

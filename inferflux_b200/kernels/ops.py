@@ -44,7 +44,8 @@ def _lib():
         lib.ifx_convert.argtypes = [c_void_p, c_int, c_void_p, c_int, c_ll, c_void_p]
         lib.ifx_rope_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.ifx_qkv_rope_kv_write.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                              c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p]
+                                              c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                              c_int, c_void_p]
         lib.ifx_gemm_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_void_p]
         lib.ifx_attn_paged_generic.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int,
                                                c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -194,9 +195,12 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tenso
 def qkv_rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
                       slot_map: Optional[torch.Tensor], k_layer: Optional[torch.Tensor],
                       v_layer: Optional[torch.Tensor], page_stride: int, page_size: int,
-                      n_heads: int, n_kv: int, head_dim: int) -> None:
+                      n_heads: int, n_kv: int, head_dim: int, partials: Optional[torch.Tensor] = None) -> None:
     """Bias add, rotate-half rotation of q (in place) and k, and the write of k
-    and v into the paged cache at ``slot_map`` (page * page_size + offset)."""
+    and v into the paged cache at ``slot_map`` (page * page_size + offset).
+    With ``partials`` (float32 [S, N, width], bfloat16 qkv, full rotation, head
+    size a multiple of 16) the rows are the sums of the S slices instead of
+    qkv's content, and qkv only receives the rotated q."""
     n, width = qkv.shape
     _need(qkv.is_contiguous() and width == (n_heads + 2 * n_kv) * head_dim, "qkv_rope_kv_write: qkv [N, (nh + 2 nkv) hd]")
     rot_dim = 2 * cos.shape[1]
@@ -208,10 +212,16 @@ def qkv_rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: torc
         _need(slot_map is not None and slot_map.dtype == torch.int32 and slot_map.numel() == n,
               "qkv_rope_kv_write: slot_map int32 [N]")
         _need(k_layer.dtype == qkv.dtype and v_layer.dtype == qkv.dtype, "qkv_rope_kv_write: cache of qkv's type")
+    n_partials = 0
+    if partials is not None:
+        _need(partials.dtype == torch.float32 and partials.is_contiguous() and partials.dim() == 3
+              and tuple(partials.shape[1:]) == (n, width) and qkv.dtype == torch.bfloat16
+              and rot_dim == head_dim and head_dim % 16 == 0, "qkv_rope_kv_write: partial sums float32 [S, N, width]")
+        n_partials = partials.shape[0]
     _check(_lib().ifx_qkv_rope_kv_write(_ptr(qkv), _code(qkv), _ptr(bias), _ptr(cos), _ptr(sin), rot_dim,
                                         _ptr(slot_map) if n_kv else None, _ptr(k_layer) if n_kv else None,
                                         _ptr(v_layer) if n_kv else None, page_stride, page_size, n, n_heads, n_kv,
-                                        head_dim, _stream()), "qkv_rope_kv_write")
+                                        head_dim, _ptr(partials), n_partials, _stream()), "qkv_rope_kv_write")
 
 
 # --------------------------------------------------------------- matrix product

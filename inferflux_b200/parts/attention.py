@@ -25,7 +25,7 @@ import torch
 from ..config.registry import register_part
 from ..kernels import ops
 from ..weights.loader import MATRIX, VECTOR, WeightSpec
-from .base import KVNeed, Part, RunInfo
+from .base import KVNeed, Part, PartialSums, RunInfo
 from .linear import Linear
 
 
@@ -101,16 +101,21 @@ class GQAttention(Part):
         attends over the cache."""
         n = x.shape[0]
         nkv_w = 0 if self.kv_shared else self.n_kv
-        qkv = self.qkv.forward(x)
         if position is not None:
             cos, sin = position
         else:
             cos = sin = torch.empty((n, 0), dtype=torch.float32, device=x.device)
+        # a few rows: the product may come as float32 partial sums, which the kernel below adds up
+        partials = None
+        qkv = self.qkv.forward(x, allow_partials=2 * cos.shape[1] == self.head_dim and self.head_dim % 16 == 0)
+        if isinstance(qkv, PartialSums):
+            partials = qkv.tensor
+            qkv = torch.empty(partials.shape[1:], dtype=x.dtype, device=x.device)
         g = run.kv_group
         k_layer, v_layer, page_stride = ctx.kv.layer_views(g, run.kv_index)
         ops.qkv_rope_kv_write(qkv, self.qkv_bias, cos, sin, ctx.slot_maps[g] if nkv_w else None,
                               k_layer if nkv_w else None, v_layer if nkv_w else None, page_stride,
-                              ctx.page_size, self.n_heads, nkv_w, self.head_dim)
+                              ctx.page_size, self.n_heads, nkv_w, self.head_dim, partials)
         attn = torch.empty((n, self.n_heads * self.head_dim), dtype=qkv.dtype, device=x.device)
         self.attend(qkv, attn, ctx, g, k_layer, v_layer, page_stride)
         return self.o.forward(attn, out_dtype=x.dtype, allow_partials=True)

@@ -321,6 +321,28 @@ def test_attention_long_context_far_key(ops):
 
 
 # --------------------------------------------------------------------- sampling
+def test_qkv_rope_from_partial_sums(ops):
+    """The RoPE + cache-write kernel given float32 partial sums of the product
+    gives what it gives for their sum rounded to bfloat16 up to that rounding,
+    and exactly what it gives when the sum is exact in bfloat16."""
+    nh, nkv, hd, ps, n = 5, 2, 32, 8, 7
+    width = (nh + 2 * nkv) * hd
+    parts = (torch.randint(-8, 9, (3, n, width), generator=torch.Generator().manual_seed(60)).float() / 4).to(DEV)
+    total = parts.sum(0)                                  # multiples of 1/4 below 8: exact in bfloat16
+    bias = _rand((width,), torch.float32, 61)
+    ang = _rand((n, hd // 2), torch.float32, 62)
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    slots = torch.tensor([3, 17, 9, 0, 30, 31, 12], dtype=torch.int32, device=DEV)
+    def run(partials):
+        pool = torch.zeros((4, 1, 2, nkv, ps, hd), dtype=torch.bfloat16, device=DEV)
+        qkv = torch.zeros((n, width), dtype=torch.bfloat16, device=DEV) if partials is not None else total.to(torch.bfloat16)
+        ops.qkv_rope_kv_write(qkv, bias, cos, sin, slots, pool[0, 0, 0], pool[0, 0, 1], pool.stride(0), ps, nh, nkv, hd, partials)
+        return qkv[:, :nh * hd].clone(), pool
+    q1, pool1 = run(None)
+    q2, pool2 = run(parts)
+    assert torch.equal(q1, q2) and torch.equal(pool1, pool2)
+
+
 def test_argmax_lowest_index_among_equal_maxima(ops):
     v = 152064
     logits = _rand((5, v), torch.float32, 30)
