@@ -198,17 +198,22 @@ def main() -> int:
     for _ in range(warmup):
         eng.step()
     torch.cuda.synchronize()
+    e2e_ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     t0 = time.perf_counter()
+    e2e_ev[0].record()
     n_e2e = 0
     while eng.has_work() and n_e2e < args.steps:
         eng.step()                                   # plan, H2D metadata, run, sample, D2H ids
         n_e2e += 1
+    e2e_ev[1].record()
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / max(1, n_e2e)
+    e2e_dev_ms = e2e_ev[0].elapsed_time(e2e_ev[1]) / max(1, n_e2e)
     h2d = runner.slab._used * 4
     while eng.has_work():
         eng.step()
     e2e = {"value": round(batch / (e2e_ms / 1e3), 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "device_ms_per_step": round(e2e_dev_ms, 4),
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
 
     out = {

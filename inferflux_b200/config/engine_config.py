@@ -34,6 +34,7 @@ class EngineConfig:
     mixed_prefill_budget_ratio: float = 1.0  # share of max_batch_tokens that prompts may take beside decodes
     max_model_len: Optional[int] = None     # default: the model's max_position_embeddings
     cuda_graphs: bool = True                # capture decode-only steps (bfloat16 only)
+    pipeline_decode: bool = True            # start a decode step before the one before it has reported its tokens
     seed: int = 0
 
     def validate(self) -> None:

@@ -24,7 +24,19 @@ from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .model import Model
 from .runner import StepRunner, torch_dtype
-from .scheduler import CacheView, Phase, Request, Scheduler, StepPlan
+from ..cache import OutOfPages, OutOfSlots
+from .scheduler import CacheView, Phase, Planned, Request, Scheduler, StepPlan
+
+
+@dataclass
+class _Launched:
+    """A step that has been started: its plan, the requests it samples for, their
+    ids on the device and (once the event has passed) on the host."""
+    plan: StepPlan
+    sampling: List[Request]
+    ids: Optional[torch.Tensor]
+    host: Optional[torch.Tensor]
+    event: Optional[object]
 
 
 @dataclass
@@ -73,6 +85,11 @@ class Engine:
         self.sampler = Sampler(model.spec.vocab_size, engine_config.device, engine_config.seed)
         self._next_id = 0
         self._requests: Dict[Hashable, Request] = {}
+        self._inflight: Optional[_Launched] = None              # a started step whose ids the host has not read yet
+        pinned = torch.device(engine_config.device).type == "cuda"
+        self._id_buffers = [torch.zeros(engine_config.max_batch_size + engine_config.max_seqs, dtype=torch.int32,
+                                        pin_memory=pinned) for _ in range(2)]
+        self._id_turn = 0
 
     # ------------------------------------------------------------ construction
     @classmethod
@@ -124,32 +141,107 @@ class Engine:
         return rid
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     def step(self) -> List[GenerationResult]:
-        """Plan one step, run it, sample; returns the requests finished by it."""
+        """Plan one step, run it, sample; returns the requests found finished.
+
+        The ids sampled by a step are read by the host one call later: a call
+        first starts the next step and only then waits for the previous step's
+        ids, when that next step is known without them (see
+        :meth:`_can_run_ahead`); its token ids then come straight from the
+        sampler's device buffer.  Otherwise the call first reads the ids and
+        plans as usual."""
+        finished: List[Request] = []
+        if self._inflight is not None and self._can_run_ahead():
+            prev = self._inflight
+            try:
+                self._inflight = self._launch(prev.plan, ahead_of=prev)
+            except (OutOfPages, OutOfSlots):
+                self._inflight = None                          # no room: nothing was taken; plan again below
+            finished += self._harvest(prev)
+            if self._inflight is not None:
+                self.scheduler.stats["steps_run_ahead"] = self.scheduler.stats.get("steps_run_ahead", 0) + 1
+                return [self._result(r) for r in finished]
+        elif self._inflight is not None:
+            prev, self._inflight = self._inflight, None
+            finished += self._harvest(prev)
         plan = self.scheduler.schedule()
-        finished = list(plan.finished)
+        finished += plan.finished
         if plan.items:
             self.scheduler.begin_step(plan)
+            self._inflight = self._launch(plan)
+            if not self.engine_config.pipeline_decode:
+                prev, self._inflight = self._inflight, None
+                finished += self._harvest(prev)
+        if finished:
+            ops.check_device_errors(self.engine_config.device)    # a kernel's bounded wait ran out: do not hand out its tokens
+        return [self._result(r) for r in finished]
+
+    def _launch(self, plan: StepPlan, ahead_of: Optional["_Launched"] = None) -> "_Launched":
+        """Start a step: run the plan's tokens, sample, start the copy of the ids
+        to the host.  ``ahead_of``: the step before this one, not yet read; the
+        plan is that step's (the same decoding requests, one token further)."""
+        if ahead_of is not None:
+            reqs = [it.request for it in plan.items]
+            entries = [StepEntry(r.rid, [0], [0]) for r in reqs]
+            logits = self.runner.step(entries, device_tokens=ahead_of.ids)
+            plan = StepPlan(items=[Planned(r, r.computed + 1, 1, True) for r in reqs])
+            sampling, extra = reqs, 1
+        else:
             entries = []
             for it in plan.items:
                 toks = it.request.token_slice(it.start, it.count)
                 entries.append(StepEntry(it.request.rid, toks, [it.count - 1] if it.samples else []))
             logits = self.runner.step(entries)
-            sampling = [it.request for it in plan.items if it.samples]
-            sampled: Dict[Hashable, int] = {}
-            if sampling:
-                ids = self.sampler.sample(
-                    logits, [r.params for r in sampling], [r.seed for r in sampling],
-                    [len(r.output) for r in sampling],
-                    [r.tokens if r.params.has_penalties else () for r in sampling])
-                for r, t in zip(sampling, ids.tolist()):
-                    sampled[r.rid] = t
-            finished += self.scheduler.finish_step(plan, sampled)
-        if finished:
-            ops.check_device_errors(self.engine_config.device)    # a kernel's bounded wait ran out: do not hand out its tokens
-        return [self._result(r) for r in finished]
+            sampling, extra = [it.request for it in plan.items if it.samples], 0
+        ids, host, event = None, None, None
+        if sampling:
+            ids = self.sampler.sample(
+                logits, [r.params for r in sampling], [r.seed for r in sampling],
+                [len(r.output) + extra for r in sampling],
+                [r.tokens if r.params.has_penalties else () for r in sampling])
+            host = self._id_buffers[self._id_turn][:len(sampling)]
+            self._id_turn ^= 1
+            host.copy_(ids, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+        return _Launched(plan, sampling, ids, host, event)
+
+    def _harvest(self, done: "_Launched") -> List[Request]:
+        """Wait for a started step's ids and record the step.  Requests that
+        finished while it was already running (it was started ahead) are
+        skipped: their extra token is dropped."""
+        sampled: Dict[Hashable, int] = {}
+        if done.event is not None:
+            done.event.synchronize()
+            for r, t in zip(done.sampling, done.host.tolist()):
+                sampled[r.rid] = t
+        plan = done.plan
+        if any(it.request.phase is Phase.FINISHED for it in plan.items):
+            plan = StepPlan(items=[it for it in plan.items if it.request.phase is not Phase.FINISHED])
+        return self.scheduler.finish_step(plan, sampled)
+
+    def _can_run_ahead(self) -> bool:
+        """Whether the step after the one in flight is known before that one's
+        ids are: it was a step of decoding requests only, nobody else waits or
+        runs, none of them reaches its token or length limit with the id it is
+        about to get, and none needs its recent tokens on the host (penalties).
+        A request that stops on an end or stop token is found out one step
+        late; that step's token for it is dropped."""
+        if not self.engine_config.pipeline_decode:
+            return False
+        prev = self._inflight
+        sch = self.scheduler
+        if sch.waiting or len(prev.plan.items) != len(sch.running) or len(prev.sampling) != len(prev.plan.items):
+            return False
+        for it in prev.plan.items:
+            r = it.request
+            if it.count != 1 or not it.samples or r.phase is not Phase.RUNNING or r.params.has_penalties:
+                return False
+            if len(r.output) + 2 > r.params.max_tokens or len(r.prompt) + len(r.output) + 2 > self.runner.max_model_len:
+                return False
+        return True
 
     def _result(self, r: Request) -> GenerationResult:
         return GenerationResult(r.rid, len(r.prompt), list(r.output), r.finish_reason or "", r.preemptions)
@@ -163,7 +255,7 @@ class Engine:
             raise ValueError("one SamplingParams per prompt (or one for all)")
         rids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         guard = 0
-        while self.scheduler.has_work():
+        while self.has_work():
             self.step()
             guard += 1
             if guard > 10_000_000:

@@ -91,7 +91,7 @@ class StepRunner:
         return self.kv.can_reserve(rid, n_new)
 
     # ---------------------------------------------------------------- step
-    def _admit(self, entries: Sequence[StepEntry]) -> None:
+    def _admit(self, entries: Sequence[StepEntry], check_tokens: bool = True) -> None:
         """Check the entries, seat new requests and hold pages for the step's
         tokens; raises before anything is taken when they do not fit."""
         if not entries:
@@ -104,7 +104,7 @@ class StepRunner:
             seen.add(e.rid)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
-            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+            if check_tokens and (min(e.tokens) < 0 or max(e.tokens) >= vocab):
                 raise ValueError(f"request {e.rid!r}: a token id is outside the vocabulary [0, {vocab})")
             for p in e.want:
                 if not 0 <= int(p) < len(e.tokens):
@@ -210,17 +210,27 @@ class StepRunner:
         self._admit(entries)
         return self._describe(entries)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the entries' tokens as one batch; float32 logits ``[wanted, vocab]``
         in the order of the entries and of each entry's ``want``.  Raises
         :class:`~inferflux_b200.cache.OutOfPages` (before anything ran) when
         the pools cannot hold the step's tokens.  The logits of a decode-only
-        step live in a buffer that the next such step overwrites."""
-        self._admit(entries)
+        step live in a buffer that the next such step overwrites.
+
+        With ``device_tokens`` (int32 on the device, one per entry, every entry
+        a single token) the token ids are taken from there instead of the
+        entries: the ids a sampler has just written need not visit the host
+        before the next step starts."""
+        self._admit(entries, check_tokens=device_tokens is None)
+        if device_tokens is not None and any(len(e.tokens) != 1 for e in entries):
+            raise ValueError("device_tokens serve entries of one token each")
         if self._graphable(entries):
-            logits = self._step_graph(entries)
+            logits = self._step_graph(entries, device_tokens)
         else:
-            logits = self.model.forward(self._describe(entries))
+            ctx = self._describe(entries)
+            if device_tokens is not None:
+                ctx.token_ids.copy_(device_tokens[:len(entries)])
+            logits = self.model.forward(ctx)
         n = 0
         for e in entries:
             self.kv.advance(e.rid, len(e.tokens))
@@ -240,7 +250,7 @@ class StepRunner:
             return False
         return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
 
-    def _step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _step_graph(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         step = self.GRAPH_WIDTH_STEP
         widths = tuple((max(len(self.kv.block_table(e.rid, g)) for e in entries) + step - 1) // step * step
                        for g in range(self.kv.num_groups))
@@ -252,6 +262,8 @@ class StepRunner:
             r = len(entries)
             slab = MetadataSlab(64 + 16 * r + sum(r * w for w in widths) + 8 * (14 + len(widths)), self.device)
             ctx = self._describe(entries, slab, widths)
+            if device_tokens is not None:
+                ctx.token_ids.copy_(device_tokens[:r])
             logits = self.model.forward(ctx)                 # this step runs eagerly (and warms the libraries up)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -268,6 +280,9 @@ class StepRunner:
                                              sm=[off(t) for t in ctx.slot_maps]))
             return logits
         self._refresh_decode(entries, rec)
+        if device_tokens is not None:
+            at = rec["at"]["tok"]
+            rec["slab"].dev[at:at + len(entries)].copy_(device_tokens[:len(entries)])
         rec["graph"].replay()
         ops.launch_count += rec["launches"]
         self.graph_replays += 1

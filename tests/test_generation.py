@@ -227,3 +227,34 @@ def test_captured_steps_follow_changes_of_the_batch(folders, dtype):
     for _ in range(3):
         decode("cad")                    # rows in another order
     assert eng.runner.graph_replays >= replays + 9
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_gives_the_same_tokens(folders, dtype):
+    """Decode steps are started before the host has read the ids of the step
+    before them.  The tokens are the same as when every step waits for its ids;
+    a request that ends on a stop token is found out one step late, and the token
+    that step made for it is dropped; a request that reaches its token limit is
+    never run past it."""
+    from inferflux_b200 import SamplingParams
+    folder, cfg, w = folders["A"]
+    prompts = [random_tokens(cfg["vocab_size"], n, 140 + n) for n in (6, 19, 11, 30)]
+    plain_run = _engine(folder, dtype, pipeline_decode=False)
+    greedy = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    base = plain_run.generate(prompts, greedy)
+    assert plain_run.stats.get("steps_run_ahead", 0) == 0
+    # request 1 stops on the token it would produce 10th, request 2 after 17 tokens, request 3 samples with a seed
+    params = [greedy,
+              SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True, stop_token_ids=[base[1].tokens[9]]),
+              SamplingParams(temperature=0.0, max_tokens=17, ignore_eos=True),
+              SamplingParams(temperature=0.9, top_p=0.9, seed=5, max_tokens=40, ignore_eos=True)]
+    want = _engine(folder, dtype, pipeline_decode=False).generate(prompts, params)
+    ahead = _engine(folder, dtype)
+    got = ahead.generate(prompts, params)
+    assert ahead.stats["steps_run_ahead"] > 10
+    for a, b in zip(want, got):
+        assert a.tokens == b.tokens and a.finish_reason == b.finish_reason
+    stop_at = base[1].tokens.index(base[1].tokens[9]) + 1
+    assert got[1].finish_reason == "stop" and len(got[1].tokens) == stop_at
+    assert got[2].finish_reason == "length" and len(got[2].tokens) == 17
+    assert ahead.stats["pages_free"] == ahead.stats["pages_total"]
