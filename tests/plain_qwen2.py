@@ -128,11 +128,23 @@ def window_of_layer(cfg: dict, layer: int) -> Optional[int]:
 
 
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
-    """Logits [T, vocab] of a whole sequence.
+    """Logits [T, vocab] of a whole sequence."""
+    return final_hidden(cfg, w, tokens) @ head_weight(cfg, w).T
+
+
+def head_weight(cfg: dict, w: Dict[str, torch.Tensor]) -> torch.Tensor:
+    """The output head: the embedding table when there is no lm_head.weight
+    (runtime/backends/cuda/native/transformer_forward.cu:2178-2183,
+    runtime/backends/cuda/native/weight_map.cpp:33-37)."""
+    return w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") or "lm_head.weight" not in w \
+        else w["lm_head.weight"]
+
+
+def final_hidden(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
+    """The normed hidden states [T, hidden] that the output head multiplies.
     runtime/backends/cuda/native/transformer_forward.cu:1341-2202: embedding (:1376-1387); per layer
     input norm (:1413-1424), attention, residual sum + post-attention norm (:1744-1754), feed-forward,
-    residual sum (:2054-2077); final norm (:2148-2151); output head, the embedding table when there
-    is no lm_head.weight (:2178-2183, runtime/backends/cuda/native/weight_map.cpp:33-37)."""
+    residual sum (:2054-2077); final norm (:2148-2151)."""
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nh)
     d = cfg.get("head_dim") or cfg["hidden_size"] // nh
@@ -146,10 +158,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> tor
         x = x + attention_block(h, w, f"{p}.self_attn", positions, nh, nkv, d, theta, window_of_layer(cfg, i))
         h = rms_norm(x, w[f"{p}.post_attention_layernorm.weight"], eps)
         x = x + mlp_block(h, w, f"{p}.mlp")
-    x = rms_norm(x, w["model.norm.weight"], eps)
-    head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") or "lm_head.weight" not in w \
-        else w["lm_head.weight"]
-    return x @ head.T
+    return rms_norm(x, w["model.norm.weight"], eps)
 
 
 def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], n_new: int) -> List[int]:
