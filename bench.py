@@ -254,6 +254,7 @@ def main() -> int:
         pflops = lin_flops + attn_flops
         out["prefill"] = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
                           "frac": round(pflops / (pms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
+                          "frac_sustained": round(pflops / (pms / 1e3) / 1e12 / peaks["bf16_tflops_sustained"], 4),
                           "tflop": round(pflops / 1e12, 3)}
         points = {}
         for b in (1, 64):

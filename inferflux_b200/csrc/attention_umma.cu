@@ -18,11 +18,11 @@
 //     at a time, so few registers are live), keeps the running maximum and sum,
 //     and writes P = exp(s - max) as packed bfloat16 back into tensor memory
 //     (tcgen05.st), from where the next MMA takes it as its A operand.
-//   * O_tile = P V is 4 tcgen05.mma (M 128, N 128, K 16) with V read in its
-//     natural [key][dim] layout (MN-major B operand) into 128 more columns; the
-//     thread folds it into its float32 row: o = o * alpha + O_tile.  The MMAs of
-//     the next tile's scores are issued together with this tile's P V, so they
-//     run while the threads fold O.
+//   * O += P V is 4 tcgen05.mma (M 128, N 128, K 16) with V read in its natural [key][dim] layout
+//     (MN-major B operand), accumulating over all key tiles in 128 more columns of tensor memory.  A
+//     row's running maximum is moved only when a tile's maximum passes it by more than 8 in exponent
+//     units; then (rarely after the first tiles) the thread scales its row of O in tensor memory.  The
+//     MMAs of the next tile's scores are issued right behind this tile's P V, and one commit covers both.
 // One thread issues the MMAs; tcgen05.commit arrives on an mbarrier that the
 // others wait on.  Two blocks fit an SM (96 KB of shared memory, 256 columns of
 // tensor memory each), so one block's softmax overlaps the other's MMAs.  Every
@@ -140,7 +140,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                          int n_heads, int n_kv, float scale, int window, int* __restrict__ error_flag) {
   pdl_enter();
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_s, bar_o;
+  __shared__ __align__(8) unsigned long long bar_s;
   __shared__ unsigned tmem_slot;
   __shared__ int bt_s[BT_CACHE_U];
   const unsigned sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -163,7 +163,6 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s)));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_o)));
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
@@ -227,20 +226,25 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     issue_qk(0);
   }
 
-  float o[UD];
-#pragma unroll
-  for (int d = 0; d < UD; ++d) o[d] = 0.0f;
   float mrow = -INFINITY, lrow = 0.0f;
   const float sl2 = scale * LOG2E_U;
   const int p_row = pos0 + tid;                                   // this thread's query position
   bool failed = false;
 
+  // O accumulates in tensor memory over all key tiles.  The running maximum of a row is only moved when a
+  // tile's maximum passes it by more than RESCALE_STEP (in exponent units): until then P stays below
+  // 2^RESCALE_STEP, which bfloat16 P and the float32 accumulator hold easily, and the row of O needs no
+  // rescaling.  When it is moved, the thread multiplies its row of O in tensor memory by 2^(old - new).
+  constexpr float RESCALE_STEP = 8.0f;
   for (int i = 0; i < n_t; ++i) {
     const int st = i & 1;
-    float alpha = 1.0f;
-    if (mbar_wait_u(smem_addr(&bar_s), (unsigned)(i & 1))) {
+    // the scores of tile i, and with them P V of tile i - 1; the outcome is made the same for the whole
+    // warp, whose tensor-memory loads and stores below are warp-wide
+    if (__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s), (unsigned)(i & 1)))) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       load_k(i + 2);                                               // the scores are done: this key stage is free
+      if (i >= 1) load_v(i + 1);                                   // P V of tile i - 1 is done: that value stage is free
+      else asm volatile("cp.async.commit_group;\n" ::);
       const int key0 = (t_begin + i) * UN;
       // this thread's row of scores
       float s[UN];
@@ -264,10 +268,14 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 #pragma unroll
       for (int c = 0; c < UN; ++c) mx = fmaxf(mx, s[c]);
       // the running maximum is kept in raw-score units; exponents are taken of (s - m) * scale * log2(e)
-      const float mnew = fmaxf(mrow, mx);
-      const float msc = mnew == -INFINITY ? 0.0f : mnew * sl2;     // a row that has seen nothing yet
-      alpha = ex2(mrow * sl2 - msc);                               // 2^-inf = 0 on the first visible tile
-      mrow = mnew;
+      float alpha = 1.0f;
+      if (mrow == -INFINITY) {
+        mrow = mx;                                                 // nothing accumulated for this row yet
+      } else if ((mx - mrow) * sl2 > RESCALE_STEP) {
+        alpha = ex2((mrow - mx) * sl2);
+        mrow = mx;
+      }
+      const float msc = mrow == -INFINITY ? 0.0f : mrow * sl2;     // a row that has seen nothing yet
       // P = 2^(s * sl2 - msc) as packed bfloat16 into tensor memory
       float ls = 0.0f;
 #pragma unroll
@@ -284,6 +292,24 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                        "r"(pk[6]), "r"(pk[7]) : "memory");
       }
       lrow = lrow * alpha + ls;
+      // a moved maximum: this row of O (complete up to tile i - 1) is scaled down; the loads and stores are
+      // warp-wide, so the warp does it when any of its rows needs it
+      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+        for (int j = 0; j < UD / 32; ++j) {
+          unsigned r[32];
+          tmem_ld32_nowait(tm_o + j * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+                       ::"r"(tm_o + j * 32), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                         "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                       : "memory");
+        }
+      }
       asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
     } else {
       failed = true;
@@ -296,55 +322,47 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const unsigned sv = sv0 + st * SKV_BYTES;
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {                             // O_tile = P V, 4 steps of 16 keys; P from tensor memory
+      for (int kk = 0; kk < 4; ++kk) {                             // O += P V, 4 steps of 16 keys; P from tensor memory
         const unsigned long long db = umma_desc(sv + kk * 16 * 128, UN * 128, 1024);   // leading offset = panel stride
         const unsigned a_t = tmem + TM_P + kk * 8;
-        const unsigned acc = kk > 0;
+        const unsigned acc = (i | kk) != 0;
         asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                      ::"r"(tmem + TM_O), "r"(a_t), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
       }
-      umma_commit(smem_addr(&bar_o));
-      if (i + 1 < n_t) issue_qk(st ^ 1);                           // the next tile's scores run while O is folded
+      if (i + 1 < n_t) issue_qk(st ^ 1);                           // its commit also tells that this P V is done
+      else umma_commit(smem_addr(&bar_s));
     }
-    if (mbar_wait_u(smem_addr(&bar_o), (unsigned)(i & 1))) {
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      load_v(i + 2);                                               // P V is done: this value stage is free
+  }
+  // the last commit (parity n_t & 1) covers the last P V
+  if (!failed && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s), (unsigned)(n_t & 1)))) failed = true;
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");             // nothing of ours is still in flight
+  const int any_failed = __syncthreads_or(failed);
+  if (!any_failed) {
+    const float inv = lrow > 0.0f ? 1.0f / lrow : 0.0f;
+    bf16* dst = out + (size_t)(tok0 + (tid < rows ? tid : 0)) * out_stride + (size_t)head * UD;
 #pragma unroll
-      for (int j = 0; j < UD / 64; ++j) {
-        unsigned r0[32], r1[32];
-        tmem_ld32_nowait(tm_o + j * 64, r0);
-        tmem_ld32_nowait(tm_o + j * 64 + 32, r1);
-        tmem_ld_wait();
+    for (int j = 0; j < UD / 32; ++j) {                            // warp-wide loads; rows beyond the portion are not stored
+      unsigned r[32];
+      tmem_ld32_nowait(tm_o + j * 32, r);
+      tmem_ld_wait();
+      if (tid < rows) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          o[j * 64 + c] = fmaf(o[j * 64 + c], alpha, __uint_as_float(r0[c]));
-          o[j * 64 + 32 + c] = fmaf(o[j * 64 + 32 + c], alpha, __uint_as_float(r1[c]));
+        for (int c = 0; c < 4; ++c) {
+          uint4 v;
+          v.x = pack2(__uint_as_float(r[c * 8]) * inv, __uint_as_float(r[c * 8 + 1]) * inv);
+          v.y = pack2(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv);
+          v.z = pack2(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv);
+          v.w = pack2(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + j * 32 + c * 8) = v;
         }
       }
-    } else {
-      failed = true;
     }
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   }
-  asm volatile("cp.async.wait_group 0;\n" ::: "memory");             // nothing of ours is still in flight
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  const int any_failed = __syncthreads_or(failed);
+  __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;\n" ::"r"(tmem) : "memory");
-  if (any_failed) {
-    if (tid == 0) atomicExch(error_flag, 1);
-    return;
-  }
-  if (tid < rows) {
-    const float inv = lrow > 0.0f ? 1.0f / lrow : 0.0f;
-    bf16* dst = out + (size_t)(tok0 + tid) * out_stride + (size_t)head * UD;
-#pragma unroll
-    for (int c = 0; c < UD / 8; ++c) {
-      uint4 v;
-      v.x = pack2(o[c * 8] * inv, o[c * 8 + 1] * inv);     v.y = pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-      v.z = pack2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); v.w = pack2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-      *reinterpret_cast<uint4*>(dst + c * 8) = v;
-    }
-  }
+  if (any_failed && tid == 0) atomicExch(error_flag, 1);
 }
 }  // namespace
 
