@@ -36,7 +36,7 @@ constexpr int UM = 128;          // query rows per block
 constexpr int UN = 64;           // keys per tile
 constexpr int UD = 128;          // head size
 constexpr int WAIT_LIMIT = 1 << 22;
-constexpr int BT_CACHE_U = 512;  // block-table entries a block keeps in shared memory
+constexpr int BT_CACHE_U = 224;  // block-table entries a block keeps in shared memory (static shared memory stays under 1 KB)
 constexpr float LOG2E_U = 1.4426950408889634f;
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -104,11 +104,15 @@ struct UmmaMeta {
   const int* entry_q_start; const int* entry_q_len; const int* entry_ctx_start;
 };
 
-// Shared memory (1024-byte aligned): Q 32 KB | K 2 x 16 KB | V 2 x 16 KB
+// Shared memory (1024-byte aligned): Q 32 KB | K 3 x 16 KB | V 2 x 16 KB
 constexpr int SQ_BYTES = 2 * UM * 128, SKV_BYTES = 2 * UN * 128;
-constexpr int SMEM_UMMA = SQ_BYTES + 4 * SKV_BYTES + 1024;
-// Tensor memory columns: S 64 | P 32 (64 packed bfloat16) | - | O 128
-constexpr unsigned TM_S = 0, TM_P = 64, TM_O = 128;
+constexpr int K_STAGES = 3, V_STAGES = 2;
+// Two blocks per SM: 2 x (1 KB static + 112 KB dynamic + 1 KB reserved) = 228 KB, all there is.  The dynamic
+// part is declared 1024-byte aligned, so it needs no slack for aligning the swizzled tiles by hand.
+constexpr int SMEM_UMMA = SQ_BYTES + (K_STAGES + V_STAGES) * SKV_BYTES;
+// Tensor memory columns: S of even tiles 64 | S of odd tiles 64 | O 128.  P (64 packed bfloat16 = 32
+// columns) is written over the first half of the scores it was made from.
+constexpr unsigned TM_S = 0, TM_O = 128;
 
 // 64 keys (or values) starting at absolute key index key0 into one stage: row = key, two panels of 64
 // dims, 16-byte chunk c of a 128-byte row stored at c ^ (row & 7).  Keys and values of a tile are loaded
@@ -139,12 +143,16 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                          PagedKV kv, UmmaMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
                          int n_heads, int n_kv, float scale, int window, int* __restrict__ error_flag) {
   pdl_enter();
-  extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_s;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bar_s[2];          // one per buffer of scores
   __shared__ unsigned tmem_slot;
   __shared__ int bt_s[BT_CACHE_U];
-  const unsigned sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
-  const unsigned sq = sbase, sk0 = sq + SQ_BYTES, sv0 = sk0 + 2 * SKV_BYTES;
+  const unsigned sbase = smem_addr(smem_raw);
+  if (sbase & 1023u) {                                          // the swizzled tiles need it; never seen, but never assumed
+    if (threadIdx.x == 0) atomicExch(error_flag, 1);
+    return;
+  }
+  const unsigned sq = sbase, sk0 = sq + SQ_BYTES, sv0 = sk0 + K_STAGES * SKV_BYTES;
   const int tid = threadIdx.x, warp = tid >> 5;
   // tiles run last to first and heads fastest: the longest blocks (of every head) start first
   const int tile = gridDim.y - 1 - blockIdx.y;
@@ -162,7 +170,8 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int t_begin = kfirst / UN, t_end = (kend - 1) / UN, n_t = t_end - t_begin + 1;
 
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s)));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s[1])));
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
@@ -190,40 +199,44 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem = tmem_slot;
   const unsigned lane_base = (unsigned)(warp * 32) << 16;        // this warp's quarter of the 128 lanes
-  const unsigned tm_s = tmem + TM_S + lane_base, tm_p = tmem + TM_P + lane_base, tm_o = tmem + TM_O + lane_base;
+  const unsigned tm_o = tmem + TM_O + lane_base;
 
   constexpr unsigned IDESC_QK = umma_idesc(UM, UN, 0), IDESC_PV = umma_idesc(UM, UD, 1);
-  auto issue_qk = [&](int st) {                                   // S = Q K^T, 8 steps of 16 dims (one thread)
-    const unsigned sk = sk0 + st * SKV_BYTES;
+  // S(t) = Q K(t)^T into the scores buffer t & 1, 8 steps of 16 dims (one thread); the commit that
+  // follows also covers every MMA issued before it
+  auto issue_qk = [&](int t) {
+    const unsigned sk = sk0 + (t % K_STAGES) * SKV_BYTES;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const unsigned long long da = umma_desc(sq + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
       const unsigned long long db = umma_desc(sk + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
-      umma_f16(tmem + TM_S, da, db, IDESC_QK, k > 0);
+      umma_f16(tmem + TM_S + (t & 1) * UN, da, db, IDESC_QK, k > 0);
     }
-    umma_commit(smem_addr(&bar_s));
+    umma_commit(smem_addr(&bar_s[t & 1]));
   };
 
-  // copy groups, in this order: [Q, K0] [V0] [K1] [V1], then K(i+2) after the scores of tile i are done and
-  // V(i+2) after its P V is done; "all but the newest two groups" therefore covers K(i+1) and V(i)
+  // Copy groups, in this order: [Q, K0] [K1] [V0] [K2]; then in iteration i [K(i+3)] once the scores of tile
+  // i are done (that key stage is free) and [V(i+1)] once P V of tile i - 1 is done (that value stage is
+  // free).  At the barrier of iteration i "all but the newest two groups" covers V(i) and K(i+2).
   auto load_k = [&](int t) {
-    if (t < n_t) load_rows64(sk0 + (t & 1) * SKV_BYTES, kbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
+    if (t < n_t) load_rows64(sk0 + (t % K_STAGES) * SKV_BYTES, kbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
     asm volatile("cp.async.commit_group;\n" ::);
   };
   auto load_v = [&](int t) {
-    if (t < n_t) load_rows64(sv0 + (t & 1) * SKV_BYTES, vbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
+    if (t < n_t) load_rows64(sv0 + (t % V_STAGES) * SKV_BYTES, vbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
     asm volatile("cp.async.commit_group;\n" ::);
   };
   load_k(0);
-  load_v(0);
   load_k(1);
-  load_v(1);
-  asm volatile("cp.async.wait_group 3;\n" ::: "memory");           // Q and K0 have landed
+  load_v(0);
+  load_k(2);
+  asm volatile("cp.async.wait_group 2;\n" ::: "memory");           // Q, K0 and K1 have landed
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // ... and are visible to the tensor core
   __syncthreads();
   if (tid == 0) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     issue_qk(0);
+    if (n_t > 1) issue_qk(1);
   }
 
   float mrow = -INFINITY, lrow = 0.0f;
@@ -235,16 +248,18 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   // tile's maximum passes it by more than RESCALE_STEP (in exponent units): until then P stays below
   // 2^RESCALE_STEP, which bfloat16 P and the float32 accumulator hold easily, and the row of O needs no
   // rescaling.  When it is moved, the thread multiplies its row of O in tensor memory by 2^(old - new).
+  //
+  // The scores of tile i + 1 are computed by the tensor core while the threads work on tile i (two buffers
+  // of scores).  MMAs issued in iteration i: P V of tile i, then the scores of tile i + 2, then a commit on
+  // the barrier of buffer i & 1; so that barrier's completion number i / 2 (parity (i >> 1) & 1) says that
+  // the scores of tile i are there, and with them P V up to tile i - 2.
   constexpr float RESCALE_STEP = 8.0f;
   for (int i = 0; i < n_t; ++i) {
-    const int st = i & 1;
-    // the scores of tile i, and with them P V of tile i - 1; the outcome is made the same for the whole
-    // warp, whose tensor-memory loads and stores below are warp-wide
-    if (__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s), (unsigned)(i & 1)))) {
+    const unsigned tm_s = tmem + TM_S + (i & 1) * UN + lane_base;  // scores of this tile; P goes over their first half
+    // the outcome of a wait is made the same for the whole warp, whose tensor-memory loads and stores are warp-wide
+    if (__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[i & 1]), (unsigned)((i >> 1) & 1)))) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      load_k(i + 2);                                               // the scores are done: this key stage is free
-      if (i >= 1) load_v(i + 1);                                   // P V of tile i - 1 is done: that value stage is free
-      else asm volatile("cp.async.commit_group;\n" ::);
+      load_k(i + 3);                                               // the scores are done: this key stage is free
       const int key0 = (t_begin + i) * UN;
       // this thread's row of scores
       float s[UN];
@@ -288,13 +303,21 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
           pk[c] = pack2(p0, p1);
         }
         asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
-                     ::"r"(tm_p + h * 8), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
+                     ::"r"(tm_s + h * 8), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
                        "r"(pk[6]), "r"(pk[7]) : "memory");
       }
       lrow = lrow * alpha + ls;
-      // a moved maximum: this row of O (complete up to tile i - 1) is scaled down; the loads and stores are
-      // warp-wide, so the warp does it when any of its rows needs it
-      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+      // P V of tile i - 1 (issued in the last iteration, long done by now) frees its value stage and makes
+      // O complete up to tile i - 1
+      if (i >= 1) {
+        // (the commit of iteration i - 1: completion number (i - 1) / 2 + 1 of the other buffer's barrier)
+        if (!__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[(i + 1) & 1]), (unsigned)((((i - 1) >> 1) + 1) & 1)))) failed = true;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      }
+      load_v(i + 1);
+      // a moved maximum: this row of O is scaled down; the loads and stores are warp-wide, so the warp does
+      // it when any of its rows needs it
+      if (i > 0 && !failed && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
         for (int j = 0; j < UD / 32; ++j) {
           unsigned r[32];
@@ -313,28 +336,31 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
     } else {
       failed = true;
+      asm volatile("cp.async.commit_group;\n" ::);
+      asm volatile("cp.async.commit_group;\n" ::);
     }
-    asm volatile("cp.async.wait_group 2;\n" ::: "memory");         // K(i+1) and V(i) have landed
+    asm volatile("cp.async.wait_group 2;\n" ::: "memory");         // V(i) and K(i+2) have landed
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     if (__syncthreads_or(failed)) { failed = true; break; }        // P is complete; everyone has read S
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const unsigned sv = sv0 + st * SKV_BYTES;
+      const unsigned sv = sv0 + (i % V_STAGES) * SKV_BYTES;
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {                             // O += P V, 4 steps of 16 keys; P from tensor memory
         const unsigned long long db = umma_desc(sv + kk * 16 * 128, UN * 128, 1024);   // leading offset = panel stride
-        const unsigned a_t = tmem + TM_P + kk * 8;
+        const unsigned a_t = tmem + TM_S + (i & 1) * UN + kk * 8;
         const unsigned acc = (i | kk) != 0;
         asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                      ::"r"(tmem + TM_O), "r"(a_t), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
       }
-      if (i + 1 < n_t) issue_qk(st ^ 1);                           // its commit also tells that this P V is done
-      else umma_commit(smem_addr(&bar_s));
+      if (i + 2 < n_t) issue_qk(i + 2);                            // over the scores (and P) of tile i; its commit covers this P V
+      else umma_commit(smem_addr(&bar_s[i & 1]));
     }
   }
-  // the last commit (parity n_t & 1) covers the last P V
-  if (!failed && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s), (unsigned)(n_t & 1)))) failed = true;
+  // the commit of the last iteration (buffer (n_t - 1) & 1, completion number (n_t - 1) / 2 + 1) covers the last P V
+  if (!failed && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[(n_t - 1) & 1]), (unsigned)((((n_t - 1) >> 1) + 1) & 1))))
+    failed = true;
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");             // nothing of ours is still in flight
   const int any_failed = __syncthreads_or(failed);
