@@ -23,8 +23,9 @@
 //     row's running maximum is moved only when a tile's maximum passes it by more than 8 in exponent
 //     units; then (rarely after the first tiles) the thread scales its row of O in tensor memory.  The
 //     MMAs of the next tile's scores are issued right behind this tile's P V, and one commit covers both.
-// One thread issues the MMAs; tcgen05.commit arrives on an mbarrier that the
-// others wait on.  Two blocks fit an SM (96 KB of shared memory, 256 columns of
+// A fifth warp issues the MMAs (one thread): the softmax threads arrive on an mbarrier when their row of
+// P is written, and wait on the mbarrier that tcgen05.commit arrives on for the next scores, so they never
+// wait for the issuing.  Two blocks fit an SM (96 KB of shared memory, 256 columns of
 // tensor memory each), so one block's softmax overlaps the other's MMAs.  Every
 // mbarrier wait is bounded: if one runs out the block sets *error_flag, waits
 // for its copies in flight, frees its tensor memory and returns.
@@ -107,6 +108,7 @@ struct UmmaMeta {
 // Shared memory (1024-byte aligned): Q 32 KB | K 3 x 16 KB | V 2 x 16 KB
 constexpr int SQ_BYTES = 2 * UM * 128, SKV_BYTES = 2 * UN * 128;
 constexpr int K_STAGES = 3, V_STAGES = 2;
+constexpr int U_THREADS = 160;   // four softmax warps (one thread per query row) and the warp that issues the MMAs
 // Two blocks per SM: 2 x (1 KB static + 112 KB dynamic + 1 KB reserved) = 228 KB, all there is.  The dynamic
 // part is declared 1024-byte aligned, so it needs no slack for aligning the swizzled tiles by hand.
 constexpr int SMEM_UMMA = SQ_BYTES + (K_STAGES + V_STAGES) * SKV_BYTES;
@@ -138,13 +140,14 @@ __device__ __forceinline__ void load_rows64(unsigned sdst, const bf16* base, con
   }
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(U_THREADS, 2)
 attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                          PagedKV kv, UmmaMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
                          int n_heads, int n_kv, float scale, int window, int* __restrict__ error_flag) {
   pdl_enter();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_s[2];          // one per buffer of scores
+  __shared__ __align__(8) unsigned long long bar_s[2];          // per buffer of scores: the tensor core is done
+  __shared__ __align__(8) unsigned long long bar_p[2];          // per buffer of scores: all 128 rows of P are written
   __shared__ unsigned tmem_slot;
   __shared__ int bt_s[BT_CACHE_U];
   const unsigned sbase = smem_addr(smem_raw);
@@ -172,6 +175,8 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s[0])));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s[1])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;\n" ::"r"(smem_addr(&bar_p[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;\n" ::"r"(smem_addr(&bar_p[1])));
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
@@ -182,13 +187,13 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   {
     const int b0 = kfirst >> kv.page_shift, b1 = (kend - 1) >> kv.page_shift;
     if (b1 - b0 < BT_CACHE_U) {
-      for (int i = tid; i <= b1 - b0; i += 128) bt_s[i] = bt[b0 + i];
+      for (int i = tid; i <= b1 - b0; i += U_THREADS) bt_s[i] = bt[b0 + i];
       bt = bt_s;
       bt_first = b0;
     }
   }
   // Q: row r (token tok0 + r), two panels of 64 dims; rows beyond the portion are zero
-  for (int idx = tid; idx < UM * 16; idx += 128) {
+  for (int idx = tid; idx < UM * 16 && tid < 128; idx += 128) {  // copies are the softmax warps' business
     const int r = idx >> 4, c = idx & 15;
     const bool ok = r < rows;
     const bf16* src = q + (size_t)(tok0 + (ok ? r : 0)) * q_stride + (size_t)head * UD + c * 8;
@@ -226,17 +231,46 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     if (t < n_t) load_rows64(sv0 + (t % V_STAGES) * SKV_BYTES, vbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
     asm volatile("cp.async.commit_group;\n" ::);
   };
-  load_k(0);
-  load_k(1);
-  load_v(0);
-  load_k(2);
-  asm volatile("cp.async.wait_group 2;\n" ::: "memory");           // Q, K0 and K1 have landed
-  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // ... and are visible to the tensor core
+  const bool softmax_warp = warp < 4;
+  if (softmax_warp) {
+    load_k(0);
+    load_k(1);
+    load_v(0);
+    load_k(2);
+    asm volatile("cp.async.wait_group 2;\n" ::: "memory");         // Q, K0 and K1 have landed
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); // ... and are visible to the tensor core
+  }
   __syncthreads();
-  if (tid == 0) {
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    issue_qk(0);
-    if (n_t > 1) issue_qk(1);
+  // The fifth warp: one thread issues every MMA.  For tile i it waits until all rows of P are written (and the
+  // copies that the softmax threads waited for before they arrived have landed), then issues P V of tile i
+  // and the scores of tile i + 2, which overwrite the scores and P of tile i.
+  if (!softmax_warp) {
+    bool mma_failed = false;
+    if ((tid & 31) == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      issue_qk(0);
+      if (n_t > 1) issue_qk(1);
+      for (int i = 0; i < n_t; ++i) {
+        if (!mbar_wait_u(smem_addr(&bar_p[i & 1]), (unsigned)((i >> 1) & 1))) { mma_failed = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned sv = sv0 + (i % V_STAGES) * SKV_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {                           // O += P V, 4 steps of 16 keys; P from tensor memory
+          const unsigned long long db = umma_desc(sv + kk * 16 * 128, UN * 128, 1024);   // leading offset = panel stride
+          const unsigned a_t = tmem + TM_S + (i & 1) * UN + kk * 8;
+          const unsigned acc = (i | kk) != 0;
+          asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                       ::"r"(tmem + TM_O), "r"(a_t), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
+        }
+        if (i + 2 < n_t) issue_qk(i + 2);                          // its commit covers this P V as well
+        else umma_commit(smem_addr(&bar_s[i & 1]));
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    const int any = __syncthreads_or(mma_failed);
+    __syncthreads();                                             // (the softmax warps write the output between these two)
+    if (any && tid == 128) atomicExch(error_flag, 1);
+    return;
   }
 
   float mrow = -INFINITY, lrow = 0.0f;
@@ -339,24 +373,11 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       asm volatile("cp.async.commit_group;\n" ::);
       asm volatile("cp.async.commit_group;\n" ::);
     }
+    if (failed) break;                                             // the issuing warp's wait for P will run out too
     asm volatile("cp.async.wait_group 2;\n" ::: "memory");         // V(i) and K(i+2) have landed
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    if (__syncthreads_or(failed)) { failed = true; break; }        // P is complete; everyone has read S
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const unsigned sv = sv0 + (i % V_STAGES) * SKV_BYTES;
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {                             // O += P V, 4 steps of 16 keys; P from tensor memory
-        const unsigned long long db = umma_desc(sv + kk * 16 * 128, UN * 128, 1024);   // leading offset = panel stride
-        const unsigned a_t = tmem + TM_S + (i & 1) * UN + kk * 8;
-        const unsigned acc = (i | kk) != 0;
-        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                     ::"r"(tmem + TM_O), "r"(a_t), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
-      }
-      if (i + 2 < n_t) issue_qk(i + 2);                            // over the scores (and P) of tile i; its commit covers this P V
-      else umma_commit(smem_addr(&bar_s[i & 1]));
-    }
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(&bar_p[i & 1])) : "memory");   // this row of P is written
   }
   // the commit of the last iteration (buffer (n_t - 1) & 1, completion number (n_t - 1) / 2 + 1) covers the last P V
   if (!failed && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[(n_t - 1) & 1]), (unsigned)((((n_t - 1) >> 1) + 1) & 1))))
@@ -413,7 +434,7 @@ IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, 
   UmmaMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_UMMA);
   if (e != cudaSuccess) return (int)e;
-  const int ifx_rc = launch_pdl(attn_prefill_umma_kernel, dim3(n_heads, n_tiles), dim3(128), SMEM_UMMA, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, tile_entry, tile_q0, n_heads, n_kv, scale, window,
+  const int ifx_rc = launch_pdl(attn_prefill_umma_kernel, dim3(n_heads, n_tiles), dim3(U_THREADS), SMEM_UMMA, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, tile_entry, tile_q0, n_heads, n_kv, scale, window,
       error_flag);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
