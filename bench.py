@@ -50,11 +50,19 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-def family_config():
-    """configs[2] of BASELINE.json: the Qwen2.5-7B layer sizes."""
-    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=3584, num_hidden_layers=28,
-                num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
-                vocab_size=152064, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+SIZES = {   # the family's layer sizes that BASELINE.json lists: layers, hidden, heads, kv heads, feed-forward, vocabulary, tied
+    "7b": (28, 3584, 28, 4, 18944, 152064, False),
+    "3b": (36, 2048, 16, 2, 11008, 151936, True),
+    "14b": (48, 5120, 40, 8, 13824, 152064, False),
+}
+
+
+def family_config(size: str = "7b"):
+    """configs[2] of BASELINE.json, the Qwen2.5-7B layer sizes (or, by name, those of its 3B and 14B entries)."""
+    layers, hidden, heads, kv_heads, inter, vocab, tied = SIZES[size]
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=hidden, num_hidden_layers=layers,
+                num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=128, intermediate_size=inter,
+                vocab_size=vocab, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=tied,
                 max_position_embeddings=32768, use_sliding_window=False, hidden_act="silu",
                 torch_dtype="bfloat16")
 
@@ -105,6 +113,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the family size (named in config)")
+    ap.add_argument("--size", default="7b", choices=sorted(SIZES), help="which of the family's layer sizes (default: the 7B ones)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
@@ -125,7 +134,7 @@ def main() -> int:
     from inferflux_b200.kernels import ops
 
     peaks, peaks_from = load_peaks()
-    cfgd = family_config()
+    cfgd = family_config(args.size)
     full_layers = cfgd["num_hidden_layers"]
     if args.layers:
         cfgd["num_hidden_layers"] = args.layers
@@ -217,12 +226,12 @@ def main() -> int:
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
 
     out = {
-        "metric": "decode tokens/s at batch 8, context 4096 (Qwen2.5-7B sizes, random bf16 weights)",
+        "metric": f"decode tokens/s at batch {batch}, context {ctx} (Qwen2.5-{args.size.upper()} sizes, random bf16 weights)",
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), uniform random token ids",
         "impl": "ours",
-        "config": {"model": "Qwen2.5-7B sizes", "layers": layers, "layers_of_family": full_layers, "hidden": h,
+        "config": {"model": f"Qwen2.5-{args.size.upper()} sizes", "layers": layers, "layers_of_family": full_layers, "hidden": h,
                    "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": inter, "vocab": vocab,
                    "global_batch": batch, "seq_len": ctx, "page_size": runner.page_size,
                    "parallelism": "single GPU", "l2": "inputs (weights + cache) exceed L2; no flush",

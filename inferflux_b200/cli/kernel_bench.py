@@ -66,11 +66,11 @@ class Case:
                     # projections whose consumer adds float32 partial sums run with the planned number of K parts
                     planned = ops.gemv_k_splits(n, k)
                     self.note = f"k_splits={planned} (planned)"
-                    outp = torch.empty(planned, rows, n, device=DEV, dtype=torch.float32)
+                    outp = torch.empty((planned, rows, n) if planned > 1 else (rows, n), device=DEV, dtype=torch.float32)
                     self.run = lambda i: ops.gemv_bf16(x, ws[i], None, outp, k_splits=planned)
                     if sweep:
                         for s in range(1, 9):
-                            outs = torch.empty(s, rows, n, device=DEV, dtype=torch.float32)
+                            outs = torch.empty((s, rows, n) if s > 1 else (rows, n), device=DEV, dtype=torch.float32)
                             self.extra.append((f"k_splits={s}", lambda i, s=s, outs=outs: ops.gemv_bf16(x, ws[i], None, outs, k_splits=s)))
             else:
                 self.run = None
