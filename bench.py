@@ -50,7 +50,7 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-SIZES = {   # the family's layer sizes that BASELINE.json lists: layers, hidden, heads, kv heads, feed-forward, vocabulary, tied
+SIZES = {   # layer sizes of three models of the family: layers, hidden, heads, kv heads, feed-forward, vocabulary, tied
     "7b": (28, 3584, 28, 4, 18944, 152064, False),
     "3b": (36, 2048, 16, 2, 11008, 151936, True),
     "14b": (48, 5120, 40, 8, 13824, 152064, False),
@@ -58,7 +58,7 @@ SIZES = {   # the family's layer sizes that BASELINE.json lists: layers, hidden,
 
 
 def family_config(size: str = "7b"):
-    """configs[2] of BASELINE.json, the Qwen2.5-7B layer sizes (or, by name, those of its 3B and 14B entries)."""
+    """A config.json of the Qwen2.5-7B layer sizes (or, by name, of the 3B and 14B ones)."""
     layers, hidden, heads, kv_heads, inter, vocab, tied = SIZES[size]
     return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=hidden, num_hidden_layers=layers,
                 num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=128, intermediate_size=inter,
