@@ -96,6 +96,8 @@ class Model:
             add("norm", layer.feed_forward_norm, layer.prefix)
         add("norm", spec.final_norm)
         add("lm_head", spec.lm_head)
+        for ps in spec.positions.values():               # a position encoding may have weights of its own
+            add("position", ps)
         return list(out.values())
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:

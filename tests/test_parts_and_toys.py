@@ -288,3 +288,167 @@ def test_layer_runs_twice_and_shared_cache(dtype):
         outs.append(runner.step([StepEntry("c", toks[pos:pos + n], list(range(n)))]).clone())
         pos += n
     assert _rel(torch.cat(outs), want) < TOL[dtype]
+
+
+# ------------------------------------------------ a toy feed-forward with routing
+def _register_top2_experts():
+    """A feed-forward that sends every token to its two best of E small experts
+    (router logits and their softmax in float32), defined in this test."""
+    from inferflux_b200.config import register_part
+    from inferflux_b200.parts.base import Part
+    from inferflux_b200.weights.loader import MATRIX, WeightSpec
+
+    class Top2Experts(Part):
+        family = "feed_forward"
+
+        @classmethod
+        def weight_specs(cls, params, prefix):
+            h, i, e = int(params["hidden"]), int(params["intermediate"]), int(params["experts"])
+            n = lambda leaf: cls.full_name(prefix, params, leaf)
+            return [WeightSpec(n("router.weight"), (e, h), MATRIX, std=1.0), WeightSpec(n("up.weight"), (e * i, h), MATRIX),
+                    WeightSpec(n("down.weight"), (e * h, i), MATRIX)]
+
+        def load(self, tensors):
+            n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+            e, h, i = (int(self.params[k]) for k in ("experts", "hidden", "intermediate"))
+            self.router = tensors.pop(n("router.weight")).float()
+            self.up = tensors.pop(n("up.weight")).float().view(e, i, h)
+            self.down = tensors.pop(n("down.weight")).float().view(e, h, i)
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            logits = xf @ self.router.T                                   # [N, E], float32
+            top, idx = torch.topk(logits, 2, dim=-1)
+            gate = torch.softmax(top, dim=-1)
+            out = torch.zeros_like(xf)
+            for k in range(2):
+                up = torch.relu(torch.einsum("nh,nih->ni", xf, self.up[idx[:, k]]))
+                out += gate[:, k:k + 1] * torch.einsum("ni,nhi->nh", up, self.down[idx[:, k]])
+            return out.to(x.dtype)
+
+    register_part("feed_forward", "top2_experts", Top2Experts)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_routed_feed_forward_is_registered_built_and_stepped(dtype):
+    """One layer has the toy routed feed-forward in place of SwiGLU; nothing in
+    the package knows it.  Whole, and in portions mixed with single tokens."""
+    from inferflux_b200.config.spec import LayerSpec, PartSpec
+    from inferflux_b200.engine import StepEntry
+    _register_top2_experts()
+    hidden, experts, inter = 48, 5, 24
+    norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
+    routed = LayerSpec("layers.1", "prenorm",
+                       PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=3, n_kv_heads=1, head_dim=16,
+                                                      qkv_bias=True, o_bias=False, window=None)), norm("n1"),
+                       PartSpec("top2_experts", dict(name="moe", hidden=hidden, intermediate=inter, experts=experts)),
+                       norm("n2"), position="rope")
+    spec = _one_layer_spec(hidden, 3, 1, 16, extra_layers=[routed])
+
+    def plain_forward(w, tokens):
+        t = len(tokens)
+        pos = torch.arange(t)
+        x = plain.embed(w["emb.weight"], tokens)
+        margins = []
+        for layer in ("layers.0", "layers.1"):
+            h = plain.rms_norm(x, w[f"{layer}.n1.weight"], 1e-6)
+            ww = {k.replace(f"{layer}.attn", "a"): v for k, v in w.items()}
+            x = x + plain.attention_block(h, ww, "a", pos, 3, 1, 16, 10000.0, None)
+            h = plain.rms_norm(x, w[f"{layer}.n2.weight"], 1e-6)
+            if layer == "layers.0":
+                x = x + plain.mlp_block(h, w, "layers.0.mlp")
+                continue
+            logits = h @ w["layers.1.moe.router.weight"].T
+            top, idx = torch.topk(logits, 3, dim=-1)
+            margins.append(float((top[:, 1] - top[:, 2]).min()))
+            gate = torch.softmax(top[:, :2], dim=-1)
+            up_w = w["layers.1.moe.up.weight"].view(experts, inter, hidden)
+            down_w = w["layers.1.moe.down.weight"].view(experts, hidden, inter)
+            out = torch.zeros_like(h)
+            for k in range(2):
+                up = torch.relu(torch.einsum("nh,nih->ni", h, up_w[idx[:, k]]))
+                out += gate[:, k:k + 1] * torch.einsum("ni,nhi->nh", up, down_w[idx[:, k]])
+            x = x + out
+        return plain.rms_norm(x, w["final.weight"], 1e-6) @ w["head.weight"].T, min(margins)
+
+    # weights with which no token's second and third router logits lie close (a near tie may go
+    # either way in bfloat16, and then the comparison would say nothing about the engine)
+    toks = torch.randint(0, 50, (37,), generator=torch.Generator().manual_seed(5)).tolist()
+    for seed in range(40, 140):
+        model, runner, w = _build(spec, dtype, seed)
+        want, margin = plain_forward(w, toks)
+        if margin > 0.3:                                 # router logits are of the order of 7 here
+            break
+    else:
+        pytest.fail("no seed with a clear routing margin")
+    got = runner.step([StepEntry("w", toks, list(range(37)))])
+    runner.end("w")
+    assert _rel(got, want) < TOL[dtype]
+    outs, pos = [], 0
+    for n in (5, 1, 1, 20, 2, 8):
+        outs.append(runner.step([StepEntry("c", toks[pos:pos + n], list(range(n)))]).clone())
+        pos += n
+    assert _rel(torch.cat(outs), want) < TOL[dtype]
+
+
+# ------------------------------------------------ a toy position encoding
+def _register_learned_rotary():
+    """Rotary positions whose frequencies are a weight of the model (one per pair
+    of dims) instead of a power law, defined in this test.  The attention part
+    takes its (cos, sin) as it takes the built-in ones."""
+    from inferflux_b200.config import register_part
+    from inferflux_b200.parts.base import Part
+    from inferflux_b200.weights.loader import VECTOR, WeightSpec
+
+    class LearnedRotary(Part):
+        family = "position"
+
+        @classmethod
+        def weight_specs(cls, params, prefix):
+            return [WeightSpec(cls.full_name(prefix, params, "freq"), (int(params["rotary_dim"]) // 2,), VECTOR, std=0.3)]
+
+        def load(self, tensors):
+            self.freq = tensors.pop(self.full_name(self.prefix, self.params, "freq")).double()
+
+        def prepare(self, ctx):
+            a = ctx.positions.double()[:, None] * self.freq[None, :]
+            return torch.cos(a).float(), torch.sin(a).float()
+
+    register_part("position", "learned_rotary", LearnedRotary)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_position_encoding_is_registered_built_and_stepped(dtype):
+    from inferflux_b200.config.spec import LayerSpec, ModelSpec, PartSpec, Run
+    from inferflux_b200.engine import StepEntry
+    _register_learned_rotary()
+    hidden, nh, nkv, hd = 64, 4, 2, 16
+    spec = _one_layer_spec(hidden, nh, nkv, hd)
+    spec.positions["rope"] = PartSpec("learned_rotary", dict(name="pos", rotary_dim=hd))
+    model, runner, w = _build(spec, dtype, 77)
+    assert "pos.freq" in w
+
+    def plain_forward(tokens):
+        t = len(tokens)
+        x = plain.embed(w["emb.weight"], tokens)
+        h = plain.rms_norm(x, w["layers.0.n1.weight"], 1e-6)
+        a = torch.arange(t, dtype=torch.float64)[:, None] * w["pos.freq"][None, :]
+        cos, sin = torch.cos(a), torch.sin(a)
+        p = "layers.0.attn"
+        q = plain.apply_rope_half((h @ w[f"{p}.q_proj.weight"].T + w[f"{p}.q_proj.bias"]).view(t, nh, hd), cos, sin)
+        k = plain.apply_rope_half((h @ w[f"{p}.k_proj.weight"].T + w[f"{p}.k_proj.bias"]).view(t, nkv, hd), cos, sin)
+        v = (h @ w[f"{p}.v_proj.weight"].T + w[f"{p}.v_proj.bias"]).view(t, nkv, hd)
+        x = x + plain.causal_gqa_attention(q, k, v, 1.0 / math.sqrt(hd)).reshape(t, nh * hd) @ w[f"{p}.o_proj.weight"].T
+        x = x + plain.mlp_block(plain.rms_norm(x, w["layers.0.n2.weight"], 1e-6), w, "layers.0.mlp")
+        return plain.rms_norm(x, w["final.weight"], 1e-6) @ w["head.weight"].T
+
+    toks = torch.randint(0, 50, (41,), generator=torch.Generator().manual_seed(6)).tolist()
+    want = plain_forward(toks)
+    got = runner.step([StepEntry("w", toks, list(range(41)))])
+    runner.end("w")
+    assert _rel(got, want) < TOL[dtype]
+    outs, pos = [], 0
+    for n in (3, 30, 1, 1, 6):
+        outs.append(runner.step([StepEntry("c", toks[pos:pos + n], list(range(n)))]).clone())
+        pos += n
+    assert _rel(torch.cat(outs), want) < TOL[dtype]
