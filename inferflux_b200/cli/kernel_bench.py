@@ -6,7 +6,7 @@
 
 ``time`` captures each kernel 20 times into a CUDA graph and times the replay with CUDA events (so the
 host's launch cost is not in the number); operands rotate between buffers larger than L2.  ``launch`` runs
-one kernel a few times eagerly, which is what ``ncu -k regex:... -s 2 -c 1`` wants.  Sizes default to the
+a kernel (and the variants timed beside it) a few times eagerly, which is what ``ncu -k regex:... -s 2 -c 1`` wants.  Sizes default to the
 Qwen2.5-7B layer sizes; ``--sizes hidden,heads,kv_heads,head_dim,intermediate,vocab`` changes them.
 The library product (cuBLAS through torch) is timed beside the weight-streaming kernel for comparison.
 """
@@ -174,10 +174,10 @@ def main(argv=None) -> int:
     sizes = tuple(int(v) for v in args.sizes.split(","))
     if args.mode == "launch":
         case = Case(args.kernel, sizes, args.rows[0], args.context)
-        if case.run is None:
-            case.run = case.extra[-1][1]
-        for i in range(args.repeat):
-            case.run(i % case.n_rot)
+        runs = ([case.run] if case.run else []) + [fn for _, fn in case.extra]     # every variant, so a profiler can pick by kernel name
+        for fn in runs:
+            for i in range(args.repeat):
+                fn(i % case.n_rot)
         torch.cuda.synchronize()
         print(f"launched {args.kernel} {args.repeat} times at rows={args.rows[0]} context={args.context}")
         return 0
