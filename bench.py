@@ -106,6 +106,39 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
+def mixed_workload(args) -> int:
+    """N requests, prompts uniform in 128..2,048 tokens, 256 greedy output tokens each, all handed to
+    Engine.generate at once: the scheduler cuts prompts into portions beside the decoding requests."""
+    import torch
+    from inferflux_b200 import Engine, SamplingParams
+    cfgd = family_config(args.size)
+    if args.layers:
+        cfgd["num_hidden_layers"] = args.layers
+    n = args.mixed
+    gen = torch.Generator().manual_seed(0)
+    lens = torch.randint(128, 2049, (n,), generator=gen).tolist()
+    prompts = [torch.randint(0, cfgd["vocab_size"], (k,), generator=gen).tolist() for k in lens]
+    eng = Engine.from_config(cfgd, seed=0, dtype="bfloat16", kv_cache_tokens=n * 2400, max_seqs=n + 1, max_batch_size=n,
+                             max_batch_tokens=4096, chunked_prefill_tokens=1024, max_model_len=4096)
+    eng.generate([prompts[0][:64]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))    # loads the kernels
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=256, ignore_eos=True))
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    out_tokens = sum(len(r.tokens) for r in res)
+    st = eng.stats
+    print(json.dumps({
+        "metric": f"mixed workload, {n} requests (Qwen2.5-{args.size.upper()} sizes, random bf16 weights)", "impl": "ours",
+        "value": round(out_tokens / dt, 1), "unit": "output tokens/s", "total_tokens_per_s": round((out_tokens + sum(lens)) / dt, 1),
+        "seconds": round(dt, 3), "n_gpus": 1, "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
+        "config": {"model": f"Qwen2.5-{args.size.upper()} sizes", "layers": cfgd["num_hidden_layers"], "requests": n,
+                   "prompt_tokens": sum(lens), "output_tokens": out_tokens, "max_batch_tokens": 4096,
+                   "chunked_prefill_tokens": 1024, "steps": st["steps"], "steps_run_ahead": st.get("steps_run_ahead", 0),
+                   "preemptions": st["preemptions"]}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -117,6 +150,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--mixed", type=int, default=0, metavar="N",
+                    help="instead of the decode step: N requests with prompts of 128 to 2,048 tokens and 256 output "
+                         "tokens each through Engine.generate (chunked prompts beside decoding requests)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -127,6 +163,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.mixed > 0:
+        return mixed_workload(args)
     warmup = max(3, args.warmup)
 
     import torch

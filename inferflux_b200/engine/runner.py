@@ -62,6 +62,7 @@ class StepRunner:
         model.attach_states(self.state_storage)
         self.slab = MetadataSlab(1 << 16, self.device)
         self._graphs = {}
+        self._graph_uses = {}
         self.graph_replays = 0
         self.steps = 0
         self.tokens_run = 0
@@ -242,6 +243,7 @@ class StepRunner:
     # ------------------------------------------------------- captured decode
     GRAPH_WIDTH_STEP = 32      # block-table widths of captured steps are multiples of this many pages
     MAX_GRAPHS = 48
+    CAPTURE_ON_USE = 3         # a shape is captured when it comes the third time; before that its steps run eagerly
 
     def _graphable(self, entries: Sequence[StepEntry]) -> bool:
         """A step of single decoded tokens, each wanting its logits, runs as a
@@ -257,6 +259,17 @@ class StepRunner:
         key = (len(entries), widths)
         rec = self._graphs.get(key)
         if rec is None:
+            # While requests join and leave, many batch sizes come once or twice; capturing costs more than
+            # running such a step eagerly.
+            seen = self._graph_uses.get(key, 0) + 1
+            self._graph_uses[key] = seen
+            if seen < self.CAPTURE_ON_USE:
+                if len(self._graph_uses) > 4096:
+                    self._graph_uses.clear()
+                ctx = self._describe(entries)
+                if device_tokens is not None:
+                    ctx.token_ids.copy_(device_tokens[:len(entries)])
+                return self.model.forward(ctx)
             if len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
             r = len(entries)

@@ -71,7 +71,7 @@ def test_prompts_then_decoding_at_family_sizes(family):
         assert int(ids[0]) == int(torch.argmax(logits[0])) and int(ids[1]) == int(torch.argmax(logits[1]))
         top = float(want_a.max())
         assert float(want_a[0, int(ids[0])]) >= top - 2 * TOL["bfloat16"] * float(want_a.abs().max())
-    assert eng.runner.graph_replays >= 6
+    assert eng.runner.graph_replays >= 4                  # two eager steps, the capture, then replays
     eng.end_request("a")
     eng.end_request("b")
     # a prompt in portions of 128 and 172 tokens gives the same logits as whole

@@ -84,7 +84,7 @@ def test_long_decoding_token_by_token(folders, name, dtype):
     for i in range(3):
         err = np.abs(np.stack(got[i]).astype(np.float64) - refs[i]).max() / np.abs(refs[i]).max()
         assert err <= TOL[dtype], f"request {i}: {err:.3e}"
-    assert eng.runner.graph_replays >= n - 4
+    assert eng.runner.graph_replays >= n - 8             # all but the first steps of the shape and its capture
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -212,7 +212,7 @@ def test_captured_steps_follow_changes_of_the_batch(folders, dtype):
 
     for k, n in (("a", 5), ("b", 17), ("c", 30)):
         prompt(k, n)
-    for _ in range(4):
+    for _ in range(7):
         decode("abc")
     replays = eng.runner.graph_replays
     assert replays >= 3
