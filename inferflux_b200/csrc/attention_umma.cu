@@ -313,9 +313,13 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
           if (!vis) s[c] = -INFINITY;
         }
       }
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, so the maxima do not wait for one another
 #pragma unroll
-      for (int c = 0; c < UN; ++c) mx = fmaxf(mx, s[c]);
+      for (int c = 0; c < UN; c += 4) {
+        mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
+        mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // the running maximum is kept in raw-score units; exponents are taken of (s - m) * scale * log2(e)
       float alpha = 1.0f;
       if (mrow == -INFINITY) {
@@ -326,21 +330,21 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       }
       const float msc = mrow == -INFINITY ? 0.0f : mrow * sl2;     // a row that has seen nothing yet
       // P = 2^(s * sl2 - msc) as packed bfloat16 into tensor memory
-      float ls = 0.0f;
+      float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int h = 0; h < 4; ++h) {
         unsigned pk[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const float p0 = ex2(fmaf(s[h * 16 + 2 * c], sl2, -msc)), p1 = ex2(fmaf(s[h * 16 + 2 * c + 1], sl2, -msc));
-          ls += p0 + p1;
+          ls4[c & 3] += p0 + p1;
           pk[c] = pack2(p0, p1);
         }
         asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
                      ::"r"(tm_s + h * 8), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
                        "r"(pk[6]), "r"(pk[7]) : "memory");
       }
-      lrow = lrow * alpha + ls;
+      lrow = lrow * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
       // P V of tile i - 1 (issued in the last iteration, long done by now) frees its value stage and makes
       // O complete up to tile i - 1
       if (i >= 1) {
