@@ -258,3 +258,48 @@ def test_running_ahead_gives_the_same_tokens(folders, dtype):
     assert got[1].finish_reason == "stop" and len(got[1].tokens) == stop_at
     assert got[2].finish_reason == "length" and len(got[2].tokens) == 17
     assert ahead.stats["pages_free"] == ahead.stats["pages_total"]
+
+
+def test_random_arrivals_preemption_and_running_ahead(folders):
+    """Thirty requests arrive at random steps into a pool that is too small for
+    them (so the youngest give way and start over), some stop on a stop token,
+    some at their token limit, some sample with a seed.  In float32 a request's
+    tokens do not depend on its company, so every request must come out as when
+    it runs alone in a roomy engine that waits for every step's ids."""
+    import random
+    from inferflux_b200 import SamplingParams
+    folder, cfg, w = folders["B"]
+    rng = random.Random(7)
+    n = 30
+    prompts = [random_tokens(cfg["vocab_size"], rng.randint(1, 90), 300 + i) for i in range(n)]
+    params = []
+    for i in range(n):
+        kind = i % 3
+        if kind == 0:
+            params.append(SamplingParams(temperature=0.0, max_tokens=rng.randint(1, 40), ignore_eos=True))
+        elif kind == 1:
+            params.append(SamplingParams(temperature=0.7, top_k=20, seed=100 + i, max_tokens=rng.randint(5, 40), ignore_eos=True))
+        else:
+            params.append(SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True,
+                                         stop_token_ids=[rng.randrange(cfg["vocab_size"]) for _ in range(60)]))
+    alone = []
+    for p, sp in zip(prompts, params):
+        alone.append(_engine(folder, "float32", pipeline_decode=False).generate([p], sp)[0])
+    eng = _engine(folder, "float32", kv_cache_tokens=400, max_seqs=6, chunked_prefill_tokens=24, max_batch_tokens=64)
+    arrive = sorted(rng.randint(0, 60) for _ in range(n))
+    done, step, nxt = {}, 0, 0
+    while nxt < n or eng.has_work():
+        while nxt < n and arrive[nxt] <= step:
+            eng.add_request(prompts[nxt], params[nxt], rid=nxt)
+            nxt += 1
+        for r in eng.step():
+            done[r.rid] = r
+        step += 1
+        assert step < 5000
+    assert len(done) == n
+    st = eng.stats
+    assert st["preemptions"] > 0 and st.get("steps_run_ahead", 0) > 0
+    for i in range(n):
+        assert done[i].tokens == alone[i].tokens and done[i].finish_reason == alone[i].finish_reason, i
+    assert st["pages_free"] == st["pages_total"]
+    eng.runner.kv.check(), eng.runner.slots.check()
