@@ -128,11 +128,19 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
                        long long partial_stride, const float* __restrict__ weight, float eps,
                        TO* __restrict__ out, const int* __restrict__ rows, int hidden, int write_residual) {
-  pdl_enter();
+  // the norm's weights are parameters: they are loaded before this kernel waits for the one before it
+  pdl_launch_dependents();
   __shared__ float red[32];
+  const int groups = hidden >> 2;
+  float4 wv[VT];
+#pragma unroll
+  for (int j = 0; j < VT; ++j) {
+    const int gidx = threadIdx.x + j * 256;
+    wv[j] = (out && gidx < groups) ? Vec4<float>::load(weight + 4 * gidx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
   const int src = rows ? rows[blockIdx.x] : blockIdx.x;
   float* r = residual + (size_t)src * hidden;
-  const int groups = hidden >> 2;
   float4 v[VT];
   float ss = 0.0f;
 #pragma unroll
@@ -160,7 +168,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
     if (gidx < groups) {
       if (write_residual) Vec4<float>::store(r + 4 * gidx, v[j]);
       if (o) {
-        const float4 w = Vec4<float>::load(weight + 4 * gidx);
+        const float4 w = wv[j];
         Vec4<TO>::store(o + 4 * gidx, make_float4(v[j].x * rstd * w.x, v[j].y * rstd * w.y,
                                                   v[j].z * rstd * w.z, v[j].w * rstd * w.w));
       }
