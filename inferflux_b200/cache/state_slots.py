@@ -15,7 +15,7 @@ slab ``[token | n_past | seq_id | kv_len] x max_batch``
 """
 from __future__ import annotations
 
-from typing import Dict, Hashable, List, Sequence, Tuple
+from typing import Dict, Hashable, List, Sequence
 
 
 class OutOfSlots(RuntimeError):

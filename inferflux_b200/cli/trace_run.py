@@ -37,7 +37,6 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
-    import numpy as np
     import torch
     from ..config import EngineConfig, build_spec, load_config
     from ..engine import Model, StepEntry, StepRunner, torch_dtype

@@ -13,7 +13,7 @@ the per-layer list here replaces that.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Optional
 
 
 @dataclass(frozen=True)

@@ -13,7 +13,7 @@ the last token only, runtime/backends/cuda/native/transformer_forward.cu:2105-21
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Dict, Hashable, List, Sequence, Tuple
 
 import torch
 

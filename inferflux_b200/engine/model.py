@@ -9,7 +9,7 @@ prompt and :2261-3358 for a decode batch.)
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List
 
 import torch
 

@@ -13,7 +13,7 @@ logits.
 """
 from __future__ import annotations
 
-from typing import Dict, Hashable, List, Optional, Sequence
+from typing import Hashable, Optional, Sequence
 
 import numpy as np
 import torch

@@ -10,7 +10,7 @@ transformer_forward.cu:2178-2189).
 """
 from __future__ import annotations
 
-from typing import Any, Dict, List
+from typing import Dict, List
 
 import torch
 

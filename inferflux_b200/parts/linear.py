@@ -4,7 +4,7 @@ The reference issues one cuBLAS call per projection with float32 accumulation
 (runtime/backends/cuda/native/cublas_gemm.cpp:84-102, ``C[M,N] = A[M,K] *
 B[N,K]^T``).  Here a float32 weight goes through the FFMA kernel of the 32-bit
 path; a bfloat16 weight goes through the library (cuBLAS via ``torch.mm``) for
-many rows and through the weight-streaming kernel (gemv_bf16.cu) for up to 32
+many rows and through the weight-streaming kernel (gemv_bf16.cu) for up to 8
 rows.  This is not a registered part: mixers and feed-forwards own their
 Linears.
 """

@@ -11,7 +11,6 @@ once per step in double precision and rounded to float32.
 """
 from __future__ import annotations
 
-from typing import Any, Dict
 
 import torch
 

@@ -7,7 +7,7 @@ only on its own logits, parameters, seed and token index, never on the batch.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 
