@@ -36,7 +36,7 @@ namespace {
 constexpr int UM = 128;          // query rows per block
 constexpr int UN = 64;           // keys per tile
 constexpr int UD = 128;          // head size
-constexpr int WAIT_LIMIT = 1 << 22;
+constexpr int WAIT_LIMIT = 1 << 20;   // tries of at most 2 microseconds each
 constexpr int BT_CACHE_U = 224;  // block-table entries a block keeps in shared memory (static shared memory stays under 1 KB)
 constexpr float LOG2E_U = 1.4426950408889634f;
 
@@ -47,8 +47,8 @@ __device__ __forceinline__ void cp_async16_u(unsigned dst, const void* src, bool
 }
 __device__ __forceinline__ bool mbar_try_wait_u(unsigned bar, unsigned parity) {
   unsigned ok;
-  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");   // a try sleeps 2 microseconds at most
   return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_u(unsigned bar, unsigned parity) {
