@@ -95,6 +95,25 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// two float32 in one 64-bit register, and arithmetic on both at once
+__device__ __forceinline__ unsigned long long pair_f32(float lo, float hi) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpair_f32(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ unsigned pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -330,21 +349,29 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       }
       const float msc = mrow == -INFINITY ? 0.0f : mrow * sl2;     // a row that has seen nothing yet
       // P = 2^(s * sl2 - msc) as packed bfloat16 into tensor memory
-      float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      // exponents and the row sum in packed pairs of float32 (one instruction for two values)
+      const unsigned long long sl2x2 = pair_f32(sl2, sl2), nmx2 = pair_f32(-msc, -msc);
+      unsigned long long ls4[4] = {0ull, 0ull, 0ull, 0ull};        // four chains of (0.0f, 0.0f) sums
 #pragma unroll
       for (int h = 0; h < 4; ++h) {
         unsigned pk[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const float p0 = ex2(fmaf(s[h * 16 + 2 * c], sl2, -msc)), p1 = ex2(fmaf(s[h * 16 + 2 * c + 1], sl2, -msc));
-          ls4[c & 3] += p0 + p1;
+          float e0, e1;
+          unpair_f32(fma_f32x2(pair_f32(s[h * 16 + 2 * c], s[h * 16 + 2 * c + 1]), sl2x2, nmx2), e0, e1);
+          const float p0 = ex2(e0), p1 = ex2(e1);
+          ls4[c & 3] = add_f32x2(ls4[c & 3], pair_f32(p0, p1));
           pk[c] = pack2(p0, p1);
         }
         asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
                      ::"r"(tm_s + h * 8), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
                        "r"(pk[6]), "r"(pk[7]) : "memory");
       }
-      lrow = lrow * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
+      {
+        float lo, hi;
+        unpair_f32(add_f32x2(add_f32x2(ls4[0], ls4[1]), add_f32x2(ls4[2], ls4[3])), lo, hi);
+        lrow = lrow * alpha + (lo + hi);
+      }
       // P V of tile i - 1 (issued in the last iteration, long done by now) frees its value stage and makes
       // O complete up to tile i - 1
       if (i >= 1) {
