@@ -20,7 +20,7 @@ from ..config.registry import register_part
 from ..kernels import ops
 from ..weights.loader import MATRIX, WeightSpec
 from .base import Part
-from .linear import GEMV_ROWS, Linear
+from .linear import Linear
 
 
 FUSED_PRODUCT_ROWS = 128   # above this many rows gate/up + activation run as one tcgen05 product (measured: 256 rows 63 us
@@ -61,7 +61,7 @@ class SwiGLU(Part):
         w = self.gate_up.weight
         act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
         fused = w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and self.hidden % 8 == 0
-        if fused and x.shape[0] <= GEMV_ROWS:
+        if fused and x.shape[0] <= ops.GEMV_MAX_ROWS:         # (up to 16 rows the fused kernel beats library product + activation)
             ops.gemv_bf16(x, w, None, act, swiglu=True)       # product and activation in one kernel
         elif fused and x.is_contiguous() and x.shape[0] > FUSED_PRODUCT_ROWS:
             ops.gemm_umma(x, w, None, act, swiglu=True)       # many rows: tcgen05 product, activation in its epilogue
