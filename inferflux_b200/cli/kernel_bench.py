@@ -126,9 +126,14 @@ class Case:
                 # causal: query i sees ctx - q_len + i + 1 keys
                 keys = sum(ctx - q_len + i + 1 for i in range(q_len))
                 self.flops = 2 * 2 * nh * hd * keys
+                extra = ()
+                if umma:
+                    splits = ops.attn_prefill_umma_splits(len(tiles), nh, ctx)
+                    self.note = f"splits={splits}"
+                    extra = (splits,)
                 self.run = lambda i: kernel(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
                                                            pools[i].stride(0), ps, bt, te, tq, len(tiles), qs, ql, cs, nh,
-                                                           nkv, hd, scale, 0)
+                                                           nkv, hd, scale, 0, *extra)
         elif name == "add_rmsnorm":
             res, delta = torch.randn(rows, h, device=DEV), torch.randn(rows, h, **bf)
             w, o = torch.ones(h, device=DEV), torch.empty(rows, h, **bf)

@@ -162,7 +162,8 @@ __device__ __forceinline__ void load_rows64(unsigned sdst, const bf16* base, con
 __global__ void __launch_bounds__(U_THREADS, 2)
 attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                          PagedKV kv, UmmaMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
-                         int n_heads, int n_kv, float scale, int window, int* __restrict__ error_flag) {
+                         int n_heads, int n_kv, float scale, int window, int* __restrict__ error_flag,
+                         float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
   pdl_enter();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bar_s[2];          // per buffer of scores: the tensor core is done
@@ -189,7 +190,21 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const bf16* vbase = (const bf16*)kv.v + (size_t)kvh * kv.head_stride;
   const int kend = pos0 + rows;                                  // keys [.., kend) may be seen
   const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the first row may see
-  const int t_begin = kfirst / UN, t_end = (kend - 1) / UN, n_t = t_end - t_begin + 1;
+  // gridDim.z > 1: the key tiles are cut into n_splits consecutive parts, one block each; the parts leave
+  // their unnormalised O and (maximum, sum) in scratch for the merge kernel.  Few query tiles over a long
+  // context (a short portion of a long prompt) would otherwise leave most of the GPU idle.
+  const int split = blockIdx.z;
+  const int t_all0 = kfirst / UN, n_all = (kend - 1) / UN - t_all0 + 1;
+  const int per_split = (n_all + n_splits - 1) / n_splits;
+  const int t_begin = t_all0 + split * per_split, n_t = min(per_split, n_all - split * per_split);
+  const size_t part_row0 = (((size_t)tile * n_heads + head) * n_splits + split) * UM;
+  if (n_t <= 0) {                                                // (block-uniform) nothing to do: a part that adds nothing
+    if (tid < rows) {
+      part_ml[(part_row0 + tid) * 2] = -INFINITY;
+      part_ml[(part_row0 + tid) * 2 + 1] = 0.0f;
+    }
+    return;
+  }
 
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s[0])));
@@ -204,7 +219,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   }
   int bt_first = 0;
   {
-    const int b0 = kfirst >> kv.page_shift, b1 = (kend - 1) >> kv.page_shift;
+    const int b0 = max(kfirst, t_begin * UN) >> kv.page_shift, b1 = (min(kend, (t_begin + n_t) * UN) - 1) >> kv.page_shift;
     if (b1 - b0 < BT_CACHE_U) {
       for (int i = tid; i <= b1 - b0; i += U_THREADS) bt_s[i] = bt[b0 + i];
       bt = bt_s;
@@ -416,7 +431,25 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");             // nothing of ours is still in flight
   const int any_failed = __syncthreads_or(failed);
-  if (!any_failed) {
+  if (!any_failed && n_splits > 1) {
+    // unnormalised O, and the row's maximum (in exponent units) and sum, for the merge kernel
+    float* po = part_o + (part_row0 + (tid < rows ? tid : 0)) * UD;
+#pragma unroll
+    for (int j = 0; j < UD / 32; ++j) {
+      unsigned r[32];
+      tmem_ld32_nowait(tm_o + j * 32, r);
+      tmem_ld_wait();
+      if (tid < rows) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(po + j * 32 + c * 4) = make_uint4(r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
+      }
+    }
+    if (tid < rows) {
+      part_ml[(part_row0 + tid) * 2] = mrow == -INFINITY ? -INFINITY : mrow * sl2;
+      part_ml[(part_row0 + tid) * 2 + 1] = lrow;
+    }
+  } else if (!any_failed) {
     const float inv = lrow > 0.0f ? 1.0f / lrow : 0.0f;
     bf16* dst = out + (size_t)(tok0 + (tid < rows ? tid : 0)) * out_stride + (size_t)head * UD;
 #pragma unroll
@@ -442,19 +475,94 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;\n" ::"r"(tmem) : "memory");
   if (any_failed && tid == 0) atomicExch(error_flag, 1);
 }
+
+// The parts of a query tile's keys put together: block (head, tile, group of MERGE_ROWS rows), thread d takes
+// column d of the group's rows.  The (maximum, sum) pairs of the group go through shared memory, where every
+// thread finds each part's factor; the loads of O of different rows do not wait for one another.
+constexpr int MERGE_ROWS = 8, MERGE_MAX_SPLITS = 64;
+__global__ void __launch_bounds__(UD)
+attn_prefill_umma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                               bf16* __restrict__ out, long long out_stride, UmmaMeta m,
+                               const int* __restrict__ tile_entry, const int* __restrict__ tile_q0, int n_heads, int n_splits) {
+  pdl_enter();
+  __shared__ float ml_s[MERGE_ROWS][MERGE_MAX_SPLITS][2];
+  const int head = blockIdx.x, tile = blockIdx.y, r0 = blockIdx.z * MERGE_ROWS, d = threadIdx.x;
+  const int e = tile_entry[tile], q0 = tile_q0[tile];
+  const int rows = min(UM, m.entry_q_len[e] - q0);
+  if (r0 >= rows) return;
+  const int tok0 = m.entry_q_start[e] + q0;
+  const size_t base = ((size_t)tile * n_heads + head) * n_splits * UM;
+  for (int i = threadIdx.x; i < MERGE_ROWS * n_splits; i += UD) {
+    const int rr = i / n_splits, sp = i - rr * n_splits;
+    const float2 v = r0 + rr < rows ? *reinterpret_cast<const float2*>(part_ml + (base + (size_t)sp * UM + r0 + rr) * 2)
+                                    : make_float2(-INFINITY, 0.0f);
+    ml_s[rr][sp][0] = v.x;
+    ml_s[rr][sp][1] = v.y;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int rr = 0; rr < MERGE_ROWS; ++rr) {
+    const int r = r0 + rr;
+    if (r >= rows) continue;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, ml_s[rr][sp][0]);
+    float l = 0.0f, acc = 0.0f;
+    for (int sp = 0; sp < n_splits; ++sp) {                       // always in the order of the parts
+      const float ms = ml_s[rr][sp][0];
+      if (ms == -INFINITY) continue;                               // a part that saw nothing (its O was not written)
+      const float f = ex2(ms - mm);
+      l += ml_s[rr][sp][1] * f;
+      acc += part_o[(base + (size_t)sp * UM + r) * UD + d] * f;
+    }
+    out[(size_t)(tok0 + r) * out_stride + (size_t)head * UD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+  }
+}
 }  // namespace
+
+// Into how many parts the keys of the query tiles are best cut: 1 when the tiles alone fill the GPU, else as
+// many as give every block a place at once, each part at least 8 key tiles of 64.
+IFX_API int ifx_attn_prefill_umma_plan(int n_tiles, int n_heads, int max_key_tiles) {
+  if (n_tiles < 1 || n_heads < 1) return 1;
+  static int resident = 0;
+  if (!resident) {
+    // Blocks per SM by shared memory and registers.  (The occupancy query answers 1 for this kernel, whose
+    // two blocks take an SM's shared memory to the byte, while two do run side by side.)
+    int dev = 0, sms = 0, smem_sm = 0, smem_reserved = 0, regs_sm = 0;
+    cudaFuncAttributes fa;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&smem_reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev) != cudaSuccess ||
+        cudaFuncGetAttributes(&fa, attn_prefill_umma_kernel) != cudaSuccess)
+      return 1;
+    const int by_smem = smem_sm / (SMEM_UMMA + (int)fa.sharedSizeBytes + smem_reserved);
+    const int by_regs = regs_sm / (fa.numRegs * U_THREADS > 0 ? fa.numRegs * U_THREADS : 1);
+    const int per_sm = by_smem < by_regs ? by_smem : by_regs;
+    resident = per_sm * sms > 0 ? per_sm * sms : sms;
+  }
+  const long long blocks = (long long)n_tiles * n_heads;
+  int s = (int)(resident / blocks);
+  if (s > max_key_tiles / 8) s = max_key_tiles / 8;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
 
 // Prompt portions, head_dim 128, query tiles of 128 tokens of one entry (tile_entry / tile_q0).
 // q rows, out rows, k_layer and v_layer 16-byte aligned.  error_flag: a device int set to 1 if a bounded
-// wait inside the kernel ran out (the output is then invalid).
+// wait inside the kernel ran out (the output is then invalid).  n_splits > 1: scratch part_o float32
+// [n_tiles * n_heads * n_splits * 128 * 128] (16-byte aligned) and part_ml float32 [n_tiles * n_heads * n_splits * 128 * 2].
 IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, long long out_stride,
                                   void* k_layer, void* v_layer, long long page_stride, int page_size,
                                   const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_q0,
                                   int n_tiles, const int* entry_q_start, const int* entry_q_len,
                                   const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
-                                  int window, int* error_flag, cudaStream_t stream) {
+                                  int window, int* error_flag, float* part_o, float* part_ml, int n_splits,
+                                  cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (head_dim != UD || n_kv < 1 || n_heads % n_kv || n_tiles > 65535 || !error_flag) return IFX_ERR_UNSUPPORTED;
+  if (n_splits < 1 || n_splits > MERGE_MAX_SPLITS || (n_splits > 1 && (!part_o || !part_ml))) return IFX_ERR_UNSUPPORTED;
+  if (n_splits > 1 && ((uintptr_t)part_o & 15)) return IFX_ERR_ALIGNMENT;
   if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
   if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return IFX_ERR_ALIGNMENT;
   if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
@@ -465,7 +573,12 @@ IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, 
   UmmaMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_UMMA);
   if (e != cudaSuccess) return (int)e;
-  const int ifx_rc = launch_pdl(attn_prefill_umma_kernel, dim3(n_heads, n_tiles), dim3(U_THREADS), SMEM_UMMA, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, tile_entry, tile_q0, n_heads, n_kv, scale, window,
-      error_flag);
+  int ifx_rc = launch_pdl(attn_prefill_umma_kernel, dim3(n_heads, n_tiles, n_splits), dim3(U_THREADS), SMEM_UMMA, stream,
+                          (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, tile_entry, tile_q0, n_heads, n_kv, scale,
+                          window, error_flag, part_o, part_ml, n_splits);
+  if (!ifx_rc) ifx_rc = IFX_LAUNCH_CHECK();
+  if (ifx_rc || n_splits == 1) return ifx_rc;
+  ifx_rc = launch_pdl(attn_prefill_umma_merge_kernel, dim3(n_heads, n_tiles, UM / MERGE_ROWS), dim3(UD), 0, stream, (const float*)part_o,
+                      (const float*)part_ml, (bf16*)out, out_stride, m, tile_entry, tile_q0, n_heads, n_splits);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }

@@ -67,7 +67,10 @@ def _lib():
         lib.ifx_attn_decode_plan.restype = c_int
         lib.ifx_attn_prefill_umma.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                              c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+                                              c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_void_p]
+        lib.ifx_attn_prefill_umma_plan.argtypes = [c_int, c_int, c_int]
+        lib.ifx_attn_prefill_umma_plan.restype = c_int
         lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.ifx_apply_penalties.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                             c_void_p, c_int, c_int, c_void_p]
@@ -400,22 +403,39 @@ def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
                       v_layer: torch.Tensor, page_stride: int, page_size: int, block_tables: torch.Tensor,
                       tile_entry: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
                       entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor,
-                      n_heads: int, n_kv: int, head_dim: int, scale: float, window: int) -> torch.Tensor:
+                      n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
+                      n_splits: int = 1) -> torch.Tensor:
     """Attention of prompt portions with tcgen05.mma and tensor-memory
     accumulators (bfloat16, head_dim 128); query tiles of 128 tokens listed by
-    tile_entry / tile_q0.  A bounded wait that runs out sets the device error
-    flag (see :func:`check_device_errors`)."""
+    tile_entry / tile_q0.  With ``n_splits`` > 1 the keys of every tile are cut
+    into that many parts (see :func:`attn_prefill_umma_splits`), merged by a
+    second kernel.  A bounded wait that runs out sets the device error flag
+    (see :func:`check_device_errors`)."""
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16,
           "attn_prefill_umma: bfloat16 operands")
     _need(head_dim == UMMA_ATTENTION_HEAD_DIM, f"attn_prefill_umma: head_dim {head_dim} is not 128")
     _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
+    part_o = part_ml = None
+    global launch_count
+    if n_splits > 1:
+        rows = n_tiles * n_heads * n_splits * 128
+        part_o = torch.empty(rows * head_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
+        launch_count += 1          # the merge kernel
     _check(_lib().ifx_attn_prefill_umma(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
                                         page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
                                         _ptr(tile_entry), _ptr(tile_q0), n_tiles, _ptr(entry_q_start),
                                         _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, n_kv, head_dim,
-                                        float(scale), int(window), _ptr(error_flag(q.device)), _stream()),
+                                        float(scale), int(window), _ptr(error_flag(q.device)), _ptr(part_o),
+                                        _ptr(part_ml), int(n_splits), _stream()),
            "attn_prefill_umma")
     return out
+
+
+def attn_prefill_umma_splits(n_tiles: int, n_heads: int, max_keys: int) -> int:
+    """Into how many parts :func:`attn_prefill_umma` is best told to cut the keys
+    of its query tiles (the kernel's own count: 1 when the tiles fill the GPU)."""
+    return max(1, int(_lib().ifx_attn_prefill_umma_plan(n_tiles, n_heads, (max_keys + 63) // 64)))
 
 
 def attn_decode_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer: torch.Tensor,

@@ -132,9 +132,11 @@ class GQAttention(Part):
                                    self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
             return
         if ctx.n_chunk_tiles and self.head_dim == ops.UMMA_ATTENTION_HEAD_DIM:
+            max_keys = min(ctx.max_ctx_len, self.window + 128) if self.window else ctx.max_ctx_len
+            splits = ops.attn_prefill_umma_splits(ctx.n_umma_tiles, self.n_heads, max_keys)
             ops.attn_prefill_umma(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
                                   ctx.block_tables[g], ctx.umma_tile_entry, ctx.umma_tile_q0, ctx.n_umma_tiles,
-                                  *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
+                                  *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, splits)
         elif ctx.n_chunk_tiles:
             ops.attn_prefill_bf16(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
                                   ctx.block_tables[g], ctx.chunk_tile_entry, ctx.chunk_tile_q0, ctx.n_chunk_tiles,

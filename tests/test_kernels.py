@@ -267,9 +267,14 @@ def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, 
         if ctiles and umma:
             utiles = [(e, q0) for e, (c, ql) in enumerate(entries) if ql > 1 for q0 in range(0, ql, 128)]
             te, tq = it([t[0] for t in utiles]).to(DEV), it([t[1] for t in utiles]).to(DEV)
-            ops.attn_prefill_umma(qd, nh * hd, out, *args, te, tq, len(utiles), md["q_start"], md["q_len"],
-                                  md["ctx_start"], nh, nkv, hd, scale, window or 0)
-            ops.check_device_errors(DEV)
+            for splits in (1, 2, 5):                      # the keys of a query tile in one part and cut into parts
+                out_u = out.clone()
+                ops.attn_prefill_umma(qd, nh * hd, out_u, *args, te, tq, len(utiles), md["q_start"], md["q_len"],
+                                      md["ctx_start"], nh, nkv, hd, scale, window or 0, splits)
+                ops.check_device_errors(DEV)
+                rows = [r for e, (c, ql) in enumerate(entries) if ql > 1 for r in range(q_start[e], q_start[e] + ql)]
+                _close(out_u[rows], want[rows], 1.5e-2, f"prompt attention, keys in {splits} parts")
+            out = out_u
         elif ctiles:
             te, tq = it([t[0] for t in ctiles]).to(DEV), it([t[1] for t in ctiles]).to(DEV)
             ops.attn_prefill_bf16(qd, nh * hd, out, *args, te, tq, len(ctiles), md["q_start"], md["q_len"],
