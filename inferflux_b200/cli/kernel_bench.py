@@ -3,12 +3,17 @@
     python -m inferflux_b200.cli.kernel_bench list
     python -m inferflux_b200.cli.kernel_bench time  [--rows 1 8 64] [--context 4096] [--kernels gemv attn_decode ...]
     python -m inferflux_b200.cli.kernel_bench launch KERNEL [--rows 8] [--context 4096] [--repeat 5]
+    INFERFLUX_B200_TIMELINE=1 python -m inferflux_b200.cli.kernel_bench timeline [--rows 8] [--context 4096] [--layers 28]
 
 ``time`` captures each kernel 20 times into a CUDA graph and times the replay with CUDA events (so the
 host's launch cost is not in the number); operands rotate between buffers larger than L2.  ``launch`` runs
 a kernel (and the variants timed beside it) a few times eagerly, which is what ``ncu -k regex:... -s 2 -c 1`` wants.  Sizes default to the
 Qwen2.5-7B layer sizes; ``--sizes hidden,heads,kv_heads,head_dim,intermediate,vocab`` changes them.
 The library product (cuBLAS through torch) is timed beside the weight-streaming kernel for comparison.
+``timeline`` needs the instrumented build that the environment variable selects (a second library, built at
+first use): every kernel notes the global timer once its predecessor is complete, and the mode prints the
+start-to-start intervals of one replayed decode step of a whole model, kernel by kernel within a layer.
+Library kernels carry no stamp: their time counts toward the kernel before them.
 """
 from __future__ import annotations
 
@@ -164,9 +169,85 @@ class Case:
             raise SystemExit(f"unknown kernel '{name}'; one of {KERNELS}")
 
 
+STAMP_FILES = ("elementwise", "rope", "gemv", "attn", "sampling")
+
+
+def _read_stamps(reset: bool):
+    """(time in ns, source file) of every stamp since the last reset, in order of time."""
+    import ctypes
+    lib = ops._lib()
+    buf = (ctypes.c_ulonglong * 4096)()
+    out = []
+    for name in STAMP_FILES:
+        fn = getattr(lib, "ifx_stamps_" + name)
+        fn.argtypes, fn.restype = [ctypes.c_void_p, ctypes.c_int], ctypes.c_int
+        k = fn(buf, int(reset))
+        out += [(buf[i], name) for i in range(k)]
+    return sorted(out)
+
+
+def timeline(sizes, layers: int, batch: int, context: int) -> int:
+    from ..kernels import build
+    if not build.TIMELINE:
+        raise SystemExit("timeline needs the instrumented build: set INFERFLUX_B200_TIMELINE=1")
+    from .. import Engine, StepEntry
+    hidden, heads, kv_heads, head_dim, inter, vocab = sizes
+    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=hidden, num_hidden_layers=layers,
+               num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, intermediate_size=inter,
+               vocab_size=vocab, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+               max_position_embeddings=32768, use_sliding_window=False, hidden_act="silu", torch_dtype="bfloat16")
+    room = context + 128
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", kv_cache_tokens=batch * room, max_seqs=batch + 1,
+                             max_model_len=room, max_batch_size=batch)
+    runner = eng.runner
+    gen = torch.Generator().manual_seed(0)
+    tok = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+    for i in range(batch):
+        t = tok(context - 16)
+        for a in range(0, len(t), 2048):
+            runner.step([StepEntry(f"r{i}", t[a:a + 2048], [])])
+    decode = lambda: runner.step([StepEntry(f"r{i}", tok(1), [0]) for i in range(batch)])
+    before = runner.graph_replays
+    for _ in range(8):
+        decode()
+    torch.cuda.synchronize()
+    _read_stamps(True)
+    decode()
+    stamps = _read_stamps(True)
+    if runner.graph_replays - before < 2 or len(stamps) < 2:
+        raise SystemExit("the decode step was not replayed from a captured graph")
+    gaps = [(name, (t2 - t) / 1000.0) for (t, name), (t2, _) in zip(stamps, stamps[1:])]
+    names = [n for n, _ in gaps]
+    # the layers are the longest stretch of the list that repeats once per layer
+    first, per_layer = 0, 0
+    for a in range(min(16, len(names))):
+        for per in range((len(names) - a) // layers, 0, -1):
+            if names[a:a + per * layers] == names[a:a + per] * layers:
+                first, per_layer = a, per
+                break
+        if per_layer:
+            break
+    if not per_layer:
+        raise SystemExit(f"no per-layer pattern in the stamped kernels: {names[:40]}")
+    print(f"one replayed decode step: batch {batch}, context {context}, {layers} layers, {len(stamps)} stamped kernels, "
+          f"{(stamps[-1][0] - stamps[0][0]) / 1000.0:.1f} us from the first stamp to the last")
+    print(f"kernels per layer: {per_layer}; start-to-start intervals, mean over layers (us):")
+    total = 0.0
+    for k in range(per_layer):
+        vals = [gaps[first + l * per_layer + k][1] for l in range(layers) if first + l * per_layer + k < len(gaps)]
+        mean = sum(vals) / len(vals)
+        total += mean
+        print(f"  {k:2d} {names[first + k]:12s} {mean:8.2f}   (min {min(vals):.2f}, max {max(vals):.2f})")
+    fmt = lambda part: ", ".join(f"{n} {d:.1f}" for n, d in part) or "none"
+    print(f"  layer {total:.2f} us; before the first layer: {fmt(gaps[:first])}; "
+          f"after the last: {fmt(gaps[first + layers * per_layer:])} (the last stamped kernel's own time is not seen)")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="kernel_bench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("mode", choices=["list", "time", "launch"])
+    ap.add_argument("mode", choices=["list", "time", "launch", "timeline"])
+    ap.add_argument("--layers", type=int, default=28, help="timeline: layers of the model")
     ap.add_argument("kernel", nargs="?")
     ap.add_argument("--kernels", nargs="*", default=None)
     ap.add_argument("--rows", nargs="*", type=int, default=[1, 8, 64])
@@ -180,6 +261,8 @@ def main(argv=None) -> int:
         print("\n".join(KERNELS))
         return 0
     sizes = tuple(int(v) for v in args.sizes.split(","))
+    if args.mode == "timeline":
+        return timeline(sizes, args.layers, args.rows[0] if len(args.rows) == 1 else 8, args.context)
     if args.mode == "launch":
         case = Case(args.kernel, sizes, args.rows[0], args.context)
         runs = ([case.run] if case.run else []) + [fn for _, fn in case.extra]     # every variant, so a profiler can pick by kernel name

@@ -685,3 +685,5 @@ IFX_API int ifx_attn_decode_plan(int n_dec, int n_heads, int n_kv, int head_dim,
   const int tiles = (max_keys + 63) / 64, per = (tiles + s - 1) / s;
   return (tiles + per - 1) / per;                              // no part without a tile
 }
+
+IFX_STAMP_READER(ifx_stamps_attn)

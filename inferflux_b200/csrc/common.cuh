@@ -90,7 +90,33 @@ struct PagedKV {
 // parameters or a step's metadata) between pdl_launch_dependents() and pdl_wait(); it must not write
 // anything there.  Kernels are launched with launch_pdl(), which sets the attribute that allows this;
 // after a kernel that never signals (a library kernel) the launch behaves like a plain one.
+#ifdef IFX_TIMELINE
+// Optional instrumentation (a build of its own, never the serving one): the first thread of a kernel's
+// first block notes the global timer once the kernel before it is complete, so that the gaps between
+// kernels can be read in place, inside a replayed graph.  One list per translation unit; the host reader
+// that IFX_STAMP_READER defines copies it out, and the lists are merged by time.
+static __device__ unsigned long long ifx_stamps[4096];
+static __device__ unsigned int ifx_stamp_count;
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned i = atomicAdd(&ifx_stamp_count, 1u);
+    if (i < 4096) ifx_stamps[i] = t;
+  }
+}
+#define IFX_STAMP_READER(name) \
+  IFX_API int name(unsigned long long* host, int reset) { \
+    unsigned int n = 0; cudaDeviceSynchronize(); cudaMemcpyFromSymbol(&n, ifx_stamp_count, sizeof(n)); \
+    if (n > 4096) n = 4096; \
+    if (n) cudaMemcpyFromSymbol(host, ifx_stamps, n * sizeof(unsigned long long)); \
+    if (reset) { unsigned int z = 0; cudaMemcpyToSymbol(ifx_stamp_count, &z, sizeof(z)); } \
+    return (int)n; }
+#else
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+#define IFX_STAMP_READER(name)
+#endif
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_enter() {
   pdl_launch_dependents();

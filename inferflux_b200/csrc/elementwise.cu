@@ -311,3 +311,5 @@ IFX_API int ifx_convert(const void* src, int src_dtype, void* dst, int dst_dtype
     return IFX_ERR_UNSUPPORTED;
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
+
+IFX_STAMP_READER(ifx_stamps_elementwise)

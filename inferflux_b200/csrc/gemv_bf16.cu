@@ -338,3 +338,5 @@ IFX_API int ifx_gemv_bf16_plan(int n_out, int K, int max_splits) {
     if (warps[s] * 100 >= best * 85) return s;
   return 1;
 }
+
+IFX_STAMP_READER(ifx_stamps_gemv)

@@ -233,3 +233,5 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
     return IFX_ERR_UNSUPPORTED;
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
+
+IFX_STAMP_READER(ifx_stamps_rope)

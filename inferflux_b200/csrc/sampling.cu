@@ -339,3 +339,5 @@ extern "C" int ifx_sample_static(const float* logits, long long row_stride, cons
                                            counters, out, vocab);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
+
+IFX_STAMP_READER(ifx_stamps_sampling)

@@ -26,6 +26,13 @@ CSRC = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)),
 LIB_NAME = "libinferflux_b200_kernels.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
+# INFERFLUX_B200_TIMELINE=1 selects an instrumented build (a library of its own beside the serving one) in
+# which every kernel notes the global timer when its predecessor is complete; cli/kernel_bench.py reads it.
+TIMELINE = os.environ.get("INFERFLUX_B200_TIMELINE", "") not in ("", "0")
+OBJ_SUFFIX = ".tl.o" if TIMELINE else ".o"
+if TIMELINE:
+    LIB_NAME = "libinferflux_b200_kernels_timeline.so"
+    NVCC_FLAGS = NVCC_FLAGS + ["-DIFX_TIMELINE"]
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
@@ -110,7 +117,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
     objs = []
     for src in srcs:
         key = _digest([src], hdr_key)
-        obj = os.path.join(out_dir, os.path.basename(src)[:-3] + f".{key}.o")
+        obj = os.path.join(out_dir, os.path.basename(src)[:-3] + f".{key}{OBJ_SUFFIX}")
         objs.append(obj)
         if force or not os.path.isfile(obj):
             todo.append((src, obj))
@@ -149,7 +156,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
     # drop objects of older source versions
     keep = {os.path.basename(o) for o in objs}
     for f in os.listdir(out_dir):
-        if f.endswith(".o") and f not in keep:
+        if f.endswith(".o") and f.endswith(".tl.o") == TIMELINE and f not in keep:
             try:
                 os.remove(os.path.join(out_dir, f))
             except OSError:
