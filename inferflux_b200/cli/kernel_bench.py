@@ -114,6 +114,15 @@ class Case:
                 self.run = lambda i: ops.attn_decode_bf16(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
                                                           pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, po, pm, nh, nkv,
                                                           hd, scale, 0, splits)
+                # the variant that adds the bias, rotates and writes the cache itself (steps of single tokens)
+                width = (nh + 2 * nkv) * hd
+                bias, cos, sin = torch.randn(width, device=DEV), torch.rand(b, hd // 2, device=DEV), torch.rand(b, hd // 2, device=DEV)
+                slots = it([int(bt[r, (ctx - 1) // ps]) * ps + (ctx - 1) % ps for r in range(b)])
+                parts = torch.randn(4, b, width, device=DEV) if rows <= 8 else None
+                self.extra.append((f"prepares q,k,v {'from 4 partial sums' if parts is not None else ''}",
+                                   lambda i: ops.attn_decode_prep_bf16(
+                                       q, bias, cos, sin, slots, parts, out, pools[i][0, 0, 0], pools[i][0, 0, 1],
+                                       pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, po, pm, nh, nkv, hd, scale, 0, splits)))
                 if sweep:
                     for s in (1, 2, 3, 4, 5, 6, 7, 8, 10, 11, 13, 16, 22, 32):
                         if s * 64 > ctx:

@@ -17,6 +17,8 @@
 // the 16 rows of an MMA tile are the query heads that share a kv head, so a
 // page is read once for all of them.
 #include "common.cuh"
+#include "rope_math.cuh"
+#include <type_traits>
 
 namespace {
 
@@ -339,12 +341,29 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned x) {
   return y;
 }
 
-template <int HD>
+// What the kernel needs to make q, k and v of its token itself (PREP): the product's output before bias and
+// rotation, as bfloat16 rows (q) or as float32 partial sums [n_partials][n_tokens][width].
+struct QkvPrep {
+  const float* bias;        // [width] or null
+  const float* cos_t;       // [n_tokens, HD / 2]
+  const float* sin_t;
+  const int* slot_map;      // [n_tokens]: page * page_size + offset of the token's key and value; null: this layer writes none
+  const float* partials;    // or null
+  int n_partials;
+  long long part_stride;    // n_tokens * width
+};
+
+// PREP: the kernel takes the place of the bias/rotation/cache-write kernel for the token it decodes.  Every
+// block adds the bias to and rotates the query heads it works on (into shared memory); the block whose
+// part of the keys ends with the token's own position does the same for the key, adds the bias to the
+// value, writes both to the cache and only then loads that tile.  With more than 8 query heads per kv head
+// several blocks write the same bytes.
+template <int HD, bool PREP>
 __global__ void __launch_bounds__(128)
 attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                         PagedKV kv, AttnMeta m, const int* __restrict__ dec_entries,
                         float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits) {
+                        int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits, QkvPrep prep) {
   // Up to pdl_wait() below the block reads only what no kernel of the step writes (the step's
   // metadata) and keys and values of tokens older than the one being decoded.
   pdl_launch_dependents();
@@ -407,7 +426,49 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 
   if (kb < ke) {                                                // block-uniform
     unsigned qb[KS][2];                                         // Q^T as the B operand: k = d, n = head g
-    {
+    if constexpr (PREP) {
+      __shared__ __align__(16) bf16 q_s[8 * HD];
+      constexpr int HALF = HD / 2, HV = HALF / 8;               // 8-wide groups per half head
+      const int width = (n_heads + 2 * n_kv) * HD;
+      const bf16* row = q + (size_t)tok * q_stride;
+      const float* part = prep.partials ? prep.partials + (size_t)tok * width : nullptr;
+      const float* ct = prep.cos_t + (size_t)tok * HALF;
+      const float* st = prep.sin_t + (size_t)tok * HALF;
+      const int slot = (prep.slot_map && ke == len) ? prep.slot_map[tok] : -1;   // ke == len: the token's own position is ours
+      const int q_items = nrows * HV, k_items = slot >= 0 ? HV : 0, v_items = slot >= 0 ? HD / 8 : 0;
+      auto items = [&](auto part_tag) {
+        constexpr bool PART = decltype(part_tag)::value;
+        for (int w = tid; w < q_items + k_items + v_items; w += 128) {
+          if (w < q_items + k_items) {
+            const bool is_q = w < q_items;
+            const int hl = is_q ? w / HV : 0, i = (is_q ? w - hl * HV : w - q_items) * 8;
+            const int base = (is_q ? h0 + hl : n_heads + kvh) * HD;
+            uint4 lo, hi;
+            rope_pairs8<PART>(row, part, prep.n_partials, prep.part_stride, prep.bias, ct, st, base + i, HALF, i, lo, hi);
+            bf16* dst = is_q ? q_s + hl * HD
+                             : (bf16*)kv.k + (size_t)(slot >> kv.page_shift) * kv.page_stride + (size_t)kvh * kv.head_stride +
+                                   (size_t)(slot & (kv.page_size - 1)) * HD;
+            *reinterpret_cast<uint4*>(dst + i) = lo;
+            *reinterpret_cast<uint4*>(dst + HALF + i) = hi;
+          } else {
+            const int d = (w - q_items - k_items) * 8;
+            bf16* dst = (bf16*)kv.v + (size_t)(slot >> kv.page_shift) * kv.page_stride + (size_t)kvh * kv.head_stride +
+                        (size_t)(slot & (kv.page_size - 1)) * HD;
+            *reinterpret_cast<uint4*>(dst + d) =
+                biased8<PART>(row, part, prep.n_partials, prep.part_stride, prep.bias, (n_heads + n_kv + kvh) * HD + d);
+          }
+        }
+      };
+      if (part) items(std::true_type{}); else items(std::false_type{});
+      if (slot >= 0) __threadfence();                           // the key and value are in memory before the tile that holds them is copied
+      __syncthreads();
+      const unsigned* pq = reinterpret_cast<const unsigned*>(q_s + (size_t)g * HD);
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        qb[k][0] = g < nrows ? pq[k * 8 + t4] : 0u;
+        qb[k][1] = g < nrows ? pq[k * 8 + 4 + t4] : 0u;
+      }
+    } else {
       const unsigned* pq = reinterpret_cast<const unsigned*>(q + (size_t)tok * q_stride + (size_t)(h0 + g) * HD);
 #pragma unroll
       for (int k = 0; k < KS; ++k) {
@@ -579,14 +640,14 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
-template <int HD>
+template <int HD, bool PREP>
 int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnMeta m,
                   const int* dec_entries, int n_dec, float* part_o, float* part_ml, int n_heads, int n_kv,
-                  float scale, int window, int n_splits, cudaStream_t stream) {
+                  float scale, int window, int n_splits, QkvPrep prep, cudaStream_t stream) {
   const size_t stage_bytes = (size_t)DSTAGES * 2 * 64 * HD * sizeof(bf16);
   const size_t red_bytes = (size_t)4 * 8 * HD * sizeof(float) + 4 * 8 * 2 * sizeof(float);
   const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
-  auto kern = attn_decode_bf16_kernel<HD>;
+  auto kern = attn_decode_bf16_kernel<HD, PREP>;
   {  // dynamic plus static shared memory may pass 48 KB
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -594,7 +655,7 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
   const int ratio = n_heads / n_kv;
   const int head_chunks = (ratio + 7) / 8;
   int rc = launch_pdl(kern, dim3(n_dec, n_kv * head_chunks, n_splits), dim3(128), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, dec_entries, part_o, part_ml, n_heads, n_kv,
-      head_chunks, scale, window, n_splits);
+      head_chunks, scale, window, n_splits, prep);
   if (!rc) rc = IFX_LAUNCH_CHECK();
   if (rc || n_splits == 1) return rc;
   rc = launch_pdl(attn_decode_merge_kernel, dim3(n_dec, n_heads), dim3(HD < 128 ? HD : 128), 0, stream, part_o, part_ml, (bf16*)out, out_stride, dec_entries, m.entry_q_start, n_heads, HD, n_splits);
@@ -641,9 +702,41 @@ IFX_API int ifx_attn_decode_bf16(const void* q, long long q_stride, void* out, l
   PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
   AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
   if (head_dim == 128)
-    return launch_decode<128>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, stream);
+    return launch_decode<128, false>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, QkvPrep{}, stream);
   if (head_dim == 64)
-    return launch_decode<64>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, stream);
+    return launch_decode<64, false>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, QkvPrep{}, stream);
+  return IFX_ERR_UNSUPPORTED;
+}
+
+// The same for a step of single tokens only, with the work of ifx_qkv_rope_kv_write folded in: qkv is the
+// product's output before bias and rotation ([n_tokens, (n_heads + 2 n_kv) * head_dim] bfloat16 rows, or
+// float32 partial sums [n_partials][n_tokens][width] of it; the bfloat16 rows are not read then), bias
+// float32 [width] or null, cos/sin float32 [n_tokens, head_dim / 2] (the whole head is rotated), slot_map
+// [n_tokens] or null for a layer that writes no keys and values.  Every token of the step must be one of the
+// decoded entries: nothing else gets its key and value written.
+IFX_API int ifx_attn_decode_prep_bf16(const void* qkv, long long qkv_stride, void* out, long long out_stride,
+                                      void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                      const int* block_tables, int bt_stride, const int* dec_entries, int n_dec,
+                                      const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
+                                      float* part_o, float* part_ml, int n_heads, int n_kv, int head_dim, float scale,
+                                      int window, int n_splits, const float* bias, const float* cos_t,
+                                      const float* sin_t, const int* slot_map, const float* partials, int n_partials,
+                                      int n_tokens, cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (n_kv < 1 || n_heads % n_kv || n_splits < 1 || n_splits > 65535 || n_tokens < n_dec) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
+  if ((qkv_stride & 7) || (((uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)partials) & 15))
+    return IFX_ERR_ALIGNMENT;
+  if (!cos_t || !sin_t || (partials && n_partials < 1) || (!partials && !qkv)) return IFX_ERR_UNSUPPORTED;
+  if (n_splits > 1 && (!part_o || !part_ml)) return IFX_ERR_UNSUPPORTED;
+  PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
+  AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
+  QkvPrep prep{bias, cos_t, sin_t, slot_map, partials, n_partials, (long long)n_tokens * (n_heads + 2 * n_kv) * head_dim};
+  if (head_dim == 128)
+    return launch_decode<128, true>(qkv, qkv_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, prep, stream);
+  if (head_dim == 64)
+    return launch_decode<64, true>(qkv, qkv_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, prep, stream);
   return IFX_ERR_UNSUPPORTED;
 }
 
@@ -656,7 +749,7 @@ int decode_resident_blocks() {
     const size_t stage_bytes = (size_t)DSTAGES * 2 * 64 * HD * sizeof(bf16);
     const size_t red_bytes = (size_t)4 * 8 * HD * sizeof(float) + 4 * 8 * 2 * sizeof(float);
     const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
-    auto kern = attn_decode_bf16_kernel<HD>;
+    auto kern = attn_decode_bf16_kernel<HD, true>;             // the variant with more static shared memory
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return -(int)e;
     int per_sm = 0, dev = 0, sms = 0;

@@ -14,6 +14,7 @@
 // per token, in double precision rounded to float32), and one kernel per layer
 // does bias + rotation + paged write for prompts and decoded tokens alike.
 #include "common.cuh"
+#include "rope_math.cuh"
 
 // cos/sin tables [n_tokens, half] from positions and inverse frequencies.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
@@ -95,35 +96,10 @@ __global__ void qkv_rope_kv_write_kernel(T* __restrict__ qkv, const float* __res
 }
 
 // Vector path (bfloat16, whole head rotated, head_dim a multiple of 16): a work item is 8
-// consecutive pairs (i .. i+7, i+half .. i+half+7) of one head: two 16-byte loads, two 16-byte stores.
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) { const float2 t = __bfloat1622float2(h[k]); f[2 * k] = t.x; f[2 * k + 1] = t.y; }
-}
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-  uint4 v;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
-  return v;
-}
-
-// 8 values of a row: from the bfloat16 row itself, or the sum (in slice order) of float32 partial sums
-// [n_partials][n_tokens][width] of the product that made it
-__device__ __forceinline__ void load8(const bf16* row, const float* part, int n_partials, long long part_stride, int e,
-                                      float (&f)[8]) {
-  if (!part) { unpack8(*reinterpret_cast<const uint4*>(row + e), f); return; }
-#pragma unroll
-  for (int k = 0; k < 8; ++k) f[k] = 0.0f;
-  for (int p = 0; p < n_partials; ++p) {
-    const float4 a = *reinterpret_cast<const float4*>(part + p * part_stride + e);
-    const float4 b = *reinterpret_cast<const float4*>(part + p * part_stride + e + 4);
-    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w; f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
-  }
-}
-
-__global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
+// consecutive pairs (i .. i+7, i+half .. i+half+7) of one head: two 16-byte loads, two 16-byte stores
+// (rope_math.cuh).
+template <bool PART>
+__global__ void __launch_bounds__(PART ? 256 : 512) qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                 const int* __restrict__ slot_map, PagedKV kv,
                                                 int n_heads, int n_kv, int head_dim,
@@ -133,7 +109,7 @@ __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const fl
   const int half = head_dim / 2, hv = half / 8;               // 8-wide groups per half head
   const int width = (n_heads + 2 * n_kv) * head_dim;
   bf16* row = qkv + (size_t)t * width;
-  const float* part = partials ? partials + (size_t)t * width : nullptr;
+  const float* part = PART ? partials + (size_t)t * width : nullptr;
   const float* ct = cos_t + (size_t)t * half;
   const float* st = sin_t + (size_t)t * half;
   const int slot = n_kv ? slot_map[t] : -1;
@@ -150,28 +126,8 @@ __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const fl
     if (w < rot_items) {
       const int h = w / hv, i = (w - h * hv) * 8;
       const int base = h * head_dim;
-      float x0[8], x1[8], c[8], s[8], b0[8], b1[8];
-      load8(row, part, n_partials, part_stride, base + i, x0);
-      load8(row, part, n_partials, part_stride, base + half + i, x1);
-      *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(ct + i);
-      *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(ct + i + 4);
-      *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(st + i);
-      *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(st + i + 4);
-      if (bias) {                                               // 16-byte aligned: head_dim is a multiple of 16
-        *reinterpret_cast<float4*>(b0) = *reinterpret_cast<const float4*>(bias + base + i);
-        *reinterpret_cast<float4*>(b0 + 4) = *reinterpret_cast<const float4*>(bias + base + i + 4);
-        *reinterpret_cast<float4*>(b1) = *reinterpret_cast<const float4*>(bias + base + half + i);
-        *reinterpret_cast<float4*>(b1 + 4) = *reinterpret_cast<const float4*>(bias + base + half + i + 4);
-      }
-      float y0[8], y1[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        float a = x0[k], b = x1[k];
-        if (bias) { a += b0[k]; b += b1[k]; }
-        y0[k] = a * c[k] - b * s[k];
-        y1[k] = a * s[k] + b * c[k];
-      }
-      const uint4 p0 = pack8(y0), p1 = pack8(y1);
+      uint4 p0, p1;
+      rope_pairs8<PART>(row, part, n_partials, part_stride, bias, ct, st, base + i, half, i, p0, p1);
       if (h < n_heads) {
         *reinterpret_cast<uint4*>(row + base + i) = p0;
         *reinterpret_cast<uint4*>(row + base + half + i) = p1;
@@ -182,15 +138,8 @@ __global__ void qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const fl
       }
     } else {
       const int e0 = (w - rot_items) * 8, h = e0 / head_dim, d = e0 - h * head_dim;
-      float x[8], bv[8];
-      load8(row, part, n_partials, part_stride, vbase + e0, x);
-      if (bias) {
-        *reinterpret_cast<float4*>(bv) = *reinterpret_cast<const float4*>(bias + vbase + e0);
-        *reinterpret_cast<float4*>(bv + 4) = *reinterpret_cast<const float4*>(bias + vbase + e0 + 4);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) x[k] += bv[k];
-      }
-      *reinterpret_cast<uint4*>(vc + (size_t)h * kv.head_stride + d) = pack8(x);
+      *reinterpret_cast<uint4*>(vc + (size_t)h * kv.head_stride + d) =
+          biased8<PART>(row, part, n_partials, part_stride, bias, vbase + e0);
     }
   }
 }
@@ -216,12 +165,17 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
                        && (page_stride & 7) == 0;
   if (dtype == IFX_BF16 && rot_dim == head_dim && head_dim % 16 == 0 && aligned) {
     const int work8 = (n_heads + n_kv) * head_dim / 16 + n_kv * head_dim / 8;
-    int th = 32;
-    while (th < 512 && th < work8) th <<= 1;
     if (partials && (((uintptr_t)partials & 15) || n_partials < 1)) return IFX_ERR_ALIGNMENT;
-    ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t, sin_t, slot_map, kv,
-                        n_heads, n_kv, head_dim, partials, n_partials,
-                        (long long)n_tokens * (n_heads + 2 * n_kv) * head_dim);
+    const int th_max = partials ? 256 : 512;                    // the kernels' launch bounds
+    int th = 32;
+    while (th < th_max && th < work8) th <<= 1;
+    const long long part_stride = (long long)n_tokens * (n_heads + 2 * n_kv) * head_dim;
+    if (partials)
+      ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel<true>, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t, sin_t,
+                          slot_map, kv, n_heads, n_kv, head_dim, partials, n_partials, part_stride);
+    else
+      ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel<false>, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t, sin_t,
+                          slot_map, kv, n_heads, n_kv, head_dim, partials, n_partials, part_stride);
     return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
   }
   if (partials) return IFX_ERR_UNSUPPORTED;                      // partial sums only on the bfloat16 vector path

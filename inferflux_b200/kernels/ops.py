@@ -56,6 +56,11 @@ def _lib():
         lib.ifx_attn_decode_bf16.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
                                              c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
+        lib.ifx_attn_decode_prep_bf16.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
+                                                  c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                  c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_attn_decode_prep_bf16.restype = c_int
         lib.ifx_gemv_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll,
                                       c_int, c_int, c_void_p]
         lib.ifx_gemm_umma.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
@@ -465,6 +470,54 @@ def attn_decode_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer:
                                        _ptr(dec_entries), n_dec, _ptr(entry_q_start), _ptr(entry_q_len),
                                        _ptr(entry_ctx_start), _ptr(part_o), _ptr(part_ml), n_heads, n_kv, head_dim,
                                        float(scale), int(window), int(n_splits), _stream()), "attn_decode_bf16")
+    return out
+
+
+def attn_decode_prep_bf16(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
+                          slot_map: Optional[torch.Tensor], partials: Optional[torch.Tensor], out: torch.Tensor,
+                          k_layer: torch.Tensor, v_layer: torch.Tensor, page_stride: int, page_size: int,
+                          block_tables: torch.Tensor, dec_entries: torch.Tensor, n_dec: int,
+                          entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor,
+                          part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], n_heads: int, n_kv: int,
+                          head_dim: int, scale: float, window: int, n_splits: int) -> torch.Tensor:
+    """:func:`attn_decode_bf16` for a step of single tokens only, with the work
+    of :func:`qkv_rope_kv_write` folded into the attention kernel: ``qkv`` is
+    the product's output before bias and rotation (or ``partials``, float32
+    [S, N, width], holds it as partial sums and qkv's content is not read);
+    the kernel rotates its own query heads and writes the token's key and
+    value into the cache (``slot_map`` None: the layer writes none) before it
+    reads them.  Every row of qkv must be one of the decoded entries."""
+    n, width = qkv.shape
+    _need(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16
+          and qkv.is_contiguous() and width == (n_heads + 2 * n_kv) * head_dim and n == n_dec,
+          "attn_decode_prep_bf16: qkv bfloat16 [n_dec, (nh + 2 nkv) hd]")
+    _need(head_dim in FAST_ATTENTION_HEAD_DIMS, f"attn_decode_prep_bf16: head_dim {head_dim} not in {FAST_ATTENTION_HEAD_DIMS}")
+    _need(tuple(cos.shape) == (n, head_dim // 2) and tuple(sin.shape) == (n, head_dim // 2) and cos.dtype == torch.float32
+          and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous(),
+          "attn_decode_prep_bf16: cos/sin float32 [N, head_dim / 2]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "attn_decode_prep_bf16: bias float32 [width]")
+    _need(slot_map is None or (slot_map.dtype == torch.int32 and slot_map.numel() == n), "attn_decode_prep_bf16: slot_map int32 [N]")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
+    n_partials = 0
+    if partials is not None:
+        _need(partials.dtype == torch.float32 and partials.is_contiguous() and partials.dim() == 3
+              and tuple(partials.shape[1:]) == (n, width), "attn_decode_prep_bf16: partial sums float32 [S, N, width]")
+        n_partials = partials.shape[0]
+    if n_splits > 1:
+        _need(part_o is not None and part_o.dtype == torch.float32
+              and part_o.numel() >= n_dec * n_heads * n_splits * head_dim
+              and part_ml is not None and part_ml.dtype == torch.float32
+              and part_ml.numel() >= n_dec * n_heads * n_splits * 2, "attn_decode_prep_bf16: scratch too small")
+    global launch_count
+    if n_splits > 1:
+        launch_count += 1          # the merge kernel
+    _check(_lib().ifx_attn_decode_prep_bf16(_ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(k_layer),
+                                            _ptr(v_layer), page_stride, page_size, _ptr(block_tables),
+                                            block_tables.stride(0), _ptr(dec_entries), n_dec, _ptr(entry_q_start),
+                                            _ptr(entry_q_len), _ptr(entry_ctx_start), _ptr(part_o), _ptr(part_ml),
+                                            n_heads, n_kv, head_dim, float(scale), int(window), int(n_splits),
+                                            _ptr(bias), _ptr(cos), _ptr(sin), _ptr(slot_map), _ptr(partials),
+                                            n_partials, n, _stream()), "attn_decode_prep_bf16")
     return out
 
 

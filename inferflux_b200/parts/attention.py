@@ -113,10 +113,16 @@ class GQAttention(Part):
             qkv = torch.empty(partials.shape[1:], dtype=x.dtype, device=x.device)
         g = run.kv_group
         k_layer, v_layer, page_stride = ctx.kv.layer_views(g, run.kv_index)
+        attn = torch.empty((n, self.n_heads * self.head_dim), dtype=qkv.dtype, device=x.device)
+        if (ctx.n_decode == n and not ctx.n_chunk_tiles and nkv_w and qkv.dtype == torch.bfloat16
+                and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and 2 * cos.shape[1] == self.head_dim):
+            # single tokens only: the attention kernel adds the bias, rotates and writes the cache itself
+            self.decode(qkv, attn, ctx, g, k_layer, v_layer, page_stride,
+                        prep=(self.qkv_bias, cos, sin, ctx.slot_maps[g], partials))
+            return self.o.forward(attn, out_dtype=x.dtype, allow_partials=True)
         ops.qkv_rope_kv_write(qkv, self.qkv_bias, cos, sin, ctx.slot_maps[g] if nkv_w else None,
                               k_layer if nkv_w else None, v_layer if nkv_w else None, page_stride,
                               ctx.page_size, self.n_heads, nkv_w, self.head_dim, partials)
-        attn = torch.empty((n, self.n_heads * self.head_dim), dtype=qkv.dtype, device=x.device)
         self.attend(qkv, attn, ctx, g, k_layer, v_layer, page_stride)
         return self.o.forward(attn, out_dtype=x.dtype, allow_partials=True)
 
@@ -142,16 +148,28 @@ class GQAttention(Part):
                                   ctx.block_tables[g], ctx.chunk_tile_entry, ctx.chunk_tile_q0, ctx.n_chunk_tiles,
                                   *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
         if ctx.n_decode:
-            n_splits = ops.attn_decode_splits(ctx.n_decode, self.n_heads, self.n_kv, self.head_dim,
-                                              min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len)
-            part_o = part_ml = None
-            if n_splits > 1:
-                rows = ctx.n_decode * self.n_heads * n_splits
-                part_o = torch.empty(rows * self.head_dim, dtype=torch.float32, device=qkv.device)
-                part_ml = torch.empty(rows * 2, dtype=torch.float32, device=qkv.device)
-            ops.attn_decode_bf16(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
-                                 ctx.block_tables[g], ctx.decode_entries, ctx.n_decode, *common, part_o, part_ml,
-                                 self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, n_splits)
+            self.decode(qkv, attn, ctx, g, k_layer, v_layer, page_stride)
+
+    def decode(self, qkv, attn, ctx, g, k_layer, v_layer, page_stride, prep=None) -> None:
+        """The step's single tokens: the keys of each are cut into as many parts
+        as fill the GPU, and merged.  ``prep`` = (bias, cos, sin, slot map,
+        partial sums or None): qkv is still the bare product and the kernel
+        prepares q, k and v itself."""
+        n_splits = ops.attn_decode_splits(ctx.n_decode, self.n_heads, self.n_kv, self.head_dim,
+                                          min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len)
+        part_o = part_ml = None
+        if n_splits > 1:
+            rows = ctx.n_decode * self.n_heads * n_splits
+            part_o = torch.empty(rows * self.head_dim, dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty(rows * 2, dtype=torch.float32, device=qkv.device)
+        meta = (k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g], ctx.decode_entries, ctx.n_decode,
+                ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start, part_o, part_ml,
+                self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, n_splits)
+        if prep is None:
+            ops.attn_decode_bf16(qkv, qkv.stride(0), attn, *meta)
+        else:
+            bias, cos, sin, slot_map, partials = prep
+            ops.attn_decode_prep_bf16(qkv, bias, cos, sin, slot_map, partials, attn, *meta)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -325,6 +325,80 @@ def test_attention_long_context_far_key(ops):
         _attention_case(ops, torch.bfloat16, 4, 1, 128, 16, None, [(4000, 1), (3990, 40)], 22, True, fast, umma)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(28, 4, 128, 16, None), (5, 1, 64, 8, None), (40, 2, 128, 16, None),
+                                                 (14, 2, 128, 4, 129), (3, 3, 64, 32, 40)])
+@pytest.mark.parametrize("n_partials", [0, 3])
+@pytest.mark.parametrize("own_key_stands_out", [False, True])
+def test_decode_attention_prepares_its_own_qkv(ops, nh, nkv, hd, ps, window, n_partials, own_key_stands_out):
+    """A step of single tokens: the decode kernel that adds the bias, rotates and writes the cache itself gives
+    bit for bit what the separate kernel followed by the plain decode kernel gives (output and cache), for
+    contexts that end at every place of a page, with the product as bfloat16 rows and as float32 partial sums.
+    In the second variant each token's own key is the one that counts: a key written late or elsewhere shows."""
+    g = torch.Generator().manual_seed(70)
+    cached = [0, 1, 15, 16, 17, 63, 64, 255, 300, 129]
+    n, width, ratio = len(cached), (nh + 2 * nkv) * hd, nh // nkv
+    pages = sum((c + 1 + ps - 1) // ps for c in cached) + 2
+    perm = torch.randperm(pages, generator=g).tolist()
+    pool = torch.zeros((pages, 1, 2, nkv, ps, hd), dtype=torch.bfloat16)
+    bt = torch.full((n, max((c + 1 + ps - 1) // ps for c in cached)), -1, dtype=torch.int32)
+    slots = []
+    for e, c in enumerate(cached):
+        for b in range((c + 1 + ps - 1) // ps):
+            bt[e, b] = perm.pop()
+        first_needed = max(0, c - window + 1) // ps if window else 0
+        for pos in range(c):
+            if pos // ps >= first_needed:
+                pool[int(bt[e, pos // ps]), 0, :, :, pos % ps] = torch.randn((2, nkv, hd), generator=g).to(torch.bfloat16)
+        slots.append(int(bt[e, c // ps]) * ps + c % ps)
+        bt[e, :first_needed] = -1
+    bias = torch.randn((width,), generator=g) * 0.5
+    prod = torch.randn((n, width), generator=g)
+    if own_key_stands_out:                                      # q + bias = 3 (k + bias) for every head of the group
+        for h in range(nh):
+            ksl = slice((nh + h // ratio) * hd, (nh + h // ratio + 1) * hd)
+            prod[:, h * hd:(h + 1) * hd] = 3.0 * (prod[:, ksl] + bias[ksl]) - bias[h * hd:(h + 1) * hd]
+    if n_partials:
+        parts = torch.randn((n_partials, n, width), generator=g)
+        parts[0] = prod - parts[1:].sum(0)
+        parts = parts.to(DEV)
+    else:
+        parts = None
+    ang = torch.randn((n, hd // 2), generator=g) * 3.0
+    cos, sin = torch.cos(ang).to(DEV), torch.sin(ang).to(DEV)
+    it = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    meta = (it(list(range(n))), n, it(list(range(n))), it([1] * n), it(cached))
+    biasd, btd, slotd = bias.to(DEV), bt.to(DEV), it(slots)
+    scale = 1.0 / math.sqrt(hd)
+    for splits in (1, 3, 8):
+        po = torch.empty(n * nh * splits * hd, dtype=torch.float32, device=DEV)
+        pm = torch.empty(n * nh * splits * 2, dtype=torch.float32, device=DEV)
+        # the separate kernels
+        pool_a, qkv_a = pool.to(DEV), prod.to(torch.bfloat16).to(DEV)
+        out_a = torch.zeros((n, nh * hd), dtype=torch.bfloat16, device=DEV)
+        ops.qkv_rope_kv_write(qkv_a, biasd, cos, sin, slotd, pool_a[0, 0, 0], pool_a[0, 0, 1], pool_a.stride(0), ps,
+                              nh, nkv, hd, parts)
+        ops.attn_decode_bf16(qkv_a, width, out_a, pool_a[0, 0, 0], pool_a[0, 0, 1], pool_a.stride(0), ps, btd, *meta,
+                             po, pm, nh, nkv, hd, scale, window or 0, splits)
+        # the one kernel
+        pool_b, qkv_b = pool.to(DEV), prod.to(torch.bfloat16).to(DEV)
+        out_b = torch.zeros((n, nh * hd), dtype=torch.bfloat16, device=DEV)
+        ops.attn_decode_prep_bf16(qkv_b, biasd, cos, sin, slotd, parts, out_b, pool_b[0, 0, 0], pool_b[0, 0, 1],
+                                  pool_b.stride(0), ps, btd, *meta, po, pm, nh, nkv, hd, scale, window or 0, splits)
+        assert torch.equal(pool_a, pool_b), f"{splits} splits: the caches differ"
+        assert torch.equal(out_a, out_b), f"{splits} splits: the outputs differ"
+        # and both against the plain attention over the cache they wrote
+        want = torch.zeros((n, nh * hd), dtype=torch.float32)
+        poolf = pool_b.float().cpu()
+        ref.attn_paged_generic(qkv_a[:, :nh * hd].float().cpu().contiguous(), nh * hd, want, poolf[0, 0, 0], poolf[0, 0, 1],
+                               poolf.stride(0), ps, bt, None, None, 0, meta[2].cpu(), meta[3].cpu(), meta[4].cpu(),
+                               nh, nkv, hd, scale, window or 0)
+        _close(out_b, want, 1.5e-2, f"decode attention that prepares q, k, v; {splits} splits")
+        if own_key_stands_out:
+            v_new = torch.stack([pool_b[s // ps, 0, 1, :, s % ps] for s in slots]).float().cpu()      # [n, nkv, hd]
+            got = out_b.float().cpu().view(n, nkv, ratio, hd)
+            assert (got - v_new[:, :, None, :]).abs().max() < 0.05, "the output is not the token's own value"
+
+
 # --------------------------------------------------------------------- sampling
 def test_qkv_rope_from_partial_sums(ops):
     """The RoPE + cache-write kernel given float32 partial sums of the product
