@@ -27,7 +27,7 @@ from ..kernels import ops
 DEV = "cuda:0"
 KERNELS = ["gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_lm_head", "attn_decode", "attn_prefill",
            "attn_prefill_umma",
-           "add_rmsnorm", "rope_kv", "swiglu", "argmax"]
+           "add_rmsnorm", "rope_kv", "swiglu", "argmax", "sample"]
 
 
 def _timeit(fn, n_rot, reps=20):
@@ -174,6 +174,20 @@ class Case:
             lg, oi = torch.randn(rows, vocab, device=DEV), torch.empty(rows, dtype=torch.int32, device=DEV)
             self.n_rot, self.bytes = 1, rows * vocab * 4
             self.run = lambda i: ops.argmax(lg, oi)
+        elif name == "sample":
+            lg = torch.randn(rows, vocab, device=DEV) * 3.0
+            oi, w = torch.empty(rows, dtype=torch.int32, device=DEV), torch.empty(rows, vocab, device=DEV)
+            f32 = lambda v: torch.full((rows,), v, dtype=torch.float32, device=DEV)
+            seeds = torch.arange(rows, dtype=torch.int64, device=DEV)
+            ctr = torch.zeros(rows, dtype=torch.int64, device=DEV)
+            self.n_rot, self.bytes = 1, rows * vocab * 4
+            self.run = None
+            for label, k, p, mp in (("temperature 0.8", 0, 1.0, 0.0), ("temperature 0.8, top-k 50", 50, 1.0, 0.0),
+                                    ("temperature 0.8, top-p 0.9", 0, 0.9, 0.0),
+                                    ("temperature 0.8, top-k 50, top-p 0.9, min-p 0.01", 50, 0.9, 0.01)):
+                tk = torch.full((rows,), k, dtype=torch.int32, device=DEV)
+                self.extra.append((label, lambda i, tk=tk, p=p, mp=mp: ops.sample(lg, w, f32(0.8), tk, f32(p), f32(mp),
+                                                                                 seeds, ctr, oi)))
         else:
             raise SystemExit(f"unknown kernel '{name}'; one of {KERNELS}")
 

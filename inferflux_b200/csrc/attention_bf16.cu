@@ -593,14 +593,42 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   }
 }
 
-// merge the splits: grid (n_dec, n_heads), HD threads
+// merge the splits: grid (n_dec, n_heads), HD threads.  Up to 16 splits (what the plan gives at the usual
+// batch sizes) are loaded in one go, maxima, sums and outputs together, so the block waits for memory once.
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, long long out_stride, const int* __restrict__ dec_entries,
                                          const int* __restrict__ entry_q_start, int n_heads, int head_dim, int n_splits) {
-  pdl_enter();
+  pdl_launch_dependents();
   const int dec = blockIdx.x, head = blockIdx.y;
-  const int tok = entry_q_start[dec_entries[dec]];
+  const int tok = entry_q_start[dec_entries[dec]];            // the step's metadata: read before the wait
+  pdl_wait();
   const size_t p0 = ((size_t)dec * n_heads + head) * n_splits;
+  if (n_splits <= 16) {
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+      float2 ml[16];
+      float po[16];
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < n_splits) {
+          ml[s] = *reinterpret_cast<const float2*>(part_ml + (p0 + s) * 2);
+          po[s] = part_o[(p0 + s) * head_dim + d];
+        }
+      float mm = -INFINITY;
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < n_splits) mm = fmaxf(mm, ml[s].x);
+      float l = 0.0f, acc = 0.0f;
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < n_splits) {
+          const float f = ml[s].x == -INFINITY ? 0.0f : fast_exp2(ml[s].x - mm);
+          l += ml[s].y * f;
+          acc += po[s] * f;
+        }
+      out[(size_t)tok * out_stride + (size_t)head * head_dim + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    }
+    return;
+  }
   float mm = -INFINITY;
 #pragma unroll 8
   for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(p0 + s) * 2]);
