@@ -33,9 +33,12 @@
  *  - No cudaMalloc, cudaFree or other allocating routine is called, here or in
  *    the kernel.
  *
- * Arguments are those of ifx_sample without `weights`; the result for a row is
- * the same token that ifx_sample returns for it.  Returns 0 on success, a
- * cudaError_t value for a CUDA failure, or one of the codes below.
+ * Arguments are those of ifx_sample without `weights`.  The kernel is the one
+ * ifx_sample uses for rows too long for a cluster's shared memory; for shorter
+ * rows ifx_sample runs a kernel that needs no scratch and adds masses as
+ * integers, and the two return the same token unless the row's uniform falls
+ * within float32 rounding of a boundary between two tokens.  Returns 0 on
+ * success, a cudaError_t value for a CUDA failure, or one of the codes below.
  */
 #pragma once
 #include <cuda_runtime.h>

@@ -7,13 +7,16 @@
 //   temperature softmax(logits / T) in three passes by one block (:216-267)
 //   top-p       repeated arg-max until the cumulative probability reaches p (:273-330)
 //   draw        one thread walks the cumulative sum against one uniform (:374-401)
-// Here one block of 1024 threads serves a row, rows run in parallel, greedy
-// returns the lowest index among equal maxima, top-k/top-p/min-p become a
-// probability threshold found by bisection on the float bit pattern, and the
-// uniform comes from a counter-based generator keyed by (seed, counter) so a
-// request's draws do not depend on the batch it is in.
-//
-// Scratch: `weights` [n_rows, vocab] float32 holds exp(logit/T - max).
+// Here rows run in parallel, greedy returns the lowest index among equal
+// maxima, top-k/top-p/min-p become a probability threshold on the float bit
+// pattern, and the uniform comes from a counter-based generator keyed by
+// (seed, counter) so a request's draws do not depend on the batch it is in.
+// A row that fits the shared memory of a thread-block cluster (up to 409,600
+// logits) is read once and held there by up to 8 blocks; the threshold is
+// found by a radix search and all masses are added as integers (see
+// sample_cluster_kernel).  Longer rows go to one block of 1024 threads per
+// row that keeps exp(logit/T - max) in the caller's scratch `weights`
+// [n_rows, vocab] float32 and bisects the threshold (sample_kernel).
 #include "common.cuh"
 
 namespace {
@@ -250,6 +253,266 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, float* __r
   __syncthreads();
   if (threadIdx.x == 0) out[row] = chosen >= 0 ? chosen : top.i;
 }
+
+// ------------------------------------------------------------------ a row on a cluster
+// The same draw for rows that fit the shared memory of a thread-block cluster (8 blocks hold up to 409,600
+// logits): every block keeps its slice of the row in shared memory, so the row is read from memory once and
+// every later pass runs on chip.  The threshold for top-k / top-p is found by a radix search over the float
+// bit pattern (three levels of 1,024 bins, histograms added across the cluster through distributed shared
+// memory) instead of 30 bisection passes each, and all masses are summed as 64-bit fixed-point integers
+// (weight * 2^39, the maximum weight is exactly 1), so the result does not depend on the order of any sum
+// nor on how many blocks share the row.
+constexpr int SC_THREADS = 1024, SC_BINS = 1024, SC_MAX_CL = 8;
+constexpr int SC_MAX_SLICE = 51200;                     // floats of a row one block keeps (200 KB)
+constexpr unsigned SC_ONE_BITS = 0x3F800000u;           // bit pattern of 1.0f, the largest weight
+
+struct SampleShared {
+  unsigned limb[3][SC_BINS];                            // counts, or masses in three 13-bit limbs: 32-bit shared-memory adds
+  unsigned long long hist[2][SC_BINS];                  // the limbs put together; two buffers: one is read by the cluster
+                                                        // while the next fills
+  unsigned long long warp_tot[32];
+  unsigned long long part_base, part_total, bcast;      // what this block tells the others
+  ArgPair best;
+  ArgPair ascratch[32];
+};
+
+__device__ __forceinline__ unsigned long long weight_fix(float w) { return __float2ull_rz(w * 549755813888.0f); }   // * 2^39
+
+__device__ __forceinline__ unsigned cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the address of the same shared-memory object in block `rank` of the cluster
+template <typename T>
+__device__ __forceinline__ const T* cluster_peer(const T* p, unsigned rank) {
+  unsigned long long out;
+  asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"((unsigned long long)p), "r"(rank));
+  return reinterpret_cast<const T*>(out);
+}
+
+// inclusive sum over the block in thread order; every thread gets its own prefix
+__device__ __forceinline__ unsigned long long block_scan_incl_u64(unsigned long long v, unsigned long long* warp_tot) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += t;
+  }
+  __syncthreads();                                      // warp_tot may still be read from the call before
+  if (lane == 31) warp_tot[warp] = v;
+  __syncthreads();
+  if (warp == 0) {                                      // the warps' totals -> what lies before each warp
+    const unsigned long long own = warp_tot[lane];
+    unsigned long long t = own;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long u = __shfl_up_sync(0xffffffffu, t, o);
+      if (lane >= o) t += u;
+    }
+    warp_tot[lane] = t - own;
+  }
+  __syncthreads();
+  return v + warp_tot[warp];
+}
+__device__ __forceinline__ unsigned long long block_total_u64(unsigned long long v, unsigned long long* warp_tot) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) warp_tot[threadIdx.x >> 5] = v;
+  __syncthreads();
+  unsigned long long t = warp_tot[threadIdx.x & 31];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+// The largest threshold T >= floor_bits such that the entries with bits >= T number (COUNT) or weigh (fixed
+// point) at least `target`; floor_bits if even that does not reach it.  w: this block's n weights.
+template <bool COUNT>
+__device__ unsigned radix_threshold(SampleShared& sh, const float* w, int n, unsigned floor_bits,
+                                    unsigned long long target, int& buffer, int cl) {
+  const int tid = threadIdx.x;
+  unsigned prefix = 0;                                  // the bits above the level's ten, once decided
+  unsigned long long above = 0;                         // count / mass of the entries above the prefix's range
+  for (int lev = 0; lev < 3; ++lev) {
+    const int shift = 20 - 10 * lev;
+    unsigned long long* h = sh.hist[buffer & 1];
+    ++buffer;
+    sh.limb[0][tid] = 0;
+    if (!COUNT) { sh.limb[1][tid] = 0; sh.limb[2][tid] = 0; }
+    __syncthreads();
+    for (int i = tid; i < n; i += SC_THREADS) {
+      const float v = w[i];
+      const unsigned b = __float_as_uint(v);
+      if (b >= floor_bits && (lev == 0 || (b >> (shift + 10)) == prefix)) {
+        const unsigned key = (b >> shift) & (SC_BINS - 1);
+        if (COUNT) {
+          atomicAdd(&sh.limb[0][key], 1u);
+        } else {                                        // a slice has at most 51,200 entries: no limb's sum passes 2^32
+          const unsigned long long q = weight_fix(v);
+          if (q) {
+            atomicAdd(&sh.limb[0][key], (unsigned)(q & 0x1FFFu));
+            atomicAdd(&sh.limb[1][key], (unsigned)((q >> 13) & 0x1FFFu));
+            atomicAdd(&sh.limb[2][key], (unsigned)(q >> 26));
+          }
+        }
+      }
+    }
+    __syncthreads();
+    h[tid] = COUNT ? (unsigned long long)sh.limb[0][tid]
+                   : (unsigned long long)sh.limb[0][tid] + ((unsigned long long)sh.limb[1][tid] << 13) +
+                         ((unsigned long long)sh.limb[2][tid] << 26);
+    cluster_sync_all();
+    const int bin = SC_BINS - 1 - tid;                  // thread order = bins from the top
+    unsigned long long part[SC_MAX_CL];
+#pragma unroll
+    for (int r = 0; r < SC_MAX_CL; ++r) part[r] = r < cl ? cluster_peer(h, r)[bin] : 0ull;   // all loads in flight together
+    unsigned long long tot = 0;
+#pragma unroll
+    for (int r = 0; r < SC_MAX_CL; ++r) tot += part[r];
+    const unsigned long long reach = block_scan_incl_u64(tot, sh.warp_tot) + above;    // entries in this bin and above it
+    const int n_reach = __syncthreads_count(reach >= target);                          // they are the last n_reach threads
+    const int chosen = n_reach > 0 ? n_reach - 1 : 0;
+    if (n_reach > 0 && n_reach < SC_BINS && tid == SC_BINS - n_reach - 1) sh.bcast = reach;   // the bins above the chosen one
+    __syncthreads();
+    if (n_reach > 0 && n_reach < SC_BINS) above = sh.bcast;
+    prefix = (prefix << 10) | (unsigned)chosen;
+    __syncthreads();                                    // bcast is free again
+  }
+  return prefix > floor_bits ? prefix : floor_bits;
+}
+
+__global__ void __launch_bounds__(SC_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, long long row_stride, const float* __restrict__ temperature,
+                      const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+                      const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
+                      int* __restrict__ out, int vocab, int cl, int slice) {
+  pdl_enter();
+  extern __shared__ __align__(16) float w_s[];          // this block's slice of the row: logits, then weights
+  __shared__ SampleShared sh;
+  const int tid = threadIdx.x;
+  const int row = blockIdx.x / cl;
+  const int rank = (int)cluster_rank();
+  const int begin = min(vocab, rank * slice), n = min(vocab, begin + slice) - begin;
+  const float* lg = logits + (size_t)row * row_stride + begin;
+  // the slice into shared memory, and its best logit
+  ArgPair best{-INFINITY, -1};
+  if ((((uintptr_t)lg) & 15) == 0) {
+    for (int i = tid * 4; i < n; i += SC_THREADS * 4) {
+      if (i + 4 <= n) {
+        const float4 v = *reinterpret_cast<const float4*>(lg + i);
+        *reinterpret_cast<float4*>(w_s + i) = v;
+        if (v.x == v.x) best = better(best, ArgPair{v.x, begin + i});
+        if (v.y == v.y) best = better(best, ArgPair{v.y, begin + i + 1});
+        if (v.z == v.z) best = better(best, ArgPair{v.z, begin + i + 2});
+        if (v.w == v.w) best = better(best, ArgPair{v.w, begin + i + 3});
+      } else {
+        for (int j = i; j < n; ++j) { const float v = lg[j]; w_s[j] = v; if (v == v) best = better(best, ArgPair{v, begin + j}); }
+      }
+    }
+  } else {
+    for (int i = tid; i < n; i += SC_THREADS) { const float v = lg[i]; w_s[i] = v; if (v == v) best = better(best, ArgPair{v, begin + i}); }
+  }
+  best = block_best(best, sh.ascratch);
+  if (tid == 0) sh.best = best;
+  cluster_sync_all();
+  ArgPair top{-INFINITY, -1};
+  {
+    ArgPair peer[SC_MAX_CL];
+#pragma unroll
+    for (int r = 0; r < SC_MAX_CL; ++r) peer[r] = r < cl ? *cluster_peer(&sh.best, r) : ArgPair{-INFINITY, -1};
+#pragma unroll
+    for (int r = 0; r < SC_MAX_CL; ++r) top = better(top, peer[r]);                 // in rank order: the lowest index among equals
+  }
+  const float temp = temperature[row];
+  if (temp <= 0.0f || top.i < 0) {
+    if (rank == 0 && tid == 0) out[row] = top.i < 0 ? 0 : top.i;
+    cluster_sync_all();                                 // no block leaves while another may still read its shared memory
+    return;
+  }
+  const float inv_t = 1.0f / temp;
+  const float mx = top.v * inv_t;
+  for (int i = tid; i < n; i += SC_THREADS) {
+    const float v = w_s[i];
+    w_s[i] = (v == v) ? expf(v * inv_t - mx) : 0.0f;    // in [0, 1], the maximum is exactly 1
+  }
+  __syncthreads();
+  int buffer = 0;
+  unsigned thr = 0u;                                    // keep entries with weight bits >= thr
+  const int k = top_k[row];
+  if (k > 0 && k < vocab) thr = radix_threshold<true>(sh, w_s, n, 0u, (unsigned long long)k, buffer, cl);
+  const float mp = min_p[row];
+  if (mp > 0.0f) thr = max(thr, __float_as_uint(fminf(mp, 1.0f)));
+  const float p = top_p[row];
+  if (p > 0.0f && p < 1.0f) {                           // the largest threshold whose kept mass is >= p of the mass kept so far
+    unsigned long long mine = 0;
+    for (int i = tid; i < n; i += SC_THREADS) { const float v = w_s[i]; if (__float_as_uint(v) >= thr) mine += weight_fix(v); }
+    mine = block_total_u64(mine, sh.warp_tot);
+    if (tid == 0) sh.part_base = mine;
+    cluster_sync_all();
+    unsigned long long base = 0;
+#pragma unroll
+    for (int r = 0; r < SC_MAX_CL; ++r) base += r < cl ? *cluster_peer(&sh.part_base, r) : 0ull;
+    unsigned long long need = (unsigned long long)((double)p * (double)base);
+    if (need < 1) need = 1;
+    thr = radix_threshold<false>(sh, w_s, n, thr, need, buffer, cl);
+  }
+  // inverse CDF over the kept entries in index order: first the block that holds the target, then the thread, then the entry
+  unsigned long long mine = 0;
+  for (int i = tid; i < n; i += SC_THREADS) { const float v = w_s[i]; if (__float_as_uint(v) >= thr) mine += weight_fix(v); }
+  const unsigned long long block_total = block_total_u64(mine, sh.warp_tot);
+  if (tid == 0) sh.part_total = block_total;
+  cluster_sync_all();
+  unsigned long long total = 0, offset = 0;
+#pragma unroll
+  for (int r = 0; r < SC_MAX_CL; ++r) {
+    const unsigned long long t = r < cl ? *cluster_peer(&sh.part_total, r) : 0ull;
+    if (r < rank) offset += t;
+    total += t;
+  }
+  const unsigned long long target = (unsigned long long)((double)uniform01(seeds[row], counters[row]) * (double)total);   // < total
+  if (target >= offset && target - offset < block_total) {                    // block-uniform
+    const unsigned long long local = target - offset;
+    const int seg = (n + SC_THREADS - 1) / SC_THREADS;
+    const int sb = min(n, tid * seg), se = min(n, sb + seg);
+    unsigned long long s = 0;
+    for (int i = sb; i < se; ++i) { const float v = w_s[i]; if (__float_as_uint(v) >= thr) s += weight_fix(v); }
+    const unsigned long long incl = block_scan_incl_u64(s, sh.warp_tot), before = incl - s;
+    if (s > 0 && before <= local && local < incl) {     // exactly one thread
+      unsigned long long run = before;
+      int pick = se - 1;
+      for (int i = sb; i < se; ++i) {
+        const float v = w_s[i];
+        if (__float_as_uint(v) >= thr) {
+          run += weight_fix(v);
+          if (local < run) { pick = i; break; }
+        }
+      }
+      out[row] = begin + pick;
+    }
+  }
+  cluster_sync_all();
+}
+
+// Blocks per row for the cluster kernel (a power of two up to 8), or 0 if the row does not fit
+inline int sample_cluster_blocks(int vocab) {
+  int cl = 1;
+  while (cl < SC_MAX_CL && (vocab + cl - 1) / cl > 8192) cl <<= 1;
+  return ((vocab + cl - 1) / cl + 3) / 4 * 4 <= SC_MAX_SLICE ? cl : 0;
+}
+
+int launch_sample_cluster(const float* logits, long long row_stride, const float* temperature, const int* top_k,
+                          const float* top_p, const float* min_p, const unsigned long long* seeds,
+                          const unsigned long long* counters, int* out, int n_rows, int vocab, int cl, cudaStream_t stream) {
+  const int slice = ((vocab + cl - 1) / cl + 3) / 4 * 4;
+  const size_t smem = (size_t)slice * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int rc = launch_pdl_cluster(sample_cluster_kernel, dim3(n_rows * cl), dim3(SC_THREADS), smem, stream, dim3(cl, 1, 1),
+                                    logits, row_stride, temperature, top_k, top_p, min_p, seeds, counters, out, vocab, cl, slice);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
 }  // namespace
 
 // out[row] = lowest index of the largest value of the row (0 for a row of NaNs).  `part` is scratch of
@@ -287,6 +550,8 @@ IFX_API int ifx_sample(const float* logits, long long row_stride, float* weights
                        const unsigned long long* counters, int* out, int n_rows, int vocab, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (vocab >= (1 << 24)) return IFX_ERR_UNSUPPORTED;
+  if (const int cl = sample_cluster_blocks(vocab))     // rows that fit a cluster's shared memory; the scratch is not used
+    return launch_sample_cluster(logits, row_stride, temperature, top_k, top_p, min_p, seeds, counters, out, n_rows, vocab, cl, stream);
   const int ifx_rc = launch_pdl(sample_kernel, dim3(n_rows), dim3(ST), 0, stream, logits, row_stride, weights, temperature, top_k, top_p, min_p, seeds,
                                            counters, out, vocab);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();

@@ -487,12 +487,16 @@ def _sample(ops, logits, temperature, top_k, top_p, min_p, seeds, counters):
     return out.tolist()
 
 
-def test_sample_matches_inverse_cdf(ops):
+@pytest.mark.parametrize("v,r,offset", [(1000, 64, 0), (152064, 16, 0), (40000, 8, 1), (8193, 8, 3), (420000, 4, 0)])
+def test_sample_matches_inverse_cdf(ops, v, r, offset):
     """For each row the drawn token is the one whose cumulative-probability
-    interval (over the kept tokens, in index order) contains the row's uniform."""
+    interval (over the kept tokens, in index order) contains the row's uniform.
+    Rows short enough for one block, rows spread over a cluster of 2 to 8
+    blocks, rows that start off a 16-byte boundary, and rows too long for a
+    cluster's shared memory (the kernel that keeps its weights in scratch)."""
     import plain_qwen2 as plain
-    v, r = 1000, 64
-    logits = _rand((r, v), torch.float32, 32, 3.0)
+    wide = _rand((r, v + offset), torch.float32, 32, 3.0)
+    logits = wide[:, offset:]
     temps = [0.8 if i % 2 else 1.3 for i in range(r)]
     ks = [0, 5, 50, 0][0:4] * (r // 4)
     ps = [1.0, 1.0, 0.9, 0.5] * (r // 4)
@@ -506,6 +510,33 @@ def test_sample_matches_inverse_cdf(ops):
         u = ref.uniform01(seeds[i], counters[i])
         lo = float(cdf[got[i] - 1]) if got[i] > 0 else 0.0
         assert lo - 1e-5 <= u <= float(cdf[got[i]]) + 1e-5, f"row {i}: u={u} not in [{lo}, {float(cdf[got[i]])}]"
+
+
+def test_sample_thresholds_at_ties_and_edges(ops):
+    """top-k keeps every token that ties with the k-th; top-p 'the smallest set of the largest that reaches p'
+    with ties at the cut kept; a row of equal logits; one finite logit among -inf; NaN never drawn."""
+    v = 20000
+    base = torch.full((6, v), -30.0)                      # weights that add up to nothing beside the few set below
+    base[0, [7, 900, 19999]] = 2.0                       # three equal maxima, top-k 2: all three stay, nothing else
+    base[1, 11], base[1, 12], base[1, 13] = 3.0, 2.0, 2.0   # top-p 0.6: the maximum alone has < 0.6 -> both ties join
+    base[2] = 0.25                                        # all equal: any token, uniform over the row
+    base[3] = float("-inf"); base[3, 4242] = -1.0        # one finite logit
+    base[4, 5] = float("nan"); base[4, 6] = 1.0           # NaN never wins nor is drawn
+    base[5, 100:200] = 1.0                                # top-k 10 with 100 equal maxima: all 100 stay
+    logits = base.to(DEV)
+    n = 200
+    seen = [set() for _ in range(6)]
+    for c in range(n):
+        got = _sample(ops, logits, [1.0] * 6, [2, 0, 0, 0, 1, 10], [1.0, 0.6, 1.0, 1.0, 1.0, 1.0], [0.0] * 6,
+                      [5, 6, 7, 8, 9, 10], [c] * 6)
+        for i in range(6):
+            seen[i].add(got[i])
+    assert seen[0] == {7, 900, 19999}
+    assert seen[1] == {11, 12, 13}
+    assert len(seen[2]) > 150 and min(seen[2]) < 2000 and max(seen[2]) > 18000
+    assert seen[3] == {4242}
+    assert seen[4] == {6}
+    assert seen[5] <= set(range(100, 200)) and len(seen[5]) > 60
 
 
 def test_sample_distribution_and_determinism(ops):
