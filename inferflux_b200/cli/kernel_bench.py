@@ -123,6 +123,16 @@ class Case:
                                    lambda i: ops.attn_decode_prep_bf16(
                                        q, bias, cos, sin, slots, parts, out, pools[i][0, 0, 0], pools[i][0, 0, 1],
                                        pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, po, pm, nh, nkv, hd, scale, 0, splits)))
+                pieces = ops.attn_decode_pieces(nh, nkv, hd, ctx)
+                pe = torch.empty(b * nh * pieces * hd, device=DEV)
+                pme = torch.empty(b * nh * pieces * 2, device=DEV)
+                pce = torch.empty(b * nh, dtype=torch.int32, device=DEV)
+                self.extra.append((f"tiles shared out evenly (pieces<={pieces})", lambda i: ops.attn_decode_even_bf16(
+                    q, out, pools[i][0, 0, 0], pools[i][0, 0, 1], pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, pe, pme,
+                    pce, nh, nkv, hd, scale, 0, pieces)))
+                self.extra.append(("tiles shared out evenly, prepares q,k,v", lambda i: ops.attn_decode_even_bf16(
+                    q, out, pools[i][0, 0, 0], pools[i][0, 0, 1], pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, pe, pme,
+                    pce, nh, nkv, hd, scale, 0, pieces, prep=(bias, cos, sin, slots, parts))))
                 if sweep:
                     for s in (1, 2, 3, 4, 5, 6, 7, 8, 10, 11, 13, 16, 22, 32):
                         if s * 64 > ctx:

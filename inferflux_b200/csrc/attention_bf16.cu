@@ -117,6 +117,27 @@ __device__ __forceinline__ void load_kv_tile64(bf16* ktile, bf16* vtile, const b
   }
 }
 
+// The same with the row's page already looked up by the caller (page < 0: the row is zero-filled).
+template <int HD>
+__device__ __forceinline__ void load_kv_tile64_paged(bf16* ktile, bf16* vtile, const bf16* kbase, const bf16* vbase,
+                                                     const PagedKV& kv, int page, int key, int tid) {
+  constexpr int CPR = HD / 8;
+  const int r = tid >> 1, half = tid & 1;
+  const bool ok = page >= 0;
+  const size_t off = ok ? (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * HD : 0;
+  const bf16* ksrc = kbase + off;
+  const bf16* vsrc = vbase + off;
+  bf16* krow = ktile + r * HD;
+  bf16* vrow = vtile + r * HD;
+  const int sw = r & 7;
+#pragma unroll
+  for (int j = 0; j < CPR / 2; ++j) {
+    const int c = j * 2 + half;
+    cp_async16(krow + ((c ^ sw) << 3), ksrc + c * 8, ok);
+    cp_async16(vrow + ((c ^ sw) << 3), vsrc + c * 8, ok);
+  }
+}
+
 constexpr int BT_CACHE = 1024;      // block-table entries a block keeps in shared memory
 
 struct AttnMeta {
@@ -645,6 +666,367 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
   }
 }
 
+// ------------------------------------------------------------------ decode, shared out evenly
+// The same attention of single tokens, with the work shared out evenly: the 64-key tiles of all units (a
+// unit = entry x kv head x chunk of 8 query heads) form one list, and block b takes the tiles
+// [b q, (b + 1) q) of it, q = max(DEC_MIN_TILES, ceil(all tiles / blocks)), whatever units they belong to.
+// Every block therefore streams the same number of bytes, however the contexts' lengths differ and
+// whether or not the number of units divides the number of blocks the GPU holds.  A unit whose tiles fall
+// to several blocks is written as partial results, one per block (piece), and merged by the second
+// kernel; a unit that one block does whole is written as output at once.  Each block derives its share
+// from the step's metadata alone, before it waits for the kernel before it.
+constexpr int DEC_MAX = 1024;        // single tokens in a step that the kernel takes
+constexpr int DEC_MIN_TILES = 4;     // a block's share is at least this many tiles
+
+struct DecWalk {                     // a place in the list of tiles: entry d (of dec_entries), unit j of it, tile t of the unit
+  int d, j, t, f;                    // f: the place in the whole list
+  int len, kfirst, tile0, n_tiles;   // of entry d: keys [kfirst, len) in tiles tile0 .. tile0 + n_tiles - 1
+  const int* bt;
+};
+
+__device__ __forceinline__ int dec_tiles(int len, int window, int& kfirst) {
+  kfirst = window > 0 ? max(0, len - window) : 0;
+  return (len - 1) / 64 - kfirst / 64 + 1;
+}
+
+// tiles per entry -> P_s[0 .. n_dec] (exclusive prefix; P_s[n_dec] = all of them); 128 threads
+__device__ __forceinline__ void dec_prefix(int* P_s, const AttnMeta& m, const int* dec_entries, int n_dec, int window) {
+  __shared__ int warp_tot[4];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int chunk = (n_dec + 127) / 128;
+  const int b = min(n_dec, tid * chunk), e = min(n_dec, b + chunk);
+  int mine = 0;
+  for (int i = b; i < e; ++i) {
+    int kf;
+    const int t = dec_tiles(m.entry_ctx_start[dec_entries[i]] + 1, window, kf);
+    P_s[i + 1] = t;
+    mine += t;
+  }
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  int before = incl - mine;
+  for (int w = 0; w < warp; ++w) before += warp_tot[w];
+  if (tid == 0) P_s[0] = 0;
+  for (int i = b; i < e; ++i) { before += P_s[i + 1]; P_s[i + 1] = before; }   // a thread's own entries only
+  __syncthreads();
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_decode_even_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
+                        PagedKV kv, AttnMeta m, const int* __restrict__ dec_entries, int n_dec,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ piece_count,
+                        int n_heads, int n_kv, int head_chunks, float scale, int window, int max_pieces,
+                        int* __restrict__ error_flag) {
+  pdl_launch_dependents();
+  constexpr int KS = HD / 16, BK = 64, TK = 16;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw);             // [DSTAGES][K|V][BK][HD]
+  __shared__ int P_s[DEC_MAX + 1];
+  __shared__ float red[2][32][KS * 4 + 4];                     // two warps' partial results, lane by lane
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const int ratio = n_heads / n_kv, H = n_kv * head_chunks;
+  // Up to pdl_wait() below the block reads only what no kernel of the step writes (the step's metadata)
+  // and keys and values of tokens older than the ones being decoded.
+  dec_prefix(P_s, m, dec_entries, n_dec, window);
+  const int W = H * P_s[n_dec];
+  const int share = max(DEC_MIN_TILES, (W + (int)gridDim.x - 1) / (int)gridDim.x);
+  const int x0 = (int)blockIdx.x * share, x1 = min(W, x0 + share);
+  if (x0 >= x1) {                                              // nothing falls to this block
+    pdl_wait();                                                // no kernel of the step ends before the one before it has
+    return;
+  }
+
+  auto enter = [&](DecWalk& w) {                               // the entry's own figures, on arriving at entry w.d
+    if (w.d < 0 || w.d >= n_dec) {                             // cannot happen; never read outside the list
+      if (error_flag) atomicExch(error_flag, IFX_DEVICE_ERR_DECODE_PIECES + 1);
+      w.d = 0;
+    }
+    const int e = dec_entries[w.d];
+    w.len = m.entry_ctx_start[e] + 1;
+    w.n_tiles = dec_tiles(w.len, window, w.kfirst);
+    w.tile0 = w.kfirst / BK;
+    w.bt = m.block_tables + (size_t)e * m.bt_stride;
+  };
+  auto advance = [&](DecWalk& w) {
+    ++w.f;
+    if (++w.t == w.n_tiles) {
+      w.t = 0;
+      if (++w.j == H) {
+        w.j = 0;
+        ++w.d;
+        if (w.f < x1) enter(w);
+      }
+    }
+  };
+  DecWalk ld;                                                  // the next tile to copy
+  {
+    int lo = 0, hi = n_dec - 1;
+    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (H * P_s[mid] <= x0) lo = mid; else hi = mid - 1; }
+    ld.d = lo;
+    enter(ld);
+    const int rem = x0 - H * P_s[lo];
+    ld.j = rem / ld.n_tiles;
+    ld.t = rem - ld.j * ld.n_tiles;
+    ld.f = x0;
+  }
+  DecWalk cs = ld;                                             // the tile being worked on
+
+  int ld_page = -1;                                            // the page of this thread's row (tid / 2) of tile ld, or -1: no such key
+  auto look_up = [&]() {
+    const int key = (ld.tile0 + ld.t) * BK + (tid >> 1);
+    ld_page = (ld.f < x1 && key >= ld.kfirst && key < ld.len) ? __ldg(ld.bt + (key >> kv.page_shift)) : -1;
+  };
+  look_up();
+  auto copy_tile = [&](int stage) {                            // all threads: tile ld of the list -> ring[stage]
+    const int kvh = ld.j / head_chunks;
+    bf16* st = ring + (size_t)stage * 2 * BK * HD;
+    load_kv_tile64_paged<HD>(st, st + BK * HD, (const bf16*)kv.k + (size_t)kvh * kv.head_stride,
+                             (const bf16*)kv.v + (size_t)kvh * kv.head_stride, kv, ld_page, (ld.tile0 + ld.t) * BK + (tid >> 1), tid);
+    advance(ld);
+    look_up();                                                 // the next tile's page: the load is under way until its copy starts
+  };
+  // The first copies start before the wait as long as they hold no token of this step (the last tile of a
+  // unit does: the kernel before this one writes it).
+  int started = 0;
+  while (started < DSTAGES - 1 && ld.f < x1 && ld.t != ld.n_tiles - 1) {
+    copy_tile(started);
+    cp_async_commit();
+    ++started;
+  }
+  pdl_wait();
+  for (; started < DSTAGES - 1; ++started) {
+    if (ld.f < x1) copy_tile(started);
+    cp_async_commit();
+  }
+
+  const float sl2 = scale * LOG2E;
+  const unsigned ring_addr = (unsigned)__cvta_generic_to_shared(ring);
+  unsigned koff[KS], voff[KS];                                  // this lane's ldmatrix rows within a stage, swizzle included
+  {
+    const int jj = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+      koff[k] = (unsigned)(((warp * TK + (jj & 1) * 8 + r) * HD + (((k * 2 + (jj >> 1)) ^ r) << 3)) * 2);
+      voff[k] = (unsigned)(((BK + warp * TK + (jj >> 1) * 8 + r) * HD + (((k * 2 + (jj & 1)) ^ r) << 3)) * 2);
+    }
+  }
+  // o[dd]: rows d = dd*16 + g (regs 0,1) and + 8 (regs 2,3); columns heads 2*t4 (regs 0,2) and 2*t4+1 (regs 1,3)
+  float o[KS][4];
+  float mcol[2], lcol[2];
+  unsigned qb[KS][2];                                          // Q^T as the B operand: k = d, n = head g
+  int tok = 0, h0 = 0, nrows = 0;
+  bool fresh = true;                                           // the next tile opens a piece
+  for (int i = 0; cs.f < x1; ++i) {
+    if (fresh) {
+      fresh = false;
+      const int kvh = cs.j / head_chunks, hc = cs.j - kvh * head_chunks;
+      h0 = kvh * ratio + hc * 8;
+      nrows = min(8, ratio - hc * 8);
+      tok = m.entry_q_start[dec_entries[cs.d]];
+#pragma unroll
+      for (int d = 0; d < KS; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
+      mcol[0] = mcol[1] = -INFINITY;
+      lcol[0] = lcol[1] = 0.0f;
+      const unsigned* pq = reinterpret_cast<const unsigned*>(q + (size_t)tok * q_stride + (size_t)(h0 + g) * HD);
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        qb[k][0] = g < nrows ? pq[k * 8 + t4] : 0u;
+        qb[k][1] = g < nrows ? pq[k * 8 + 4 + t4] : 0u;
+      }
+    }
+    cp_async_wait<DSTAGES - 2>();                               // tile i has landed (for this thread)
+    __syncthreads();                                            // ... for all; and tile i - 1 is no longer read
+    if (ld.f < x1) copy_tile((i + DSTAGES - 1) % DSTAGES);
+    cp_async_commit();
+    const int kb = cs.kfirst, ke = cs.len;
+    const int key0 = (cs.tile0 + cs.t) * BK + warp * TK;        // this warp's 16 keys of the tile
+    if (key0 < ke && key0 + TK > kb) {                          // warp-uniform: something of ours is in range
+      const unsigned stage = ring_addr + (unsigned)((i % DSTAGES) * 2 * BK * HD * 2);
+      float s[4] = {0.f, 0.f, 0.f, 0.f};                        // (key g | g+8) x (head 2*t4 | 2*t4+1)
+      {
+        unsigned ka[KS][4];                                     // all key fragments first, then the MMAs
+#pragma unroll
+        for (int k = 0; k < KS; ++k) ldmatrix_x4_at(ka[k], stage + koff[k]);
+#pragma unroll
+        for (int k = 0; k < KS; ++k) mma_bf16(s, ka[k], qb[k][0], qb[k][1]);
+      }
+      const bool in0 = key0 + g >= kb && key0 + g < ke, in1 = key0 + g + 8 >= kb && key0 + g + 8 < ke;
+      if (!in0) { s[0] = -INFINITY; s[1] = -INFINITY; }
+      if (!in1) { s[2] = -INFINITY; s[3] = -INFINITY; }
+      float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+      float alpha[2], msc[2];                                   // maxima are kept in raw-score units
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                             // over the 8 lanes that hold the other keys
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+        const float mnew = fmaxf(mcol[h], mx[h]);
+        msc[h] = mnew == -INFINITY ? 0.0f : mnew * sl2;
+        alpha[h] = fast_exp2(mcol[h] * sl2 - msc[h]);
+        mcol[h] = mnew;
+      }
+      float p[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) p[c] = fast_exp2(fmaf(s[c], sl2, -msc[c & 1]));
+      lcol[0] = lcol[0] * alpha[0] + p[0] + p[2];
+      lcol[1] = lcol[1] * alpha[1] + p[1] + p[3];
+      if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {   // a maximum moved: rescale o
+#pragma unroll
+        for (int d = 0; d < KS; ++d) { o[d][0] *= alpha[0]; o[d][1] *= alpha[1]; o[d][2] *= alpha[0]; o[d][3] *= alpha[1]; }
+      }
+      // P^T as the B operand (k = key, n = head): transpose the two 8x8 blocks
+      const unsigned pb0 = movmatrix_trans(pack_bf16(p[0], p[1]));
+      const unsigned pb1 = movmatrix_trans(pack_bf16(p[2], p[3]));
+      {
+        unsigned va[KS][4];                                     // V^T as the A operand: rows d, columns keys
+#pragma unroll
+        for (int d = 0; d < KS; ++d) ldmatrix_x4_trans_at(va[d], stage + voff[d]);
+#pragma unroll
+        for (int d = 0; d < KS; ++d) mma_bf16(o[d], va[d], pb0, pb1);
+      }
+    }
+    if (cs.t == cs.n_tiles - 1 || cs.f == x1 - 1) {             // the piece ends here (block-uniform): the four warps' results become one
+      fresh = true;
+      float mm[2], ll[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mm[h] = mcol[h] == -INFINITY ? -INFINITY : mcol[h] * sl2;   // to exponent units
+        ll[h] = lcol[h];
+        ll[h] += __shfl_xor_sync(0xffffffffu, ll[h], 4);
+        ll[h] += __shfl_xor_sync(0xffffffffu, ll[h], 8);
+        ll[h] += __shfl_xor_sync(0xffffffffu, ll[h], 16);
+      }
+      auto put = [&](int slot) {
+        float* r = red[slot][lane];
+#pragma unroll
+        for (int d = 0; d < KS; ++d) { r[d * 4] = o[d][0]; r[d * 4 + 1] = o[d][1]; r[d * 4 + 2] = o[d][2]; r[d * 4 + 3] = o[d][3]; }
+        r[KS * 4] = mm[0]; r[KS * 4 + 1] = mm[1]; r[KS * 4 + 2] = ll[0]; r[KS * 4 + 3] = ll[1];
+      };
+      auto take = [&](int slot) {
+        const float* r = red[slot][lane];
+        float fa[2], fb[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float mo = r[KS * 4 + h], mn = fmaxf(mm[h], mo);
+          fa[h] = mm[h] == -INFINITY ? 0.0f : fast_exp2(mm[h] - mn);
+          fb[h] = mo == -INFINITY ? 0.0f : fast_exp2(mo - mn);
+          ll[h] = ll[h] * fa[h] + r[KS * 4 + 2 + h] * fb[h];
+          mm[h] = mn;
+        }
+#pragma unroll
+        for (int d = 0; d < KS; ++d) {
+          o[d][0] = o[d][0] * fa[0] + r[d * 4] * fb[0];
+          o[d][1] = o[d][1] * fa[1] + r[d * 4 + 1] * fb[1];
+          o[d][2] = o[d][2] * fa[0] + r[d * 4 + 2] * fb[0];
+          o[d][3] = o[d][3] * fa[1] + r[d * 4 + 3] * fb[1];
+        }
+      };
+      if (warp >= 2) put(warp - 2);
+      __syncthreads();
+      if (warp < 2) take(warp);
+      __syncthreads();
+      if (warp == 1) put(0);
+      __syncthreads();
+      if (warp == 0) {
+        take(0);
+        const int xs = H * P_s[cs.d] + cs.j * cs.n_tiles;       // where the unit starts in the list
+        const int first = xs / share, pieces = (xs + cs.n_tiles - 1) / share - first + 1;
+        bool pieces_ok = true;
+        const int piece = (int)blockIdx.x - first;
+        if (pieces > max_pieces || piece < 0 || piece >= pieces) {                              // the caller's bound on the contexts was too low: say so, write nothing
+          if (error_flag && lane == 0) atomicExch(error_flag, IFX_DEVICE_ERR_DECODE_PIECES);
+          pieces_ok = false;
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int hl = 2 * t4 + c;
+          if (hl < nrows && g == 0) piece_count[cs.d * n_heads + h0 + hl] = pieces_ok ? pieces : 0;   // for the merge kernel
+          if (hl < nrows && pieces_ok) {
+            const int head = h0 + hl;
+            if (pieces == 1) {
+              const float inv = ll[c] > 0.0f ? 1.0f / ll[c] : 0.0f;
+              bf16* dst = out + (size_t)tok * out_stride + (size_t)head * HD;
+#pragma unroll
+              for (int d = 0; d < KS; ++d) {
+                dst[d * 16 + g] = __float2bfloat16_rn(o[d][c] * inv);
+                dst[d * 16 + g + 8] = __float2bfloat16_rn(o[d][c + 2] * inv);
+              }
+            } else {
+              const size_t pp = ((size_t)cs.d * n_heads + head) * max_pieces + piece;
+              float* dst = part_o + pp * HD;
+#pragma unroll
+              for (int d = 0; d < KS; ++d) { dst[d * 16 + g] = o[d][c]; dst[d * 16 + g + 8] = o[d][c + 2]; }
+              if (g == 0) { part_ml[pp * 2] = mm[c]; part_ml[pp * 2 + 1] = ll[c]; }
+            }
+          }
+        }
+      }
+    }
+    advance(cs);
+  }
+  cp_async_wait<0>();
+}
+
+// merge the pieces of the units that several blocks shared: grid (n_dec, n_heads), HD threads.  piece_count
+// [n_dec, n_heads]: into how many pieces the attention kernel cut the head's keys (1: it wrote the output itself).
+__global__ void attn_decode_even_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const int* __restrict__ piece_count, bf16* __restrict__ out,
+                                              long long out_stride, const int* __restrict__ dec_entries,
+                                              const int* __restrict__ entry_q_start, int n_heads, int head_dim,
+                                              int max_pieces) {
+  pdl_launch_dependents();
+  const int dec = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+  const int tok = entry_q_start[dec_entries[dec]];            // the step's metadata: read before the wait
+  pdl_wait();
+  const int n_pieces = piece_count[dec * n_heads + head];
+  if (n_pieces <= 1) return;
+  const size_t p0 = ((size_t)dec * n_heads + head) * max_pieces;
+  if (n_pieces <= 16) {
+    for (int d = tid; d < head_dim; d += blockDim.x) {
+      float2 ml[16];
+      float po[16];
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < n_pieces) {
+          ml[s] = *reinterpret_cast<const float2*>(part_ml + (p0 + s) * 2);
+          po[s] = part_o[(p0 + s) * head_dim + d];
+        }
+      float mm = -INFINITY;
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < n_pieces) mm = fmaxf(mm, ml[s].x);
+      float l = 0.0f, acc = 0.0f;
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < n_pieces) {
+          const float f = ml[s].x == -INFINITY ? 0.0f : fast_exp2(ml[s].x - mm);
+          l += ml[s].y * f;
+          acc += po[s] * f;
+        }
+      out[(size_t)tok * out_stride + (size_t)head * head_dim + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    }
+    return;
+  }
+  float mm = -INFINITY;
+#pragma unroll 8
+  for (int s = 0; s < n_pieces; ++s) mm = fmaxf(mm, part_ml[(p0 + s) * 2]);
+  for (int d = tid; d < head_dim; d += blockDim.x) {
+    float l = 0.0f, acc = 0.0f;
+#pragma unroll 8
+    for (int s = 0; s < n_pieces; ++s) {
+      const float ms = part_ml[(p0 + s) * 2];
+      const float f = ms == -INFINITY ? 0.0f : fast_exp2(ms - mm);
+      l += part_ml[(p0 + s) * 2 + 1] * f;
+      acc += part_o[(p0 + s) * head_dim + d] * f;
+    }
+    out[(size_t)tok * out_stride + (size_t)head * head_dim + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+  }
+}
+
 PagedKV make_kv(void* k_layer, void* v_layer, long long page_stride, int page_size, int head_dim) {
   PagedKV kv;
   kv.k = k_layer; kv.v = v_layer; kv.page_stride = page_stride;
@@ -687,6 +1069,50 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
   if (!rc) rc = IFX_LAUNCH_CHECK();
   if (rc || n_splits == 1) return rc;
   rc = launch_pdl(attn_decode_merge_kernel, dim3(n_dec, n_heads), dim3(HD < 128 ? HD : 128), 0, stream, part_o, part_ml, (bf16*)out, out_stride, dec_entries, m.entry_q_start, n_heads, HD, n_splits);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+// Blocks of the even-share decode kernel that the GPU holds at once (asked once per head size); negative: a CUDA error.
+template <int HD>
+int even_resident_blocks() {
+  static int resident = 0;
+  if (!resident) {
+    const size_t smem = (size_t)DSTAGES * 2 * 64 * HD * sizeof(bf16);
+    auto kern = attn_decode_even_kernel<HD>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return -(int)e;
+    int per_sm = 0, dev = 0, sms = 0;
+    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 128, smem)) != cudaSuccess) return -(int)e;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return -(int)e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return -(int)e;
+    resident = per_sm * sms > 0 ? per_sm * sms : 1;
+  }
+  return resident;
+}
+
+// Pieces a unit can fall into when no context is longer than max_keys: a block's share is at least
+// DEC_MIN_TILES tiles, and at least the unit's own tiles times the units per entry over the blocks.
+inline int even_max_pieces(int max_keys, int blocks, int units_per_entry) {
+  const int tiles = (max_keys + 63) / 64 + 1;                  // a window may begin in the middle of a tile
+  const int by_min = (tiles + DEC_MIN_TILES - 2) / DEC_MIN_TILES + 1, by_blocks = blocks / units_per_entry + 2;
+  return by_min < by_blocks ? by_min : by_blocks;
+}
+
+template <int HD>
+int launch_decode_even(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnMeta m,
+                       const int* dec_entries, int n_dec, float* part_o, float* part_ml, int* piece_count, int n_heads,
+                       int n_kv, float scale, int window, int max_pieces, int* error_flag, cudaStream_t stream) {
+  const int blocks = even_resident_blocks<HD>();
+  if (blocks < 0) return -blocks;
+  const size_t smem = (size_t)DSTAGES * 2 * 64 * HD * sizeof(bf16);
+  const int head_chunks = (n_heads / n_kv + 7) / 8;
+  int rc = launch_pdl(attn_decode_even_kernel<HD>, dim3(blocks), dim3(128), smem, stream, (const bf16*)q, q_stride,
+                      (bf16*)out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, piece_count, n_heads, n_kv, head_chunks,
+                      scale, window, max_pieces, error_flag);
+  if (!rc) rc = IFX_LAUNCH_CHECK();
+  if (rc) return rc;
+  rc = launch_pdl(attn_decode_even_merge_kernel, dim3(n_dec, n_heads), dim3(HD < 128 ? HD : 128), 0, stream, (const float*)part_o,
+                  (const float*)part_ml, (const int*)piece_count, (bf16*)out, out_stride, dec_entries, m.entry_q_start, n_heads, HD,
+                  max_pieces);
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 }  // namespace
@@ -805,6 +1231,48 @@ IFX_API int ifx_attn_decode_plan(int n_dec, int n_heads, int n_kv, int head_dim,
   if (s < 1) s = 1;
   const int tiles = (max_keys + 63) / 64, per = (tiles + s - 1) / s;
   return (tiles + per - 1) / per;                              // no part without a tile
+}
+
+// Attention of single tokens with the tiles of all entries shared out evenly over the blocks the GPU holds
+// (attn_decode_even_kernel): for steps whose contexts differ much in length.  q is rotated already and the
+// step's keys and values are in the cache (ifx_qkv_rope_kv_write).  Scratch: part_o float32 [n_dec * n_heads *
+// max_pieces * head_dim], part_ml float32 [n_dec * n_heads * max_pieces * 2], piece_count int [n_dec *
+// n_heads]; max_pieces from ifx_attn_decode_even_pieces for a bound on the contexts' lengths (new token
+// included; with a window, the window); error_flag: a device int that the kernel sets to 2 if it meets a
+// longer context (it then writes nothing for that entry).
+IFX_API int ifx_attn_decode_even_bf16(const void* q, long long q_stride, void* out, long long out_stride,
+                                      void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                      const int* block_tables, int bt_stride, const int* dec_entries, int n_dec,
+                                      const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
+                                      float* part_o, float* part_ml, int* piece_count, int n_heads, int n_kv,
+                                      int head_dim, float scale, int window, int max_pieces, int* error_flag,
+                                      cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (n_kv < 1 || n_heads % n_kv || max_pieces < 1 || n_dec > DEC_MAX || !error_flag) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  if ((q_stride & 1) || ((uintptr_t)q & 3)) return IFX_ERR_ALIGNMENT;
+  if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
+  if (!part_o || !part_ml || !piece_count || ((uintptr_t)part_ml & 7)) return IFX_ERR_UNSUPPORTED;
+  PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
+  AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
+  if (head_dim == 128)
+    return launch_decode_even<128>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, piece_count, n_heads, n_kv, scale, window, max_pieces, error_flag, stream);
+  if (head_dim == 64)
+    return launch_decode_even<64>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, piece_count, n_heads, n_kv, scale, window, max_pieces, error_flag, stream);
+  return IFX_ERR_UNSUPPORTED;
+}
+
+// Blocks that the even-share decode kernel runs (what the GPU holds at once).  Negative: a CUDA error.
+IFX_API int ifx_attn_decode_even_blocks(int head_dim) {
+  return head_dim == 128 ? even_resident_blocks<128>() : head_dim == 64 ? even_resident_blocks<64>() : 1;
+}
+
+// The scratch's pieces per (entry, head) for contexts of at most max_keys keys.  Negative: a CUDA error.
+IFX_API int ifx_attn_decode_even_pieces(int n_heads, int n_kv, int head_dim, int max_keys) {
+  if (n_kv < 1 || n_heads < n_kv || max_keys < 1) return 1;
+  const int blocks = head_dim == 128 ? even_resident_blocks<128>() : head_dim == 64 ? even_resident_blocks<64>() : 1;
+  if (blocks < 0) return blocks;
+  return even_max_pieces(max_keys, blocks, n_kv * ((n_heads / n_kv + 7) / 8));
 }
 
 IFX_STAMP_READER(ifx_stamps_attn)

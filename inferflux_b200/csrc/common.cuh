@@ -20,6 +20,10 @@ enum IfxError : int {
   IFX_ERR_UNSUPPORTED = 100001,   // a size or type the kernel does not take
   IFX_ERR_ALIGNMENT = 100002,     // a pointer or stride that breaks an alignment rule
 };
+// What a kernel writes into the device error word that its caller passes: 1 = a bounded wait ran out,
+// 2 = the decode attention kernel met a context longer than the bound it was launched with.
+constexpr int IFX_DEVICE_ERR_WAIT = 1, IFX_DEVICE_ERR_DECODE_PIECES = 2;
+
 
 typedef __nv_bfloat16 bf16;
 

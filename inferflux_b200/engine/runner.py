@@ -20,7 +20,7 @@ import torch
 
 from ..cache import OutOfPages, OutOfSlots, KVCacheManager, KVCacheStorage, StateSlotManager, StateSlotStorage, bytes_per_token
 from ..config.engine_config import EngineConfig
-from .batch import CHUNK_TILE, QUERY_TILE, UMMA_TILE, MetadataSlab, StepContext, StepEntry
+from .batch import CHUNK_TILE, QUERY_TILE, UMMA_TILE, MetadataSlab, StepContext, StepEntry, contexts_skewed
 from ..kernels import ops
 from .model import Model
 
@@ -204,7 +204,8 @@ class StepRunner:
             block_tables=d_tabs, slot_maps=d_sm, want_rows=d_want, n_want=len(want_rows),
             max_q_len=int(lens.max()),
             max_ctx_len=int((starts + lens).max()) if widths is None else max(out_widths) * ps,
-            page_size=ps, kv=self.kv_storage, dtype=self.dtype, device=self.device)
+            page_size=ps, kv=self.kv_storage, dtype=self.dtype, device=self.device,
+            decode_skewed=contexts_skewed([int(starts[i]) + 1 for i in dec_entries]))
 
     def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
         """Reserve pages for the step's tokens and describe the step on the device."""
@@ -256,7 +257,8 @@ class StepRunner:
         step = self.GRAPH_WIDTH_STEP
         widths = tuple((max(len(self.kv.block_table(e.rid, g)) for e in entries) + step - 1) // step * step
                        for g in range(self.kv.num_groups))
-        key = (len(entries), widths)
+        # the attention kernel for single tokens is chosen by how much the contexts differ: part of the shape
+        key = (len(entries), widths, contexts_skewed([self.kv.length(e.rid) + 1 for e in entries]))
         rec = self._graphs.get(key)
         if rec is None:
             # While requests join and leave, many batch sizes come once or twice; capturing costs more than

@@ -61,6 +61,13 @@ def _lib():
                                                   c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int,
                                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.ifx_attn_decode_prep_bf16.restype = c_int
+        lib.ifx_attn_decode_even_bf16.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
+                                                  c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int,
+                                                  c_void_p, c_void_p]
+        lib.ifx_attn_decode_even_bf16.restype = c_int
+        lib.ifx_attn_decode_even_pieces.argtypes = [c_int, c_int, c_int, c_int]
+        lib.ifx_attn_decode_even_pieces.restype = c_int
         lib.ifx_gemv_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll,
                                       c_int, c_int, c_void_p]
         lib.ifx_gemm_umma.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
@@ -335,9 +342,14 @@ def check_device_errors(device) -> None:
     reads one word back from the device, so it synchronises)."""
     key = torch.device(device).index or 0
     flag = _error_flags.get(key)
-    if flag is not None and int(flag.item()) != 0:
-        flag.zero_()
-        raise KernelError("a kernel gave up waiting on a barrier (bounded wait ran out); its output is invalid")
+    if flag is not None:
+        code = int(flag.item())
+        if code != 0:
+            flag.zero_()
+            if code == 2:
+                raise KernelError("decode attention met a context longer than the bound its scratch was sized for; "
+                                  "its output is invalid")
+            raise KernelError("a kernel gave up waiting on a barrier (bounded wait ran out); its output is invalid")
 
 
 def matmul_library(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -536,6 +548,58 @@ def attn_decode_splits(n_dec: int, n_heads: int, n_kv: int, head_dim: int, max_k
             raise KernelError(f"attn_decode_splits: CUDA error {-s}")
         _decode_plans[key] = s
     return _decode_plans[key]
+
+
+DECODE_EVEN_MAX_ENTRIES = 1024        # single tokens per call of attn_decode_even_bf16
+
+
+def attn_decode_pieces(n_heads: int, n_kv: int, head_dim: int, max_keys: int) -> int:
+    """Pieces per (entry, head) that :func:`attn_decode_even_bf16`'s scratch must
+    have room for when no entry sees more than ``max_keys`` keys."""
+    key = ("even", n_heads, n_kv, head_dim, (max_keys + 63) // 64)
+    if key not in _decode_plans:
+        if len(_decode_plans) > 65536:
+            _decode_plans.clear()
+        s = int(_lib().ifx_attn_decode_even_pieces(n_heads, n_kv, head_dim, max_keys))
+        if s < 1:
+            raise KernelError(f"attn_decode_pieces: CUDA error {-s}")
+        _decode_plans[key] = s
+    return _decode_plans[key]
+
+
+def attn_decode_even_bf16(q: torch.Tensor, out: torch.Tensor, k_layer: torch.Tensor, v_layer: torch.Tensor,
+                          page_stride: int, page_size: int, block_tables: torch.Tensor, dec_entries: torch.Tensor,
+                          n_dec: int, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
+                          entry_ctx_start: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                          piece_count: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
+                          max_pieces: int) -> torch.Tensor:
+    """Tensor-core attention of single decoded tokens (entries listed in
+    dec_entries, at most DECODE_EVEN_MAX_ENTRIES) for steps whose contexts
+    differ much in length: the 64-key tiles of all entries are shared out
+    evenly over the blocks the GPU holds, so the longest context does not set
+    the time; what several blocks share is merged by a second kernel.
+    ``max_pieces`` from :func:`attn_decode_pieces`; scratch part_o float32
+    [n_dec * n_heads * max_pieces * head_dim], part_ml float32 [... * 2],
+    piece_count int32 [n_dec * n_heads].  A context beyond the bound that
+    max_pieces was made for sets the device error flag."""
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16,
+          "attn_decode_even_bf16: bfloat16 operands")
+    _need(head_dim in FAST_ATTENTION_HEAD_DIMS, f"attn_decode_even_bf16: head_dim {head_dim} not in {FAST_ATTENTION_HEAD_DIMS}")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
+    _need(1 <= n_dec <= DECODE_EVEN_MAX_ENTRIES, f"attn_decode_even_bf16: 1 to {DECODE_EVEN_MAX_ENTRIES} entries")
+    _need(part_o.dtype == torch.float32 and part_o.numel() >= n_dec * n_heads * max_pieces * head_dim
+          and part_ml.dtype == torch.float32 and part_ml.numel() >= n_dec * n_heads * max_pieces * 2
+          and piece_count.dtype == torch.int32 and piece_count.numel() >= n_dec * n_heads,
+          "attn_decode_even_bf16: scratch too small")
+    global launch_count
+    launch_count += 1          # the merge kernel
+    _check(_lib().ifx_attn_decode_even_bf16(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
+                                            page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
+                                            _ptr(dec_entries), n_dec, _ptr(entry_q_start), _ptr(entry_q_len),
+                                            _ptr(entry_ctx_start), _ptr(part_o), _ptr(part_ml), _ptr(piece_count), n_heads,
+                                            n_kv, head_dim, float(scale), int(window), int(max_pieces),
+                                            _ptr(error_flag(q.device)), _stream()), "attn_decode_even_bf16")
+    return out
 
 
 # --------------------------------------------------------------------- sampling

@@ -115,7 +115,8 @@ class GQAttention(Part):
         k_layer, v_layer, page_stride = ctx.kv.layer_views(g, run.kv_index)
         attn = torch.empty((n, self.n_heads * self.head_dim), dtype=qkv.dtype, device=x.device)
         if (ctx.n_decode == n and not ctx.n_chunk_tiles and nkv_w and qkv.dtype == torch.bfloat16
-                and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and 2 * cos.shape[1] == self.head_dim):
+                and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and 2 * cos.shape[1] == self.head_dim
+                and not self._share_by_tiles(ctx)):
             # single tokens only: the attention kernel adds the bias, rotates and writes the cache itself
             self.decode(qkv, attn, ctx, g, k_layer, v_layer, page_stride,
                         prep=(self.qkv_bias, cos, sin, ctx.slot_maps[g], partials))
@@ -150,13 +151,32 @@ class GQAttention(Part):
         if ctx.n_decode:
             self.decode(qkv, attn, ctx, g, k_layer, v_layer, page_stride)
 
+    def _share_by_tiles(self, ctx) -> bool:
+        """Contexts of very different lengths (and no window that evens them
+        out): the kernel that shares the tiles of all entries out evenly."""
+        return (ctx.decode_skewed and ctx.n_decode <= ops.DECODE_EVEN_MAX_ENTRIES
+                and not (self.window and self.window < 1024))
+
     def decode(self, qkv, attn, ctx, g, k_layer, v_layer, page_stride, prep=None) -> None:
-        """The step's single tokens: the keys of each are cut into as many parts
-        as fill the GPU, and merged.  ``prep`` = (bias, cos, sin, slot map,
-        partial sums or None): qkv is still the bare product and the kernel
-        prepares q, k and v itself."""
-        n_splits = ops.attn_decode_splits(ctx.n_decode, self.n_heads, self.n_kv, self.head_dim,
-                                          min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len)
+        """The step's single tokens.  Contexts of about the same length: the keys
+        of each are cut into as many parts as fill the GPU, and merged; with
+        ``prep`` = (bias, cos, sin, slot map, partial sums or None) qkv is
+        still the bare product and the kernel prepares q, k and v itself.
+        Contexts of very different lengths: all their tiles are shared out
+        evenly over the blocks."""
+        max_keys = min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len
+        if prep is None and self._share_by_tiles(ctx):
+            pieces = ops.attn_decode_pieces(self.n_heads, self.n_kv, self.head_dim, max_keys)
+            rows = ctx.n_decode * self.n_heads * pieces
+            part_o = torch.empty(rows * self.head_dim, dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty(rows * 2, dtype=torch.float32, device=qkv.device)
+            count = torch.empty(ctx.n_decode * self.n_heads, dtype=torch.int32, device=qkv.device)
+            ops.attn_decode_even_bf16(qkv, attn, k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g],
+                                      ctx.decode_entries, ctx.n_decode, ctx.entry_q_start, ctx.entry_q_len,
+                                      ctx.entry_ctx_start, part_o, part_ml, count, self.n_heads, self.n_kv, self.head_dim,
+                                      self.scale, self.window, pieces)
+            return
+        n_splits = ops.attn_decode_splits(ctx.n_decode, self.n_heads, self.n_kv, self.head_dim, max_keys)
         part_o = part_ml = None
         if n_splits > 1:
             rows = ctx.n_decode * self.n_heads * n_splits

@@ -303,3 +303,40 @@ def test_random_arrivals_preemption_and_running_ahead(folders):
         assert done[i].tokens == alone[i].tokens and done[i].finish_reason == alone[i].finish_reason, i
     assert st["pages_free"] == st["pages_total"]
     eng.runner.kv.check(), eng.runner.slots.check()
+
+
+def test_decoding_with_contexts_of_very_different_lengths(monkeypatch):
+    """One request with 1,150 tokens of context beside three short ones: attention for the single tokens
+    shares the tiles of all four out evenly over its blocks (the other kernel would make the long context
+    wait alone), in eager steps and in captured ones; the logits are the plain implementation's."""
+    from inferflux_b200 import StepEntry
+    from inferflux_b200.kernels import ops
+    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=96, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=160, vocab_size=500,
+               rope_theta=300000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1536,
+               use_sliding_window=False, hidden_act="silu", torch_dtype="bfloat16")
+    folder = make_model_folder(cfg, seed=91, sharpen=4.0)
+    _, cfg, w = (folder, *plain.load_folder(folder))
+    calls = {"even": 0, "split": 0}
+    even, split, prep = ops.attn_decode_even_bf16, ops.attn_decode_bf16, ops.attn_decode_prep_bf16
+    monkeypatch.setattr(ops, "attn_decode_even_bf16", lambda *a, **k: (calls.__setitem__("even", calls["even"] + 1), even(*a, **k))[1])
+    monkeypatch.setattr(ops, "attn_decode_bf16", lambda *a, **k: (calls.__setitem__("split", calls["split"] + 1), split(*a, **k))[1])
+    monkeypatch.setattr(ops, "attn_decode_prep_bf16", lambda *a, **k: (calls.__setitem__("split", calls["split"] + 1), prep(*a, **k))[1])
+    steps = 12
+    lengths = [1150, 30, 75, 12]
+    seqs = [random_tokens(cfg["vocab_size"], n + steps, 300 + i) for i, n in enumerate(lengths)]
+    refs = [plain.forward(cfg, w, s).numpy() for s in seqs]
+    eng = _engine(folder, "bfloat16", kv_cache_tokens=2048, max_model_len=1536)
+    for i, (s, n) in enumerate(zip(seqs, lengths)):
+        for a in range(0, n, 512):
+            eng.run_step([StepEntry(f"r{i}", s[a:min(n, a + 512)], [])])
+    worst = 0.0
+    for p in range(steps):
+        logits = eng.run_step([StepEntry(f"r{i}", [s[n + p]], [0]) for i, (s, n) in enumerate(zip(seqs, lengths))]).cpu().numpy()
+        for i, n in enumerate(lengths):
+            ref = refs[i][n + p]
+            worst = max(worst, float(np.abs(logits[i].astype(np.float64) - ref).max() / np.abs(ref).max()))
+    assert worst <= TOL["bfloat16"], f"{worst:.3e}"
+    assert calls["even"] > 0 and calls["split"] == 0, calls          # layers x (eager steps + the capture)
+    assert eng.runner.graph_replays >= steps - 4
+    ops.check_device_errors("cuda:0")

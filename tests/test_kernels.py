@@ -287,6 +287,18 @@ def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, 
                 ops.attn_decode_bf16(qd, nh * hd, out_d, *args, it(decs).to(DEV), len(decs), md["q_start"], md["q_len"],
                                      md["ctx_start"], po, pm, nh, nkv, hd, scale, window or 0, splits)
                 _close(out_d, want, 1.5e-2, f"decode attention, {splits} splits")
+            # the kernel that shares the tiles of all entries out evenly, with exact and with loose bounds on the contexts
+            longest = max(min(c + 1, window) if window else c + 1 for c, ql in entries if ql == 1)
+            for bound in (longest, 4 * longest + 100):
+                pieces = ops.attn_decode_pieces(nh, nkv, hd, bound)
+                out_e = out.clone()
+                po = torch.full((len(decs) * nh * pieces * hd,), float("nan"), dtype=torch.float32, device=DEV)
+                pm = torch.full((len(decs) * nh * pieces * 2,), float("nan"), dtype=torch.float32, device=DEV)
+                pc = torch.full((len(decs) * nh,), -7, dtype=torch.int32, device=DEV)
+                ops.attn_decode_even_bf16(qd, out_e, *args, it(decs).to(DEV), len(decs), md["q_start"], md["q_len"],
+                                          md["ctx_start"], po, pm, pc, nh, nkv, hd, scale, window or 0, pieces)
+                ops.check_device_errors(DEV)
+                _close(out_e, want, 1.5e-2, f"decode attention, tiles shared out evenly, {pieces} pieces")
             out = out_d
     _close(out, want, 2e-5 if dtype == torch.float32 else 1.5e-2, "attention")
     return out.float().cpu(), want

@@ -220,3 +220,14 @@ def test_token_slice_equals_the_slice_of_all_tokens():
     for start in range(0, 8):
         for count in range(1, 9 - start):
             assert r.token_slice(start, count) == r.tokens[start:start + count]
+
+
+def test_contexts_skewed_rule():
+    """Which steps of single tokens count as having contexts of very different lengths."""
+    from inferflux_b200.engine.batch import contexts_skewed
+    assert not contexts_skewed([4096] * 8)                     # equal
+    assert not contexts_skewed([4096])                         # one request
+    assert not contexts_skewed([900, 10, 10, 10])              # nothing long
+    assert contexts_skewed([32768] + [1024] * 63)
+    assert contexts_skewed([1150, 30, 75, 12])
+    assert not contexts_skewed([2048, 1800, 1500, 1900])       # longest below 1.5 times the mean
