@@ -25,7 +25,7 @@ import torch
 from ..kernels import ops
 
 DEV = "cuda:0"
-KERNELS = ["gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_lm_head", "attn_decode", "attn_prefill",
+KERNELS = ["gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_lm_head", "attn_decode", "attn_decode_skewed", "attn_prefill",
            "attn_prefill_umma",
            "add_rmsnorm", "rope_kv", "swiglu", "argmax", "sample"]
 
@@ -88,28 +88,35 @@ class Case:
                         gu = torch.empty(rows, wrows, **bf)
                         self.extra.append(("library + swiglu", lambda i: ops.swiglu(torch.mm(x, ws[i].t(), out=gu), outg)))
             self.extra.append(("library", lambda i: torch.mm(x, ws[i].t())))
-        elif name in ("attn_decode", "attn_prefill", "attn_prefill_umma"):
+        elif name in ("attn_decode", "attn_decode_skewed", "attn_prefill", "attn_prefill_umma"):
             ps = 16
-            decode = name == "attn_decode"
+            decode = name.startswith("attn_decode")
             b = rows if decode else 1
             q_len = 1 if decode else rows
             ctx = context
+            # skewed: the first request has the whole context, the others a thirtieth of it
+            ctxs = [ctx] + [max(1, ctx // 30)] * (b - 1) if name == "attn_decode_skewed" else [ctx] * b
             nblk = (ctx + ps - 1) // ps
-            pages = b * nblk
+            pages = sum((c + ps - 1) // ps for c in ctxs)
             self.n_rot = max(2, int(300e6 // (pages * 2 * nkv * ps * hd * 2)) + 1)
             pools = [torch.randn(pages, 1, 2, nkv, ps, hd, **bf) for _ in range(self.n_rot)]
-            bt = torch.randperm(pages, device=DEV).int().view(b, nblk).contiguous()
+            perm, bt_host, at = torch.randperm(pages).int(), torch.full((b, nblk), -1, dtype=torch.int32), 0
+            for r, c in enumerate(ctxs):
+                k = (c + ps - 1) // ps
+                bt_host[r, :k] = perm[at:at + k]
+                at += k
+            bt = bt_host.to(DEV)
             n = b * q_len
             q = torch.randn(n, (nh + 2 * nkv) * hd, **bf)
             out = torch.empty(n, nh * hd, **bf)
-            qs, ql, cs = it([i * q_len for i in range(b)]), it([q_len] * b), it([ctx - q_len] * b)
+            qs, ql, cs = it([i * q_len for i in range(b)]), it([q_len] * b), it([c - q_len for c in ctxs])
             scale = hd ** -0.5
             if decode:
                 dec = it(list(range(b)))
                 splits = ops.attn_decode_splits(b, nh, nkv, hd, ctx)
                 po = torch.empty(b * nh * splits * hd, device=DEV)
                 pm = torch.empty(b * nh * splits * 2, device=DEV)
-                self.bytes = b * ctx * nkv * hd * 2 * 2
+                self.bytes = sum(ctxs) * nkv * hd * 2 * 2
                 self.note = f"splits={splits}"
                 self.run = lambda i: ops.attn_decode_bf16(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
                                                           pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, po, pm, nh, nkv,
@@ -117,7 +124,7 @@ class Case:
                 # the variant that adds the bias, rotates and writes the cache itself (steps of single tokens)
                 width = (nh + 2 * nkv) * hd
                 bias, cos, sin = torch.randn(width, device=DEV), torch.rand(b, hd // 2, device=DEV), torch.rand(b, hd // 2, device=DEV)
-                slots = it([int(bt[r, (ctx - 1) // ps]) * ps + (ctx - 1) % ps for r in range(b)])
+                slots = it([int(bt_host[r, (c - 1) // ps]) * ps + (c - 1) % ps for r, c in enumerate(ctxs)])
                 parts = torch.randn(4, b, width, device=DEV) if rows <= 8 else None
                 self.extra.append((f"prepares q,k,v {'from 4 partial sums' if parts is not None else ''}",
                                    lambda i: ops.attn_decode_prep_bf16(
@@ -130,9 +137,6 @@ class Case:
                 self.extra.append((f"tiles shared out evenly (pieces<={pieces})", lambda i: ops.attn_decode_even_bf16(
                     q, out, pools[i][0, 0, 0], pools[i][0, 0, 1], pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, pe, pme,
                     pce, nh, nkv, hd, scale, 0, pieces)))
-                self.extra.append(("tiles shared out evenly, prepares q,k,v", lambda i: ops.attn_decode_even_bf16(
-                    q, out, pools[i][0, 0, 0], pools[i][0, 0, 1], pools[i].stride(0), ps, bt, dec, b, qs, ql, cs, pe, pme,
-                    pce, nh, nkv, hd, scale, 0, pieces, prep=(bias, cos, sin, slots, parts))))
                 if sweep:
                     for s in (1, 2, 3, 4, 5, 6, 7, 8, 10, 11, 13, 16, 22, 32):
                         if s * 64 > ctx:
