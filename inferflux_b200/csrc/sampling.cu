@@ -383,7 +383,7 @@ __device__ unsigned radix_threshold(SampleShared& sh, const float* w, int n, uns
   return prefix > floor_bits ? prefix : floor_bits;
 }
 
-__global__ void __launch_bounds__(SC_THREADS)
+__global__ void __launch_bounds__(SC_THREADS, 2)        // two blocks per SM: 32 registers a thread
 sample_cluster_kernel(const float* __restrict__ logits, long long row_stride, const float* __restrict__ temperature,
                       const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
                       const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
