@@ -147,6 +147,55 @@ __global__ void penalties_kernel(float* __restrict__ logits, long long row_strid
   }
 }
 
+// The same penalties from the tokens themselves, kept on the device: ring [n_slots, ring_size] holds each
+// request's tokens in order of arrival, written round and round; totals[slot] = how many were written in
+// all.  Row r belongs to the request in slots[r] (negative: no penalties for this row) and counts its
+// latest min(last_n[r], total, ring_size) tokens.  A thread per token: the first occurrence of an id within
+// the window applies the penalties for all of them.
+__global__ void penalties_ring_kernel(float* __restrict__ logits, long long row_stride, const int* __restrict__ ring,
+                                      int ring_size, const int* __restrict__ totals, const int* __restrict__ slots,
+                                      const int* __restrict__ last_n, const float* __restrict__ rep,
+                                      const float* __restrict__ freq, const float* __restrict__ pres, int vocab) {
+  pdl_enter();
+  extern __shared__ int window[];                       // [ring_size]
+  const int row = blockIdx.x;
+  const int slot = slots[row];
+  if (slot < 0) return;
+  const int total = totals[slot];
+  const int n = min(min(last_n[row], total), ring_size);
+  for (int t = threadIdx.x; t < n; t += blockDim.x) window[t] = ring[(size_t)slot * ring_size + (total - 1 - t) % ring_size];
+  __syncthreads();
+  float* lg = logits + (size_t)row * row_stride;
+  for (int t = threadIdx.x; t < n; t += blockDim.x) {
+    const int id = window[t];
+    if (id < 0 || id >= vocab) continue;
+    int count = 0;
+    bool first = true;
+    for (int u = 0; u < n; ++u)
+      if (window[u] == id) { ++count; if (u < t) first = false; }
+    if (!first) continue;
+    float v = lg[id];
+    const float r = rep[row];
+    v = v > 0.0f ? v / r : v * r;
+    v -= freq[row] * (float)count;
+    v -= pres[row];
+    lg[id] = v;
+  }
+}
+
+// ring[slots[r]] gets ids[r] as its next token (rows with a negative slot are skipped)
+__global__ void ring_append_kernel(int* __restrict__ ring, int ring_size, int* __restrict__ totals,
+                                   const int* __restrict__ slots, const int* __restrict__ ids, int n_rows) {
+  pdl_enter();
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n_rows) return;
+  const int slot = slots[row];
+  if (slot < 0) return;
+  const int t = totals[slot];
+  ring[(size_t)slot * ring_size + t % ring_size] = ids[row];
+  totals[slot] = t + 1;
+}
+
 // sum / count over the entries whose weight bits are >= bits
 __device__ __forceinline__ void block_sum_count_ge(const float* w, int n, unsigned bits, float* red,
                                                    float* sum_out, int* count_out) {
@@ -264,7 +313,6 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, float* __r
 // nor on how many blocks share the row.
 constexpr int SC_THREADS = 1024, SC_BINS = 1024, SC_MAX_CL = 8;
 constexpr int SC_MAX_SLICE = 51200;                     // floats of a row one block keeps (200 KB)
-constexpr unsigned SC_ONE_BITS = 0x3F800000u;           // bit pattern of 1.0f, the largest weight
 
 struct SampleShared {
   unsigned limb[3][SC_BINS];                            // counts, or masses in three 13-bit limbs: 32-bit shared-memory adds
@@ -542,6 +590,28 @@ IFX_API int ifx_apply_penalties(float* logits, long long row_stride, const int* 
   if (n_rows <= 0 || max_recent <= 0) return 0;
   const int ifx_rc = launch_pdl(penalties_kernel, dim3(n_rows), dim3(128), 0, stream, logits, row_stride, recent_ids, recent_counts, n_recent, max_recent,
                                                rep, freq, pres, vocab);
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
+}
+
+// Penalties from the device-resident token rings (penalties_ring_kernel), and the rings' update with the
+// tokens just sampled.  ring_size at most 4096.
+IFX_API int ifx_apply_penalties_ring(float* logits, long long row_stride, const int* ring, int ring_size,
+                                     const int* totals, const int* slots, const int* last_n, const float* rep,
+                                     const float* freq, const float* pres, int n_rows, int vocab, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (ring_size < 1 || ring_size > 4096) return IFX_ERR_UNSUPPORTED;
+  const int threads = ring_size < 256 ? (ring_size + 31) / 32 * 32 : 256;
+  const int ifx_rc = launch_pdl(penalties_ring_kernel, dim3(n_rows), dim3(threads), (size_t)ring_size * sizeof(int), stream, logits,
+                                row_stride, ring, ring_size, totals, slots, last_n, rep, freq, pres, vocab);
+  return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
+}
+
+IFX_API int ifx_ring_append(int* ring, int ring_size, int* totals, const int* slots, const int* ids, int n_rows,
+                            cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (ring_size < 1) return IFX_ERR_UNSUPPORTED;
+  const int ifx_rc = launch_pdl(ring_append_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, ring, ring_size, totals, slots, ids,
+                                n_rows);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 

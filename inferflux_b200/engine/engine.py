@@ -82,7 +82,8 @@ class Engine:
         self.engine_config = engine_config
         self.runner = StepRunner(model, engine_config)
         self.scheduler = Scheduler(engine_config, _RunnerCacheView(self.runner), self.runner.max_model_len)
-        self.sampler = Sampler(model.spec.vocab_size, engine_config.device, engine_config.seed)
+        self.sampler = Sampler(model.spec.vocab_size, engine_config.device, engine_config.seed, engine_config.max_seqs)
+        self._ring_seeded: Dict[Hashable, int] = {}             # request -> its count of preemptions when its ring was seeded
         self._next_id = 0
         self._requests: Dict[Hashable, Request] = {}
         self._inflight: Optional[_Launched] = None              # a started step whose ids the host has not read yet
@@ -197,10 +198,18 @@ class Engine:
             sampling, extra = [it.request for it in plan.items if it.samples], 0
         ids, host, event = None, None, None
         if sampling:
+            slots = [self.runner.slots.slot(r.rid) for r in sampling]
+            for r, slot in zip(sampling, slots):
+                # a request that samples for the first time (or again after giving way) has all its tokens on the
+                # host: its ring of recent tokens starts from them; from then on the sampler appends on the device
+                if self.sampler.serves_from_ring(r.params) and self._ring_seeded.get(r.rid) != r.preemptions:
+                    self.sampler.seed_ring(slot, r.tokens)
+                    self._ring_seeded[r.rid] = r.preemptions
             ids = self.sampler.sample(
                 logits, [r.params for r in sampling], [r.seed for r in sampling],
                 [len(r.output) + extra for r in sampling],
-                [r.tokens if r.params.has_penalties else () for r in sampling])
+                [r.tokens if r.params.has_penalties and not self.sampler.serves_from_ring(r.params) else ()
+                 for r in sampling], slots)
             host = self._id_buffers[self._id_turn][:len(sampling)]
             self._id_turn ^= 1
             host.copy_(ids, non_blocking=True)
@@ -220,13 +229,17 @@ class Engine:
         plan = done.plan
         if any(it.request.phase is Phase.FINISHED for it in plan.items):
             plan = StepPlan(items=[it for it in plan.items if it.request.phase is not Phase.FINISHED])
-        return self.scheduler.finish_step(plan, sampled)
+        finished = self.scheduler.finish_step(plan, sampled)
+        for r in finished:
+            self._ring_seeded.pop(r.rid, None)
+        return finished
 
     def _can_run_ahead(self) -> bool:
         """Whether the step after the one in flight is known before that one's
         ids are: it was a step of decoding requests only, nobody else waits or
         runs, none of them reaches its token or length limit with the id it is
-        about to get, and none needs its recent tokens on the host (penalties).
+        about to get, and none needs its recent tokens on the host (penalties
+        over a window longer than the sampler's rings on the device).
         A request that stops on an end or stop token is found out one step
         late; that step's token for it is dropped."""
         if not self.engine_config.pipeline_decode:
@@ -237,7 +250,9 @@ class Engine:
             return False
         for it in prev.plan.items:
             r = it.request
-            if it.count != 1 or not it.samples or r.phase is not Phase.RUNNING or r.params.has_penalties:
+            if it.count != 1 or not it.samples or r.phase is not Phase.RUNNING:
+                return False
+            if r.params.has_penalties and not self.sampler.serves_from_ring(r.params):
                 return False
             if len(r.output) + 2 > r.params.max_tokens or len(r.prompt) + len(r.output) + 2 > self.runner.max_model_len:
                 return False

@@ -86,6 +86,11 @@ def _lib():
         lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.ifx_apply_penalties.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                             c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_apply_penalties_ring.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_apply_penalties_ring.restype = c_int
+        lib.ifx_ring_append.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        lib.ifx_ring_append.restype = c_int
         lib.ifx_sample.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_int, c_int, c_void_p]
         for name in ("ifx_embed_gather", "ifx_add_rmsnorm", "ifx_swiglu", "ifx_convert", "ifx_rope_table",
@@ -631,6 +636,35 @@ def apply_penalties(logits: torch.Tensor, recent_ids: torch.Tensor, recent_count
     _check(_lib().ifx_apply_penalties(_ptr(logits), logits.stride(0), _ptr(recent_ids), _ptr(recent_counts),
                                       _ptr(n_recent), recent_ids.shape[1], _ptr(rep), _ptr(freq), _ptr(pres), r, v,
                                       _stream()), "apply_penalties")
+
+
+def apply_penalties_ring(logits: torch.Tensor, ring: torch.Tensor, totals: torch.Tensor, slots: torch.Tensor,
+                         last_n: torch.Tensor, rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> None:
+    """The penalties of :func:`apply_penalties` over each row's latest tokens,
+    read from rings on the device: ``ring`` int32 [n_slots, ring_size] holds a
+    request's tokens in order of arrival, written round and round,
+    ``totals[slot]`` how many were written in all; row r is the request in
+    ``slots[r]`` (negative: leave the row alone) and counts its latest
+    ``last_n[r]`` tokens (at most ring_size)."""
+    r, v = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "apply_penalties_ring: float32 logits")
+    _need(ring.dtype == torch.int32 and ring.dim() == 2 and ring.is_contiguous() and totals.dtype == torch.int32
+          and totals.numel() >= ring.shape[0], "apply_penalties_ring: ring int32 [slots, size], totals int32 [slots]")
+    _need(slots.dtype == torch.int32 and slots.numel() >= r and last_n.dtype == torch.int32 and last_n.numel() >= r
+          and all(t.dtype == torch.float32 and t.numel() >= r for t in (rep, freq, pres)),
+          "apply_penalties_ring: one slot, window and penalty triple per row")
+    _check(_lib().ifx_apply_penalties_ring(_ptr(logits), logits.stride(0), _ptr(ring), ring.shape[1], _ptr(totals),
+                                           _ptr(slots), _ptr(last_n), _ptr(rep), _ptr(freq), _ptr(pres), r, v, _stream()),
+           "apply_penalties_ring")
+
+
+def ring_append(ring: torch.Tensor, totals: torch.Tensor, slots: torch.Tensor, ids: torch.Tensor) -> None:
+    """ids[r] becomes the next token of the request in slots[r] (negative: skipped)."""
+    _need(ring.dtype == torch.int32 and ring.dim() == 2 and ring.is_contiguous() and totals.dtype == torch.int32
+          and slots.dtype == torch.int32 and ids.dtype == torch.int32 and slots.numel() >= ids.numel(),
+          "ring_append: int32 operands")
+    _check(_lib().ifx_ring_append(_ptr(ring), ring.shape[1], _ptr(totals), _ptr(slots), _ptr(ids), ids.numel(), _stream()),
+           "ring_append")
 
 
 def sample(logits: torch.Tensor, weights: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,

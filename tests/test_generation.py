@@ -340,3 +340,47 @@ def test_decoding_with_contexts_of_very_different_lengths(monkeypatch):
     assert calls["even"] > 0 and calls["split"] == 0, calls          # layers x (eager steps + the capture)
     assert eng.runner.graph_replays >= steps - 4
     ops.check_device_errors("cuda:0")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_penalties_from_the_device_run_ahead_and_survive_preemption(folders, dtype):
+    """Requests with repetition, frequency and presence penalties keep their recent tokens in rings on the
+    device, so their decode steps are started ahead like any others; the tokens are those of the engine that
+    waits for every step and counts on the host, also when pages run out and a request gives way and starts
+    again, and for a window longer than the rings (counted on the host, beside ring-served requests)."""
+    from inferflux_b200 import SamplingParams
+    folder, cfg, w = folders["A"]
+    prompts = [random_tokens(cfg["vocab_size"], n, 170 + n) for n in (9, 21, 14, 33)]
+    params = [SamplingParams(temperature=0.0, max_tokens=60, repetition_penalty=1.4, ignore_eos=True),
+              SamplingParams(temperature=0.0, max_tokens=60, frequency_penalty=0.8, presence_penalty=0.4, penalty_last_n=10,
+                             ignore_eos=True),
+              SamplingParams(temperature=0.9, seed=3, max_tokens=60, repetition_penalty=1.2, presence_penalty=0.5,
+                             ignore_eos=True),
+              SamplingParams(temperature=0.0, max_tokens=60, ignore_eos=True)]
+    # the first token of request 0 under its penalty, by the plain implementation
+    want0 = plain.apply_penalties(plain.forward(cfg, w, prompts[0])[-1], prompts[0][-64:], 1.4, 0.0, 0.0)
+    waiting = _engine(folder, dtype, pipeline_decode=False)
+    waiting.sampler.max_seqs = 0                            # no rings: every window is counted on the host
+    want = waiting.generate(prompts, params)
+    assert waiting.stats.get("steps_run_ahead", 0) == 0
+    if dtype == "float32":
+        assert want[0].tokens[0] == int(torch.argmax(want0))
+    ahead = _engine(folder, dtype)
+    got = ahead.generate(prompts, params)
+    assert ahead.stats["steps_run_ahead"] > 20
+    for a, b in zip(want, got):
+        assert a.tokens == b.tokens
+    # few pages: requests give way and start again, their rings are seeded again
+    tight = _engine(folder, dtype, kv_cache_tokens=192)
+    got = tight.generate(prompts, params)
+    assert tight.stats["preemptions"] > 0
+    for a, b in zip(want, got):
+        assert a.tokens == b.tokens
+    # a window beyond the rings beside one within them
+    long_window = [SamplingParams(temperature=0.0, max_tokens=30, repetition_penalty=1.3, penalty_last_n=1000, ignore_eos=True),
+                   params[1]]
+    a = _engine(folder, dtype, pipeline_decode=False)
+    a.sampler.max_seqs = 0
+    b = _engine(folder, dtype)
+    for x, y in zip(a.generate(prompts[:2], long_window), b.generate(prompts[:2], long_window)):
+        assert x.tokens == y.tokens

@@ -489,6 +489,39 @@ def test_penalties(ops):
     _close(logits, want, 1e-6, "penalties")
 
 
+def test_penalties_from_rings_on_the_device(ops):
+    """The penalties counted from each request's ring of tokens on the device are those counted on the host
+    from the same tokens: windows shorter and longer than what the request has, rings that have wrapped
+    around, rows without penalties, tokens appended by the kernel."""
+    v, size, n_slots = 700, 16, 6
+    g = torch.Generator().manual_seed(44)
+    history = [torch.randint(0, 40, (n,), generator=g).tolist() for n in (5, 16, 23, 40, 0, 9)]   # per slot, 0..39: many repeats
+    ring = torch.zeros((n_slots, size), dtype=torch.int32, device=DEV)
+    totals = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    one = lambda x: torch.tensor([x], dtype=torch.int32, device=DEV)
+    for slot, h in enumerate(history):                       # token by token, through the append kernel
+        for t in h:
+            ops.ring_append(ring, totals, one(slot), one(t))
+    assert totals.tolist() == [len(h) for h in history]
+    rows = [(3, 8, 1.3, 0.2, 0.5), (1, 16, 1.0, 0.7, 0.0), (0, 64, 2.0, 0.0, 0.0), (-1, 8, 1.5, 0.5, 0.5),
+            (2, 5, 1.1, 0.1, 0.1), (4, 8, 1.7, 0.3, 0.2), (5, 1, 1.2, 0.0, 1.0)]      # slot, window, rep, freq, pres
+    logits = _rand((len(rows), v), torch.float32, 45, 2.0)
+    want = logits.clone().cpu()
+    for i, (slot, window, rep, freq, pres) in enumerate(rows):
+        if slot < 0:
+            continue
+        n = min(window, size, len(history[slot]))
+        seen = history[slot][len(history[slot]) - n:]
+        ids = sorted(set(seen))
+        ref.apply_penalties(want[i:i + 1], torch.tensor([ids]), torch.tensor([[seen.count(t) for t in ids]]),
+                            torch.tensor([len(ids)]), torch.tensor([rep]), torch.tensor([freq]), torch.tensor([pres]))
+    f = lambda vals, dt: torch.tensor(vals, dtype=dt, device=DEV)
+    ops.apply_penalties_ring(logits, ring, totals, f([r[0] for r in rows], torch.int32), f([r[1] for r in rows], torch.int32),
+                             f([r[2] for r in rows], torch.float32), f([r[3] for r in rows], torch.float32),
+                             f([r[4] for r in rows], torch.float32))
+    _close(logits, want, 1e-6, "penalties from the rings")
+
+
 def _sample(ops, logits, temperature, top_k, top_p, min_p, seeds, counters):
     r, v = logits.shape
     f = lambda x, dt: torch.tensor(x, dtype=dt, device=DEV)
