@@ -88,6 +88,11 @@ class Case:
                         gu = torch.empty(rows, wrows, **bf)
                         self.extra.append(("library + swiglu", lambda i: ops.swiglu(torch.mm(x, ws[i].t(), out=gu), outg)))
             self.extra.append(("library", lambda i: torch.mm(x, ws[i].t())))
+            if not sw and rows <= ops.SKINNY_MAX_ROWS:
+                sp = ops.gemm_umma_skinny_parts(n, k)
+                outp = torch.empty(sp, rows, n, device=DEV)
+                self.extra.append((f"tcgen05, weights as the tiles' rows, K in {sp} parts",
+                                   lambda i: ops.gemm_umma_skinny(x, ws[i], outp)))
         elif name in ("attn_decode", "attn_decode_skewed", "attn_prefill", "attn_prefill_umma"):
             ps = 16
             decode = name.startswith("attn_decode")

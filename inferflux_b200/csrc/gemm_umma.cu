@@ -151,11 +151,17 @@ __device__ __forceinline__ void p_arrive_leader(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(bar & LEADER_MASK) : "memory");
 }
 
-template <bool SWIGLU, typename TOut>
+// MODE 0: out = A W^T (+ bias); 1: SwiGLU of the two halves of W; 2: few rows of A.  In mode 2 the operands
+// change places, so that the 256 rows of a tile are rows of the weights and its (few) columns the tokens: the
+// kernel is given the weights as map_a (M = their rows) and the activations as map_w (n_out = the tokens, all
+// in one tile), K is cut into k_parts parts that are tiles of their own, and the epilogue writes each part's
+// sums transposed, as float32 [k_parts][tokens][ldo] part_stride elements apart, for the consumer to add.
+template <int MODE, typename TOut>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       TOut* __restrict__ out, long long ldo, const float* __restrict__ bias, int M, int n_out, int K,
-                      int tile_n, int* __restrict__ error_flag) {
+                      int tile_n, int* __restrict__ error_flag, int k_parts, long long part_stride) {
+  constexpr bool SWIGLU = MODE == 1, SKINNY = MODE == 2;
   pdl_enter();
   extern __shared__ unsigned char g_smem_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * P_STAGES + 4];    // full[s], empty[s], acc_full[2], acc_empty[2]
@@ -194,8 +200,9 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
   // tile_n: accumulator columns of a tile (a multiple of 16 up to 256; SwiGLU: 256 = 128 gate + 128 up)
   const int out_cols = SWIGLU ? 128 : tile_n;
-  const int m_tiles = (M + 255) / 256, n_tiles = (n_out + out_cols - 1) / out_cols;
+  const int m_tiles = (M + 255) / 256, n_tiles = SKINNY ? k_parts : (n_out + out_cols - 1) / out_cols;
   const int tiles = m_tiles * n_tiles, k_steps = (K + TK - 1) / TK;
+  const int part_steps = SKINNY ? (k_steps + k_parts - 1) / k_parts : k_steps;   // no part is empty: the host sees to that
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int w_half_rows = tile_n / 2;                            // rows of W this block loads per step
   bool gave_up = false;
@@ -206,9 +213,10 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       unsigned phase = 0;
       for (int t = pair; t < tiles && !gave_up; t += n_pairs) {
         const int m0 = (t % m_tiles) * 256 + (int)rank * 128;
-        const int n0 = (t / m_tiles) * out_cols;
+        const int n0 = SKINNY ? 0 : (t / m_tiles) * out_cols;
         const int w_row = SWIGLU ? (int)rank * n_out + n0 : n0 + (int)rank * w_half_rows;
-        for (int ks = 0; ks < k_steps; ++ks) {
+        const int ks0 = SKINNY ? (t / m_tiles) * part_steps : 0, ks1 = SKINNY ? min(k_steps, ks0 + part_steps) : k_steps;
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!g_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { gave_up = true; break; }
           const unsigned sa = sbase + stage * P_STAGE_BYTES, sw = sa + P_HALF_BYTES;
           const unsigned full = (bar_full + 8 * stage) & LEADER_MASK;
@@ -230,12 +238,13 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (!g_wait(bar_acc_empty + 8 * acc, acc_parity ^ 1u, abort_flag)) { gave_up = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const unsigned d = tmem + (unsigned)(acc * 256);
-        for (int ks = 0; ks < k_steps; ++ks) {
+        const int ks0 = SKINNY ? (t / m_tiles) * part_steps : 0, ks1 = SKINNY ? min(k_steps, ks0 + part_steps) : k_steps;
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!g_wait(bar_full + 8 * stage, phase, abort_flag)) { gave_up = true; break; }
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const unsigned sa = sbase + stage * P_STAGE_BYTES, sw = sa + P_HALF_BYTES;
 #pragma unroll
-          for (int k = 0; k < TK / 16; ++k) p_mma(d, g_desc(sa + k * 32), g_desc(sw + k * 32), idesc, (ks | k) != 0);
+          for (int k = 0; k < TK / 16; ++k) p_mma(d, g_desc(sa + k * 32), g_desc(sw + k * 32), idesc, ks != ks0 || k != 0);
           p_commit_both(bar_empty + 8 * stage);                  // both blocks' stage is free once these MMAs have read it
           if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -250,13 +259,28 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     for (int t = pair; t < tiles; t += n_pairs, ++count) {
       const int acc = count & 1;
       const unsigned acc_parity = (unsigned)(count >> 1) & 1u;
-      const int m0 = (t % m_tiles) * 256, n0 = (t / m_tiles) * out_cols;
+      const int m0 = (t % m_tiles) * 256, n0 = SKINNY ? 0 : (t / m_tiles) * out_cols;
       if (!g_wait(bar_acc_full + 8 * acc, acc_parity, abort_flag)) { gave_up = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const unsigned taddr = tmem + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * 256);
       const int row = m0 + row_in_tile;
-      TOut* orow = out + (size_t)(row < M ? row : 0) * ldo;
-      if (SWIGLU) {
+      TOut* orow = out + (size_t)(row < M ? row : 0) * (SKINNY ? 1 : ldo);
+      if (SKINNY) {                                              // this lane's row of the weights is a column of the output
+        TOut* opart = orow + (size_t)(t / m_tiles) * part_stride;
+#pragma unroll 1
+        for (int c = 0; c * 32 < tile_n; ++c) {
+          float v[32];
+          if (tile_n - c * 32 >= 32) g_tmem_ld32(taddr + c * 32, v);
+          else g_tmem_ld16(taddr + c * 32, v);                   // warp-uniform: the tile's last 16 columns
+          if (row < M) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int token = c * 32 + i;
+              if (token < n_out) opart[(size_t)token * ldo] = (TOut)v[i];   // a warp's lanes write 32 neighbours
+            }
+          }
+        }
+      } else if (SWIGLU) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           float gate[32], up[32];
@@ -342,7 +366,7 @@ int pick_tile_n(int M, int n_out, int pairs) {
 template <bool SWIGLU, typename TOut>
 int launch_gemm_pair(const void* A, long long lda, const void* W, const float* bias, void* out, long long ldo, int M, int n_out,
                      int K, int* error_flag, cudaStream_t stream) {
-  auto kern = gemm_umma_pair_kernel<SWIGLU, TOut>;
+  auto kern = gemm_umma_pair_kernel<SWIGLU ? 1 : 0, TOut>;
   static int sms = 0;
   if (!sms) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
@@ -360,7 +384,54 @@ int launch_gemm_pair(const void* A, long long lda, const void* W, const float* b
   const int tiles = ((M + 255) / 256) * ((n_out + out_cols - 1) / out_cols);
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_a, map_w, (TOut*)out,
-                          ldo, bias, M, n_out, K, tile_n, error_flag);
+                          ldo, bias, M, n_out, K, tile_n, error_flag, 1, 0ll);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+// Parts into which the product of a few rows cuts K: as many as give every pair of SMs a tile, each part at
+// least 8 steps of 64, none empty.
+int skinny_parts(int n_out, int K, int pairs) {
+  const int m_tiles = (n_out + 255) / 256, k_steps = (K + TK - 1) / TK;
+  int parts = pairs / m_tiles;
+  if (parts > k_steps / 8) parts = k_steps / 8;
+  if (parts < 1) parts = 1;
+  const int per = (k_steps + parts - 1) / parts;
+  return (k_steps + per - 1) / per;
+}
+
+int device_sms(int* sms) {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+  }
+  *sms = n;
+  return 0;
+}
+
+int launch_gemm_skinny(const void* X, long long ldx, const void* W, float* out, long long ldo, int tokens, int n_out, int K,
+                       int k_parts, long long part_stride, int* error_flag, cudaStream_t stream) {
+  auto kern = gemm_umma_pair_kernel<2, float>;
+  static bool ready = false;
+  if (!ready) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    ready = true;
+  }
+  int sms = 0;
+  int rc = device_sms(&sms);
+  if (rc) return rc;
+  const int tile_n = tokens <= 32 ? 32 : (tokens + 15) / 16 * 16;      // the tokens, all in one tile
+  CUtensorMap map_w, map_x;
+  rc = make_map(&map_w, W, n_out, K, K, 128);
+  if (!rc) rc = make_map(&map_x, X, tokens, K, ldx, tile_n / 2);
+  if (rc) return rc;
+  const int tiles = ((n_out + 255) / 256) * k_parts;
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_w, map_x, out, ldo,
+                          (const float*)nullptr, n_out, tokens, K, tile_n, error_flag, k_parts, part_stride);
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 }  // namespace
@@ -382,4 +453,27 @@ IFX_API int ifx_gemm_umma(const void* A, long long lda, const void* W, const flo
     return swiglu ? launch_gemm_pair<true, float>(A, lda, W, bias, out, ldo, M, n_out, K, error_flag, stream)
                   : launch_gemm_pair<false, float>(A, lda, W, bias, out, ldo, M, n_out, K, error_flag, stream);
   return IFX_ERR_UNSUPPORTED;
+}
+
+// The product of a few rows (17 to 256 tokens) against weights that must stream from memory once: out
+// [k_parts][tokens][n_out] float32 (rows ldo elements apart, parts part_stride) holds partial sums over the
+// k_parts parts of K, to be added by the consumer; k_parts from ifx_gemm_umma_skinny_parts.  The weights' rows
+// are the 256 rows of the tensor-core tiles and the tokens their columns, so a tile streams 256 rows of W
+// through shared memory once for all tokens.  X rows ldx elements apart; K and ldx multiples of 8; X and W
+// 16-byte aligned.
+IFX_API int ifx_gemm_umma_skinny(const void* X, long long ldx, const void* W, float* out, long long ldo, long long part_stride,
+                                 int tokens, int n_out, int K, int k_parts, int* error_flag, cudaStream_t stream) {
+  if (tokens <= 0 || n_out <= 0) return 0;
+  if (tokens > 256 || K <= 0 || (K & 7) || (ldx & 7) || !error_flag || k_parts < 1) return IFX_ERR_UNSUPPORTED;
+  const int k_steps = (K + TK - 1) / TK, per = (k_steps + k_parts - 1) / k_parts;
+  if ((k_steps + per - 1) / per != k_parts) return IFX_ERR_UNSUPPORTED;            // a part would be empty
+  if (((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 3)) return IFX_ERR_ALIGNMENT;
+  return launch_gemm_skinny(X, ldx, W, out, ldo, tokens, n_out, K, k_parts, part_stride, error_flag, stream);
+}
+
+IFX_API int ifx_gemm_umma_skinny_parts(int n_out, int K) {
+  int sms = 0;
+  const int rc = device_sms(&sms);
+  if (rc) return -rc;
+  return skinny_parts(n_out, K, sms / 2);
 }

@@ -73,6 +73,11 @@ def _lib():
         lib.ifx_gemm_umma.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
                                       c_void_p, c_void_p]
         lib.ifx_gemm_umma.restype = c_int
+        lib.ifx_gemm_umma_skinny.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int,
+                                             c_void_p, c_void_p]
+        lib.ifx_gemm_umma_skinny.restype = c_int
+        lib.ifx_gemm_umma_skinny_parts.argtypes = [c_int, c_int]
+        lib.ifx_gemm_umma_skinny_parts.restype = c_int
         lib.ifx_gemv_bf16_plan.argtypes = [c_int, c_int, c_int]
         lib.ifx_gemv_bf16_plan.restype = c_int
         lib.ifx_attn_decode_plan.argtypes = [c_int, c_int, c_int, c_int, c_int]
@@ -312,6 +317,39 @@ def gemm_umma(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     _check(_lib().ifx_gemm_umma(_ptr(x), x.stride(0) if m > 1 else k, _ptr(w), _ptr(bias), _ptr(out), out.stride(0),
                                 _code(out), m, n, k, 1 if swiglu else 0, _ptr(error_flag(x.device)), _stream()),
            "gemm_umma")
+    return out
+
+
+SKINNY_MAX_ROWS = 256       # rows of x that gemm_umma_skinny takes
+
+
+def gemm_umma_skinny_parts(n: int, k: int) -> int:
+    """Into how many parts :func:`gemm_umma_skinny` cuts K for an [n, k] matrix."""
+    key = ("skinny", n, k)
+    if key not in _gemv_plans:
+        s = int(_lib().ifx_gemm_umma_skinny_parts(n, k))
+        if s < 1:
+            raise KernelError(f"gemm_umma_skinny_parts: CUDA error {-s}")
+        _gemv_plans[key] = s
+    return _gemv_plans[key]
+
+
+def gemm_umma_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Partial sums of x[M, K] @ w[N, K]^T for a few rows (up to
+    SKINNY_MAX_ROWS), where the time goes to reading w once: out float32
+    [S, M, N], S = ``gemm_umma_skinny_parts(N, K)`` parts of K, to be added by
+    the consumer.  tcgen05 with the operands' places changed: 256 rows of w are
+    the rows of a tile and the rows of x its columns."""
+    m, k = x.shape
+    s, m2, n = out.shape
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == (n, k),
+          "gemm_umma_skinny: bfloat16 x [M, K], w [N, K]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and m2 == m and 1 <= m <= SKINNY_MAX_ROWS
+          and s == gemm_umma_skinny_parts(n, k), "gemm_umma_skinny: out float32 [parts, M, N]")
+    _need(k % 8 == 0 and x.stride(1) == 1 and (m == 1 or x.stride(0) % 8 == 0),
+          "gemm_umma_skinny: K and the row stride of x must be multiples of 8")
+    _check(_lib().ifx_gemm_umma_skinny(_ptr(x), x.stride(0) if m > 1 else k, _ptr(w), _ptr(out), n, m * n, m, n, k, s,
+                                       _ptr(error_flag(x.device)), _stream()), "gemm_umma_skinny")
     return out
 
 

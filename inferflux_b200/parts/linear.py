@@ -4,8 +4,9 @@ The reference issues one cuBLAS call per projection with float32 accumulation
 (runtime/backends/cuda/native/cublas_gemm.cpp:84-102, ``C[M,N] = A[M,K] *
 B[N,K]^T``).  Here a float32 weight goes through the FFMA kernel of the 32-bit
 path; a bfloat16 weight goes through the library (cuBLAS via ``torch.mm``) for
-many rows and through the weight-streaming kernel (gemv_bf16.cu) for up to 8
-rows.  This is not a registered part: mixers and feed-forwards own their
+many rows, through the weight-streaming kernel (gemv_bf16.cu) for up to 8
+rows, and through the tcgen05 kernel with the operands' places changed
+(gemm_umma.cu) for up to 128 rows against a long K.  This is not a registered part: mixers and feed-forwards own their
 Linears.
 """
 from __future__ import annotations
@@ -19,6 +20,10 @@ from .base import PartialSums
 
 
 GEMV_ROWS = 8     # up to this many rows go to the weight-streaming kernel (it matches the library there)
+# From 9 to 128 rows a product is still bound by reading W once.  The tcgen05 kernel with the weights as the
+# tiles' rows beats the library there by a tenth when K is long (the down projection: 27 against 31 us at 64
+# rows); with a short K its set-up weighs more than it saves (qkv, o: 10 against 9 us), so those stay.
+FEW_ROWS, FEW_ROWS_MIN_K = 128, 8192
 
 
 class Linear:
@@ -56,6 +61,11 @@ class Linear:
                 return PartialSums(ops.gemv_bf16(x, w, self.bias, y, k_splits=splits))
             y = torch.empty((m, self.out_features), dtype=out_dtype, device=x.device)
             return ops.gemv_bf16(x, w, self.bias, y)
+        if (allow_partials and self.bias is None and m <= FEW_ROWS and self.in_features >= FEW_ROWS_MIN_K
+                and self.in_features % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0):
+            parts = ops.gemm_umma_skinny_parts(self.out_features, self.in_features)
+            y = torch.empty((parts, m, self.out_features), dtype=torch.float32, device=x.device)
+            return PartialSums(ops.gemm_umma_skinny(x, w, y))
         y = ops.matmul_library(x, w, torch.float32 if (out_dtype == torch.float32 or self.bias is not None)
                                else torch.bfloat16)
         if self.bias is not None:

@@ -649,6 +649,26 @@ def test_gemm_umma_swiglu(ops, m, inter, k):
     _close(out, gate / (1 + torch.exp(-gate)) * up, 6e-3, "gemm_umma swiglu")
 
 
+@pytest.mark.parametrize("m", [1, 17, 32, 40, 64, 100, 256])
+@pytest.mark.parametrize("n,k", [(3584, 3584), (4608, 3584), (3584, 18944), (100, 96), (300, 1096), (257, 64)])
+def test_gemm_umma_skinny(ops, m, n, k):
+    """The tcgen05 product for a few rows (weights as the tiles' rows, K cut into parts that the consumer adds)
+    against float64: rows and columns that do not fill a tile, K with a tail, one-hot rows that tell the
+    transposed store apart from a plain one."""
+    x, w = _rand((m, k), torch.bfloat16, 80), _rand((n, k), torch.bfloat16, 81, 0.1)
+    x[m // 2] = 0
+    x[m // 2, k // 3] = 1.0                                # this row of the result is column k // 3 of w
+    parts = ops.gemm_umma_skinny_parts(n, k)
+    out = torch.full((parts, m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_umma_skinny(x, w, out)
+    ops.check_device_errors(DEV)
+    got = out.double().sum(0).cpu()
+    want = x.double().cpu() @ w.double().cpu().T
+    assert torch.isfinite(out).all()
+    _close(got, want, 1e-5, f"few-row product in {parts} parts")
+    assert torch.equal(got[m // 2].float(), w[:, k // 3].float().cpu())
+
+
 def test_gemv_plan_depends_on_the_matrix_only(ops):
     """The number of K parts is the kernel's own choice from the matrix sizes; it
     is within bounds, repeatable, and 1 where K is too short to cut."""
