@@ -172,7 +172,7 @@ class Case:
             w, o = torch.ones(h, device=DEV), torch.empty(rows, h, **bf)
             self.n_rot, self.bytes = 1, rows * h * (4 + 4 + 2 + 2)
             self.run = lambda i: ops.add_rmsnorm(res, delta, w, 1e-6, o)
-            if rows <= 16:                                   # as after a product that came in parts of K
+            if rows <= 128:                                  # as after a product that came in parts of K
                 parts = torch.randn(5, rows, h, device=DEV)
                 self.extra.append(("5 partial sums", lambda i: ops.add_rmsnorm(res, parts, w, 1e-6, o, n_partials=5)))
         elif name == "swiglu":
