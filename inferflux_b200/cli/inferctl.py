@@ -10,6 +10,7 @@ engine in-process.  There is no tokenizer either: prompts are token ids.
 
     inferctl completion --model DIR --prompt "5 17 3" --max-tokens 16 [--temperature 0.8 --seed 7 ...]
     inferctl completion --model DIR --prompt-file prompts.txt --max-tokens 16     (one prompt of ids per line)
+    inferctl completion --random config.json --weights-seed 0 --prompt "5 17 3"   (random weights, no folder written)
     inferctl models --model DIR          the configuration and the tensors the model wants
     inferctl status                      device, kernel library
     inferctl random --config config.json --seed 0 --out DIR     write a random-weights model folder
@@ -28,7 +29,10 @@ def _ids(text: str) -> List[int]:
 
 
 def _add_engine_options(p: argparse.ArgumentParser) -> None:
-    p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    p.add_argument("--model", help="folder with config.json and model.safetensors")
+    p.add_argument("--random", metavar="CONFIG.json",
+                   help="instead of --model: a config.json whose model gets random weights from --weights-seed")
+    p.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights (with --random)")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--ctx-size", type=int, default=None, help="most tokens of one request (default: the model's)")
     p.add_argument("--batch-size", type=int, default=16384, help="most tokens of one step (max_batch_tokens)")
@@ -40,11 +44,14 @@ def _add_engine_options(p: argparse.ArgumentParser) -> None:
 
 def _engine(args):
     from .. import Engine
-    return Engine.from_pretrained(
-        args.model, dtype=args.dtype, max_model_len=args.ctx_size, max_batch_tokens=args.batch_size,
-        max_batch_size=args.max_parallel_sequences, max_seqs=max(args.max_parallel_sequences, 1),
-        chunked_prefill_tokens=args.chunked_prefill_tokens, kv_cache_tokens=args.kv_cache_tokens,
-        page_size=args.page_size)
+    options = dict(dtype=args.dtype, max_model_len=args.ctx_size, max_batch_tokens=args.batch_size,
+                   max_batch_size=args.max_parallel_sequences, max_seqs=max(args.max_parallel_sequences, 1),
+                   chunked_prefill_tokens=args.chunked_prefill_tokens, kv_cache_tokens=args.kv_cache_tokens,
+                   page_size=args.page_size)
+    if args.random is not None:
+        with open(args.random) as f:
+            return Engine.from_config(json.load(f), seed=args.weights_seed, as_written=True, **options)
+    return Engine.from_pretrained(args.model, **options)
 
 
 def cmd_completion(args) -> int:
@@ -58,12 +65,15 @@ def cmd_completion(args) -> int:
     if not prompts:
         print("inferctl completion: give --prompt or --prompt-file (token ids)", file=sys.stderr)
         return 2
+    if (args.model is None) == (args.random is None):
+        print("inferctl completion: give exactly one of --model and --random", file=sys.stderr)
+        return 2
     eng = _engine(args)
     params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
                             frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty,
                             repetition_penalty=args.repetition_penalty, seed=args.seed, max_tokens=args.max_tokens,
                             stop_token_ids=_ids(args.stop) if args.stop else [])
-    out = {"model": args.model, "dtype": args.dtype}
+    out = {"model": args.model or f"random:{args.random}:{args.weights_seed}", "dtype": args.dtype}
     if args.top_n:
         # the probe's view: the top logits after the (first) prompt
         import torch

@@ -4,6 +4,7 @@ own: it builds the same model and :class:`StepRunner` that generation uses and
 calls its step function.
 
     trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    trace_run --random CONFIG.json --seed S --dtype ... (random weights, no folder is written)
 
 Steps come on standard input, one JSON object a line:
 
@@ -11,7 +12,10 @@ Steps come on standard input, one JSON object a line:
 
 For a step that wants logits, ``DIR/<step>.f32`` gets them as little-endian
 float32 ``[wanted, vocab]`` in the order of the entries and of ``want``.  After
-every step a line ``done <step>`` is printed and flushed.
+every step a line ``done <step>`` is printed and flushed.  A line
+``{"stats": true}`` is no step: it is answered by one line ``stats {...}``
+with the cache pools' counters (pages in all, free, handed out so far, handed
+out again after an earlier use) and the steps and tokens run.
 
 The reference's nearest tools are its first-token probe
 (tests/tools/first_token_probe.cpp:191-274, one prompt, top-N logits) and its
@@ -28,7 +32,10 @@ import sys
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    ap.add_argument("--model", help="folder with config.json and model.safetensors")
+    ap.add_argument("--random", metavar="CONFIG.json",
+                    help="instead of --model: a config.json whose model gets random weights from --seed")
+    ap.add_argument("--seed", type=int, default=0, help="seed of the random weights (with --random)")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
@@ -46,10 +53,19 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print("trace_run: no CUDA device is available; this engine has no CPU path", file=sys.stderr)
         return 1
+    if (args.model is None) == (args.random is None):
+        ap.error("give exactly one of --model and --random")
     print("trace_run: preparing kernels and model ...", file=sys.stderr, flush=True)
-    config = load_config(args.model)
-    model = Model(build_spec(config), torch_dtype(args.dtype), args.device)
-    model.load_folder(args.model)
+    if args.model is not None:
+        config = load_config(args.model)
+        model = Model(build_spec(config), torch_dtype(args.dtype), args.device)
+        model.load_folder(args.model)
+    else:
+        from ..weights.random_init import random_tensors_as_loaded
+        with open(args.random) as f:
+            config = load_config(json.load(f))
+        model = Model(build_spec(config), torch_dtype(args.dtype), args.device)
+        model.load(random_tensors_as_loaded(model.weight_specs(), args.seed, torch_dtype(args.dtype), args.device))
     ecfg = EngineConfig(dtype=args.dtype, device=args.device, page_size=args.page_size,
                         kv_cache_tokens=max(args.page_size, args.max_tokens), max_seqs=64)
     runner = StepRunner(model, ecfg)
@@ -60,6 +76,13 @@ def main(argv=None) -> int:
         if not line:
             continue
         rec = json.loads(line)
+        if rec.get("stats"):
+            pools = runner.kv.pools
+            print("stats " + json.dumps({
+                "pages_total": [p.num_pages for p in pools], "pages_free": [p.num_free for p in pools],
+                "page_allocations": [p.allocations for p in pools], "page_reuses": [p.reuses for p in pools],
+                "steps": runner.steps, "tokens": runner.tokens_run}), flush=True)
+            continue
         step = rec["step"]
         entries = [StepEntry(str(e["id"]), [int(t) for t in e["tokens"]], [int(p) for p in e.get("want", [])])
                    for e in rec.get("entries", [])]

@@ -106,10 +106,12 @@ class Engine:
 
     @classmethod
     def from_config(cls, config: Union[ModelConfig, dict], seed: int = 0, dtype: str = "bfloat16",
-                    **engine_options) -> "Engine":
-        """A model of ``config``'s architecture with random weights from ``seed``,
-        made directly on the device (no folder is written)."""
-        from ..weights.random_init import random_tensors
+                    as_written: bool = False, **engine_options) -> "Engine":
+        """A model of ``config``'s architecture with random weights from ``seed``
+        (no folder is written).  By default they are drawn on the device, which
+        is quick for large models; ``as_written`` draws them on the CPU, the very
+        tensors of the folder that ``write_random_model`` writes for the seed."""
+        from ..weights.random_init import random_tensors, random_tensors_as_loaded
         ecfg = EngineConfig(dtype=dtype, **engine_options)
         ecfg.validate()
         _require_cuda(ecfg.device)
@@ -117,7 +119,10 @@ class Engine:
             config = load_config(config)
         td = torch_dtype(dtype)
         model = Model(build_spec(config), td, ecfg.device)
-        model.load(random_tensors(model.weight_specs(), seed, td, torch.float32, ecfg.device))
+        if as_written:
+            model.load(random_tensors_as_loaded(model.weight_specs(), seed, td, ecfg.device))
+        else:
+            model.load(random_tensors(model.weight_specs(), seed, td, torch.float32, ecfg.device))
         return cls(model, config, ecfg)
 
     # -------------------------------------------------------------- requests
@@ -163,6 +168,8 @@ class Engine:
             finished += self._harvest(prev)
             if self._inflight is not None:
                 self.scheduler.stats["steps_run_ahead"] = self.scheduler.stats.get("steps_run_ahead", 0) + 1
+                if finished:
+                    ops.check_device_errors(self.engine_config.device)    # as below: no tokens of a failed step
                 return [self._result(r) for r in finished]
         elif self._inflight is not None:
             prev, self._inflight = self._inflight, None

@@ -92,9 +92,10 @@ class StepRunner:
         return self.kv.can_reserve(rid, n_new)
 
     # ---------------------------------------------------------------- step
-    def _admit(self, entries: Sequence[StepEntry], check_tokens: bool = True) -> None:
+    def _admit(self, entries: Sequence[StepEntry], check_tokens: bool = True) -> list:
         """Check the entries, seat new requests and hold pages for the step's
-        tokens; raises before anything is taken when they do not fit."""
+        tokens; raises before anything is taken when they do not fit.  Returns
+        the requests that this call seated."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         vocab = self.model.spec.vocab_size
@@ -129,6 +130,7 @@ class StepRunner:
             self.begin(e.rid)
         for e in entries:
             self.kv.reserve(e.rid, len(e.tokens))
+        return [e.rid for e in new]
 
     def _describe(self, entries: Sequence[StepEntry], slab: Optional[MetadataSlab] = None,
                   widths: Optional[Sequence[int]] = None) -> StepContext:
@@ -219,20 +221,31 @@ class StepRunner:
         the pools cannot hold the step's tokens.  The logits of a decode-only
         step live in a buffer that the next such step overwrites.
 
+        If describing or running the step raises (metadata that does not fit, a
+        shape a kernel refuses), the requests that this call seated are ended
+        again, so their slots and pages are back; requests known before keep
+        the pages held for this step's tokens (their cached length is
+        unchanged, the pages serve the next attempt) until they end.
+
         With ``device_tokens`` (int32 on the device, one per entry, every entry
         a single token) the token ids are taken from there instead of the
         entries: the ids a sampler has just written need not visit the host
         before the next step starts."""
-        self._admit(entries, check_tokens=device_tokens is None)
         if device_tokens is not None and any(len(e.tokens) != 1 for e in entries):
             raise ValueError("device_tokens serve entries of one token each")
-        if self._graphable(entries):
-            logits = self._step_graph(entries, device_tokens)
-        else:
-            ctx = self._describe(entries)
-            if device_tokens is not None:
-                ctx.token_ids.copy_(device_tokens[:len(entries)])
-            logits = self.model.forward(ctx)
+        seated = self._admit(entries, check_tokens=device_tokens is None)
+        try:
+            if self._graphable(entries):
+                logits = self._step_graph(entries, device_tokens)
+            else:
+                ctx = self._describe(entries)
+                if device_tokens is not None:
+                    ctx.token_ids.copy_(device_tokens[:len(entries)])
+                logits = self.model.forward(ctx)
+        except BaseException:
+            for rid in seated:
+                self.end(rid)
+            raise
         n = 0
         for e in entries:
             self.kv.advance(e.rid, len(e.tokens))

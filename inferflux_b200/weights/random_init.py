@@ -45,6 +45,20 @@ def random_tensors(specs: Iterable[WeightSpec], seed: int, dtype: torch.dtype = 
     return out
 
 
+def random_tensors_as_loaded(specs: Iterable[WeightSpec], seed: int, engine_dtype: torch.dtype,
+                             device: str) -> Dict[str, torch.Tensor]:
+    """The tensors an engine of ``engine_dtype`` would hold after loading the
+    folder that :func:`write_random_model` writes for the same seed (bfloat16
+    storage, drawn on the CPU), without writing it: the command line's
+    ``--random CONFIG.json`` gives the same model as ``inferctl random``
+    followed by ``--model``."""
+    from .loader import storage_dtype
+    specs = list(specs)
+    kinds = {s.name: s.kind for s in specs}
+    stored = random_tensors(specs, seed, torch.bfloat16, None, "cpu")
+    return {n: t.to(storage_dtype(t.dtype, kinds[n], engine_dtype)).to(device) for n, t in stored.items()}
+
+
 def write_random_model(folder: str, config, seed: int, dtype: torch.dtype = torch.bfloat16,
                        vector_dtype: torch.dtype = None) -> str:
     """Write ``config.json`` and ``model.safetensors`` for ``config`` (a typed

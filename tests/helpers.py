@@ -22,8 +22,7 @@ TINY_A = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_siz
 TINY_B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=96, num_hidden_layers=3,
               num_attention_heads=3, num_key_value_heads=1, head_dim=32, intermediate_size=256, vocab_size=1000,
               rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=512,
-              use_sliding_window=True, sliding_window=40, max_window_layers=1, hidden_act="silu",
-              torch_dtype="bfloat16")
+              use_sliding_window=False, hidden_act="silu", torch_dtype="bfloat16")
 # head_dim * heads != hidden, 5 query heads per kv head, an odd vocabulary
 TINY_C = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=80, num_hidden_layers=2,
               num_attention_heads=10, num_key_value_heads=2, head_dim=48, intermediate_size=136, vocab_size=777,
@@ -35,7 +34,9 @@ TINY_D = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_siz
               rope_theta=200000.0, rms_norm_eps=2e-6, tie_word_embeddings=True, max_position_embeddings=400,
               use_sliding_window=True, sliding_window=70, max_window_layers=1, hidden_act="silu",
               torch_dtype="bfloat16")
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# B's sizes with a window of 40 keys on all layers but the first: two cache groups, pages given back behind the window
+TINY_E = dict(TINY_B, use_sliding_window=True, sliding_window=40, max_window_layers=1)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 # Largest |engine - plain| allowed, as a fraction of the largest |plain logit|.
 # float32: a few hundred float32 roundings; bfloat16: 8-bit mantissas through every layer.
@@ -74,11 +75,11 @@ def random_tokens(vocab: int, n: int, seed: int) -> List[int]:
 class TraceProcess:
     """A running bin/trace_run: send steps, wait for ``done``, read logits."""
 
-    def __init__(self, model_dir: str, dtype: str, max_tokens: int, extra: Sequence[str] = ()):
+    def __init__(self, model_dir: Optional[str], dtype: str, max_tokens: int, extra: Sequence[str] = ()):
         self.out = tempfile.mkdtemp(prefix="ifx_trace_")
         self.step_no = 0
-        cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
-               "--out", self.out, "--max-tokens", str(max_tokens), *extra]
+        cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), *(["--model", model_dir] if model_dir else []),
+               "--dtype", dtype, "--out", self.out, "--max-tokens", str(max_tokens), *extra]
         self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
 
     def step(self, entries: Sequence[dict], end: Sequence[str] = ()) -> Optional[np.ndarray]:
@@ -96,6 +97,15 @@ class TraceProcess:
             return None
         arr = np.fromfile(os.path.join(self.out, f"{n}.f32"), dtype="<f4")
         return arr.reshape(wanted, -1)
+
+    def stats(self) -> dict:
+        """The counters of the cache pools and of the step function."""
+        self.proc.stdin.write(json.dumps({"stats": True}) + "\n")
+        self.proc.stdin.flush()
+        line = self.proc.stdout.readline()
+        if not line.startswith("stats "):
+            raise RuntimeError(f"trace_run answered {line!r} to a request for its counters")
+        return json.loads(line[len("stats "):])
 
     def close(self) -> int:
         self.proc.stdin.close()

@@ -6,7 +6,7 @@ import os
 import subprocess
 import sys
 
-from helpers import ROOT, TINY_B
+from helpers import ROOT, TINY_E
 
 
 def _run(*args):
@@ -17,7 +17,7 @@ def _run(*args):
 
 def test_random_then_models(tmp_path):
     cfg = tmp_path / "config.json"
-    cfg.write_text(json.dumps(TINY_B))
+    cfg.write_text(json.dumps(TINY_E))
     out = _run("random", "--config", str(cfg), "--seed", "3", "--out", str(tmp_path / "m"), "--float32-vectors")
     assert out["architecture"] == "Qwen2ForCausalLM"
     assert sorted(os.listdir(tmp_path / "m")) == ["config.json", "model.safetensors"]

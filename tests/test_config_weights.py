@@ -8,7 +8,7 @@ import struct
 import pytest
 import torch
 
-from helpers import TINY_A, TINY_B, make_model_folder
+from helpers import TINY_A, TINY_B, TINY_E, make_model_folder
 from inferflux_b200.config import (ConfigError, Qwen2Config, build_spec, load_config, register_architecture,
                                    registered_architectures, resolve_architecture)
 from inferflux_b200.config.spec import LayerSpec, ModelSpec, PartSpec, Run
@@ -19,13 +19,14 @@ from inferflux_b200.weights.random_init import random_tensors, write_random_mode
 
 
 def test_config_reads_every_key():
-    c = Qwen2Config.from_dict(TINY_B)
+    c = Qwen2Config.from_dict(TINY_E)
     assert (c.hidden_size, c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads, c.head_dim) == (96, 3, 3, 1, 32)
     assert (c.intermediate_size, c.vocab_size, c.max_position_embeddings) == (256, 1000, 512)
     assert c.rope_theta == 1e6 and c.rms_norm_eps == 1e-5 and not c.tie_word_embeddings
     assert [c.window_of_layer(i) for i in range(3)] == [None, 40, 40]
     a = Qwen2Config.from_dict(TINY_A)
     assert a.tie_word_embeddings and [a.window_of_layer(i) for i in range(2)] == [None, None]
+    assert [Qwen2Config.from_dict(TINY_B).window_of_layer(i) for i in range(3)] == [None, None, None]
 
 
 def test_config_defaults_and_errors():
@@ -59,7 +60,7 @@ def test_registry_by_architecture_or_model_type():
 
 
 def test_spec_is_data_per_layer():
-    spec = build_spec(Qwen2Config.from_dict(TINY_B))
+    spec = build_spec(Qwen2Config.from_dict(TINY_E))
     assert len(spec.layers) == 3 and [r.layer for r in spec.schedule] == [0, 1, 2]
     assert [l.mixer.params["window"] for l in spec.layers] == [None, 40, 40]
     assert spec.layers[0].mixer.kind == "gqa_attention" and spec.layers[0].feed_forward.kind == "swiglu"

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(scope="module")
 def folders():
     out = {}
-    for name in ("A", "B", "D"):
+    for name in ("A", "B", "D", "E"):
         folder = make_model_folder(TINY[name], seed=40 + ord(name), sharpen=4.0)
         out[name] = (folder, *plain.load_folder(folder))
     return out
@@ -44,7 +44,7 @@ def _check_greedy(cfg, w, prompt, tokens, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
 def test_greedy_generation_through_the_entry_point(folders, name, dtype):
     from inferflux_b200 import SamplingParams
     folder, cfg, w = folders[name]
@@ -91,7 +91,7 @@ def test_long_decoding_token_by_token(folders, name, dtype):
 def test_first_tokens_of_a_sequence(folders, dtype):
     """Position 0 alone, positions 0-1, and a one-token prompt beside longer ones."""
     from inferflux_b200 import StepEntry
-    folder, cfg, w = folders["B"]
+    folder, cfg, w = folders["E"]
     a, b, c = (random_tokens(cfg["vocab_size"], n, 80 + n) for n in (1, 2, 19))
     eng = _engine(folder, dtype)
     logits = eng.run_step([StepEntry("a", a, [0]), StepEntry("b", b, [0, 1]), StepEntry("c", c, [0, 18])]).cpu().double()
@@ -268,7 +268,7 @@ def test_random_arrivals_preemption_and_running_ahead(folders):
     it runs alone in a roomy engine that waits for every step's ids."""
     import random
     from inferflux_b200 import SamplingParams
-    folder, cfg, w = folders["B"]
+    folder, cfg, w = folders["E"]
     rng = random.Random(7)
     n = 30
     prompts = [random_tokens(cfg["vocab_size"], rng.randint(1, 90), 300 + i) for i in range(n)]
@@ -384,3 +384,27 @@ def test_penalties_from_the_device_run_ahead_and_survive_preemption(folders, dty
     b = _engine(folder, dtype)
     for x, y in zip(a.generate(prompts[:2], long_window), b.generate(prompts[:2], long_window)):
         assert x.tokens == y.tokens
+
+
+@pytest.mark.parametrize("pipeline", [True, False])
+def test_a_failed_step_hands_out_no_tokens(folders, pipeline):
+    """When a kernel's bounded wait runs out it sets the device's error word.
+    The engine reads the word before it returns finished requests, whether the
+    call that finds them ran ahead of the host or not.  The word is set here by
+    hand; no kernel is made to fail."""
+    from inferflux_b200 import SamplingParams
+    from inferflux_b200.kernels import ops
+    folder, cfg, w = folders["A"]
+    eng = _engine(folder, "bfloat16", pipeline_decode=pipeline)
+    prompts = [random_tokens(cfg["vocab_size"], 9, 500 + i) for i in range(2)]
+    for i, p in enumerate(prompts):
+        eng.add_request(p, SamplingParams(temperature=0.0, max_tokens=6 + 20 * i, ignore_eos=True))
+    for _ in range(4):
+        assert eng.step() == []
+    if pipeline:
+        assert eng.stats["steps_run_ahead"] > 0
+    ops.error_flag(eng.engine_config.device).fill_(1)
+    with pytest.raises(ops.KernelError):
+        for _ in range(8):                                # the first request reaches its limit within these steps
+            eng.step()
+    assert int(ops.error_flag(eng.engine_config.device).item()) == 0     # read and cleared

@@ -7,7 +7,7 @@ import math
 import torch
 
 import plain_qwen2 as plain
-from helpers import TINY_A, TINY_B, make_model_folder, random_tokens
+from helpers import TINY_A, TINY_B, TINY_E, make_model_folder, random_tokens
 
 
 def test_rms_norm():
@@ -55,7 +55,7 @@ def test_attention_is_causal_and_windowed():
 
 
 def test_forward_prefix_property_and_tied_head(tmp_path):
-    for name, cfg in (("a", TINY_A), ("b", TINY_B)):
+    for name, cfg in (("a", TINY_A), ("b", TINY_B), ("e", TINY_E)):
         folder = make_model_folder(cfg, 2, str(tmp_path / name))
         c, w = plain.load_folder(folder)
         toks = random_tokens(cfg["vocab_size"], 60, 9)

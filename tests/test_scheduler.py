@@ -231,3 +231,30 @@ def test_contexts_skewed_rule():
     assert contexts_skewed([32768] + [1024] * 63)
     assert contexts_skewed([1150, 30, 75, 12])
     assert not contexts_skewed([2048, 1800, 1500, 1900])       # longest below 1.5 times the mean
+
+
+def test_a_step_that_fails_gives_back_what_it_seated(tmp_path):
+    """The step function seats new requests and holds pages before it runs.
+    When the run raises (here: on the CPU every kernel refuses), requests
+    seated by that call are ended again; one known before keeps its place."""
+    import torch
+    from helpers import TINY_A, make_model_folder
+    from inferflux_b200.config import EngineConfig, build_spec, load_config
+    from inferflux_b200.engine import Model, StepEntry, StepRunner
+    from inferflux_b200.kernels.ops import KernelError
+    folder = make_model_folder(TINY_A, 0, str(tmp_path / "m"))
+    model = Model(build_spec(load_config(folder)), torch.float32, "cpu")
+    model.load_folder(folder)
+    runner = StepRunner(model, EngineConfig(dtype="float32", device="cpu", kv_cache_tokens=256, max_seqs=2))
+    free = runner.kv.num_free(0)
+    with pytest.raises(KernelError):
+        runner.step([StepEntry("a", [1, 2, 3], [2])])
+    assert not runner.has("a") and runner.slots.num_free == 2 and runner.kv.num_free(0) == free
+    runner.begin("known")
+    with pytest.raises(KernelError):
+        runner.step([StepEntry("known", list(range(20)), []), StepEntry("new", [4], [0])])
+    assert runner.has("known") and not runner.has("new") and runner.slots.num_free == 1
+    assert runner.length("known") == 0 and runner.kv.num_free(0) == free - 2     # 20 tokens: two pages stay held
+    runner.end("known")
+    assert runner.kv.num_free(0) == free and runner.slots.num_free == 2
+    runner.kv.check()

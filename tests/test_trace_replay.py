@@ -16,8 +16,14 @@ from helpers import TINY, TOL, TraceProcess, make_model_folder, random_tokens, r
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [70, 33, 5, 130, 64, 97], "B": [70, 40, 9, 150, 65, 111, 1], "C": [50, 81, 17, 100],
-           "D": [150, 66, 3, 129, 90]}
-MAX_LIVE_TOKENS = 4 * 192      # four live requests of at most 192 tokens (rounded up to 64)
+           "D": [150, 66, 3, 129, 90], "E": [70, 40, 9, 150, 65, 111, 1]}
+
+
+def max_live_tokens(lengths) -> int:
+    """What --max-tokens promises to hold: the four longest requests, each
+    rounded up to a multiple of 64.  All requests together, replayed twice in
+    the mixed test, are more than that, so pages must be used again."""
+    return sum((n + 63) // 64 * 64 for n in sorted(lengths)[-4:])
 
 
 class Case:
@@ -25,11 +31,11 @@ class Case:
         cfg = TINY[name]
         self.name, self.dtype = name, dtype
         self.folder = make_model_folder(cfg, seed=ord(name), sharpen=4.0,
-                                        vector_dtype=torch.float32 if name == "B" else None)
+                                        vector_dtype=torch.float32 if name in "BE" else None)
         self.cfg, self.weights = plain.load_folder(self.folder)
         self.requests = [random_tokens(cfg["vocab_size"], n, 100 + i) for i, n in enumerate(LENGTHS[name])]
         self.refs = [plain.forward(self.cfg, self.weights, r).numpy() for r in self.requests]
-        self.proc = TraceProcess(self.folder, dtype, MAX_LIVE_TOKENS)
+        self.proc = TraceProcess(self.folder, dtype, max_live_tokens(LENGTHS[name]))
 
     def check(self, rid_index: int, start: int, got: np.ndarray, what: str):
         ref = self.refs[rid_index][start:start + got.shape[0]]
@@ -43,7 +49,7 @@ class Case:
 _cases = {}
 
 
-@pytest.fixture(params=[(n, d) for n in ("A", "B", "C", "D") for d in ("float32", "bfloat16")],
+@pytest.fixture(params=[(n, d) for n in ("A", "B", "C", "D", "E") for d in ("float32", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}", scope="module")
 def case(request):
     key = request.param
@@ -99,9 +105,10 @@ def test_mixed_with_page_reuse(case):
     others; requests join as others end, so freed pages are used again."""
     rng = random.Random(7)
     order = list(range(len(case.requests))) * 2          # every request twice: the pool turns over
+    before = case.proc.stats()
+    assert 2 * sum(LENGTHS[case.name]) > max_live_tokens(LENGTHS[case.name])
     waiting = [(f"m{j}_{i}", i) for j, i in enumerate(order)]
     live = {}                                            # rid -> [request index, position]
-    worst = 0.0
     while waiting or live:
         while waiting and len(live) < 4:
             rid, i = waiting.pop(0)
@@ -126,6 +133,33 @@ def test_mixed_with_page_reuse(case):
         row = 0
         for i, pos, want in checks:
             for w in want:
-                worst = max(worst, case.check(i, pos + w, got[row:row + 1], "mixed"))
+                case.check(i, pos + w, got[row:row + 1], "mixed")
                 row += 1
-    assert worst > 0.0
+    after = case.proc.stats()
+    handed_out = [a - b for a, b in zip(after["page_allocations"], before["page_allocations"])]
+    used_again = [a - b for a, b in zip(after["page_reuses"], before["page_reuses"])]
+    # more pages were handed out than the pool has, so some were used a second time during this very test
+    assert all(h > t for h, t in zip(handed_out, after["pages_total"])), (handed_out, after)
+    assert all(u > 0 for u in used_again), (used_again, after)
+    assert after["pages_free"] == after["pages_total"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_weights_without_a_folder(tmp_path, dtype):
+    """``--random CONFIG.json --seed S`` is the model that ``inferctl random``
+    writes for that configuration and seed: the same logits, bit for bit."""
+    import json
+    from inferflux_b200.config import load_config
+    from inferflux_b200.weights.random_init import write_random_model
+    cfg = TINY["C"]
+    folder = write_random_model(str(tmp_path / "m"), load_config(dict(cfg)), 5)
+    (tmp_path / "c.json").write_text(json.dumps(cfg))
+    toks = random_tokens(cfg["vocab_size"], 40, 3)
+    step = [dict(id="a", tokens=toks, want=[0, 17, 39])]
+    from_folder = TraceProcess(folder, dtype, 64)
+    from_seed = TraceProcess(None, dtype, 64, extra=["--random", str(tmp_path / "c.json"), "--seed", "5"])
+    a, b = from_folder.step(step, end=["a"]), from_seed.step(step, end=["a"])
+    assert from_folder.close() == 0 and from_seed.close() == 0
+    assert np.array_equal(a, b)
+    ref = plain.forward(*plain.load_folder(folder), toks).numpy()[[0, 17, 39]]
+    assert rel_err(a, ref) <= TOL[dtype]

@@ -54,6 +54,40 @@ def test_static_sampler_matches_the_regular_one_twice():
         assert got.tolist() == want.tolist(), f"call {call}"
 
 
+def test_static_calls_back_to_back_on_one_stream():
+    """Three calls queued on one stream with no synchronisation between them,
+    of different sizes (so each finds the leftovers of the one before in the
+    shared array), one of them reading rows that are further apart than they
+    are long.  Calls on one stream run in order, which is the rule of use; each
+    must still give what the regular entry point gives for its input."""
+    from inferflux_b200.kernels import ops
+    from inferflux_b200.kernels.build import library
+    lib = library()
+    f = lambda x, dt: torch.tensor(x, dtype=dt, device=DEV)
+    cases = []
+    for call, (rows, vocab, stride) in enumerate([(8, 50000, 50000), (3, 777, 1024), (6, 152064, 152064)]):
+        g = torch.Generator().manual_seed(40 + call)
+        wide = (torch.randn((rows, stride), generator=g) * 3.0).to(DEV)
+        logits = wide[:, :vocab]                                   # row_stride > vocab in the second case
+        temperature = f([0.9, 1.2, 0.7, 1.0, 0.0, 1.5, 0.6, 1.1][:rows], torch.float32)
+        top_k = f([0, 50, 0, 8, 0, 0, 3, 400][:rows], torch.int32)
+        top_p = f([1.0, 0.9, 0.8, 1.0, 1.0, 0.95, 1.0, 0.7][:rows], torch.float32)
+        min_p = f([0.0, 0.0, 0.0, 0.05, 0.0, 0.0, 0.0, 0.01][:rows], torch.float32)
+        seeds = f([70 + i for i in range(rows)], torch.int64)
+        counters = f([5 * i + call for i in range(rows)], torch.int64)
+        want = torch.empty(rows, dtype=torch.int32, device=DEV)
+        ops.sample(logits.contiguous(), torch.empty(rows * vocab, dtype=torch.float32, device=DEV), temperature,
+                   top_k, top_p, min_p, seeds, counters, want)
+        got = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+        cases.append((logits, temperature, top_k, top_p, min_p, seeds, counters, got, want))
+    torch.cuda.synchronize()
+    for c in cases:                                               # queued one behind the other
+        assert _call_static(lib, *c[:8]) == 0
+    torch.cuda.synchronize()
+    for i, c in enumerate(cases):
+        assert c[7].tolist() == c[8].tolist(), f"call {i}"
+
+
 def test_static_sampler_refuses_what_does_not_fit():
     from inferflux_b200.kernels.build import library
     lib = library()
