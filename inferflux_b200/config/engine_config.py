@@ -33,7 +33,7 @@ class EngineConfig:
     chunked_prefill_tokens: int = 512       # most prompt tokens of one request per step
     mixed_prefill_budget_ratio: float = 1.0  # share of max_batch_tokens that prompts may take beside decodes
     max_model_len: Optional[int] = None     # default: the model's max_position_embeddings
-    cuda_graphs: bool = True                # capture decode-only steps (bfloat16 only)
+    cuda_graphs: bool = True                # capture decode-only steps as CUDA graphs
     pipeline_decode: bool = True            # start a decode step before the one before it has reported its tokens
     seed: int = 0
 

@@ -395,16 +395,19 @@ def test_a_failed_step_hands_out_no_tokens(folders, pipeline):
     from inferflux_b200 import SamplingParams
     from inferflux_b200.kernels import ops
     folder, cfg, w = folders["A"]
-    eng = _engine(folder, "bfloat16", pipeline_decode=pipeline)
     prompts = [random_tokens(cfg["vocab_size"], 9, 500 + i) for i in range(2)]
-    for i, p in enumerate(prompts):
-        eng.add_request(p, SamplingParams(temperature=0.0, max_tokens=6 + 20 * i, ignore_eos=True))
+    drawn = dict(temperature=1.5, seed=5, max_tokens=30)                 # in float32 the draws do not depend on the batch
+    first = _engine(folder, "float32").generate(prompts[:1], SamplingParams(ignore_eos=True, **drawn))[0].tokens
+    k = next(i for i in range(5, 30) if first[i] not in first[:i])       # stops at its k-th token, on a stop token:
+    eng = _engine(folder, "float32", pipeline_decode=pipeline)           # found out one step late when running ahead
+    eng.add_request(prompts[0], SamplingParams(stop_token_ids=[first[k]], **drawn))
+    eng.add_request(prompts[1], SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True))
     for _ in range(4):
         assert eng.step() == []
     if pipeline:
         assert eng.stats["steps_run_ahead"] > 0
     ops.error_flag(eng.engine_config.device).fill_(1)
     with pytest.raises(ops.KernelError):
-        for _ in range(8):                                # the first request reaches its limit within these steps
+        for _ in range(k + 2):
             eng.step()
     assert int(ops.error_flag(eng.engine_config.device).item()) == 0     # read and cleared
