@@ -4,12 +4,23 @@ package: it reads the model folder with the ``safetensors`` library and does
 its own arithmetic, by default in float64.
 
 It rests on the reference's formulas (cited per function; paths are those of
-vjsingh1984/inferflux).  The reference's own model code cannot be compiled or
-imported here on the CPU: its forward is CUDA-only and includes a header of an
-absent submodule (runtime/backends/llama/llama_cpp_backend.h:19 includes
-llama.h), and it has no CPU model path
-(runtime/backends/cpu/cpu_backend.cpp:47-54 echoes tokens).  So there is no
-golden output of the reference to compare with.
+vjsingh1984/inferflux).  The reference's whole model cannot be compiled or
+imported here: its forward includes a header of an absent submodule
+(runtime/backends/llama/llama_cpp_backend.h:19 includes llama.h) and it has no
+CPU model path (runtime/backends/cpu/cpu_backend.cpp:47-54 echoes tokens), so
+there is no golden output of a whole model.  What pins each formula instead:
+
+* ``embed``, ``rms_norm``, ``rope_angles`` + ``apply_rope_half``, ``silu_mul``,
+  the bias add and ``causal_gqa_attention`` (group ratios 7, 3 and 5, prompt
+  portions over a longer context and single tokens) are compared with the
+  reference's own kernels, compiled unmodified for sm_100a, in
+  ``tests/test_reference_kernels.py``;
+* every function, and ``forward`` as a whole over tiny models A, B and E, is
+  compared with a second implementation written separately in C++
+  (``inferflux_b200/csrc/host_reference``) in ``tests/test_host_reference.py``;
+* the arrangement of a layer, the tied head and the rule by which layers get a
+  window (``window_of_layer``) rest on the reading alone: the reference's leaf
+  kernels do not cover the first two, and it reads none of the window keys.
 """
 from __future__ import annotations
 

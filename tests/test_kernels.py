@@ -1,5 +1,7 @@
-"""Each CUDA kernel alone against its plain PyTorch float32 reference
-(tests/kernel_refs.py), at sizes other than the engine's test models: row
+"""Each CUDA kernel alone against its two references, the plain PyTorch one
+(tests/kernel_refs.py) and the host-side C++ one (csrc/host_reference), which
+tests/checked_refs.py also holds against each other, at sizes other than the
+engine's test models: row
 lengths that are no power of two, head sizes in steps of 16, odd head counts
 and group ratios, page sizes 4 to 64.  Where random inputs would hide a fault
 (one far key among hundreds, a window's edge, a page border) the inputs are
@@ -11,7 +13,8 @@ import math
 import pytest
 import torch
 
-import kernel_refs as ref
+import checked_refs as ref
+from inferflux_b200.kernels import host_reference as host
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -43,6 +46,7 @@ def test_embed_gather(ops, dtype, vocab, hidden):
     out = torch.empty((5, hidden), dtype=torch.float32, device=DEV)
     ops.embed_gather(table, ids, out)
     assert torch.equal(out.cpu(), table.cpu()[ids.cpu().long()].float())
+    assert torch.equal(out.cpu(), host.embed_gather(table.float().cpu(), ids.cpu(), torch.empty((5, hidden))))
 
 
 @pytest.mark.parametrize("hidden", [24, 100, 3584, 5120 + 8])
@@ -105,6 +109,7 @@ def test_gemm_f32(ops, m, n, k):
     ops.gemm_f32(a, w, b, out)
     want = a.double().cpu() @ w.double().cpu().T + b.double().cpu()
     _close(out, want, 2e-6, "gemm_f32")
+    _close(out, host.gemm(a.cpu(), w.cpu(), b.cpu(), torch.empty((m, n))), 2e-6, "gemm_f32 against the C++ loops")
     # a row's result does not depend on the other rows (bitwise)
     one = torch.empty((1, n), dtype=torch.float32, device=DEV)
     ops.gemm_f32(a[m - 1:m], w, b, one)
@@ -445,6 +450,7 @@ def test_argmax_lowest_index_among_equal_maxima(ops):
     ops.argmax(logits, out)
     want = [77, v - 1, 0, 0, int(torch.argmax(logits[4].cpu()))]
     assert out.tolist() == want
+    assert host.argmax(logits.cpu(), torch.empty(5, dtype=torch.int32)).tolist() == want
     # a strided view (rows of a wider buffer)
     wide = torch.zeros((3, 1000), device=DEV)
     wide[:, 300] = 1.0
@@ -474,6 +480,7 @@ def test_argmax_of_wide_rows_in_slices(ops, v):
         ops.argmax(logits, out)
         assert out.tolist() == [slice_len - 1, slice_len, slice_len + 5, v - 3, v // 2,
                                 int(torch.argmax(logits[5].cpu()))], (v, stride)
+        assert host.argmax(logits.cpu(), torch.empty(6, dtype=torch.int32)).tolist() == out.tolist()
 
 
 def test_penalties(ops):
@@ -555,6 +562,12 @@ def test_sample_matches_inverse_cdf(ops, v, r, offset):
         u = ref.uniform01(seeds[i], counters[i])
         lo = float(cdf[got[i] - 1]) if got[i] > 0 else 0.0
         assert lo - 1e-5 <= u <= float(cdf[got[i]]) + 1e-5, f"row {i}: u={u} not in [{lo}, {float(cdf[got[i]])}]"
+        # the C++ loops: the same kept set, and the same token unless u lies within rounding of an interval's end
+        kept_c = host.kept_probabilities(logits[i].cpu().contiguous(), temps[i], ks[i], ps[i], mps[i])
+        assert torch.equal(kept_c > 0, kept > 0) and float((kept_c - kept).abs().max()) < 1e-7   # float32 temperature there
+        assert host.uniform01(seeds[i], counters[i]) == u
+        tok_c = host.inverse_cdf(kept_c, u)
+        assert tok_c == got[i] or min(abs(u - lo), abs(u - float(cdf[got[i]]))) < 1e-5, (i, tok_c, got[i])
 
 
 def test_sample_thresholds_at_ties_and_edges(ops):
