@@ -2,10 +2,12 @@
 table per request and group, and the rules by which pages come and go.
 
 A *group* holds the runs (layer executions) whose mixers ask for the same
-:class:`~inferflux_b200.parts.base.KVNeed` (heads, head size, window).  Each
-group has a page pool of its own; one page holds ``page_size`` tokens of every
-run of the group, laid out ``[page][run][k|v][kv_head][slot][head_dim]`` so
-that one (page, run, k|v, head) tile is contiguous.
+:class:`~inferflux_b200.parts.base.KVNeed` (what a token caches: streams of
+``heads x width`` elements, and a window).  Each group has a page pool of its
+own; one page holds ``page_size`` tokens of every run of the group, laid out
+``[page][run][stream][head][slot][width]`` so that one (page, run, stream,
+head) tile is contiguous.  For attention the streams are keys and values of
+equal shape, which gives ``[page][run][k|v][kv_head][slot][head_dim]``.
 
 Pages are taken before a step for the tokens the step brings
 (:meth:`KVCacheManager.reserve`), and given back when the request ends
@@ -164,23 +166,38 @@ class KVCacheStorage:
                  page_size: int, dtype, device: str):
         import torch
         self.page_size = page_size
+        self.needs = list(needs)
         self.pools = []
         for need, n_runs, pages in zip(needs, runs_per_group, num_pages):
             # zeros, not empty: a masked key is multiplied by 0, which must not meet a NaN
-            self.pools.append(torch.zeros((pages, n_runs, 2, need.n_kv_heads, page_size, need.head_dim),
+            self.pools.append(torch.zeros((pages, n_runs, page_size * need.elements_per_token),
                                           dtype=dtype, device=device))
 
+    def stream_views(self, group: int, index: int):
+        """For one run: {stream name: its ``[heads, page_size, width]`` block
+        inside page 0}, and the number of elements between pages.  Page p's
+        block lies ``p * stride`` elements further on."""
+        import torch
+        pool, ps = self.pools[group], self.page_size
+        views, at = {}, pool[0, index].storage_offset()
+        for s in self.needs[group].streams:
+            views[s.name] = torch.as_strided(pool, (s.heads, ps, s.width), (ps * s.width, s.width, 1), at)
+            at += s.heads * ps * s.width
+        return views, pool.stride(0)
+
     def layer_views(self, group: int, index: int):
-        """(keys of page 0, values of page 0, elements between pages) of one run."""
-        pool = self.pools[group]
-        return pool[0, index, 0], pool[0, index, 1], pool.stride(0)
+        """(keys of page 0, values of page 0, elements between pages) of one run
+        whose streams are ``k`` and ``v``."""
+        views, stride = self.stream_views(group, index)
+        return views["k"], views["v"], stride
 
     def bytes(self) -> int:
         return sum(p.numel() * p.element_size() for p in self.pools)
 
 
 def bytes_per_token(needs: Sequence[KVNeed], runs_per_group: Sequence[int], element_size: int) -> int:
-    """Cache bytes one token takes over all groups: 2 * runs * kv_heads *
-    head_dim * element size each (the reference's planner has the same
-    product, runtime/backends/cuda/native/kv_cache_planner.h:22-37)."""
-    return sum(2 * r * n.n_kv_heads * n.head_dim * element_size for n, r in zip(needs, runs_per_group))
+    """Cache bytes one token takes over all groups: runs * elements of all
+    streams * element size each; for keys and values that is 2 * runs *
+    kv_heads * head_dim (the reference's planner has the same product,
+    runtime/backends/cuda/native/kv_cache_planner.h:22-37)."""
+    return sum(r * n.elements_per_token * element_size for n, r in zip(needs, runs_per_group))

@@ -109,7 +109,8 @@ def cmd_models(args) -> int:
     print(json.dumps({"id": args.model, "architecture": cfg.architecture, "config": cfg.to_dict(),
                       "tensors": len(specs), "parameters": sum(int(torch.tensor(s.shape).prod()) for s in specs
                                                                if s.kind != "ignored"),
-                      "cache_groups": [{"kv_heads": n.n_kv_heads, "head_dim": n.head_dim, "window": n.window, "runs": r}
+                      "cache_groups": [{"streams": [{"name": s.name, "heads": s.heads, "width": s.width}
+                                                    for s in n.streams], "window": n.window, "runs": r}
                                        for n, r in zip(model.kv_needs, model.runs_per_group)]}))
     return 0
 

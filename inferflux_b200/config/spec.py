@@ -29,19 +29,31 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: its weight-name prefix, its parts and how they are arranged.
+    """One layer: its weight-name prefix, how its parts are arranged, and the
+    parts themselves by the role each plays in that arrangement.
+
+    Which roles there are is the arrangement's business: it declares them with
+    the family of part that fills each (``prenorm``: ``mixer``, ``mixer_norm``,
+    ``feed_forward``, ``feed_forward_norm``); the model builds whatever the
+    layer lists and hands the lot to the arrangement.  A block with more norms,
+    with one norm for two parallel branches or without a feed-forward is
+    another arrangement with other roles, not a change to this class.
 
     ``position`` names an entry of :attr:`ModelSpec.positions` (or None for a
-    mixer that needs no position encoding).
+    layer whose mixer needs no position encoding).
     """
 
     prefix: str
     arrangement: str
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Dict[str, PartSpec]
     position: Optional[str] = None
+
+    def part(self, role: str) -> PartSpec:
+        try:
+            return self.parts[role]
+        except KeyError:
+            raise KeyError(f"layer '{self.prefix}' has no part in the role '{role}'; "
+                           f"it has {sorted(self.parts)}") from None
 
 
 @dataclass(frozen=True)

@@ -15,11 +15,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Sequence, Tuple
 
+import numpy as np
 import torch
-
-QUERY_TILE = 16     # tokens per query tile of the generic attention kernel
-CHUNK_TILE = 64     # tokens per query tile of the mma.sync kernel for prompt portions
-UMMA_TILE = 128     # tokens per query tile of the tcgen05 kernel for prompt portions
 
 
 @dataclass
@@ -30,6 +27,10 @@ class StepEntry:
     rid: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+
+
+class SlabFull(RuntimeError):
+    """The step's metadata does not fit the slab it is written into."""
 
 
 class MetadataSlab:
@@ -70,7 +71,7 @@ class MetadataSlab:
         n = len(values)
         start = (self._used + align - 1) // align * align
         if start + n > self.capacity:
-            raise RuntimeError(f"step metadata needs {start + n} words, the slab holds {self.capacity}")
+            raise SlabFull(f"step metadata needs {start + n} words, the slab holds {self.capacity}")
         if n:
             self._np[start:start + n] = values
         self._used = start + n
@@ -87,31 +88,36 @@ class MetadataSlab:
 
 
 @dataclass
+class StepLayout:
+    """The shape of a step on the host, from which parts derive the metadata of
+    their own kernels (:meth:`~inferflux_b200.parts.base.Part.describe_step`)."""
+
+    n_entries: int
+    n_tokens: int
+    page_size: int
+    q_len: np.ndarray                         # [R] new tokens of each entry
+    q_start: np.ndarray                       # [R] row of each entry's first new token
+    ctx_start: np.ndarray                     # [R] tokens cached before each entry's new ones
+
+
+@dataclass
 class StepContext:
-    """What parts see of a step.  All tensors are int32 on the device."""
+    """What parts see of a step.  All tensors are int32 on the device.  What
+    only one kind of part needs (the tile lists of the attention kernels, say)
+    is not here but in ``extras`` under that part's ``describe_key``."""
 
     n_tokens: int
     n_entries: int
     entries: List[StepEntry]                  # host view, in batch order
     ctx_starts: List[int]                     # host: tokens cached before each entry's new ones
     slots: List[int]                          # host: state slot of each entry
+    layout: StepLayout
     token_ids: torch.Tensor                   # [N]
     positions: torch.Tensor                   # [N]
     entry_q_start: torch.Tensor               # [R] row of each entry's first new token
     entry_q_len: torch.Tensor                 # [R]
     entry_ctx_start: torch.Tensor             # [R]
     entry_slot: torch.Tensor                  # [R]
-    tile_entry: torch.Tensor                  # [T] query tiles of QUERY_TILE tokens
-    tile_q0: torch.Tensor                     # [T]
-    n_tiles: int
-    chunk_tile_entry: torch.Tensor            # [Tc] tiles of CHUNK_TILE tokens over entries with more than one token
-    chunk_tile_q0: torch.Tensor               # [Tc]
-    n_chunk_tiles: int
-    umma_tile_entry: torch.Tensor             # [Tu] tiles of UMMA_TILE tokens over the same entries
-    umma_tile_q0: torch.Tensor                # [Tu]
-    n_umma_tiles: int
-    decode_entries: torch.Tensor              # [D] entries that bring exactly one token
-    n_decode: int
     block_tables: List[torch.Tensor]          # per cache group [R, max_blocks]
     slot_maps: List[torch.Tensor]             # per cache group [N]
     want_rows: torch.Tensor                   # [W] rows whose logits are wanted
@@ -122,23 +128,8 @@ class StepContext:
     kv: object                                # KVCacheStorage
     dtype: torch.dtype
     device: str
-    position_tables: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
-    extras: Dict[str, object] = field(default_factory=dict)
-    decode_skewed: bool = False               # the single tokens' contexts differ much in length (contexts_skewed)
+    position_tables: Dict[str, object] = field(default_factory=dict)   # position name -> what its prepare() returned
+    extras: Dict[str, object] = field(default_factory=dict)            # describe_key -> what describe_step() returned
 
     def buffer(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
-
-
-def contexts_skewed(lengths) -> bool:
-    """Whether the contexts of a step's single tokens differ so much in length
-    that attention should share its work out by tiles and not by requests: the
-    longest is at least 1,024 tokens and at least 1.5 times the mean.  With
-    equal contexts the kernel that gives every request its own blocks is about
-    a fifth faster; with one long context among short ones it takes as long as
-    the long one alone."""
-    n = len(lengths)
-    if n < 2:
-        return False
-    longest = max(lengths)
-    return longest >= 1024 and 2 * longest * n >= 3 * sum(lengths)

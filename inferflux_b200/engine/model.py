@@ -31,16 +31,49 @@ class Model:
         self.lm_head = mk("lm_head", spec.lm_head)
         self.positions = {name: mk("position", ps) for name, ps in spec.positions.items()}
         self.blocks = []
-        self._layer_parts = []
+        self._layer_parts: List[Dict[str, object]] = []
         for layer in spec.layers:
-            mixer = mk("mixer", layer.mixer, layer.prefix)
-            mixer_norm = mk("norm", layer.mixer_norm, layer.prefix)
-            ffn = mk("feed_forward", layer.feed_forward, layer.prefix)
-            ffn_norm = mk("norm", layer.feed_forward_norm, layer.prefix)
-            self._layer_parts.append((mixer, mixer_norm, ffn, ffn_norm))
             arrangement = part_class("arrangement", layer.arrangement)
-            self.blocks.append(arrangement(mixer, mixer_norm, ffn, ffn_norm, layer.position))
+            parts = {role: mk(family, layer.parts[role], layer.prefix)
+                     for role, family in self._roles(layer).items()}
+            self._layer_parts.append(parts)
+            self.blocks.append(arrangement(parts, layer.position))
         self._plan_cache()
+        self._describers = self._collect_describers()
+
+    @staticmethod
+    def _roles(layer) -> Dict[str, str]:
+        """role -> family for the parts a layer lists, checked against what its
+        arrangement declares."""
+        arrangement = part_class("arrangement", layer.arrangement)
+        declared = dict(arrangement.roles)
+        optional = set(getattr(arrangement, "optional_roles", ()))
+        unknown = sorted(set(layer.parts) - set(declared))
+        missing = sorted(set(declared) - optional - set(layer.parts))
+        if unknown or missing:
+            raise ValueError(f"layer '{layer.prefix}' ({layer.arrangement}): "
+                             + (f"missing parts {missing}; " if missing else "")
+                             + (f"parts in roles the arrangement does not have {unknown}; " if unknown else "")
+                             + f"its roles are {sorted(declared)}")
+        return {role: family for role, family in declared.items() if role in layer.parts}
+
+    def _collect_describers(self):
+        """One part per ``describe_key``: those asked to describe each step."""
+        out = {}
+        every = [self.embedding, self.final_norm, self.lm_head, *self.positions.values()]
+        for parts in self._layer_parts:
+            every += list(parts.values())
+        for p in every:
+            key = getattr(p, "describe_key", None)
+            if key is not None and key not in out:
+                out[key] = p
+        return out
+
+    def describe_step(self, layout, put) -> Dict[str, object]:
+        return {key: p.describe_step(layout, put) for key, p in self._describers.items()}
+
+    def step_shape(self, layout) -> tuple:
+        return tuple((key, p.step_shape(layout)) for key, p in self._describers.items())
 
     # ------------------------------------------------------------- cache plan
     def _plan_cache(self) -> None:
@@ -51,8 +84,20 @@ class Model:
         self.state_needs: List[List[StateNeed]] = []
         for i, run in enumerate(spec.schedule):
             layer = spec.layers[run.layer]
-            cls = part_class("mixer", layer.mixer.kind)
-            need = cls.kv_need(layer.mixer.params)
+            need, states = None, []
+            for role, family in self._roles(layer).items():
+                ps = layer.parts[role]
+                cls = part_class(family, ps.kind)
+                if not hasattr(cls, "kv_need"):
+                    continue
+                n = cls.kv_need(ps.params)
+                if n is not None:
+                    if need is not None:
+                        raise ValueError(f"layer {run.layer}: two parts ask for a paged cache; a run has one")
+                    need = n
+                states += list(cls.state_needs(ps.params))
+            if len({s.name for s in states}) != len(states):
+                raise ValueError(f"layer {run.layer}: two state tensors of its parts have the same name")
             info = RunInfo(run_index=i)
             if run.cache_of is not None:
                 if need is not None:
@@ -69,7 +114,7 @@ class Model:
                 g = self.kv_needs.index(need)
                 info.kv_group, info.kv_index = g, self.runs_per_group[g]
                 self.runs_per_group[g] += 1
-            self.state_needs.append(list(cls.state_needs(layer.mixer.params)))
+            self.state_needs.append(states)
             self.runs.append(info)
 
     def attach_states(self, storage) -> None:
@@ -90,10 +135,8 @@ class Model:
                     out[w.name] = w
         add("embedding", spec.embedding)
         for layer in spec.layers:
-            add("mixer", layer.mixer, layer.prefix)
-            add("norm", layer.mixer_norm, layer.prefix)
-            add("feed_forward", layer.feed_forward, layer.prefix)
-            add("norm", layer.feed_forward_norm, layer.prefix)
+            for role, family in self._roles(layer).items():
+                add(family, layer.parts[role], layer.prefix)
         add("norm", spec.final_norm)
         add("lm_head", spec.lm_head)
         for ps in spec.positions.values():               # a position encoding may have weights of its own
@@ -107,7 +150,7 @@ class Model:
         self.lm_head.load(tensors)
         self.final_norm.load(tensors)
         for parts in self._layer_parts:
-            for p in parts:
+            for p in parts.values():
                 p.load(tensors)
         for p in self.positions.values():
             p.load(tensors)

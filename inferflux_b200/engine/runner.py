@@ -20,7 +20,7 @@ import torch
 
 from ..cache import OutOfPages, OutOfSlots, KVCacheManager, KVCacheStorage, StateSlotManager, StateSlotStorage, bytes_per_token
 from ..config.engine_config import EngineConfig
-from .batch import CHUNK_TILE, QUERY_TILE, UMMA_TILE, MetadataSlab, StepContext, StepEntry, contexts_skewed
+from .batch import MetadataSlab, SlabFull, StepContext, StepEntry, StepLayout
 from ..kernels import ops
 from .model import Model
 
@@ -132,38 +132,43 @@ class StepRunner:
             self.kv.reserve(e.rid, len(e.tokens))
         return [e.rid for e in new]
 
-    def _describe(self, entries: Sequence[StepEntry], slab: Optional[MetadataSlab] = None,
-                  widths: Optional[Sequence[int]] = None) -> StepContext:
-        """Write the step's metadata into a slab (the runner's own unless one is
-        given) and return the context whose tensors are views of it.  With
-        ``widths`` the block tables are padded to those widths, so that steps
-        of the same shape have the same layout."""
-        ps = self.page_size
+    def _layout(self, entries: Sequence[StepEntry]) -> StepLayout:
         r = len(entries)
         lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=r)
         starts = np.fromiter((self.kv.length(e.rid) for e in entries), dtype=np.int64, count=r)
         q_start = np.zeros(r, dtype=np.int64)
         np.cumsum(lens[:-1], out=q_start[1:])
-        n = int(lens.sum())
+        return StepLayout(n_entries=r, n_tokens=int(lens.sum()), page_size=self.page_size, q_len=lens,
+                          q_start=q_start, ctx_start=starts)
+
+    def _describe(self, entries: Sequence[StepEntry], slab: Optional[MetadataSlab] = None,
+                  widths: Optional[Sequence[int]] = None) -> StepContext:
+        """Write the step's metadata into a slab (the runner's own unless one is
+        given) and return the context whose tensors are views of it.  With
+        ``widths`` the block tables are padded to those widths, so that steps
+        of the same shape have the same layout.  The runner writes what every
+        part needs (tokens, positions, entries, block tables, cache slots,
+        wanted rows); parts that describe the step for their own kernels add to
+        the same slab before it is copied."""
+        if slab is not None:
+            return self._describe_into(entries, slab, widths)
+        while True:
+            try:
+                return self._describe_into(entries, self.slab, widths)
+            except SlabFull:
+                self.slab = MetadataSlab(2 * self.slab.capacity, self.device)
+
+    def _describe_into(self, entries: Sequence[StepEntry], slab: MetadataSlab,
+                       widths: Optional[Sequence[int]]) -> StepContext:
+        ps = self.page_size
+        layout = self._layout(entries)
+        r, n, lens, starts, q_start = layout.n_entries, layout.n_tokens, layout.q_len, layout.ctx_start, layout.q_start
         token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
         entry_of_token = np.repeat(np.arange(r), lens)
         offs = np.arange(n) - q_start[entry_of_token]
         positions = starts[entry_of_token] + offs
         slots = [self.slots.slot(e.rid) for e in entries]
         want_rows = [int(q_start[i]) + int(p) for i, e in enumerate(entries) for p in e.want]
-        tile_entry, tile_q0, ctile_entry, ctile_q0, dec_entries = [], [], [], [], []
-        utile_entry, utile_q0 = [], []
-        for i in range(r):
-            ln = int(lens[i])
-            if ln == 1:
-                tile_entry.append(i), tile_q0.append(0), dec_entries.append(i)
-                continue
-            for q0 in range(0, ln, QUERY_TILE):
-                tile_entry.append(i), tile_q0.append(q0)
-            for q0 in range(0, ln, CHUNK_TILE):
-                ctile_entry.append(i), ctile_q0.append(q0)
-            for q0 in range(0, ln, UMMA_TILE):
-                utile_entry.append(i), utile_q0.append(q0)
         groups = self.kv.num_groups
         tables, slot_maps, out_widths = [], [], []
         for g in range(groups):
@@ -180,34 +185,21 @@ class StepRunner:
             slot_maps.append(pages.astype(np.int64) * ps + positions % ps)
             tables.append(arr.reshape(-1))
             out_widths.append(width)
-        need = 4 * (14 + groups) + 2 * n + 5 * r + 2 * len(tile_entry) + 3 * len(ctile_entry) + len(want_rows) \
-            + sum(t.size for t in tables) + groups * n + 64
-        if slab is None:
-            if need > self.slab.capacity:
-                self.slab = MetadataSlab(max(need, 2 * self.slab.capacity), self.device)
-            slab = self.slab
         slab.begin()
         d_tok, d_pos = slab.put(token_ids), slab.put(positions)
         d_qs, d_ql, d_cs, d_sl = slab.put(q_start), slab.put(lens), slab.put(starts), slab.put(slots)
-        d_te, d_tq = slab.put(tile_entry), slab.put(tile_q0)
-        d_cte, d_ctq, d_dec = slab.put(ctile_entry), slab.put(ctile_q0), slab.put(dec_entries)
-        d_ute, d_utq = slab.put(utile_entry), slab.put(utile_q0)
         d_want = slab.put(want_rows)
         d_tabs = [slab.put(t).view(r, w) for t, w in zip(tables, out_widths)]
         d_sm = [slab.put(sm) for sm in slot_maps]
+        extras = self.model.describe_step(layout, slab.put)
         slab.upload()
         return StepContext(
-            n_tokens=n, n_entries=r, entries=list(entries), ctx_starts=starts.tolist(), slots=slots,
+            n_tokens=n, n_entries=r, entries=list(entries), ctx_starts=starts.tolist(), slots=slots, layout=layout,
             token_ids=d_tok, positions=d_pos, entry_q_start=d_qs, entry_q_len=d_ql, entry_ctx_start=d_cs,
-            entry_slot=d_sl, tile_entry=d_te, tile_q0=d_tq, n_tiles=len(tile_entry),
-            chunk_tile_entry=d_cte, chunk_tile_q0=d_ctq, n_chunk_tiles=len(ctile_entry),
-            umma_tile_entry=d_ute, umma_tile_q0=d_utq, n_umma_tiles=len(utile_entry),
-            decode_entries=d_dec, n_decode=len(dec_entries),
-            block_tables=d_tabs, slot_maps=d_sm, want_rows=d_want, n_want=len(want_rows),
+            entry_slot=d_sl, block_tables=d_tabs, slot_maps=d_sm, want_rows=d_want, n_want=len(want_rows),
             max_q_len=int(lens.max()),
             max_ctx_len=int((starts + lens).max()) if widths is None else max(out_widths) * ps,
-            page_size=ps, kv=self.kv_storage, dtype=self.dtype, device=self.device,
-            decode_skewed=contexts_skewed([int(starts[i]) + 1 for i in dec_entries]))
+            page_size=ps, kv=self.kv_storage, dtype=self.dtype, device=self.device, extras=extras)
 
     def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
         """Reserve pages for the step's tokens and describe the step on the device."""
@@ -270,8 +262,8 @@ class StepRunner:
         step = self.GRAPH_WIDTH_STEP
         widths = tuple((max(len(self.kv.block_table(e.rid, g)) for e in entries) + step - 1) // step * step
                        for g in range(self.kv.num_groups))
-        # the attention kernel for single tokens is chosen by how much the contexts differ: part of the shape
-        key = (len(entries), widths, contexts_skewed([self.kv.length(e.rid) + 1 for e in entries]))
+        # what else decides which kernels the parts launch (attention: how much the contexts differ) is part of the shape
+        key = (len(entries), widths, self.model.step_shape(self._layout(entries)))
         rec = self._graphs.get(key)
         if rec is None:
             # While requests join and leave, many batch sizes come once or twice; capturing costs more than
@@ -288,8 +280,14 @@ class StepRunner:
             if len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
             r = len(entries)
-            slab = MetadataSlab(64 + 16 * r + sum(r * w for w in widths) + 8 * (14 + len(widths)), self.device)
-            ctx = self._describe(entries, slab, widths)
+            words = 64 + 16 * r + sum(r * w for w in widths) + 8 * (14 + len(widths))
+            while True:                                      # a slab of this step's own, as large as its metadata
+                slab = MetadataSlab(words, self.device)
+                try:
+                    ctx = self._describe(entries, slab, widths)
+                    break
+                except SlabFull:
+                    words *= 2
             if device_tokens is not None:
                 ctx.token_ids.copy_(device_tokens[:r])
             logits = self.model.forward(ctx)                 # this step runs eagerly (and warms the libraries up)

@@ -25,14 +25,15 @@ def build_qwen2_spec(cfg: Qwen2Config) -> ModelSpec:
         layers.append(LayerSpec(
             prefix=f"model.layers.{i}",
             arrangement="prenorm",
-            mixer=PartSpec("gqa_attention", dict(
-                name="self_attn", hidden=h, n_heads=cfg.num_attention_heads,
-                n_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
-                qkv_bias=True, o_bias=False, window=cfg.window_of_layer(i))),
-            mixer_norm=PartSpec("rmsnorm", dict(name="input_layernorm", hidden=h, eps=cfg.rms_norm_eps)),
-            feed_forward=PartSpec("swiglu", dict(name="mlp", hidden=h, intermediate=cfg.intermediate_size)),
-            feed_forward_norm=PartSpec("rmsnorm", dict(name="post_attention_layernorm", hidden=h,
-                                                       eps=cfg.rms_norm_eps)),
+            parts=dict(
+                mixer=PartSpec("gqa_attention", dict(
+                    name="self_attn", hidden=h, n_heads=cfg.num_attention_heads,
+                    n_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
+                    qkv_bias=True, o_bias=False, window=cfg.window_of_layer(i))),
+                mixer_norm=PartSpec("rmsnorm", dict(name="input_layernorm", hidden=h, eps=cfg.rms_norm_eps)),
+                feed_forward=PartSpec("swiglu", dict(name="mlp", hidden=h, intermediate=cfg.intermediate_size)),
+                feed_forward_norm=PartSpec("rmsnorm", dict(name="post_attention_layernorm", hidden=h,
+                                                           eps=cfg.rms_norm_eps))),
             position="rope",
         ))
     return ModelSpec(

@@ -18,6 +18,7 @@ than ``window - 1`` positions behind the query; the reference has no window.
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional
 
 import torch
@@ -29,13 +30,80 @@ from .base import KVNeed, Part, PartialSums, RunInfo
 from .linear import Linear
 
 
+QUERY_TILE = 16     # tokens per query tile of the generic attention kernel
+CHUNK_TILE = 64     # tokens per query tile of the mma.sync kernel for prompt portions
+UMMA_TILE = 128     # tokens per query tile of the tcgen05 kernel for prompt portions
+
+
+def contexts_skewed(lengths) -> bool:
+    """Whether the contexts of a step's single tokens differ so much in length
+    that attention should share its work out by tiles and not by requests: the
+    longest is at least 1,024 tokens and at least 1.5 times the mean.  With
+    equal contexts the kernel that gives every request its own blocks is about
+    a fifth faster; with one long context among short ones it takes as long as
+    the long one alone."""
+    n = len(lengths)
+    if n < 2:
+        return False
+    longest = max(lengths)
+    return longest >= 1024 and 2 * longest * n >= 3 * sum(lengths)
+
+
+@dataclass
+class AttentionStep:
+    """What the attention kernels read of a step beyond the common metadata: the
+    step's query tiles at the three tile sizes of the kernels, and which entries
+    bring a single token.  int32 device tensors with their lengths."""
+
+    tile_entry: torch.Tensor                  # [T] query tiles of QUERY_TILE tokens (all entries)
+    tile_q0: torch.Tensor                     # [T] first query of the tile within its entry
+    n_tiles: int
+    chunk_tile_entry: torch.Tensor            # [Tc] tiles of CHUNK_TILE tokens over entries with more than one token
+    chunk_tile_q0: torch.Tensor
+    n_chunk_tiles: int
+    umma_tile_entry: torch.Tensor             # [Tu] tiles of UMMA_TILE tokens over the same entries
+    umma_tile_q0: torch.Tensor
+    n_umma_tiles: int
+    decode_entries: torch.Tensor              # [D] entries that bring exactly one token
+    n_decode: int
+    decode_skewed: bool                       # their contexts differ much in length (contexts_skewed)
+
+
 class GQAttention(Part):
     """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``,
     ``qkv_bias``, ``o_bias``, ``window`` (None or int), ``kv_shared`` (True: the
     layer has only q and o and reads another run's cache), ``scale`` (None =
-    ``1/sqrt(head_dim)``), ``name``."""
+    ``1/sqrt(head_dim)``), ``name``.
+
+    Position: a pair ``(cos, sin)`` of float32 ``[N, r/2]`` tensors (``r`` even,
+    at most ``head_dim``): the first ``r`` dimensions of every query and key
+    head are rotated in split-half pairs ``(i, i + r/2)``; None = no rotation."""
 
     family = "mixer"
+    describe_key = "gqa_attention"
+
+    # -- the step's description, once for all attention layers ------------
+    def describe_step(self, layout, put) -> AttentionStep:
+        tile_entry, tile_q0, ctile_entry, ctile_q0, utile_entry, utile_q0, dec = [], [], [], [], [], [], []
+        for i in range(layout.n_entries):
+            ln = int(layout.q_len[i])
+            if ln == 1:
+                tile_entry.append(i), tile_q0.append(0), dec.append(i)
+                continue
+            for q0 in range(0, ln, QUERY_TILE):
+                tile_entry.append(i), tile_q0.append(q0)
+            for q0 in range(0, ln, CHUNK_TILE):
+                ctile_entry.append(i), ctile_q0.append(q0)
+            for q0 in range(0, ln, UMMA_TILE):
+                utile_entry.append(i), utile_q0.append(q0)
+        return AttentionStep(
+            put(tile_entry), put(tile_q0), len(tile_entry), put(ctile_entry), put(ctile_q0), len(ctile_entry),
+            put(utile_entry), put(utile_q0), len(utile_entry), put(dec), len(dec),
+            contexts_skewed([int(layout.ctx_start[i]) + 1 for i in dec]))
+
+    def step_shape(self, layout) -> tuple:
+        """The kernel for single tokens is chosen by how much the contexts differ."""
+        return (contexts_skewed([int(c) + 1 for c, n in zip(layout.ctx_start, layout.q_len) if n == 1]),)
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
@@ -77,8 +145,8 @@ class GQAttention(Part):
     def kv_need(cls, params: Dict[str, Any]) -> Optional[KVNeed]:
         if params.get("kv_shared"):
             return None
-        return KVNeed(int(params["n_kv_heads"]), int(params["head_dim"]),
-                      int(params["window"]) if params.get("window") else None)
+        return KVNeed.keys_and_values(int(params["n_kv_heads"]), int(params["head_dim"]),
+                                      int(params["window"]) if params.get("window") else None)
 
     # -- weights ---------------------------------------------------------
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -101,7 +169,11 @@ class GQAttention(Part):
         attends over the cache."""
         n = x.shape[0]
         nkv_w = 0 if self.kv_shared else self.n_kv
+        step: AttentionStep = ctx.extras[self.describe_key]
         if position is not None:
+            if not (isinstance(position, (tuple, list)) and len(position) == 2):
+                raise TypeError("gqa_attention takes its position as a pair (cos, sin) of [N, r/2] float32 tensors; "
+                                f"the layer's position encoding gave {type(position).__name__}")
             cos, sin = position
         else:
             cos = sin = torch.empty((n, 0), dtype=torch.float32, device=x.device)
@@ -114,20 +186,20 @@ class GQAttention(Part):
         g = run.kv_group
         k_layer, v_layer, page_stride = ctx.kv.layer_views(g, run.kv_index)
         attn = torch.empty((n, self.n_heads * self.head_dim), dtype=qkv.dtype, device=x.device)
-        if (ctx.n_decode == n and not ctx.n_chunk_tiles and nkv_w and qkv.dtype == torch.bfloat16
+        if (step.n_decode == n and not step.n_chunk_tiles and nkv_w and qkv.dtype == torch.bfloat16
                 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and 2 * cos.shape[1] == self.head_dim
-                and not self._share_by_tiles(ctx)):
+                and not self._share_by_tiles(step)):
             # single tokens only: the attention kernel adds the bias, rotates and writes the cache itself
-            self.decode(qkv, attn, ctx, g, k_layer, v_layer, page_stride,
+            self.decode(qkv, attn, ctx, step, g, k_layer, v_layer, page_stride,
                         prep=(self.qkv_bias, cos, sin, ctx.slot_maps[g], partials))
             return self.o.forward(attn, out_dtype=x.dtype, allow_partials=True)
         ops.qkv_rope_kv_write(qkv, self.qkv_bias, cos, sin, ctx.slot_maps[g] if nkv_w else None,
                               k_layer if nkv_w else None, v_layer if nkv_w else None, page_stride,
                               ctx.page_size, self.n_heads, nkv_w, self.head_dim, partials)
-        self.attend(qkv, attn, ctx, g, k_layer, v_layer, page_stride)
+        self.attend(qkv, attn, ctx, step, g, k_layer, v_layer, page_stride)
         return self.o.forward(attn, out_dtype=x.dtype, allow_partials=True)
 
-    def attend(self, qkv, attn, ctx, g, k_layer, v_layer, page_stride) -> None:
+    def attend(self, qkv, attn, ctx, step, g, k_layer, v_layer, page_stride) -> None:
         """bfloat16 with a head size the tensor-core kernels take: prompt
         portions go to the tcgen05 kernel (head size 128) or the mma.sync kernel
         (64), single tokens to the split decode kernel; anything else (float32,
@@ -135,29 +207,29 @@ class GQAttention(Part):
         common = (ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start)
         if qkv.dtype != torch.bfloat16 or self.head_dim not in ops.FAST_ATTENTION_HEAD_DIMS:
             ops.attn_paged_generic(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
-                                   ctx.block_tables[g], ctx.tile_entry, ctx.tile_q0, ctx.n_tiles, *common,
+                                   ctx.block_tables[g], step.tile_entry, step.tile_q0, step.n_tiles, *common,
                                    self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
             return
-        if ctx.n_chunk_tiles and self.head_dim == ops.UMMA_ATTENTION_HEAD_DIM:
+        if step.n_chunk_tiles and self.head_dim == ops.UMMA_ATTENTION_HEAD_DIM:
             max_keys = min(ctx.max_ctx_len, self.window + 128) if self.window else ctx.max_ctx_len
-            splits = ops.attn_prefill_umma_splits(ctx.n_umma_tiles, self.n_heads, max_keys)
+            splits = ops.attn_prefill_umma_splits(step.n_umma_tiles, self.n_heads, max_keys)
             ops.attn_prefill_umma(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
-                                  ctx.block_tables[g], ctx.umma_tile_entry, ctx.umma_tile_q0, ctx.n_umma_tiles,
+                                  ctx.block_tables[g], step.umma_tile_entry, step.umma_tile_q0, step.n_umma_tiles,
                                   *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, splits)
-        elif ctx.n_chunk_tiles:
+        elif step.n_chunk_tiles:
             ops.attn_prefill_bf16(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
-                                  ctx.block_tables[g], ctx.chunk_tile_entry, ctx.chunk_tile_q0, ctx.n_chunk_tiles,
+                                  ctx.block_tables[g], step.chunk_tile_entry, step.chunk_tile_q0, step.n_chunk_tiles,
                                   *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window)
-        if ctx.n_decode:
-            self.decode(qkv, attn, ctx, g, k_layer, v_layer, page_stride)
+        if step.n_decode:
+            self.decode(qkv, attn, ctx, step, g, k_layer, v_layer, page_stride)
 
-    def _share_by_tiles(self, ctx) -> bool:
+    def _share_by_tiles(self, step) -> bool:
         """Contexts of very different lengths (and no window that evens them
         out): the kernel that shares the tiles of all entries out evenly."""
-        return (ctx.decode_skewed and ctx.n_decode <= ops.DECODE_EVEN_MAX_ENTRIES
+        return (step.decode_skewed and step.n_decode <= ops.DECODE_EVEN_MAX_ENTRIES
                 and not (self.window and self.window < 1024))
 
-    def decode(self, qkv, attn, ctx, g, k_layer, v_layer, page_stride, prep=None) -> None:
+    def decode(self, qkv, attn, ctx, step, g, k_layer, v_layer, page_stride, prep=None) -> None:
         """The step's single tokens.  Contexts of about the same length: the keys
         of each are cut into as many parts as fill the GPU, and merged; with
         ``prep`` = (bias, cos, sin, slot map, partial sums or None) qkv is
@@ -165,24 +237,24 @@ class GQAttention(Part):
         Contexts of very different lengths: all their tiles are shared out
         evenly over the blocks."""
         max_keys = min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len
-        if prep is None and self._share_by_tiles(ctx):
+        if prep is None and self._share_by_tiles(step):
             pieces = ops.attn_decode_pieces(self.n_heads, self.n_kv, self.head_dim, max_keys)
-            rows = ctx.n_decode * self.n_heads * pieces
+            rows = step.n_decode * self.n_heads * pieces
             part_o = torch.empty(rows * self.head_dim, dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty(rows * 2, dtype=torch.float32, device=qkv.device)
-            count = torch.empty(ctx.n_decode * self.n_heads, dtype=torch.int32, device=qkv.device)
+            count = torch.empty(step.n_decode * self.n_heads, dtype=torch.int32, device=qkv.device)
             ops.attn_decode_even_bf16(qkv, attn, k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g],
-                                      ctx.decode_entries, ctx.n_decode, ctx.entry_q_start, ctx.entry_q_len,
+                                      step.decode_entries, step.n_decode, ctx.entry_q_start, ctx.entry_q_len,
                                       ctx.entry_ctx_start, part_o, part_ml, count, self.n_heads, self.n_kv, self.head_dim,
                                       self.scale, self.window, pieces)
             return
-        n_splits = ops.attn_decode_splits(ctx.n_decode, self.n_heads, self.n_kv, self.head_dim, max_keys)
+        n_splits = ops.attn_decode_splits(step.n_decode, self.n_heads, self.n_kv, self.head_dim, max_keys)
         part_o = part_ml = None
         if n_splits > 1:
-            rows = ctx.n_decode * self.n_heads * n_splits
+            rows = step.n_decode * self.n_heads * n_splits
             part_o = torch.empty(rows * self.head_dim, dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty(rows * 2, dtype=torch.float32, device=qkv.device)
-        meta = (k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g], ctx.decode_entries, ctx.n_decode,
+        meta = (k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g], step.decode_entries, step.n_decode,
                 ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start, part_o, part_ml,
                 self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, n_splits)
         if prep is None:

@@ -17,13 +17,34 @@ from ..weights.loader import WeightSpec
 
 
 @dataclass(frozen=True)
-class KVNeed:
-    """Keys and values in pages: per token ``n_kv_heads * head_dim`` keys and as
-    many values; ``window`` None = every key is kept, w = only the last w."""
+class CacheStream:
+    """One tensor that a mixer keeps per token in the paged cache: ``heads``
+    vectors of ``width`` elements.  Within a page a stream lies as
+    ``[head][slot][width]``, so one head's vectors of a page are contiguous."""
 
-    n_kv_heads: int
-    head_dim: int
+    name: str
+    heads: int
+    width: int
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """What a mixer keeps per token in pages: one or more streams (keys and
+    values for attention; a single latent vector for a mixer that caches
+    one), and for how long: ``window`` None = every token is kept, w = only
+    the last w.  Runs whose mixers ask for equal needs share a cache group."""
+
+    streams: Tuple[CacheStream, ...]
     window: Optional[int] = None
+
+    @classmethod
+    def keys_and_values(cls, n_kv_heads: int, head_dim: int, window: Optional[int] = None) -> "KVNeed":
+        """``n_kv_heads * head_dim`` keys and as many values per token."""
+        return cls((CacheStream("k", n_kv_heads, head_dim), CacheStream("v", n_kv_heads, head_dim)), window)
+
+    @property
+    def elements_per_token(self) -> int:
+        return sum(s.heads * s.width for s in self.streams)
 
 
 @dataclass(frozen=True)
@@ -47,7 +68,33 @@ class PartialSums:
 
 class Part:
     """Base of all parts.  ``params`` are the PartSpec's parameters, ``prefix``
-    the weight-name prefix of the enclosing layer ("" at model level)."""
+    the weight-name prefix of the enclosing layer ("" at model level).
+
+    Interfaces by family (``x`` = ``[N, hidden]`` rows of the step's flattened
+    tokens, ``ctx`` = the step's :class:`~inferflux_b200.engine.batch.StepContext`):
+
+    * ``mixer``: ``forward(x, ctx, run, position) -> Tensor | PartialSums``.
+      ``run`` is the :class:`RunInfo` of this execution of the layer (its cache
+      group and index, its state tensors); ``position`` is whatever the position
+      encoding named by the layer returned from ``prepare`` for this step, or
+      None.
+    * ``feed_forward``: ``forward(x, ctx) -> Tensor | PartialSums``.
+    * ``norm``: ``forward(residual, delta, out=None, rows=None) -> Tensor``:
+      adds ``delta`` (tensor, PartialSums or None) into the float32 residual
+      unless ``rows`` selects rows, returns the normed rows.
+    * ``position``: ``prepare(ctx) -> object``, once per step for all layers.
+      The contract between a position encoding and the mixers that consume it
+      is the type of that object.  The built-in ``gqa_attention`` takes a pair
+      ``(cos, sin)`` of float32 ``[N, r/2]`` tensors, ``r <= head_dim`` even,
+      and rotates the first ``r`` dimensions of every query and key head in
+      split-half pairs ``(i, i + r/2)``; any position part that returns such a
+      pair serves it.  A mixer with another idea of position defines its own
+      object and says so in its docstring.
+    * ``embedding``: ``forward(token_ids) -> float32 [N, hidden]``;
+      ``lm_head``: ``forward(x) -> float32 [rows, vocab]``.
+
+    Any part may describe the step for its kernels (:meth:`describe_step`).
+    """
 
     family = ""
 
@@ -79,6 +126,31 @@ class Part:
     @classmethod
     def state_needs(cls, params: Dict[str, Any]) -> List[StateNeed]:
         return []
+
+    # -- the step -------------------------------------------------------
+    #: Parts with the same key share one description per step (the key names the
+    #: kind of description, e.g. the tile lists of one family of kernels); None =
+    #: the part needs none.
+    describe_key: Optional[str] = None
+
+    def describe_step(self, layout, put) -> object:
+        """Per-step metadata for this part's kernels, derived on the host from
+        ``layout`` (:class:`~inferflux_b200.engine.batch.StepLayout`: how many
+        tokens each entry brings and how many it has cached).  ``put(values)``
+        appends int32 values to the step's metadata (one host-to-device copy for
+        the whole step) and returns their device view.  The result is kept in
+        ``ctx.extras[describe_key]``.  Called once per step and key, before the
+        copy; in a captured step of single tokens the copy is repeated with new
+        token ids, positions and block tables only, so what this writes for such
+        a step may depend on the number of entries and on :meth:`step_shape`
+        alone."""
+        return None
+
+    def step_shape(self, layout) -> tuple:
+        """What, beyond the number of entries and the width of the block tables,
+        decides which kernels this part launches in a step of single tokens (it
+        becomes part of the key under which such steps are captured)."""
+        return ()
 
 
 @dataclass

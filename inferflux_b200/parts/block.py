@@ -15,7 +15,7 @@ transformer_forward.cu:2054-2077).
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 
@@ -24,13 +24,19 @@ from .base import RunInfo
 
 
 class PreNormBlock:
-    family = "arrangement"
+    """An arrangement declares its roles (role -> family of the part that fills
+    it) and is built from the layer's parts by role; ``optional_roles`` may be
+    left out of a layer."""
 
-    def __init__(self, mixer, mixer_norm, feed_forward, feed_forward_norm, position_name: Optional[str]):
-        self.mixer = mixer
-        self.mixer_norm = mixer_norm
-        self.feed_forward = feed_forward
-        self.feed_forward_norm = feed_forward_norm
+    family = "arrangement"
+    roles = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm"}
+    optional_roles = frozenset()
+
+    def __init__(self, parts: Dict[str, object], position_name: Optional[str]):
+        self.mixer = parts["mixer"]
+        self.mixer_norm = parts["mixer_norm"]
+        self.feed_forward = parts["feed_forward"]
+        self.feed_forward_norm = parts["feed_forward_norm"]
         self.position_name = position_name
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx, run: RunInfo) -> torch.Tensor:

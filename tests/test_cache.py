@@ -29,7 +29,7 @@ def test_pool_alloc_free_reuse():
 
 
 def test_block_tables_grow_by_pages():
-    kv = KVCacheManager([KVNeed(2, 16)], [8], 16)
+    kv = KVCacheManager([KVNeed.keys_and_values(2, 16)], [8], 16)
     kv.add_request("a")
     assert kv.pages_needed("a", 1) == [1] and kv.pages_needed(None, 33) == [3]
     kv.reserve("a", 17)
@@ -47,7 +47,7 @@ def test_block_tables_grow_by_pages():
 
 
 def test_failed_reservation_takes_nothing():
-    kv = KVCacheManager([KVNeed(2, 16), KVNeed(2, 16, window=8)], [10, 2], 4)
+    kv = KVCacheManager([KVNeed.keys_and_values(2, 16), KVNeed.keys_and_values(2, 16, window=8)], [10, 2], 4)
     kv.add_request("a")
     with pytest.raises(OutOfPages) as e:
         kv.reserve("a", 12)                      # group 1 has 2 pages, 3 are needed
@@ -58,7 +58,7 @@ def test_failed_reservation_takes_nothing():
 
 def test_window_gives_pages_back():
     w, ps = 10, 4
-    kv = KVCacheManager([KVNeed(1, 16), KVNeed(1, 16, window=w)], [64, 64], ps)
+    kv = KVCacheManager([KVNeed.keys_and_values(1, 16), KVNeed.keys_and_values(1, 16, window=w)], [64, 64], ps)
     kv.add_request("a")
     length = 0
     for n in (7, 1, 1, 9, 2, 30, 1, 1, 1):
@@ -79,7 +79,7 @@ def test_window_gives_pages_back():
 
 def test_random_request_orders_lose_nothing():
     rng = random.Random(0)
-    needs = [KVNeed(2, 16), KVNeed(1, 32, window=24)]
+    needs = [KVNeed.keys_and_values(2, 16), KVNeed.keys_and_values(1, 32, window=24)]
     for trial in range(30):
         ps = rng.choice([4, 16, 64])
         pages = [rng.randint(6, 40), rng.randint(6, 40)]
@@ -136,7 +136,7 @@ def test_state_slots():
 
 def test_table_stamp_changes_with_the_tables():
     """The stamp tells a holder of a copy of the block tables whether it is still right."""
-    kv = KVCacheManager([KVNeed(2, 16), KVNeed(2, 16, window=20)], [8, 8], 16)
+    kv = KVCacheManager([KVNeed.keys_and_values(2, 16), KVNeed.keys_and_values(2, 16, window=20)], [8, 8], 16)
     kv.add_request("a")
     s0 = kv.table_stamp("a")
     kv.reserve("a", 10)

@@ -62,8 +62,9 @@ def test_registry_by_architecture_or_model_type():
 def test_spec_is_data_per_layer():
     spec = build_spec(Qwen2Config.from_dict(TINY_E))
     assert len(spec.layers) == 3 and [r.layer for r in spec.schedule] == [0, 1, 2]
-    assert [l.mixer.params["window"] for l in spec.layers] == [None, 40, 40]
-    assert spec.layers[0].mixer.kind == "gqa_attention" and spec.layers[0].feed_forward.kind == "swiglu"
+    assert [l.part("mixer").params["window"] for l in spec.layers] == [None, 40, 40]
+    assert spec.layers[0].part("mixer").kind == "gqa_attention" and spec.layers[0].part("feed_forward").kind == "swiglu"
+    assert sorted(spec.layers[0].parts) == ["feed_forward", "feed_forward_norm", "mixer", "mixer_norm"]
     m = Model(spec, torch.float32, "cpu")
     # layers with and without a window are cache groups of their own
     assert [n.window for n in m.kv_needs] == [None, 40] and m.runs_per_group == [1, 2]
@@ -228,11 +229,11 @@ def test_another_architecture_can_be_registered():
 
     def build(cfg):
         norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=cfg.width, eps=1e-5))
-        layer = LayerSpec("blocks.0", "prenorm",
-                          PartSpec("gqa_attention", dict(name="attn", hidden=cfg.width, n_heads=2, n_kv_heads=1,
-                                                         head_dim=16, qkv_bias=False, o_bias=True, window=None)),
-                          norm("n1"), PartSpec("swiglu", dict(name="ff", hidden=cfg.width, intermediate=48)),
-                          norm("n2"), position=None)
+        layer = LayerSpec("blocks.0", "prenorm", dict(
+            mixer=PartSpec("gqa_attention", dict(name="attn", hidden=cfg.width, n_heads=2, n_kv_heads=1,
+                                                 head_dim=16, qkv_bias=False, o_bias=True, window=None)),
+            mixer_norm=norm("n1"), feed_forward=PartSpec("swiglu", dict(name="ff", hidden=cfg.width, intermediate=48)),
+            feed_forward_norm=norm("n2")), position=None)
         return ModelSpec("ToyLM", cfg.width, 50, 64, PartSpec("token_embedding", dict(name="emb", vocab=50, hidden=cfg.width)),
                          norm("final"), PartSpec("linear_head", dict(name="head", vocab=50, hidden=cfg.width, tied_to=None)),
                          {}, [layer], [Run(0)])

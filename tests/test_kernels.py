@@ -208,7 +208,7 @@ def test_rope_and_kv_write(ops, dtype, nh, nkv, hd, rot, ps):
 def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, fast, umma=False):
     """entries: list of (cached tokens, new tokens).  Builds a paged cache with
     scattered pages, runs the kernel(s) and the reference."""
-    from inferflux_b200.engine.batch import CHUNK_TILE, QUERY_TILE
+    from inferflux_b200.parts.attention import CHUNK_TILE, QUERY_TILE
     g = torch.Generator().manual_seed(seed)
     n = sum(q for _, q in entries)
     total_pages = sum((c + q + ps - 1) // ps for c, q in entries) + 3

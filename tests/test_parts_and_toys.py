@@ -1,7 +1,9 @@
 """Each part alone against the plain implementation, and the generality of
 the layer description: a toy mixer with per-request state of its own that is
 defined here, registered, built into a model and stepped without any change to
-the package; a layer that runs twice; a layer that reads another run's cache."""
+the package; a layer that runs twice; a layer that reads another run's cache; a
+routed feed-forward; a position encoding with weights; a block with four norms;
+a mixer that caches one latent vector per token instead of keys and values."""
 from __future__ import annotations
 
 import math
@@ -97,11 +99,11 @@ def test_embedding_and_head_alone(dtype):
 def _one_layer_spec(hidden, nh, nkv, hd, window=None, extra_layers=(), schedule=None):
     from inferflux_b200.config.spec import LayerSpec, ModelSpec, PartSpec, Run
     norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
-    attn = LayerSpec("layers.0", "prenorm",
-                     PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
-                                                    qkv_bias=True, o_bias=False, window=window)),
-                     norm("n1"), PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=2 * hidden)), norm("n2"),
-                     position="rope")
+    attn = LayerSpec("layers.0", "prenorm", dict(
+        mixer=PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                                             qkv_bias=True, o_bias=False, window=window)),
+        mixer_norm=norm("n1"), feed_forward=PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=2 * hidden)),
+        feed_forward_norm=norm("n2")), position="rope")
     layers = [attn, *extra_layers]
     return ModelSpec("Toy", hidden, 50, 512, PartSpec("token_embedding", dict(name="emb", vocab=50, hidden=hidden)),
                      norm("final"), PartSpec("linear_head", dict(name="head", vocab=50, hidden=hidden, tied_to=None)),
@@ -194,11 +196,13 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     _register_running_mean()
     hidden = 48
     norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
-    toy = LayerSpec("layers.1", "prenorm", PartSpec("running_mean", dict(name="rm", hidden=hidden)), norm("n1"),
-                    PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=80)), norm("n2"), position=None)
+    toy = LayerSpec("layers.1", "prenorm", dict(
+        mixer=PartSpec("running_mean", dict(name="rm", hidden=hidden)), mixer_norm=norm("n1"),
+        feed_forward=PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=80)), feed_forward_norm=norm("n2")),
+        position=None)
     spec = _one_layer_spec(hidden, 3, 1, 16, extra_layers=[toy])
     model, runner, w = _build(spec, dtype, 21)
-    assert model.state_needs[1][0].name == "sum" and model.kv_needs[0].n_kv_heads == 1
+    assert model.state_needs[1][0].name == "sum" and model.kv_needs[0].streams[0].heads == 1
     assert runner.state_storage.of_run(1)["sum"].shape == (4, hidden)
 
     def plain_forward(tokens):
@@ -243,11 +247,11 @@ def test_layer_runs_twice_and_shared_cache(dtype):
     from inferflux_b200.engine import StepEntry
     hidden, nh, nkv, hd = 64, 4, 2, 16
     norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
-    shared = LayerSpec("layers.1", "prenorm",
-                       PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
-                                                      qkv_bias=False, o_bias=False, window=None, kv_shared=True)),
-                       norm("n1"), PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=96)), norm("n2"),
-                       position="rope")
+    shared = LayerSpec("layers.1", "prenorm", dict(
+        mixer=PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                                             qkv_bias=False, o_bias=False, window=None, kv_shared=True)),
+        mixer_norm=norm("n1"), feed_forward=PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=96)),
+        feed_forward_norm=norm("n2")), position="rope")
     # run 0: layer 0; run 1: layer 1 reading run 0's keys and values; run 2: layer 0 again (a cache of its own)
     spec = _one_layer_spec(hidden, nh, nkv, hd, extra_layers=[shared], schedule=[Run(0), Run(1, cache_of=0), Run(0)])
     model, runner, w = _build(spec, dtype, 31)
@@ -338,11 +342,11 @@ def test_toy_routed_feed_forward_is_registered_built_and_stepped(dtype):
     _register_top2_experts()
     hidden, experts, inter = 48, 5, 24
     norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
-    routed = LayerSpec("layers.1", "prenorm",
-                       PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=3, n_kv_heads=1, head_dim=16,
-                                                      qkv_bias=True, o_bias=False, window=None)), norm("n1"),
-                       PartSpec("top2_experts", dict(name="moe", hidden=hidden, intermediate=inter, experts=experts)),
-                       norm("n2"), position="rope")
+    routed = LayerSpec("layers.1", "prenorm", dict(
+        mixer=PartSpec("gqa_attention", dict(name="attn", hidden=hidden, n_heads=3, n_kv_heads=1, head_dim=16,
+                                             qkv_bias=True, o_bias=False, window=None)), mixer_norm=norm("n1"),
+        feed_forward=PartSpec("top2_experts", dict(name="moe", hidden=hidden, intermediate=inter, experts=experts)),
+        feed_forward_norm=norm("n2")), position="rope")
     spec = _one_layer_spec(hidden, 3, 1, 16, extra_layers=[routed])
 
     def plain_forward(w, tokens):
@@ -452,3 +456,134 @@ def test_toy_position_encoding_is_registered_built_and_stepped(dtype):
         outs.append(runner.step([StepEntry("c", toks[pos:pos + n], list(range(n)))]).clone())
         pos += n
     assert _rel(torch.cat(outs), want) < TOL[dtype]
+
+
+# ------------------------- a block with four norms around a mixer that caches one latent vector per token
+def _register_sandwich_and_latent():
+    """Two toys defined in this test.  ``sandwich``: an arrangement with a norm
+    before and a norm after each branch, so six roles instead of four.
+    ``latent_attention``: a mixer that keeps one vector of ``latent`` elements
+    per token in the paged cache (a single stream, no keys and values) and
+    attends over those vectors."""
+    from inferflux_b200.config import register_part
+    from inferflux_b200.parts.base import CacheStream, KVNeed, Part, PartialSums
+    from inferflux_b200.weights.loader import MATRIX, WeightSpec
+
+    def dense(y):
+        return y.tensor.sum(0) if isinstance(y, PartialSums) else y.float()
+
+    class SandwichBlock:
+        family = "arrangement"
+        roles = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm", "feed_forward": "feed_forward",
+                 "feed_forward_norm": "norm", "feed_forward_post_norm": "norm"}
+        optional_roles = frozenset()
+
+        def __init__(self, parts, position_name):
+            self.p, self.position_name = parts, position_name
+
+        def forward(self, residual, delta, ctx, run):
+            p = self.p
+            x = p["mixer_norm"].forward(residual, delta)
+            position = ctx.position_tables.get(self.position_name) if self.position_name else None
+            a = p["mixer_post_norm"].forward(dense(p["mixer"].forward(x, ctx, run, position)), None)
+            x2 = p["feed_forward_norm"].forward(residual, a)
+            return p["feed_forward_post_norm"].forward(dense(p["feed_forward"].forward(x2, ctx)), None)
+
+    class LatentAttention(Part):
+        family = "mixer"
+
+        @classmethod
+        def weight_specs(cls, params, prefix):
+            h, l = int(params["hidden"]), int(params["latent"])
+            n = lambda leaf: cls.full_name(prefix, params, leaf)
+            return [WeightSpec(n("down.weight"), (l, h), MATRIX, std=0.3), WeightSpec(n("up.weight"), (h, l), MATRIX, std=0.3)]
+
+        @classmethod
+        def kv_need(cls, params):
+            return KVNeed((CacheStream("latent", 1, int(params["latent"])),), None)
+
+        def load(self, tensors):
+            n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+            self.down, self.up = tensors.pop(n("down.weight")).float(), tensors.pop(n("up.weight")).float()
+
+        def forward(self, x, ctx, run, position):
+            g, ps, l = run.kv_group, ctx.page_size, int(self.params["latent"])
+            views, stride = ctx.kv.stream_views(g, run.kv_index)
+            pool = ctx.kv.pools[g]
+            cache = torch.as_strided(pool, (pool.shape[0], ps, l), (stride, l, 1), views["latent"].storage_offset())
+            slots = ctx.slot_maps[g].long()
+            cache[slots // ps, slots % ps] = (x.float() @ self.down.T).to(cache.dtype)
+            out = torch.empty((x.shape[0], self.up.shape[0]), dtype=torch.float32, device=x.device)
+            row = 0
+            for e, (entry, start) in enumerate(zip(ctx.entries, ctx.ctx_starts)):
+                n, total = len(entry.tokens), start + len(entry.tokens)
+                table = ctx.block_tables[g][e, :(total + ps - 1) // ps].long()
+                lat = cache[table].reshape(-1, l)[:total].float()
+                s = lat[start:] @ lat.T / math.sqrt(l)
+                keys = torch.arange(total, device=x.device)[None, :]
+                s = s.masked_fill(keys > torch.arange(start, total, device=x.device)[:, None], float("-inf"))
+                out[row:row + n] = torch.softmax(s, -1) @ lat @ self.up.T
+                row += n
+            return out.to(x.dtype)
+
+    register_part("arrangement", "sandwich", SandwichBlock)
+    register_part("mixer", "latent_attention", LatentAttention)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_block_with_four_norms_and_a_latent_cache(dtype):
+    from inferflux_b200.config.spec import LayerSpec, PartSpec
+    from inferflux_b200.engine import StepEntry
+    _register_sandwich_and_latent()
+    hidden, latent = 64, 24
+    norm = lambda name: PartSpec("rmsnorm", dict(name=name, hidden=hidden, eps=1e-6))
+    toy = LayerSpec("layers.1", "sandwich", dict(
+        mixer=PartSpec("latent_attention", dict(name="lat", hidden=hidden, latent=latent)), mixer_norm=norm("n1"),
+        mixer_post_norm=norm("p1"), feed_forward=PartSpec("swiglu", dict(name="mlp", hidden=hidden, intermediate=96)),
+        feed_forward_norm=norm("n2"), feed_forward_post_norm=norm("p2")), position=None)
+    spec = _one_layer_spec(hidden, 4, 2, 16, extra_layers=[toy])
+    # a layer that lists a role its arrangement does not have, or lacks one, is refused with both named
+    from inferflux_b200.engine import Model
+    import dataclasses
+    bad = dataclasses.replace(toy, arrangement="prenorm")
+    with pytest.raises(ValueError, match="mixer_post_norm"):
+        Model(_one_layer_spec(hidden, 4, 2, 16, extra_layers=[bad]), dtype, DEV)
+    model, runner, w = _build(spec, dtype, 91)
+    # two cache groups: keys and values of layer 0, one latent vector a token of layer 1
+    assert [[s.name for s in n.streams] for n in model.kv_needs] == [["k", "v"], ["latent"]]
+    assert runner.kv_storage.pools[1].shape[2] == 16 * latent and "layers.1.p2.weight" in w
+
+    def plain_forward(tokens):
+        t = len(tokens)
+        x = plain.embed(w["emb.weight"], tokens)
+        h = plain.rms_norm(x, w["layers.0.n1.weight"], 1e-6)
+        x = x + plain.attention_block(h, {k.replace("layers.0.attn", "a"): v for k, v in w.items()}, "a",
+                                      torch.arange(t), 4, 2, 16, 10000.0, None)
+        x = x + plain.mlp_block(plain.rms_norm(x, w["layers.0.n2.weight"], 1e-6), w, "layers.0.mlp")
+        c = plain.rms_norm(x, w["layers.1.n1.weight"], 1e-6) @ w["layers.1.lat.down.weight"].T
+        s = (c @ c.T / math.sqrt(latent)).masked_fill(torch.arange(t)[None, :] > torch.arange(t)[:, None], float("-inf"))
+        a = torch.softmax(s, -1) @ c @ w["layers.1.lat.up.weight"].T
+        x = x + plain.rms_norm(a, w["layers.1.p1.weight"], 1e-6)
+        f = plain.mlp_block(plain.rms_norm(x, w["layers.1.n2.weight"], 1e-6), w, "layers.1.mlp")
+        x = x + plain.rms_norm(f, w["layers.1.p2.weight"], 1e-6)
+        return plain.rms_norm(x, w["final.weight"], 1e-6) @ w["head.weight"].T
+
+    toks_a = torch.randint(0, 50, (40,), generator=torch.Generator().manual_seed(11)).tolist()
+    toks_b = torch.randint(0, 50, (23,), generator=torch.Generator().manual_seed(12)).tolist()
+    want_a, want_b = plain_forward(toks_a), plain_forward(toks_b)
+    got = runner.step([StepEntry("w", toks_a, list(range(40)))])
+    runner.end("w")
+    assert _rel(got, want_a) < TOL[dtype]
+    outs = {"a": [], "b": []}
+    plan = [[("a", 0, 7), ("b", 0, 2)], [("a", 7, 1), ("b", 2, 20)], [("a", 8, 31)], [("a", 39, 1), ("b", 22, 1)]]
+    for step in plan:
+        entries = [StepEntry(r, (toks_a if r == "a" else toks_b)[lo:lo + n], list(range(n))) for r, lo, n in step]
+        logits = runner.step(entries)
+        row = 0
+        for r, lo, n in step:
+            outs[r].append(logits[row:row + n].clone())
+            row += n
+    assert _rel(torch.cat(outs["a"]), want_a) < TOL[dtype]
+    assert _rel(torch.cat(outs["b"]), want_b) < TOL[dtype]
+    runner.end("a"), runner.end("b")
+    runner.kv.check()

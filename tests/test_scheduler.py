@@ -18,7 +18,7 @@ class FakeCache(CacheView):
     """The real page and slot bookkeeping without any device memory."""
 
     def __init__(self, pages, page_size=16, max_seqs=8, needs=None):
-        self.kv = KVCacheManager(needs or [KVNeed(1, 16)], pages, page_size)
+        self.kv = KVCacheManager(needs or [KVNeed.keys_and_values(1, 16)], pages, page_size)
         self.slots = StateSlotManager(max_seqs)
 
     def pages_needed(self, rid, n_new):
@@ -224,7 +224,7 @@ def test_token_slice_equals_the_slice_of_all_tokens():
 
 def test_contexts_skewed_rule():
     """Which steps of single tokens count as having contexts of very different lengths."""
-    from inferflux_b200.engine.batch import contexts_skewed
+    from inferflux_b200.parts.attention import contexts_skewed
     assert not contexts_skewed([4096] * 8)                     # equal
     assert not contexts_skewed([4096])                         # one request
     assert not contexts_skewed([900, 10, 10, 10])              # nothing long
