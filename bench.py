@@ -106,6 +106,28 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
+def reference_arm() -> int:
+    """The reference as a whole cannot run here: it is a C++/CMake server that pip cannot install, and its
+    forward does not compile offline (it includes llama.h of a submodule that is empty in the snapshot).  The
+    line says so.  What of the reference does compile, its own attention kernels, is timed at the benchmark's
+    shapes and added under "kernels" as the kernels to beat; they are no end-to-end number."""
+    line = {"impl": "reference", "unavailable":
+            "vjsingh1984/inferflux is a C++/CMake server with no setup.py or pyproject.toml (pip: 'Directory is not "
+            "installable'), and its forward includes llama.h of an empty submodule, so it cannot be built offline"}
+    try:
+        import torch
+        from baseline import reference_kernels
+        if torch.cuda.is_available() and reference_kernels.source_root() is not None:
+            from baseline.reference_kernels import yardsticks
+            line["kernels"] = yardsticks.measure()
+            line["kernels_note"] = ("the reference's own attention kernels (flash_attention.cu, compiled unmodified "
+                                    "for sm_100a), one layer of the Qwen2.5-7B sizes; not an end-to-end figure")
+    except Exception as e:                                   # the arm must still print its line
+        line["kernels_error"] = f"{type(e).__name__}: {e}"[:300]
+    print(json.dumps(line))
+    return 0
+
+
 def mixed_workload(args) -> int:
     """N requests, prompts uniform in 128..2,048 tokens, 256 greedy output tokens each, all handed to
     Engine.generate at once: the scheduler cuts prompts into portions beside the decoding requests."""
@@ -156,10 +178,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "vjsingh1984/inferflux is a C++/CMake server with no setup.py or pyproject.toml: "
-                          "pip reports 'Directory is not installable' offline"}))
-        return 0
+        return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -225,19 +244,30 @@ def main() -> int:
         return ms, launches
 
     greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
-    clocks = ClockSampler()
+
+    def clocked(fn, *a):
+        """fn(*a) with the GPU's clocks and throttle reasons sampled meanwhile."""
+        sampler = ClockSampler()
+        sampler.start()
+        res = fn(*a)
+        return res, sampler.stop()
+
+    def decode_bytes(b, steps):
+        """What a decode step at batch b must read: every weight once and the live requests' cache
+        (at the mean context of the timed steps)."""
+        return weight_bytes + b * (ctx - steps // 2) * kv_bytes_per_token
 
     # ---- headline: decode at `batch`, device-timed
-    clocks.start()
-    ms_step, launches = time_decode(batch, args.steps, warmup)
-    clock_rec = clocks.stop()
+    (ms_step, launches), clock_rec = clocked(time_decode, batch, args.steps, warmup)
     value = batch / (ms_step / 1e3)
-    step_bytes = weight_bytes + batch * (ctx - args.steps // 2) * kv_bytes_per_token
+    step_bytes = decode_bytes(batch, args.steps)
     achieved = step_bytes / (ms_step / 1e3) / 1e9
 
-    # ---- end to end: the Python entry point, host tokens in, host tokens out
-    prompts = [torch.randint(0, vocab, (ctx - args.steps - warmup - 16,), generator=gen).tolist() for _ in range(batch)]
-    params = SamplingParams(temperature=0.0, max_tokens=args.steps + warmup + 16, ignore_eos=True)
+    # ---- end to end: the Python entry point, host tokens in, host tokens out; at least 200 steps, so that
+    # one stall of the host does not decide the figure
+    e2e_steps = max(args.steps, 200)
+    prompts = [torch.randint(0, vocab, (ctx - e2e_steps - warmup - 16,), generator=gen).tolist() for _ in range(batch)]
+    params = SamplingParams(temperature=0.0, max_tokens=e2e_steps + warmup + 16, ignore_eos=True)
     for p in prompts:
         eng.add_request(p, params)
     while any(not r.decoding for r in eng.scheduler.running) or eng.scheduler.waiting:
@@ -249,18 +279,23 @@ def main() -> int:
     t0 = time.perf_counter()
     e2e_ev[0].record()
     n_e2e = 0
-    while eng.has_work() and n_e2e < args.steps:
+    e2e_clocks = ClockSampler()
+    e2e_clocks.start()
+    while eng.has_work() and n_e2e < e2e_steps:
         eng.step()                                   # plan, H2D metadata, run, sample, D2H ids
         n_e2e += 1
     e2e_ev[1].record()
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / max(1, n_e2e)
     e2e_dev_ms = e2e_ev[0].elapsed_time(e2e_ev[1]) / max(1, n_e2e)
+    e2e_clock_rec = e2e_clocks.stop()
     h2d = runner.slab._used * 4
     while eng.has_work():
         eng.step()
     e2e = {"value": round(batch / (e2e_ms / 1e3), 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-           "device_ms_per_step": round(e2e_dev_ms, 4),
+           "device_ms_per_step": round(e2e_dev_ms, 4), "steps": n_e2e,
+           "mean_context": ctx - 16 - e2e_steps // 2, "sm_mhz": e2e_clock_rec["sm_mhz"],
+           "reasons": e2e_clock_rec["reasons"],
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
 
     out = {
@@ -287,26 +322,36 @@ def main() -> int:
             runner.step([StepEntry(f"pw{i}", toks, [T - 1])])
             runner.end(f"pw{i}")
         torch.cuda.synchronize()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         reps = 5
-        ev[0].record()
-        for i in range(reps):
-            runner.step([StepEntry(f"p{i}", toks, [T - 1])])
-            runner.end(f"p{i}")
-        ev[1].record()
-        torch.cuda.synchronize()
-        pms = ev[0].elapsed_time(ev[1]) / reps
+
+        def time_prefill():
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            ev[0].record()
+            for i in range(reps):
+                runner.step([StepEntry(f"p{i}", toks, [T - 1])])
+                runner.end(f"p{i}")
+            ev[1].record()
+            torch.cuda.synchronize()
+            return ev[0].elapsed_time(ev[1]) / reps
+        pms, pclock = clocked(time_prefill)
         lin_flops = 2 * T * layers * ((nh + 2 * nkv) * hd * h + nh * hd * h + 3 * h * inter) + 2 * vocab * h
         attn_flops = layers * 2 * 2 * nh * hd * (T * (T + 1) // 2)
         pflops = lin_flops + attn_flops
         out["prefill"] = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
                           "frac": round(pflops / (pms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
                           "frac_sustained": round(pflops / (pms / 1e3) / 1e12 / peaks["bf16_tflops_sustained"], 4),
-                          "tflop": round(pflops / 1e12, 3)}
+                          "tflop": round(pflops / 1e12, 3), "sm_mhz": pclock["sm_mhz"], "reasons": pclock["reasons"]}
         points = {}
         for b in (1, 64):
-            ms_b, _ = time_decode(b, min(args.steps, 32), 3)
+            steps_b = min(args.steps, 32)
+            (ms_b, _), bclock = clocked(time_decode, b, steps_b, 3)
+            gbs = decode_bytes(b, steps_b) / (ms_b / 1e3) / 1e9
             points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 2)
+            points[f"decode_b{b}_ms"] = round(ms_b, 4)
+            points[f"decode_b{b}_gbs"] = round(gbs, 1)
+            points[f"decode_b{b}_frac"] = round(gbs / peaks["hbm_gbs"], 4)
+            points[f"decode_b{b}_sm_mhz"] = bclock["sm_mhz"]
+            points[f"decode_b{b}_reasons"] = ",".join(bclock["reasons"])
         out["points"] = points
     print(json.dumps(out))
     return 0
