@@ -10,12 +10,15 @@
 //
 // One block takes 128 consecutive new tokens of one request and one head.
 //   * Q (128 x 128), and per step a tile of 64 keys and 64 values, lie in shared
-//     memory in the 128-byte-swizzle layouts the tensor core reads (written with
-//     16-byte cp.async from the paged cache; two stages, loads run a tile ahead).
+//     memory in the 128-byte-swizzle layouts the tensor core reads.  Q is written
+//     once with 16-byte cp.async.  Keys and values come from the paged cache by
+//     TMA (cp.async.bulk.tensor over a 4-D map (dim, slot, kv head, page) of the
+//     run's pages): one box per page and 64-dim panel, issued by one thread of a
+//     warp of its own, three key stages and two value stages ahead of their use,
+//     with mbarriers both ways (a stage has landed / a stage has been read).
 //   * S = Q K^T is one chain of 8 tcgen05.mma (M 128, N 64, K 16) into 64
 //     columns of tensor memory.  Thread r then owns row r: it reads its scores
-//     with tcgen05.ld (once for the maximum, once more for the exponentials, 32
-//     at a time, so few registers are live), keeps the running maximum and sum,
+//     with tcgen05.ld, keeps the running maximum and sum,
 //     and writes P = exp(s - max) as packed bfloat16 back into tensor memory
 //     (tcgen05.st), from where the next MMA takes it as its A operand.
 //   * O += P V is 4 tcgen05.mma (M 128, N 128, K 16) with V read in its natural [key][dim] layout
@@ -25,11 +28,15 @@
 //     MMAs of the next tile's scores are issued right behind this tile's P V, and one commit covers both.
 // A fifth warp issues the MMAs (one thread): the softmax threads arrive on an mbarrier when their row of
 // P is written, and wait on the mbarrier that tcgen05.commit arrives on for the next scores, so they never
-// wait for the issuing.  Two blocks fit an SM (96 KB of shared memory, 256 columns of
+// wait for the issuing, nor (since the copies have a warp of their own) for memory.  Two blocks fit an SM
+// (112 KB of shared memory, 256 columns of
 // tensor memory each), so one block's softmax overlaps the other's MMAs.  Every
-// mbarrier wait is bounded: if one runs out the block sets *error_flag, waits
-// for its copies in flight, frees its tensor memory and returns.
+// mbarrier wait is bounded: if one runs out the block sets *error_flag, and
+// since every issued copy is waited for before the MMA that reads it, nothing is
+// in flight when the block frees its tensor memory and returns.
 #include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
 
 namespace {
 
@@ -127,7 +134,8 @@ struct UmmaMeta {
 // Shared memory (1024-byte aligned): Q 32 KB | K 3 x 16 KB | V 2 x 16 KB
 constexpr int SQ_BYTES = 2 * UM * 128, SKV_BYTES = 2 * UN * 128;
 constexpr int K_STAGES = 3, V_STAGES = 2;
-constexpr int U_THREADS = 160;   // four softmax warps (one thread per query row) and the warp that issues the MMAs
+// four softmax warps (one thread per query row), the warp that issues the MMAs, the warp that issues the copies
+constexpr int U_THREADS = 192;
 // Two blocks per SM: 2 x (1 KB static + 112 KB dynamic + 1 KB reserved) = 228 KB, all there is.  The dynamic
 // part is declared 1024-byte aligned, so it needs no slack for aligning the swizzled tiles by hand.
 constexpr int SMEM_UMMA = SQ_BYTES + (K_STAGES + V_STAGES) * SKV_BYTES;
@@ -135,39 +143,29 @@ constexpr int SMEM_UMMA = SQ_BYTES + (K_STAGES + V_STAGES) * SKV_BYTES;
 // columns) is written over the first half of the scores it was made from.
 constexpr unsigned TM_S = 0, TM_O = 128;
 
-// 64 keys (or values) starting at absolute key index key0 into one stage: row = key, two panels of 64
-// dims, 16-byte chunk c of a 128-byte row stored at c ^ (row & 7).  Keys and values of a tile are loaded
-// at different times (a key stage is free as soon as its scores are done), so each has its own call.
-__device__ __forceinline__ void load_rows64(unsigned sdst, const bf16* base, const PagedKV& kv, const int* bt,
-                                            int bt_first, int key0, int lo, int hi, int tid) {
-  const int r = tid >> 1, half = tid & 1;
-  const int key = key0 + r;
-  bool ok = key >= lo && key < hi;
-  size_t off = 0;
-  if (ok) {
-    const int page = bt[(key >> kv.page_shift) - bt_first];
-    ok = page >= 0;
-    if (ok) off = (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * UD;
-  }
-  const bf16* src = base + off;
-  const unsigned row = (unsigned)r * 128u;
-  const int sw = r & 7;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int c = j * 2 + half;                                 // 16-byte chunk of the 256-byte row
-    cp_async16_u(sdst + (unsigned)(c >> 3) * (UN * 128) + row + (unsigned)(((c & 7) ^ sw) << 4), src + c * 8, ok);
-  }
+// One TMA box of the paged cache into shared memory: 64 dims (one 128-byte panel row) x box_slots tokens of
+// one page and kv head, written in the 128-byte swizzle that the MMA descriptors expect (the swizzle goes by
+// the bits of the shared-memory address, so boxes of a few rows line up into one 64-row panel).  The first
+// coordinate is 0 or 64 elements, i.e. a multiple of 128 bytes.  A page of -1 (given back behind a window,
+// or beyond the request's last key) is outside the tensor and reads as zeros.  No multicast.
+__device__ __forceinline__ void tma_load_kv(unsigned dst, const CUtensorMap* map, int dim0, int slot0, int kvh, int page,
+                                            unsigned bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+               ::"r"(dst), "l"(map), "r"(dim0), "r"(slot0), "r"(kvh), "r"(page), "r"(bar) : "memory");
 }
 
 __global__ void __launch_bounds__(U_THREADS, 2)
 attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
-                         PagedKV kv, UmmaMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
-                         int n_heads, int n_kv, float scale, int window, int* __restrict__ error_flag,
-                         float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
+                         const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                         int page_size, int page_shift, UmmaMeta m, const int* __restrict__ tile_entry,
+                         const int* __restrict__ tile_q0, int n_heads, int n_kv, float scale, int window,
+                         int* __restrict__ error_flag, float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
   pdl_enter();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bar_s[2];          // per buffer of scores: the tensor core is done
   __shared__ __align__(8) unsigned long long bar_p[2];          // per buffer of scores: all 128 rows of P are written
+  __shared__ __align__(8) unsigned long long k_full[K_STAGES], k_free[K_STAGES];   // a key stage has landed / was read
+  __shared__ __align__(8) unsigned long long v_full[V_STAGES], v_free[V_STAGES];
   __shared__ unsigned tmem_slot;
   __shared__ int bt_s[BT_CACHE_U];
   const unsigned sbase = smem_addr(smem_raw);
@@ -186,8 +184,6 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int pos0 = m.entry_ctx_start[e] + q0;
   const int kvh = head / (n_heads / n_kv);
   const int* bt = m.block_tables + (size_t)e * m.bt_stride;
-  const bf16* kbase = (const bf16*)kv.k + (size_t)kvh * kv.head_stride;
-  const bf16* vbase = (const bf16*)kv.v + (size_t)kvh * kv.head_stride;
   const int kend = pos0 + rows;                                  // keys [.., kend) may be seen
   const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the first row may see
   // gridDim.z > 1: the key tiles are cut into n_splits consecutive parts, one block each; the parts leave
@@ -207,10 +203,12 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   }
 
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s[0])));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(&bar_s[1])));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;\n" ::"r"(smem_addr(&bar_p[0])));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;\n" ::"r"(smem_addr(&bar_p[1])));
+    auto init = [](unsigned long long* b, int count) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(b)), "r"(count));
+    };
+    init(&bar_s[0], 1), init(&bar_s[1], 1), init(&bar_p[0], 128), init(&bar_p[1], 128);
+    for (int i = 0; i < K_STAGES; ++i) init(&k_full[i], 1), init(&k_free[i], 1);
+    for (int i = 0; i < V_STAGES; ++i) init(&v_full[i], 1), init(&v_free[i], 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
@@ -219,7 +217,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   }
   int bt_first = 0;
   {
-    const int b0 = max(kfirst, t_begin * UN) >> kv.page_shift, b1 = (min(kend, (t_begin + n_t) * UN) - 1) >> kv.page_shift;
+    const int b0 = max(kfirst, t_begin * UN) >> page_shift, b1 = (min(kend, (t_begin + n_t) * UN) - 1) >> page_shift;
     if (b1 - b0 < BT_CACHE_U) {
       for (int i = tid; i <= b1 - b0; i += U_THREADS) bt_s[i] = bt[b0 + i];
       bt = bt_s;
@@ -227,67 +225,97 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     }
   }
   // Q: row r (token tok0 + r), two panels of 64 dims; rows beyond the portion are zero
-  for (int idx = tid; idx < UM * 16 && tid < 128; idx += 128) {  // copies are the softmax warps' business
+  for (int idx = tid; idx < UM * 16 && tid < 128; idx += 128) {  // the softmax warps copy it, once
     const int r = idx >> 4, c = idx & 15;
     const bool ok = r < rows;
     const bf16* src = q + (size_t)(tok0 + (ok ? r : 0)) * q_stride + (size_t)head * UD + c * 8;
     cp_async16_u(sq + (unsigned)(c >> 3) * (UM * 128) + (unsigned)r * 128u + (unsigned)(((c & 7) ^ (r & 7)) << 4), src, ok);
   }
+  if (tid < 128) {
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); // Q is visible to the tensor core
+  }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  __syncthreads();                                               // bt_s, barriers, tensor-memory address
+  __syncthreads();                                               // bt_s, barriers, tensor-memory address, Q
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem = tmem_slot;
-  const unsigned lane_base = (unsigned)(warp * 32) << 16;        // this warp's quarter of the 128 lanes
+  const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 lanes
   const unsigned tm_o = tmem + TM_O + lane_base;
 
-  constexpr unsigned IDESC_QK = umma_idesc(UM, UN, 0), IDESC_PV = umma_idesc(UM, UD, 1);
-  // S(t) = Q K(t)^T into the scores buffer t & 1, 8 steps of 16 dims (one thread); the commit that
-  // follows also covers every MMA issued before it
-  auto issue_qk = [&](int t) {
-    const unsigned sk = sk0 + (t % K_STAGES) * SKV_BYTES;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const unsigned long long da = umma_desc(sq + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
-      const unsigned long long db = umma_desc(sk + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
-      umma_f16(tmem + TM_S + (t & 1) * UN, da, db, IDESC_QK, k > 0);
+  // ---- the sixth warp: one thread copies the key and value tiles, a stage ahead of their use.  Key stage
+  // t % 3 is free once the scores of tile t - 3 are done, value stage t % 2 once P V of tile t - 2 is (the
+  // issuing thread commits onto k_free / v_free).  Order of the copies: K0 K1 V0 K2, then V(t) K(t+2).
+  if (warp == 5) {
+    bool copy_failed = false;
+    if ((tid & 31) == 0) {
+      const int box_slots = min(page_size, UN);                    // tokens per box: a page, or 64 of a longer page
+      auto copy_tile = [&](const CUtensorMap* map, unsigned sdst, int t, unsigned bar) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(SKV_BYTES) : "memory");
+        for (int b = 0; b * box_slots < UN; ++b) {
+          const int key = (t_begin + t) * UN + b * box_slots;
+          const int block = key >> page_shift;
+          int page = -1;                                           // boxes wholly outside [kfirst, kend) read as zeros
+          if (key < kend && key + box_slots > kfirst) page = bt[block - bt_first];
+          const int slot0 = key & (page_size - 1);
+          tma_load_kv(sdst + (unsigned)b * box_slots * 128u, map, 0, slot0, kvh, page, bar);
+          tma_load_kv(sdst + UN * 128 + (unsigned)b * box_slots * 128u, map, 64, slot0, kvh, page, bar);
+        }
+      };
+      auto copy_k = [&](int t) {
+        if (t >= n_t || copy_failed) return;
+        const int st = t % K_STAGES;
+        if (t >= K_STAGES && !mbar_wait_u(smem_addr(&k_free[st]), (unsigned)((t / K_STAGES - 1) & 1))) { copy_failed = true; return; }
+        copy_tile(&map_k, sk0 + st * SKV_BYTES, t, smem_addr(&k_full[st]));
+      };
+      auto copy_v = [&](int t) {
+        if (t >= n_t || copy_failed) return;
+        const int st = t % V_STAGES;
+        if (t >= V_STAGES && !mbar_wait_u(smem_addr(&v_free[st]), (unsigned)((t / V_STAGES - 1) & 1))) { copy_failed = true; return; }
+        copy_tile(&map_v, sv0 + st * SKV_BYTES, t, smem_addr(&v_full[st]));
+      };
+      copy_k(0), copy_k(1), copy_v(0), copy_k(2);
+      for (int t = 1; t < n_t && !copy_failed; ++t) copy_v(t), copy_k(t + 2);
     }
-    umma_commit(smem_addr(&bar_s[t & 1]));
-  };
-
-  // Copy groups, in this order: [Q, K0] [K1] [V0] [K2]; then in iteration i [K(i+3)] once the scores of tile
-  // i are done (that key stage is free) and [V(i+1)] once P V of tile i - 1 is done (that value stage is
-  // free).  At the barrier of iteration i "all but the newest two groups" covers V(i) and K(i+2).
-  auto load_k = [&](int t) {
-    if (t < n_t) load_rows64(sk0 + (t % K_STAGES) * SKV_BYTES, kbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
-    asm volatile("cp.async.commit_group;\n" ::);
-  };
-  auto load_v = [&](int t) {
-    if (t < n_t) load_rows64(sv0 + (t % V_STAGES) * SKV_BYTES, vbase, kv, bt, bt_first, (t_begin + t) * UN, kfirst, kend, tid);
-    asm volatile("cp.async.commit_group;\n" ::);
-  };
-  const bool softmax_warp = warp < 4;
-  if (softmax_warp) {
-    load_k(0);
-    load_k(1);
-    load_v(0);
-    load_k(2);
-    asm volatile("cp.async.wait_group 2;\n" ::: "memory");         // Q, K0 and K1 have landed
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); // ... and are visible to the tensor core
+    // Every copy that was issued is waited for by the issuing thread before its MMA, and the block ends
+    // only after the last MMA: nothing is in flight when this warp leaves.  (If a wait ran out, the two
+    // barriers below still hold the block together and the error is recorded.)
+    const int any = __syncthreads_or(copy_failed);
+    __syncthreads();
+    if (any && tid == 160) atomicExch(error_flag, 1);
+    return;
   }
-  __syncthreads();
-  // The fifth warp: one thread issues every MMA.  For tile i it waits until all rows of P are written (and the
-  // copies that the softmax threads waited for before they arrived have landed), then issues P V of tile i
-  // and the scores of tile i + 2, which overwrite the scores and P of tile i.
-  if (!softmax_warp) {
+
+  constexpr unsigned IDESC_QK = umma_idesc(UM, UN, 0), IDESC_PV = umma_idesc(UM, UD, 1);
+  // ---- the fifth warp: one thread issues every MMA.  S(t) = Q K(t)^T into the scores buffer t & 1, 8 steps of
+  // 16 dims; a commit covers every MMA issued before it.  For tile i it waits until all rows of P are written,
+  // then issues P V of tile i and the scores of tile i + 2, which overwrite the scores and P of tile i.
+  if (warp == 4) {
     bool mma_failed = false;
     if ((tid & 31) == 0) {
+      auto issue_qk = [&](int t) {
+        const int st = t % K_STAGES;
+        if (!mbar_wait_u(smem_addr(&k_full[st]), (unsigned)((t / K_STAGES) & 1))) { mma_failed = true; return; }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned sk = sk0 + st * SKV_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const unsigned long long da = umma_desc(sq + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
+          const unsigned long long db = umma_desc(sk + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
+          umma_f16(tmem + TM_S + (t & 1) * UN, da, db, IDESC_QK, k > 0);
+        }
+        umma_commit(smem_addr(&k_free[st]));
+        umma_commit(smem_addr(&bar_s[t & 1]));
+      };
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       issue_qk(0);
-      if (n_t > 1) issue_qk(1);
-      for (int i = 0; i < n_t; ++i) {
+      if (n_t > 1 && !mma_failed) issue_qk(1);
+      for (int i = 0; i < n_t && !mma_failed; ++i) {
         if (!mbar_wait_u(smem_addr(&bar_p[i & 1]), (unsigned)((i >> 1) & 1))) { mma_failed = true; break; }
+        const int st = i % V_STAGES;
+        if (!mbar_wait_u(smem_addr(&v_full[st]), (unsigned)((i / V_STAGES) & 1))) { mma_failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const unsigned sv = sv0 + (i % V_STAGES) * SKV_BYTES;
+        const unsigned sv = sv0 + st * SKV_BYTES;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {                           // O += P V, 4 steps of 16 keys; P from tensor memory
           const unsigned long long db = umma_desc(sv + kk * 16 * 128, UN * 128, 1024);   // leading offset = panel stride
@@ -296,6 +324,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
           asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                        ::"r"(tmem + TM_O), "r"(a_t), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
         }
+        umma_commit(smem_addr(&v_free[st]));
         if (i + 2 < n_t) issue_qk(i + 2);                          // its commit covers this P V as well
         else umma_commit(smem_addr(&bar_s[i & 1]));
       }
@@ -327,7 +356,6 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     // the outcome of a wait is made the same for the whole warp, whose tensor-memory loads and stores are warp-wide
     if (__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[i & 1]), (unsigned)((i >> 1) & 1)))) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      load_k(i + 3);                                               // the scores are done: this key stage is free
       const int key0 = (t_begin + i) * UN;
       // this thread's row of scores
       float s[UN];
@@ -387,41 +415,34 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
         unpair_f32(add_f32x2(add_f32x2(ls4[0], ls4[1]), add_f32x2(ls4[2], ls4[3])), lo, hi);
         lrow = lrow * alpha + (lo + hi);
       }
-      // P V of tile i - 1 (issued in the last iteration, long done by now) frees its value stage and makes
-      // O complete up to tile i - 1
-      if (i >= 1) {
-        // (the commit of iteration i - 1: completion number (i - 1) / 2 + 1 of the other buffer's barrier)
+      // a moved maximum: this row of O is scaled down; the loads and stores are warp-wide, so the warp does
+      // it when any of its rows needs it.  O must then be complete up to tile i - 1: the commit of iteration
+      // i - 1 (completion number (i - 1) / 2 + 1 of the other buffer's barrier) says so.
+      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
         if (!__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[(i + 1) & 1]), (unsigned)((((i - 1) >> 1) + 1) & 1)))) failed = true;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      }
-      load_v(i + 1);
-      // a moved maximum: this row of O is scaled down; the loads and stores are warp-wide, so the warp does
-      // it when any of its rows needs it
-      if (i > 0 && !failed && __any_sync(0xffffffffu, alpha != 1.0f)) {
+        if (!failed) {
 #pragma unroll
-        for (int j = 0; j < UD / 32; ++j) {
-          unsigned r[32];
-          tmem_ld32_nowait(tm_o + j * 32, r);
-          tmem_ld_wait();
+          for (int j = 0; j < UD / 32; ++j) {
+            unsigned r[32];
+            tmem_ld32_nowait(tm_o + j * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-          asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-                       ::"r"(tm_o + j * 32), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                         "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-                       : "memory");
+            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+                         ::"r"(tm_o + j * 32), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                         : "memory");
+          }
         }
       }
       asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
     } else {
       failed = true;
-      asm volatile("cp.async.commit_group;\n" ::);
-      asm volatile("cp.async.commit_group;\n" ::);
     }
     if (failed) break;                                             // the issuing warp's wait for P will run out too
-    asm volatile("cp.async.wait_group 2;\n" ::: "memory");         // V(i) and K(i+2) have landed
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(&bar_p[i & 1])) : "memory");   // this row of P is written
   }
@@ -429,7 +450,6 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   if (!failed && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[(n_t - 1) & 1]), (unsigned)((((n_t - 1) >> 1) + 1) & 1))))
     failed = true;
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  asm volatile("cp.async.wait_group 0;\n" ::: "memory");             // nothing of ours is still in flight
   const int any_failed = __syncthreads_or(failed);
   if (!any_failed && n_splits > 1) {
     // unnormalised O, and the row's maximum (in exponent units) and sum, for the merge kernel
@@ -517,6 +537,28 @@ attn_prefill_umma_merge_kernel(const float* __restrict__ part_o, const float* __
     out[(size_t)(tok0 + r) * out_stride + (size_t)head * UD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
   }
 }
+// One run's keys (or values) in the paged cache as a 4-D tensor for TMA: (dim, slot in the page, kv head, page),
+// boxes of 64 dims x min(page, 64) slots of one head and page, 128-byte swizzle, zeros outside the tensor.
+int make_kv_map(CUtensorMap* map, const void* base, int head_dim, int page_size, int n_kv, int num_pages,
+                long long page_stride) {
+  static PFN_cuTensorMapEncodeTiled_v12000 enc = nullptr;
+  if (!enc) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return IFX_ERR_UNSUPPORTED;
+    enc = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  }
+  cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)n_kv, (cuuint64_t)num_pages};
+  cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2, (cuuint64_t)page_stride * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)(page_size < UN ? page_size : UN), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : IFX_ERR_UNSUPPORTED;
+}
 }  // namespace
 
 // Into how many parts the keys of the query tiles are best cut: 1 when the tiles alone fill the GPU, else as
@@ -558,24 +600,26 @@ IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, 
                                   int n_tiles, const int* entry_q_start, const int* entry_q_len,
                                   const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
                                   int window, int* error_flag, float* part_o, float* part_ml, int n_splits,
-                                  cudaStream_t stream) {
+                                  int num_pages, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (head_dim != UD || n_kv < 1 || n_heads % n_kv || n_tiles > 65535 || !error_flag) return IFX_ERR_UNSUPPORTED;
   if (n_splits < 1 || n_splits > MERGE_MAX_SPLITS || (n_splits > 1 && (!part_o || !part_ml))) return IFX_ERR_UNSUPPORTED;
   if (n_splits > 1 && ((uintptr_t)part_o & 15)) return IFX_ERR_ALIGNMENT;
-  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1)) || num_pages < 1) return IFX_ERR_UNSUPPORTED;
   if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return IFX_ERR_ALIGNMENT;
   if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
-  PagedKV kv;
-  kv.k = k_layer; kv.v = v_layer; kv.page_stride = page_stride;
-  kv.head_stride = page_size * head_dim; kv.page_size = page_size; kv.page_shift = 0;
-  while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  CUtensorMap map_k, map_v;
+  int ifx_rc = make_kv_map(&map_k, k_layer, head_dim, page_size, n_kv, num_pages, page_stride);
+  if (!ifx_rc) ifx_rc = make_kv_map(&map_v, v_layer, head_dim, page_size, n_kv, num_pages, page_stride);
+  if (ifx_rc) return ifx_rc;
   UmmaMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_UMMA);
   if (e != cudaSuccess) return (int)e;
-  int ifx_rc = launch_pdl(attn_prefill_umma_kernel, dim3(n_heads, n_tiles, n_splits), dim3(U_THREADS), SMEM_UMMA, stream,
-                          (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, tile_entry, tile_q0, n_heads, n_kv, scale,
-                          window, error_flag, part_o, part_ml, n_splits);
+  ifx_rc = launch_pdl(attn_prefill_umma_kernel, dim3(n_heads, n_tiles, n_splits), dim3(U_THREADS), SMEM_UMMA, stream,
+                      (const bf16*)q, q_stride, (bf16*)out, out_stride, map_k, map_v, page_size, page_shift, m,
+                      tile_entry, tile_q0, n_heads, n_kv, scale, window, error_flag, part_o, part_ml, n_splits);
   if (!ifx_rc) ifx_rc = IFX_LAUNCH_CHECK();
   if (ifx_rc || n_splits == 1) return ifx_rc;
   ifx_rc = launch_pdl(attn_prefill_umma_merge_kernel, dim3(n_heads, n_tiles, UM / MERGE_ROWS), dim3(UD), 0, stream, (const float*)part_o,

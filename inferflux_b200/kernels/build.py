@@ -33,6 +33,14 @@ OBJ_SUFFIX = ".tl.o" if TIMELINE else ".o"
 if TIMELINE:
     LIB_NAME = "libinferflux_b200_kernels_timeline.so"
     NVCC_FLAGS = NVCC_FLAGS + ["-DIFX_TIMELINE"]
+# INFERFLUX_B200_NVCC_EXTRA="-DX=1 ..." adds compiler flags (kernel experiments); such a build is a library of
+# its own too, named after the flags, so it never stands in for the serving one.
+EXTRA = os.environ.get("INFERFLUX_B200_NVCC_EXTRA", "").split()
+if EXTRA:
+    tag = hashlib.sha256(" ".join(EXTRA).encode()).hexdigest()[:8]
+    LIB_NAME = LIB_NAME[:-3] + f"_{tag}.so"
+    OBJ_SUFFIX = f".x{tag}" + OBJ_SUFFIX
+    NVCC_FLAGS = NVCC_FLAGS + EXTRA
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
@@ -156,7 +164,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
     # drop objects of older source versions
     keep = {os.path.basename(o) for o in objs}
     for f in os.listdir(out_dir):
-        if f.endswith(".o") and f.endswith(".tl.o") == TIMELINE and f not in keep:
+        if f.endswith(OBJ_SUFFIX) and (EXTRA or ".x" not in f) and f.endswith(".tl.o") == TIMELINE and f not in keep:
             try:
                 os.remove(os.path.join(out_dir, f))
             except OSError:

@@ -85,7 +85,7 @@ def _lib():
         lib.ifx_attn_prefill_umma.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                               c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-                                              c_void_p, c_int, c_void_p]
+                                              c_void_p, c_int, c_int, c_void_p]
         lib.ifx_attn_prefill_umma_plan.argtypes = [c_int, c_int, c_int]
         lib.ifx_attn_prefill_umma_plan.restype = c_int
         lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
@@ -475,6 +475,12 @@ def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
           "attn_prefill_umma: bfloat16 operands")
     _need(head_dim == UMMA_ATTENTION_HEAD_DIM, f"attn_prefill_umma: head_dim {head_dim} is not 128")
     _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
+    # The kernel reads the cache through a TMA tensor map, which wants to know how many pages lie behind page 0:
+    # as many as fit between the view's start and the end of the storage it is a view of.
+    n_elems = k_layer.untyped_storage().nbytes() // k_layer.element_size()
+    last = max(k_layer.storage_offset(), v_layer.storage_offset()) + n_kv * page_size * head_dim
+    num_pages = (n_elems - last) // page_stride + 1 if n_elems >= last else 0
+    _need(num_pages >= 1, "attn_prefill_umma: k_layer / v_layer are not views of page 0 of a paged pool")
     part_o = part_ml = None
     global launch_count
     if n_splits > 1:
@@ -487,7 +493,7 @@ def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
                                         _ptr(tile_entry), _ptr(tile_q0), n_tiles, _ptr(entry_q_start),
                                         _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, n_kv, head_dim,
                                         float(scale), int(window), _ptr(error_flag(q.device)), _ptr(part_o),
-                                        _ptr(part_ml), int(n_splits), _stream()),
+                                        _ptr(part_ml), int(n_splits), int(num_pages), _stream()),
            "attn_prefill_umma")
     return out
 
