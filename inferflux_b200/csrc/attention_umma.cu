@@ -243,35 +243,41 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 lanes
   const unsigned tm_o = tmem + TM_O + lane_base;
 
-  // ---- the sixth warp: one thread copies the key and value tiles, a stage ahead of their use.  Key stage
+  // ---- the sixth warp copies the key and value tiles, a stage ahead of their use.  Key stage
   // t % 3 is free once the scores of tile t - 3 are done, value stage t % 2 once P V of tile t - 2 is (the
   // issuing thread commits onto k_free / v_free).  Order of the copies: K0 K1 V0 K2, then V(t) K(t+2).
   if (warp == 5) {
     bool copy_failed = false;
-    if ((tid & 31) == 0) {
+    {
+      // The boxes of a tile (a page and a 64-dim panel each) are issued by the lanes of the warp side by side:
+      // one thread alone, looking up a page and issuing two boxes at a time, takes longer over a tile than the
+      // tensor core takes to use it.
+      const int lane = tid & 31;
       const int box_slots = min(page_size, UN);                    // tokens per box: a page, or 64 of a longer page
+      const int n_boxes = 2 * (UN / box_slots);                    // boxes of one tile of keys (or values)
       auto copy_tile = [&](const CUtensorMap* map, unsigned sdst, int t, unsigned bar) {
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(SKV_BYTES) : "memory");
-        for (int b = 0; b * box_slots < UN; ++b) {
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(SKV_BYTES) : "memory");
+        __syncwarp();
+        for (int i = lane; i < n_boxes; i += 32) {
+          const int b = i >> 1, panel = i & 1;
           const int key = (t_begin + t) * UN + b * box_slots;
-          const int block = key >> page_shift;
           int page = -1;                                           // boxes wholly outside [kfirst, kend) read as zeros
-          if (key < kend && key + box_slots > kfirst) page = bt[block - bt_first];
-          const int slot0 = key & (page_size - 1);
-          tma_load_kv(sdst + (unsigned)b * box_slots * 128u, map, 0, slot0, kvh, page, bar);
-          tma_load_kv(sdst + UN * 128 + (unsigned)b * box_slots * 128u, map, 64, slot0, kvh, page, bar);
+          if (key < kend && key + box_slots > kfirst) page = bt[(key >> page_shift) - bt_first];
+          tma_load_kv(sdst + panel * (UN * 128) + (unsigned)b * box_slots * 128u, map, panel * 64, key & (page_size - 1),
+                      kvh, page, bar);
         }
       };
       auto copy_k = [&](int t) {
         if (t >= n_t || copy_failed) return;
         const int st = t % K_STAGES;
-        if (t >= K_STAGES && !mbar_wait_u(smem_addr(&k_free[st]), (unsigned)((t / K_STAGES - 1) & 1))) { copy_failed = true; return; }
+        if (t >= K_STAGES && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&k_free[st]), (unsigned)((t / K_STAGES - 1) & 1)))) { copy_failed = true; return; }
         copy_tile(&map_k, sk0 + st * SKV_BYTES, t, smem_addr(&k_full[st]));
       };
       auto copy_v = [&](int t) {
         if (t >= n_t || copy_failed) return;
         const int st = t % V_STAGES;
-        if (t >= V_STAGES && !mbar_wait_u(smem_addr(&v_free[st]), (unsigned)((t / V_STAGES - 1) & 1))) { copy_failed = true; return; }
+        if (t >= V_STAGES && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&v_free[st]), (unsigned)((t / V_STAGES - 1) & 1)))) { copy_failed = true; return; }
         copy_tile(&map_v, sv0 + st * SKV_BYTES, t, smem_addr(&v_full[st]));
       };
       copy_k(0), copy_k(1), copy_v(0), copy_k(2);
