@@ -123,8 +123,10 @@ template <> struct Vec4<bf16> {
   }
 };
 
-template <typename TD, typename TO, int VT>
-__global__ void __launch_bounds__(256)
+// NTH threads a row, each with VT groups of four elements: the row is spread over as many threads as it has
+// groups (up to 1,024), so that all its loads are in flight at once; a step of a few rows is all latency.
+template <typename TD, typename TO, int VT, int NTH>
+__global__ void __launch_bounds__(NTH)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
                        long long partial_stride, const float* __restrict__ weight, float eps,
                        TO* __restrict__ out, const int* __restrict__ rows, int hidden, int write_residual) {
@@ -135,7 +137,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
   float4 wv[VT];
 #pragma unroll
   for (int j = 0; j < VT; ++j) {
-    const int gidx = threadIdx.x + j * 256;
+    const int gidx = threadIdx.x + j * NTH;
     wv[j] = (out && gidx < groups) ? Vec4<float>::load(weight + 4 * gidx) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   pdl_wait();
@@ -145,14 +147,21 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
   float ss = 0.0f;
 #pragma unroll
   for (int j = 0; j < VT; ++j) {
-    const int gidx = threadIdx.x + j * 256;
+    const int gidx = threadIdx.x + j * NTH;
     if (gidx < groups) {
       float4 x = Vec4<float>::load(r + 4 * gidx);
       if (delta) {
         const TD* d = delta + (size_t)src * hidden + 4 * gidx;
-        for (int p = 0; p < n_partials; ++p) {
-          const float4 y = Vec4<TD>::load(d + (size_t)p * partial_stride);
-          x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+        // the slices are asked for together (up to 8 at a time) and added in index order: one wait for
+        // memory instead of one per slice
+        for (int p0 = 0; p0 < n_partials; p0 += 8) {
+          float4 y[8];
+#pragma unroll
+          for (int p = 0; p < 8; ++p)
+            y[p] = p0 + p < n_partials ? Vec4<TD>::load(d + (size_t)(p0 + p) * partial_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int p = 0; p < 8; ++p)
+            if (p0 + p < n_partials) { x.x += y[p].x; x.y += y[p].y; x.z += y[p].z; x.w += y[p].w; }
         }
       }
       v[j] = x;
@@ -164,7 +173,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
   TO* o = out ? out + (size_t)blockIdx.x * hidden : nullptr;
 #pragma unroll
   for (int j = 0; j < VT; ++j) {
-    const int gidx = threadIdx.x + j * 256;
+    const int gidx = threadIdx.x + j * NTH;
     if (gidx < groups) {
       if (write_residual) Vec4<float>::store(r + 4 * gidx, v[j]);
       if (o) {
@@ -183,14 +192,19 @@ static int launch_add_rmsnorm(float* residual, const void* delta, int n_partials
   int ifx_rc = 0;
   const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0
                        && (partial_stride & 3) == 0;
-  if (hidden % 4 == 0 && aligned && hidden <= 4 * 8 * 256) {
+  if (hidden % 4 == 0 && aligned && hidden <= 4 * 2 * 1024) {
     const int groups = hidden / 4;
-    if (groups <= 4 * 256)
-      ifx_rc = launch_pdl(add_rmsnorm_vec_kernel<TD, TO, 4>, dim3(n_rows), dim3(256), 0, stream, residual, (const TD*)delta, n_partials, partial_stride,
-                                                                    weight, eps, (TO*)out, rows, hidden, write_residual);
-    else
-      ifx_rc = launch_pdl(add_rmsnorm_vec_kernel<TD, TO, 8>, dim3(n_rows), dim3(256), 0, stream, residual, (const TD*)delta, n_partials, partial_stride,
-                                                                    weight, eps, (TO*)out, rows, hidden, write_residual);
+    // the shape depends on the row length only, never on the number of rows: a row is summed the same way
+    // whatever else is in the batch
+#define IFX_NORM_LAUNCH(VT, NTH)                                                                                     \
+    ifx_rc = launch_pdl(add_rmsnorm_vec_kernel<TD, TO, VT, NTH>, dim3(n_rows), dim3(NTH), 0, stream, residual,       \
+                        (const TD*)delta, n_partials, partial_stride, weight, eps, (TO*)out, rows, hidden, write_residual)
+    if (groups <= 128) IFX_NORM_LAUNCH(1, 128);
+    else if (groups <= 256) IFX_NORM_LAUNCH(1, 256);
+    else if (groups <= 512) IFX_NORM_LAUNCH(1, 512);
+    else if (groups <= 1024) IFX_NORM_LAUNCH(1, 1024);
+    else IFX_NORM_LAUNCH(2, 1024);
+#undef IFX_NORM_LAUNCH
     return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
   }
   const size_t smem = (size_t)hidden * sizeof(float);
