@@ -123,10 +123,44 @@ template <> struct Vec4<bf16> {
   }
 };
 
-// NTH threads a row, each with VT groups of four elements: the row is spread over as many threads as it has
-// groups (up to 1,024), so that all its loads are in flight at once; a step of a few rows is all latency.
-template <typename TD, typename TO, int VT, int NTH>
-__global__ void __launch_bounds__(NTH)
+// Residual add + RMSNorm, rows whose length is a multiple of 4, 16-byte accesses.  Two shapes of one computation:
+//   narrow: 256 threads a row, thread t takes the groups of four elements t, t + 256, ... (J of them) - many rows;
+//   wide:   one thread per group (up to 1,024 threads, two groups each beyond that), so that all loads of a row are
+//           in flight at once - a step of a few rows, which is all latency.
+// Both add a row's squares in the same order, so a row's result does not depend on which shape ran it (that is,
+// on how many rows the step has): per thread-of-the-narrow-shape the groups t, t + 256, ... one after the other,
+// then the warp tree, then the tree over the 8 warps.  The wide shape passes its groups' sums through shared
+// memory to get there.
+__device__ __forceinline__ float group_squares(const float4& x) {
+  return __fmaf_rn(x.w, x.w, __fmaf_rn(x.z, x.z, __fmaf_rn(x.y, x.y, __fmul_rn(x.x, x.x))));
+}
+template <typename TD>
+__device__ __forceinline__ float4 row_group(const float* r, const TD* delta, int n_partials, long long partial_stride,
+                                            size_t at) {
+  float4 x = Vec4<float>::load(r + at);
+  if (delta) {
+    const TD* d = delta + at;
+    // the slices are asked for together (up to 8 at a time) and added in index order: one wait for memory
+    // instead of one per slice
+    for (int p0 = 0; p0 < n_partials; p0 += 8) {
+      float4 y[8];
+#pragma unroll
+      for (int p = 0; p < 8; ++p)
+        y[p] = p0 + p < n_partials ? Vec4<TD>::load(d + (size_t)(p0 + p) * partial_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int p = 0; p < 8; ++p)
+        if (p0 + p < n_partials) { x.x += y[p].x; x.y += y[p].y; x.z += y[p].z; x.w += y[p].w; }
+    }
+  }
+  return x;
+}
+template <typename TO>
+__device__ __forceinline__ void store_normed(TO* o, const float4& v, float rstd, const float4& w) {
+  Vec4<TO>::store(o, make_float4(v.x * rstd * w.x, v.y * rstd * w.y, v.z * rstd * w.z, v.w * rstd * w.w));
+}
+
+template <typename TD, typename TO, int J>
+__global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
                        long long partial_stride, const float* __restrict__ weight, float eps,
                        TO* __restrict__ out, const int* __restrict__ rows, int hidden, int write_residual) {
@@ -134,56 +168,99 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
   pdl_launch_dependents();
   __shared__ float red[32];
   const int groups = hidden >> 2;
-  float4 wv[VT];
+  float4 wv[J];
 #pragma unroll
-  for (int j = 0; j < VT; ++j) {
-    const int gidx = threadIdx.x + j * NTH;
+  for (int j = 0; j < J; ++j) {
+    const int gidx = threadIdx.x + j * 256;
     wv[j] = (out && gidx < groups) ? Vec4<float>::load(weight + 4 * gidx) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   pdl_wait();
   const int src = rows ? rows[blockIdx.x] : blockIdx.x;
   float* r = residual + (size_t)src * hidden;
-  float4 v[VT];
+  const TD* d = delta ? delta + (size_t)src * hidden : nullptr;
+  float4 v[J];
   float ss = 0.0f;
 #pragma unroll
-  for (int j = 0; j < VT; ++j) {
-    const int gidx = threadIdx.x + j * NTH;
+  for (int j = 0; j < J; ++j) {
+    const int gidx = threadIdx.x + j * 256;
     if (gidx < groups) {
-      float4 x = Vec4<float>::load(r + 4 * gidx);
-      if (delta) {
-        const TD* d = delta + (size_t)src * hidden + 4 * gidx;
-        // the slices are asked for together (up to 8 at a time) and added in index order: one wait for
-        // memory instead of one per slice
-        for (int p0 = 0; p0 < n_partials; p0 += 8) {
-          float4 y[8];
-#pragma unroll
-          for (int p = 0; p < 8; ++p)
-            y[p] = p0 + p < n_partials ? Vec4<TD>::load(d + (size_t)(p0 + p) * partial_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int p = 0; p < 8; ++p)
-            if (p0 + p < n_partials) { x.x += y[p].x; x.y += y[p].y; x.z += y[p].z; x.w += y[p].w; }
-        }
-      }
-      v[j] = x;
-      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+      v[j] = row_group<TD>(r, d, n_partials, partial_stride, (size_t)4 * gidx);
+      ss = __fadd_rn(ss, group_squares(v[j]));
     }
   }
   ss = block_sum(ss, red);
   const float rstd = rsqrtf(ss / (float)hidden + eps);
   TO* o = out ? out + (size_t)blockIdx.x * hidden : nullptr;
 #pragma unroll
-  for (int j = 0; j < VT; ++j) {
-    const int gidx = threadIdx.x + j * NTH;
+  for (int j = 0; j < J; ++j) {
+    const int gidx = threadIdx.x + j * 256;
     if (gidx < groups) {
       if (write_residual) Vec4<float>::store(r + 4 * gidx, v[j]);
-      if (o) {
-        const float4 w = wv[j];
-        Vec4<TO>::store(o + 4 * gidx, make_float4(v[j].x * rstd * w.x, v[j].y * rstd * w.y,
-                                                  v[j].z * rstd * w.z, v[j].w * rstd * w.w));
-      }
+      if (o) store_normed<TO>(o + 4 * gidx, v[j], rstd, wv[j]);
     }
   }
 }
+
+// The wide shape: JT * 256 threads (JT = min(J, 4)), thread (jt, t) with t its index among 256 takes the groups
+// (jt + v * JT) * 256 + t for v < VT, which are the narrow shape's j = jt + v * JT of its thread t.
+template <typename TD, typename TO, int J>
+__global__ void __launch_bounds__((J < 4 ? J : 4) * 256)
+add_rmsnorm_wide_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
+                        long long partial_stride, const float* __restrict__ weight, float eps,
+                        TO* __restrict__ out, const int* __restrict__ rows, int hidden, int write_residual) {
+  constexpr int JT = J < 4 ? J : 4, VT = (J + JT - 1) / JT;
+  pdl_launch_dependents();
+  __shared__ float sq[J][256];
+  __shared__ float red[8];
+  const int groups = hidden >> 2;
+  const int t = threadIdx.x & 255, jt = threadIdx.x >> 8, lane = threadIdx.x & 31;
+  float4 wv[VT];
+#pragma unroll
+  for (int vv = 0; vv < VT; ++vv) {
+    const int gidx = (jt + vv * JT) * 256 + t;
+    wv[vv] = (out && jt + vv * JT < J && gidx < groups) ? Vec4<float>::load(weight + 4 * gidx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* r = residual + (size_t)src * hidden;
+  const TD* d = delta ? delta + (size_t)src * hidden : nullptr;
+  float4 v[VT];
+#pragma unroll
+  for (int vv = 0; vv < VT; ++vv) {
+    const int j = jt + vv * JT, gidx = j * 256 + t;
+    if (j < J) {
+      float e = 0.0f;
+      if (gidx < groups) {
+        v[vv] = row_group<TD>(r, d, n_partials, partial_stride, (size_t)4 * gidx);
+        e = group_squares(v[vv]);
+      }
+      sq[j][t] = e;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 256) {                                     // the narrow shape's thread t: its groups one after the other
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < J; ++j)
+      if (j * 256 + t < groups) ss = __fadd_rn(ss, sq[j][t]);
+    ss = warp_sum(ss);
+    if (lane == 0) red[t >> 5] = ss;
+  }
+  __syncthreads();
+  const float total = warp_sum(lane < 8 ? red[lane] : 0.0f);   // as block_sum does for 8 warps
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  TO* o = out ? out + (size_t)blockIdx.x * hidden : nullptr;
+#pragma unroll
+  for (int vv = 0; vv < VT; ++vv) {
+    const int j = jt + vv * JT, gidx = j * 256 + t;
+    if (j < J && gidx < groups) {
+      if (write_residual) Vec4<float>::store(r + 4 * gidx, v[vv]);
+      if (o) store_normed<TO>(o + 4 * gidx, v[vv], rstd, wv[vv]);
+    }
+  }
+}
+
+constexpr int NORM_WIDE_MAX_ROWS = 64;   // up to this many rows a step is latency, not bandwidth
 
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* residual, const void* delta, int n_partials, long long partial_stride,
@@ -192,19 +269,24 @@ static int launch_add_rmsnorm(float* residual, const void* delta, int n_partials
   int ifx_rc = 0;
   const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0
                        && (partial_stride & 3) == 0;
-  if (hidden % 4 == 0 && aligned && hidden <= 4 * 2 * 1024) {
-    const int groups = hidden / 4;
-    // the shape depends on the row length only, never on the number of rows: a row is summed the same way
-    // whatever else is in the batch
-#define IFX_NORM_LAUNCH(VT, NTH)                                                                                     \
-    ifx_rc = launch_pdl(add_rmsnorm_vec_kernel<TD, TO, VT, NTH>, dim3(n_rows), dim3(NTH), 0, stream, residual,       \
-                        (const TD*)delta, n_partials, partial_stride, weight, eps, (TO*)out, rows, hidden, write_residual)
-    if (groups <= 128) IFX_NORM_LAUNCH(1, 128);
-    else if (groups <= 256) IFX_NORM_LAUNCH(1, 256);
-    else if (groups <= 512) IFX_NORM_LAUNCH(1, 512);
-    else if (groups <= 1024) IFX_NORM_LAUNCH(1, 1024);
-    else IFX_NORM_LAUNCH(2, 1024);
-#undef IFX_NORM_LAUNCH
+  if (hidden % 4 == 0 && aligned && hidden <= 4 * 8 * 256) {
+    const int j = (hidden / 4 + 255) / 256;                     // groups per thread of the narrow shape
+    const bool wide = n_rows <= NORM_WIDE_MAX_ROWS;
+#define IFX_NORM_CASE(J)                                                                                              \
+    case J:                                                                                                           \
+      ifx_rc = wide ? launch_pdl(add_rmsnorm_wide_kernel<TD, TO, J>, dim3(n_rows), dim3((J < 4 ? J : 4) * 256), 0, stream,    \
+                                 residual, (const TD*)delta, n_partials, partial_stride, weight, eps, (TO*)out, rows, hidden, \
+                                 write_residual)                                                                      \
+                    : launch_pdl(add_rmsnorm_vec_kernel<TD, TO, J>, dim3(n_rows), dim3(256), 0, stream, residual,     \
+                                 (const TD*)delta, n_partials, partial_stride, weight, eps, (TO*)out, rows, hidden,   \
+                                 write_residual);                                                                     \
+      break;
+    switch (j) {
+      IFX_NORM_CASE(1) IFX_NORM_CASE(2) IFX_NORM_CASE(3) IFX_NORM_CASE(4)
+      IFX_NORM_CASE(5) IFX_NORM_CASE(6) IFX_NORM_CASE(7) IFX_NORM_CASE(8)
+      default: return IFX_ERR_UNSUPPORTED;
+    }
+#undef IFX_NORM_CASE
     return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
   }
   const size_t smem = (size_t)hidden * sizeof(float);

@@ -80,6 +80,24 @@ def test_add_rmsnorm(ops, hidden, ddt, odt):
     _close(out3, out3_ref, 1e-5 if odt == torch.float32 else 8e-3, "no delta")
 
 
+@pytest.mark.parametrize("hidden", [24, 100, 1024, 2048, 3584, 5120, 8192])
+@pytest.mark.parametrize("parts", [1, 5])
+def test_add_rmsnorm_same_bits_whatever_the_number_of_rows(ops, hidden, parts):
+    """A step of a few rows spreads a row over up to 1,024 threads, a step of many rows gives it 256; the squares
+    are added in the same order in both, so a row's residual and normed values are the same bit for bit."""
+    n_small, n_big = 3, 100
+    res = _rand((n_big, hidden), torch.float32, 50)
+    delta = _rand((parts, n_big, hidden), torch.float32, 51)
+    w = _rand((hidden,), torch.float32, 52) + 1.0
+    big_res, small_res = res.clone(), res[:n_small].clone()
+    big_out = torch.empty((n_big, hidden), dtype=torch.float32, device=DEV)
+    small_out = torch.empty((n_small, hidden), dtype=torch.float32, device=DEV)
+    ops.add_rmsnorm(big_res, delta if parts > 1 else delta[0], w, 1e-6, big_out, n_partials=parts)
+    small_delta = delta[:, :n_small].contiguous()
+    ops.add_rmsnorm(small_res, small_delta if parts > 1 else small_delta[0], w, 1e-6, small_out, n_partials=parts)
+    assert torch.equal(small_res, big_res[:n_small]) and torch.equal(small_out, big_out[:n_small])
+
+
 def test_add_rmsnorm_partials(ops):
     n, hidden, parts = 5, 200, 3
     res = _rand((n, hidden), torch.float32, 5)
