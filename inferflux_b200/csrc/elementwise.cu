@@ -138,7 +138,10 @@ template <typename TD>
 __device__ __forceinline__ float4 row_group(const float* r, const TD* delta, int n_partials, long long partial_stride,
                                             size_t at) {
   float4 x = Vec4<float>::load(r + at);
-  if (delta) {
+  if (delta && n_partials == 1) {
+    const float4 y = Vec4<TD>::load(delta + at);
+    x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+  } else if (delta) {
     const TD* d = delta + at;
     // the slices are asked for together (up to 8 at a time) and added in index order: one wait for memory
     // instead of one per slice

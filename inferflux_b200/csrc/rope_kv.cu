@@ -144,6 +144,70 @@ __global__ void __launch_bounds__(PART ? 256 : 512) qkv_rope_kv_write_bf16x8_ker
   }
 }
 
+// The same for steps of many tokens (no partial sums): a block takes TOK consecutive tokens and a thread the same
+// 8-wide item of each of them, so that its loads of all TOK tokens are in flight together and it reads the bias
+// once.  The arithmetic per item is rope_pairs8 / biased8 as above.
+template <int TOK>
+__global__ void __launch_bounds__(512) qkv_rope_kv_write_bf16x8_many_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
+                                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                const int* __restrict__ slot_map, PagedKV kv, int n_tokens,
+                                                int n_heads, int n_kv, int head_dim) {
+  pdl_enter();
+  const int t0 = blockIdx.x * TOK;
+  const int half = head_dim / 2, hv = half / 8;
+  const int width = (n_heads + 2 * n_kv) * head_dim;
+  const int rot_items = (n_heads + n_kv) * hv, v_items = n_kv * head_dim / 8;
+  const int vbase = (n_heads + n_kv) * head_dim;
+  for (int w = threadIdx.x; w < rot_items + v_items; w += blockDim.x) {
+    if (w < rot_items) {
+      const int h = w / hv, i = (w - h * hv) * 8;
+      const int base = h * head_dim;
+      uint4 p0[TOK], p1[TOK];
+#pragma unroll
+      for (int k = 0; k < TOK; ++k) {
+        const int t = min(t0 + k, n_tokens - 1);
+        rope_pairs8<false>(qkv + (size_t)t * width, nullptr, 0, 0, bias, cos_t + (size_t)t * half, sin_t + (size_t)t * half,
+                           base + i, half, i, p0[k], p1[k]);
+      }
+#pragma unroll
+      for (int k = 0; k < TOK; ++k) {
+        const int t = t0 + k;
+        if (t >= n_tokens) break;
+        if (h < n_heads) {
+          bf16* row = qkv + (size_t)t * width;
+          *reinterpret_cast<uint4*>(row + base + i) = p0[k];
+          *reinterpret_cast<uint4*>(row + base + half + i) = p1[k];
+        } else {
+          const int slot = slot_map[t];
+          if (slot >= 0) {
+            bf16* dst = (bf16*)kv.k + (size_t)(slot >> kv.page_shift) * kv.page_stride + (size_t)(h - n_heads) * kv.head_stride +
+                        (size_t)(slot & (kv.page_size - 1)) * head_dim;
+            *reinterpret_cast<uint4*>(dst + i) = p0[k];
+            *reinterpret_cast<uint4*>(dst + half + i) = p1[k];
+          }
+        }
+      }
+    } else {
+      const int e0 = (w - rot_items) * 8, h = e0 / head_dim, d = e0 - h * head_dim;
+      uint4 v[TOK];
+#pragma unroll
+      for (int k = 0; k < TOK; ++k) {
+        const int t = min(t0 + k, n_tokens - 1);
+        v[k] = biased8<false>(qkv + (size_t)t * width, nullptr, 0, 0, bias, vbase + e0);
+      }
+#pragma unroll
+      for (int k = 0; k < TOK; ++k) {
+        const int t = t0 + k;
+        if (t >= n_tokens) break;
+        const int slot = slot_map[t];
+        if (slot >= 0)
+          *reinterpret_cast<uint4*>((bf16*)kv.v + (size_t)(slot >> kv.page_shift) * kv.page_stride + (size_t)h * kv.head_stride +
+                                    (size_t)(slot & (kv.page_size - 1)) * head_dim + d) = v[k];
+      }
+    }
+  }
+}
+
 IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const float* cos_t, const float* sin_t,
                                   int rot_dim, const int* slot_map, void* k_layer, void* v_layer,
                                   long long page_stride, int page_size, int n_tokens, int n_heads, int n_kv,
@@ -170,7 +234,11 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
     int th = 32;
     while (th < th_max && th < work8) th <<= 1;
     const long long part_stride = (long long)n_tokens * (n_heads + 2 * n_kv) * head_dim;
-    if (partials)
+    constexpr int MANY_TOK = 4;
+    if (!partials && n_kv > 0 && n_tokens >= 64 * MANY_TOK)
+      ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_many_kernel<MANY_TOK>, dim3((n_tokens + MANY_TOK - 1) / MANY_TOK), dim3(th), 0,
+                          stream, (bf16*)qkv, bias, cos_t, sin_t, slot_map, kv, n_tokens, n_heads, n_kv, head_dim);
+    else if (partials)
       ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel<true>, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t, sin_t,
                           slot_map, kv, n_heads, n_kv, head_dim, partials, n_partials, part_stride);
     else

@@ -193,10 +193,11 @@ def test_gemv_swiglu(ops, m, inter, k, impl):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rot,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 4), (10, 2, 48, 24, 8),
                                               (28, 4, 128, 128, 16), (5, 5, 80, 80, 64), (2, 0, 64, 64, 16)])
-def test_rope_and_kv_write(ops, dtype, nh, nkv, hd, rot, ps):
-    n, pages, layers = 19, 9, 2
-    positions = torch.tensor([0, 1, 2, 3, 500, 501, 4095, 31, 32, 33, 7, 8, 9, 10, 11, 12, 13, 14, 15],
-                             dtype=torch.int32, device=DEV)
+@pytest.mark.parametrize("n", [19, 301])        # 301 tokens: the kernel that takes several tokens a block
+def test_rope_and_kv_write(ops, dtype, nh, nkv, hd, rot, ps, n):
+    pages, layers = (n + ps - 1) // ps + 7, 2
+    first = [0, 1, 2, 3, 500, 501, 4095, 31, 32, 33, 7, 8, 9, 10, 11, 12, 13, 14, 15]
+    positions = torch.tensor((first + list(range(600, 600 + n)))[:n], dtype=torch.int32, device=DEV)
     inv = torch.pow(torch.tensor(1e6, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).to(DEV)
     cos = torch.empty((n, rot // 2), dtype=torch.float32, device=DEV)
     sin = torch.empty_like(cos)
