@@ -72,7 +72,7 @@ class Case:
                     planned = ops.gemv_k_splits(n, k)
                     self.note = f"k_splits={planned} (planned)"
                     outp = torch.empty((planned, rows, n) if planned > 1 else (rows, n), device=DEV, dtype=torch.float32)
-                    self.run = lambda i: ops.gemv_bf16(x, ws[i], None, outp, k_splits=planned)
+                    self.run = lambda i, outp=outp, planned=planned: ops.gemv_bf16(x, ws[i], None, outp, k_splits=planned)
                     if sweep:
                         for s in range(1, 9):
                             outs = torch.empty((s, rows, n) if s > 1 else (rows, n), device=DEV, dtype=torch.float32)
@@ -90,9 +90,9 @@ class Case:
             self.extra.append(("library", lambda i: torch.mm(x, ws[i].t())))
             if not sw and rows <= ops.SKINNY_MAX_ROWS:
                 sp = ops.gemm_umma_skinny_parts(n, k)
-                outp = torch.empty(sp, rows, n, device=DEV)
+                outs = torch.empty(sp, rows, n, device=DEV)
                 self.extra.append((f"tcgen05, weights as the tiles' rows, K in {sp} parts",
-                                   lambda i: ops.gemm_umma_skinny(x, ws[i], outp)))
+                                   lambda i, outs=outs: ops.gemm_umma_skinny(x, ws[i], outs)))
         elif name in ("attn_decode", "attn_decode_skewed", "attn_prefill", "attn_prefill_umma"):
             ps = 16
             decode = name.startswith("attn_decode")
