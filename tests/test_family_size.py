@@ -1,7 +1,9 @@
-"""The engine at the layer sizes of a real model of the family (Qwen2.5-7B:
-hidden 3584, 28 query heads on 4 key/value heads of size 128, feed-forward
-18944, vocabulary 152064), cut to two layers so that the plain implementation
-can follow on the CPU, in float32 and in bfloat16.
+"""The engine at the layer sizes of real models of the family, cut to two layers
+so that the plain implementation can follow on the CPU, in float32 and in
+bfloat16: Qwen2.5-7B (hidden 3584, 28 query heads on 4 key/value heads of size
+128, feed-forward 18944, vocabulary 152064, a head of its own) and Qwen2.5-3B
+(hidden 2048, 16 query heads on 2 key/value heads, feed-forward 11008,
+vocabulary 151936, the head tied to the embedding).
 
 At these sizes the engine takes the paths that the tiny models never reach and
 whose speed the benchmark reports: the tcgen05 attention and product kernels
@@ -27,10 +29,16 @@ from helpers import TOL, random_tokens
 
 pytestmark = pytest.mark.gpu
 
-FAMILY = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=3584, num_hidden_layers=2,
-              num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
-              vocab_size=152064, max_position_embeddings=4096, rope_theta=1e6, rms_norm_eps=1e-6,
-              tie_word_embeddings=False, use_sliding_window=False)
+FAMILIES = {
+    "7b": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=3584, num_hidden_layers=2,
+               num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
+               vocab_size=152064, max_position_embeddings=4096, rope_theta=1e6, rms_norm_eps=1e-6,
+               tie_word_embeddings=False, use_sliding_window=False),
+    "3b": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=2048, num_hidden_layers=2,
+               num_attention_heads=16, num_key_value_heads=2, head_dim=128, intermediate_size=11008,
+               vocab_size=151936, max_position_embeddings=4096, rope_theta=1e6, rms_norm_eps=1e-6,
+               tie_word_embeddings=True, use_sliding_window=False),
+}
 # N(0, 0.02) weights at hidden 3584 already give scores with a standard deviation near 1.4 and so a peaked
 # softmax, in which one wrong key shows.  Doubling q and k (scores four times as large) also passes in float32,
 # but then the rounding of q and k to bfloat16 alone moves the logits by 3 % and says nothing about the engine.
@@ -52,38 +60,33 @@ class Oracle:
     """The plain implementation's hidden states for every sequence the tests
     use, computed once; logits at wanted places on demand."""
 
-    def __init__(self):
+    def __init__(self, name):
+        self.cfg = dict(FAMILIES[name])
         from inferflux_b200.config import load_config
         from inferflux_b200.config.registry import build_spec
         from inferflux_b200.engine.model import Model
         from inferflux_b200.weights.random_init import random_tensors
-        self.config = load_config(dict(FAMILY))
+        self.config = load_config(dict(self.cfg))
         specs = Model(build_spec(self.config), torch.bfloat16, "cpu").weight_specs()
         self.tensors = random_tensors(specs, 7, torch.bfloat16, torch.float32, "cpu")
         for name, t in self.tensors.items():
             if name.endswith(("q_proj.weight", "k_proj.weight")):
                 self.tensors[name] = (t.float() * SHARPEN).to(t.dtype)
         self.weights = Widened(self.tensors)
-        vocab = FAMILY["vocab_size"]
+        vocab = self.cfg["vocab_size"]
         self.seqs = {f"long{i}": random_tokens(vocab, n, 200 + i) for i, n in enumerate(LONG)}
         self.seqs.update({f"short{i}": random_tokens(vocab, 30, 300 + i) for i in range(N_SHORT)})
         self._hidden = {}
 
     def hidden(self, key):
         if key not in self._hidden:
-            self._hidden[key] = plain.final_hidden(dict(FAMILY), self.weights, self.seqs[key])
+            self._hidden[key] = plain.final_hidden(dict(self.cfg), self.weights, self.seqs[key])
         return self._hidden[key]
 
 
-_oracle = None
-
-
-@pytest.fixture(scope="module")
-def oracle():
-    global _oracle
-    if _oracle is None:
-        _oracle = Oracle()
-    return _oracle
+@pytest.fixture(scope="module", params=sorted(FAMILIES))
+def oracle(request):
+    return Oracle(request.param)
 
 
 @pytest.fixture(scope="module", params=["float32", "bfloat16"])
@@ -128,7 +131,7 @@ class Checker:
         assert self.rows
         got = torch.stack(self.rows).double()
         hidden = torch.stack([self.oracle.hidden(k)[p] for k, p in self.keys])
-        head = self.oracle.tensors["lm_head.weight"]
+        head = plain.head_weight(self.oracle.cfg, self.oracle.tensors)
         worst = torch.zeros(len(self.rows), dtype=torch.float64)
         scale = torch.zeros(len(self.rows), dtype=torch.float64)
         for v0 in range(0, head.shape[0], 16384):
