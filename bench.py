@@ -172,6 +172,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--e2e-steps", type=int, default=200,
+                    help="steps of the end-to-end loop (at least --steps; a profiler's launch list wants few)")
     ap.add_argument("--mixed", type=int, default=0, metavar="N",
                     help="instead of the decode step: N requests with prompts of 128 to 2,048 tokens and 256 output "
                          "tokens each through Engine.generate (chunked prompts beside decoding requests)")
@@ -265,7 +267,7 @@ def main() -> int:
 
     # ---- end to end: the Python entry point, host tokens in, host tokens out; at least 200 steps, so that
     # one stall of the host does not decide the figure
-    e2e_steps = max(args.steps, 200)
+    e2e_steps = max(args.steps, args.e2e_steps)
     prompts = [torch.randint(0, vocab, (ctx - e2e_steps - warmup - 16,), generator=gen).tolist() for _ in range(batch)]
     params = SamplingParams(temperature=0.0, max_tokens=e2e_steps + warmup + 16, ignore_eos=True)
     for p in prompts:
