@@ -30,6 +30,9 @@ KERNELS = ["gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_lm_head", "a
            "add_rmsnorm", "rope_kv", "swiglu", "argmax", "sample"]
 
 
+PAGE_SIZE = 16      # tokens a page of the attention workloads (--page-size)
+
+
 def _timeit(fn, n_rot, reps=20):
     for i in range(3):
         fn(i % n_rot)
@@ -94,7 +97,7 @@ class Case:
                 self.extra.append((f"tcgen05, weights as the tiles' rows, K in {sp} parts",
                                    lambda i, outs=outs: ops.gemm_umma_skinny(x, ws[i], outs)))
         elif name in ("attn_decode", "attn_decode_skewed", "attn_prefill", "attn_prefill_umma"):
-            ps = 16
+            ps = PAGE_SIZE
             decode = name.startswith("attn_decode")
             b = rows if decode else 1
             q_len = 1 if decode else rows
@@ -153,7 +156,7 @@ class Case:
                             qs, ql, cs, pos, pms, nh, nkv, hd, scale, 0, s)))
             else:
                 umma = name.endswith("umma")
-                tiles = [(0, q0) for q0 in range(0, q_len, 128 if umma else 64)]
+                tiles = [(0, q0) for q0 in range(0, q_len, ops.UMMA_ATTENTION_TILE if umma else 64)]
                 te, tq = it([t[0] for t in tiles]), it([t[1] for t in tiles])
                 kernel = ops.attn_prefill_umma if umma else ops.attn_prefill_bf16
                 # causal: query i sees ctx - q_len + i + 1 keys
@@ -295,10 +298,12 @@ def main(argv=None) -> int:
     ap.add_argument("--rows", nargs="*", type=int, default=[1, 8, 64])
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--repeat", type=int, default=5)
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens a page of the attention workloads' cache")
     ap.add_argument("--sweep", action="store_true", help="time: also other numbers of K parts (small products) and of key splits (decode attention)")
     ap.add_argument("--sizes", default="3584,28,4,128,18944,152064",
                     help="hidden,heads,kv_heads,head_dim,intermediate,vocab")
     args = ap.parse_args(argv)
+    globals()["PAGE_SIZE"] = args.page_size
     if args.mode == "list":
         print("\n".join(KERNELS))
         return 0

@@ -8,30 +8,39 @@
 // (runtime/backends/cuda/kernels/flash_attention.cu:52-173,
 // runtime/backends/cuda/kernels/flash_attention_mma.cuh:153-379).
 //
-// One block takes 128 consecutive new tokens of one request and one head.
-//   * Q (128 x 128), and per step a tile of 64 keys and 64 values, lie in shared
+// One block takes 256 consecutive new tokens of one request and one head, as two
+// query tiles ("slots") of 128 rows that share every key and value tile the block
+// brings in; it has an SM to itself (192 KB of shared memory, all 512 columns of
+// tensor memory).
+//   * Q (2 x 128 x 128), and per step a tile of 64 keys and 64 values, lie in shared
 //     memory in the 128-byte-swizzle layouts the tensor core reads.  Q is written
 //     once with 16-byte cp.async.  Keys and values come from the paged cache by
 //     TMA (cp.async.bulk.tensor over a 4-D map (dim, slot, kv head, page) of the
-//     run's pages): one box per page and 64-dim panel, issued by one thread of a
-//     warp of its own, three key stages and two value stages ahead of their use,
-//     with mbarriers both ways (a stage has landed / a stage has been read).
-//   * S = Q K^T is one chain of 8 tcgen05.mma (M 128, N 64, K 16) into 64
-//     columns of tensor memory.  Thread r then owns row r: it reads its scores
-//     with tcgen05.ld, keeps the running maximum and sum,
-//     and writes P = exp(s - max) as packed bfloat16 back into tensor memory
+//     run's pages): one box per page and 64-dim panel, issued by the lanes of two
+//     warps of their own (one for keys, one for values), four stages each ahead of
+//     their use, with mbarriers both ways (a stage has landed / a stage has been
+//     read by both slots).
+//   * Per slot, S = Q K^T is one chain of 8 tcgen05.mma (M 128, N 64, K 16) into 64
+//     columns of tensor memory, of which the slot has two (the scores of tile i + 1
+//     are computed while the threads work on tile i).  Thread r then owns row r: it
+//     reads its scores with tcgen05.ld, keeps the running maximum and sum, and
+//     writes P = exp(s - max) as packed bfloat16 back over the scores
 //     (tcgen05.st), from where the next MMA takes it as its A operand.
-//   * O += P V is 4 tcgen05.mma (M 128, N 128, K 16) with V read in its natural [key][dim] layout
-//     (MN-major B operand), accumulating over all key tiles in 128 more columns of tensor memory.  A
-//     row's running maximum is moved only when a tile's maximum passes it by more than 8 in exponent
-//     units; then (rarely after the first tiles) the thread scales its row of O in tensor memory.  The
-//     MMAs of the next tile's scores are issued right behind this tile's P V, and one commit covers both.
-// A fifth warp issues the MMAs (one thread): the softmax threads arrive on an mbarrier when their row of
-// P is written, and wait on the mbarrier that tcgen05.commit arrives on for the next scores, so they never
-// wait for the issuing, nor (since the copies have a warp of their own) for memory.  Two blocks fit an SM
-// (112 KB of shared memory, 256 columns of
-// tensor memory each), so one block's softmax overlaps the other's MMAs.  Every
-// mbarrier wait is bounded: if one runs out the block sets *error_flag, and
+//   * O += P V is 4 tcgen05.mma (M 128, N 128, K 16) with V read in its natural
+//     [key][dim] layout (MN-major B operand), accumulating over all key tiles in
+//     128 more columns of the slot.  A row's running maximum is moved only when a
+//     tile's maximum passes it by more than 8 in exponent units; then (rarely
+//     after the first tiles) the thread scales its row of O in tensor memory.
+//     The MMAs of the scores two tiles on are issued right behind a tile's P V,
+//     and one commit covers both.
+// Each slot has a warp whose one thread issues its MMAs: the slot's softmax threads
+// arrive on an mbarrier when their row of P is written, and wait on the mbarrier
+// that tcgen05.commit arrives on for the next scores.  (One thread issuing for both
+// slots measured a quarter slower: an issue waits for room in the tensor core's
+// queue, and the other slot's P then waits behind it.)  What bounds the kernel at
+// this tile shape is the number of MMA instructions, about 50 cycles each whatever
+// their N: 12 a tile and slot.
+// Every mbarrier wait is bounded: if one runs out the block sets *error_flag, and
 // since every issued copy is waited for before the MMA that reads it, nothing is
 // in flight when the block frees its tensor memory and returns.
 #include "common.cuh"
@@ -40,7 +49,7 @@
 
 namespace {
 
-constexpr int UM = 128;          // query rows per block
+constexpr int UM = 128;          // query rows per slot; a block has two slots (256 consecutive tokens)
 constexpr int UN = 64;           // keys per tile
 constexpr int UD = 128;          // head size
 constexpr int WAIT_LIMIT = 1 << 20;   // tries of at most 2 microseconds each
@@ -131,17 +140,17 @@ struct UmmaMeta {
   const int* entry_q_start; const int* entry_q_len; const int* entry_ctx_start;
 };
 
-// Shared memory (1024-byte aligned): Q 32 KB | K 3 x 16 KB | V 2 x 16 KB
+// Shared memory (1024-byte aligned): Q of the two query tiles 2 x 32 KB | K 4 x 16 KB | V 4 x 16 KB
 constexpr int SQ_BYTES = 2 * UM * 128, SKV_BYTES = 2 * UN * 128;
-constexpr int K_STAGES = 3, V_STAGES = 2;
-// four softmax warps (one thread per query row), the warp that issues the MMAs, the warp that issues the copies
-constexpr int U_THREADS = 192;
-// Two blocks per SM: 2 x (1 KB static + 112 KB dynamic + 1 KB reserved) = 228 KB, all there is.  The dynamic
-// part is declared 1024-byte aligned, so it needs no slack for aligning the swizzled tiles by hand.
-constexpr int SMEM_UMMA = SQ_BYTES + (K_STAGES + V_STAGES) * SKV_BYTES;
-// Tensor memory columns: S of even tiles 64 | S of odd tiles 64 | O 128.  P (64 packed bfloat16 = 32
-// columns) is written over the first half of the scores it was made from.
-constexpr unsigned TM_S = 0, TM_O = 128;
+constexpr int K_STAGES = 4, V_STAGES = 4;
+// A block takes 256 consecutive tokens of one request and one head as two query tiles ("slots") of 128 rows,
+// which share every key and value tile the block brings in.  Eight softmax warps (one thread per query row of
+// the two tiles), a warp per slot that issues its MMAs, a warp that copies keys and one that copies values.
+constexpr int U_SOFTMAX = 2 * UM, U_THREADS = U_SOFTMAX + 128;
+constexpr int SMEM_UMMA = 2 * SQ_BYTES + (K_STAGES + V_STAGES) * SKV_BYTES;
+// Tensor memory, all 512 columns, per slot 256: S of even tiles 64 | S of odd tiles 64 | O 128.  P (64 packed
+// bfloat16 = 32 columns) is written over the first half of the scores it was made from.
+constexpr unsigned TM_SLOT = 256, TM_S = 0, TM_O = 128;
 
 // One TMA box of the paged cache into shared memory: 64 dims (one 128-byte panel row) x box_slots tokens of
 // one page and kv head, written in the 128-byte swizzle that the MMA descriptors expect (the swizzle goes by
@@ -154,7 +163,7 @@ __device__ __forceinline__ void tma_load_kv(unsigned dst, const CUtensorMap* map
                ::"r"(dst), "l"(map), "r"(dim0), "r"(slot0), "r"(kvh), "r"(page), "r"(bar) : "memory");
 }
 
-__global__ void __launch_bounds__(U_THREADS, 2)
+__global__ void __launch_bounds__(U_THREADS, 1)
 attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                          const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          int page_size, int page_shift, UmmaMeta m, const int* __restrict__ tile_entry,
@@ -162,8 +171,8 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                          int* __restrict__ error_flag, float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
   pdl_enter();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_s[2];          // per buffer of scores: the tensor core is done
-  __shared__ __align__(8) unsigned long long bar_p[2];          // per buffer of scores: all 128 rows of P are written
+  __shared__ __align__(8) unsigned long long bar_s[2][2];       // per slot and buffer of scores: the tensor core is done
+  __shared__ __align__(8) unsigned long long bar_p[2][2];       // per slot and buffer of scores: all 128 rows of P are written
   __shared__ __align__(8) unsigned long long k_full[K_STAGES], k_free[K_STAGES];   // a key stage has landed / was read
   __shared__ __align__(8) unsigned long long v_full[V_STAGES], v_free[V_STAGES];
   __shared__ unsigned tmem_slot;
@@ -173,19 +182,20 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     if (threadIdx.x == 0) atomicExch(error_flag, 1);
     return;
   }
-  const unsigned sq = sbase, sk0 = sq + SQ_BYTES, sv0 = sk0 + K_STAGES * SKV_BYTES;
+  const unsigned sq0 = sbase, sk0 = sq0 + 2 * SQ_BYTES, sv0 = sk0 + K_STAGES * SKV_BYTES;
   const int tid = threadIdx.x, warp = tid >> 5;
   // tiles run last to first and heads fastest: the longest blocks (of every head) start first
   const int tile = gridDim.y - 1 - blockIdx.y;
   const int e = tile_entry[tile], q0 = tile_q0[tile], head = blockIdx.x;
-  const int rows = min(UM, m.entry_q_len[e] - q0);
-  if (rows <= 0) return;
+  const int rows_all = min(2 * UM, m.entry_q_len[e] - q0);
+  if (rows_all <= 0) return;
   const int tok0 = m.entry_q_start[e] + q0;
   const int pos0 = m.entry_ctx_start[e] + q0;
   const int kvh = head / (n_heads / n_kv);
   const int* bt = m.block_tables + (size_t)e * m.bt_stride;
-  const int kend = pos0 + rows;                                  // keys [.., kend) may be seen
-  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the first row may see
+  const int rows0 = min(UM, rows_all), rows1 = rows_all - rows0;  // rows of the two slots (the second may have none)
+  const int kend = pos0 + rows_all;                              // keys [.., kend) may be seen by the block's last row
+  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the block's first row may see
   // gridDim.z > 1: the key tiles are cut into n_splits consecutive parts, one block each; the parts leave
   // their unnormalised O and (maximum, sum) in scratch for the merge kernel.  Few query tiles over a long
   // context (a short portion of a long prompt) would otherwise leave most of the GPU idle.
@@ -193,26 +203,33 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int t_all0 = kfirst / UN, n_all = (kend - 1) / UN - t_all0 + 1;
   const int per_split = (n_all + n_splits - 1) / n_splits;
   const int t_begin = t_all0 + split * per_split, n_t = min(per_split, n_all - split * per_split);
-  const size_t part_row0 = (((size_t)tile * n_heads + head) * n_splits + split) * UM;
+  const size_t part_row0 = (((size_t)tile * n_heads + head) * n_splits + split) * (2 * UM);
   if (n_t <= 0) {                                                // (block-uniform) nothing to do: a part that adds nothing
-    if (tid < rows) {
+    if (tid < rows_all) {
       part_ml[(part_row0 + tid) * 2] = -INFINITY;
       part_ml[(part_row0 + tid) * 2 + 1] = 0.0f;
     }
     return;
   }
+  // Which of the block's tiles a slot takes part in.  Both begin at the block's first tile (with a window the
+  // second slot's first tiles may lie wholly before its rows' windows: they come out masked).  The first slot
+  // stops where its last row's keys end, up to two tiles before the second; the second, when it has rows,
+  // takes every tile, so it is always the last to read a stage.
+  const int n_t0 = max(0, min(n_t, (pos0 + rows0 - 1) / UN + 1 - t_begin));
+  const int n_t1 = rows1 > 0 ? n_t : 0;
 
   if (tid == 0) {
     auto init = [](unsigned long long* b, int count) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(b)), "r"(count));
     };
-    init(&bar_s[0], 1), init(&bar_s[1], 1), init(&bar_p[0], 128), init(&bar_p[1], 128);
-    for (int i = 0; i < K_STAGES; ++i) init(&k_full[i], 1), init(&k_free[i], 1);
-    for (int i = 0; i < V_STAGES; ++i) init(&v_full[i], 1), init(&v_free[i], 1);
+    for (int sl = 0; sl < 2; ++sl)
+      for (int i = 0; i < 2; ++i) init(&bar_s[sl][i], 1), init(&bar_p[sl][i], UM);
+    for (int i = 0; i < K_STAGES; ++i) init(&k_full[i], 1), init(&k_free[i], 2);
+    for (int i = 0; i < V_STAGES; ++i) init(&v_full[i], 1), init(&v_free[i], 2);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;\n" ::"r"(smem_addr(&tmem_slot)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(smem_addr(&tmem_slot)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   int bt_first = 0;
@@ -224,14 +241,14 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       bt_first = b0;
     }
   }
-  // Q: row r (token tok0 + r), two panels of 64 dims; rows beyond the portion are zero
-  for (int idx = tid; idx < UM * 16 && tid < 128; idx += 128) {  // the softmax warps copy it, once
-    const int r = idx >> 4, c = idx & 15;
-    const bool ok = r < rows;
+  // Q of both slots: row r (token tok0 + r), two panels of 64 dims per slot; rows beyond the portion are zero
+  for (int idx = tid; idx < 2 * UM * 16 && tid < U_SOFTMAX; idx += U_SOFTMAX) {  // the softmax warps copy it, once
+    const int r = idx >> 4, c = idx & 15, sl = r >> 7, rr = r & (UM - 1);
+    const bool ok = r < rows_all;
     const bf16* src = q + (size_t)(tok0 + (ok ? r : 0)) * q_stride + (size_t)head * UD + c * 8;
-    cp_async16_u(sq + (unsigned)(c >> 3) * (UM * 128) + (unsigned)r * 128u + (unsigned)(((c & 7) ^ (r & 7)) << 4), src, ok);
+    cp_async16_u(sq0 + sl * SQ_BYTES + (unsigned)(c >> 3) * (UM * 128) + (unsigned)rr * 128u + (unsigned)(((c & 7) ^ (rr & 7)) << 4), src, ok);
   }
-  if (tid < 128) {
+  if (tid < U_SOFTMAX) {
     asm volatile("cp.async.commit_group;\n" ::);
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); // Q is visible to the tensor core
@@ -240,18 +257,15 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   __syncthreads();                                               // bt_s, barriers, tensor-memory address, Q
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem = tmem_slot;
-  const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 lanes
-  const unsigned tm_o = tmem + TM_O + lane_base;
 
-  // ---- the sixth warp copies the key and value tiles, a stage ahead of their use.  Key stage
-  // t % 3 is free once the scores of tile t - 3 are done, value stage t % 2 once P V of tile t - 2 is (the
-  // issuing thread commits onto k_free / v_free).  Order of the copies: K0 K1 V0 K2, then V(t) K(t+2).
-  if (warp == 5) {
+  // ---- the last two warps copy the key tiles and the value tiles, up to four tiles ahead of their use.  A
+  // stage is free once the MMAs of both slots that read it are done (each issuing thread commits onto k_free /
+  // v_free).  The boxes of a tile (a page and a 64-dim panel each) are issued by the lanes of the warp side by
+  // side, and keys and values by a warp each: issuing a box takes a thread over a hundred cycles, and one warp
+  // alone for the sixteen boxes of a step of 16-token pages held the tensor core up.
+  if (warp >= U_SOFTMAX / 32 + 2) {
     bool copy_failed = false;
     {
-      // The boxes of a tile (a page and a 64-dim panel each) are issued by the lanes of the warp side by side:
-      // one thread alone, looking up a page and issuing two boxes at a time, takes longer over a tile than the
-      // tensor core takes to use it.
       const int lane = tid & 31;
       const int box_slots = min(page_size, UN);                    // tokens per box: a page, or 64 of a longer page
       const int n_boxes = 2 * (UN / box_slots);                    // boxes of one tile of keys (or values)
@@ -268,38 +282,46 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                       kvh, page, bar);
         }
       };
-      auto copy_k = [&](int t) {
-        if (t >= n_t || copy_failed) return;
-        const int st = t % K_STAGES;
-        if (t >= K_STAGES && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&k_free[st]), (unsigned)((t / K_STAGES - 1) & 1)))) { copy_failed = true; return; }
-        copy_tile(&map_k, sk0 + st * SKV_BYTES, t, smem_addr(&k_full[st]));
-      };
-      auto copy_v = [&](int t) {
-        if (t >= n_t || copy_failed) return;
-        const int st = t % V_STAGES;
-        if (t >= V_STAGES && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&v_free[st]), (unsigned)((t / V_STAGES - 1) & 1)))) { copy_failed = true; return; }
-        copy_tile(&map_v, sv0 + st * SKV_BYTES, t, smem_addr(&v_full[st]));
-      };
-      copy_k(0), copy_k(1), copy_v(0), copy_k(2);
-      for (int t = 1; t < n_t && !copy_failed; ++t) copy_v(t), copy_k(t + 2);
+      const bool values = warp == U_SOFTMAX / 32 + 3;
+      const CUtensorMap* map = values ? &map_v : &map_k;
+      const unsigned s0 = values ? sv0 : sk0;
+      unsigned long long* full = values ? v_full : k_full;
+      unsigned long long* free_ = values ? v_free : k_free;
+      const int n_stages = values ? V_STAGES : K_STAGES;
+      for (int t = 0; t < n_t; ++t) {
+        const int st = t % n_stages;
+        if (t >= n_stages && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&free_[st]), (unsigned)((t / n_stages - 1) & 1)))) { copy_failed = true; break; }
+        copy_tile(map, s0 + st * SKV_BYTES, t, smem_addr(&full[st]));
+      }
     }
     // Every copy that was issued is waited for by the issuing thread before its MMA, and the block ends
     // only after the last MMA: nothing is in flight when this warp leaves.  (If a wait ran out, the two
     // barriers below still hold the block together and the error is recorded.)
     const int any = __syncthreads_or(copy_failed);
     __syncthreads();
-    if (any && tid == 160) atomicExch(error_flag, 1);
+    if (any && (tid & 31) == 0) atomicExch(error_flag, 1);
     return;
   }
 
   constexpr unsigned IDESC_QK = umma_idesc(UM, UN, 0), IDESC_PV = umma_idesc(UM, UD, 1);
-  // ---- the fifth warp: one thread issues every MMA.  S(t) = Q K(t)^T into the scores buffer t & 1, 8 steps of
-  // 16 dims; a commit covers every MMA issued before it.  For tile i it waits until all rows of P are written,
-  // then issues P V of tile i and the scores of tile i + 2, which overwrite the scores and P of tile i.
-  if (warp == 4) {
+  // ---- the ninth and tenth warp: one thread of each issues the MMAs of its slot.  S(t) = Q K(t)^T into the
+  // slot's scores buffer t & 1 (8 steps of 16 dims); for tile i, once all the slot's rows of P are written,
+  // P V of tile i and then the scores of tile i + 2, which overwrite the scores and P of tile i; one commit on
+  // the slot's barrier covers both.  The tensor core works on one slot while the threads of the other are at
+  // their scores.
+  if (warp == U_SOFTMAX / 32 || warp == U_SOFTMAX / 32 + 1) {
     bool mma_failed = false;
     if ((tid & 31) == 0) {
-      auto issue_qk = [&](int t) {
+      const int sl = warp - U_SOFTMAX / 32;
+      const int n_mine = sl ? n_t1 : n_t0, n_other = sl ? n_t0 : n_t1;
+      const unsigned tm = tmem + sl * TM_SLOT, sq = sq0 + sl * SQ_BYTES;
+      // a stage goes back to the copy warp after two arrivals: one from each slot, or both from the only
+      // slot that reads the tile
+      auto hand_back = [&](unsigned long long* bar, int t) {
+        umma_commit(smem_addr(bar));
+        if (t >= n_other) umma_commit(smem_addr(bar));
+      };
+      auto issue_qk = [&](int t) {                                 // the slot's scores of tile t
         const int st = t % K_STAGES;
         if (!mbar_wait_u(smem_addr(&k_full[st]), (unsigned)((t / K_STAGES) & 1))) { mma_failed = true; return; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -308,43 +330,49 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
         for (int k = 0; k < 8; ++k) {
           const unsigned long long da = umma_desc(sq + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
           const unsigned long long db = umma_desc(sk + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
-          umma_f16(tmem + TM_S + (t & 1) * UN, da, db, IDESC_QK, k > 0);
+          umma_f16(tm + TM_S + (t & 1) * UN, da, db, IDESC_QK, k > 0);
         }
-        umma_commit(smem_addr(&k_free[st]));
-        umma_commit(smem_addr(&bar_s[t & 1]));
+        hand_back(&k_free[st], t);
+        umma_commit(smem_addr(&bar_s[sl][t & 1]));
       };
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      issue_qk(0);
-      if (n_t > 1 && !mma_failed) issue_qk(1);
-      for (int i = 0; i < n_t && !mma_failed; ++i) {
-        if (!mbar_wait_u(smem_addr(&bar_p[i & 1]), (unsigned)((i >> 1) & 1))) { mma_failed = true; break; }
+      for (int t = 0; t < 2 && t < n_mine && !mma_failed; ++t) issue_qk(t);
+      for (int i = 0; i < n_mine && !mma_failed; ++i) {
+        if (!mbar_wait_u(smem_addr(&bar_p[sl][i & 1]), (unsigned)((i >> 1) & 1))) { mma_failed = true; break; }
         const int st = i % V_STAGES;
         if (!mbar_wait_u(smem_addr(&v_full[st]), (unsigned)((i / V_STAGES) & 1))) { mma_failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const unsigned sv = sv0 + st * SKV_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {                           // O += P V, 4 steps of 16 keys; P from tensor memory
+        for (int kk = 0; kk < 4; ++kk) {                // O += P V, 4 steps of 16 keys; P from tensor memory
           const unsigned long long db = umma_desc(sv + kk * 16 * 128, UN * 128, 1024);   // leading offset = panel stride
-          const unsigned a_t = tmem + TM_S + (i & 1) * UN + kk * 8;
           const unsigned acc = (i | kk) != 0;
           asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                       ::"r"(tmem + TM_O), "r"(a_t), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
+                       ::"r"(tm + TM_O), "r"(tm + TM_S + (i & 1) * UN + kk * 8), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
         }
-        umma_commit(smem_addr(&v_free[st]));
-        if (i + 2 < n_t) issue_qk(i + 2);                          // its commit covers this P V as well
-        else umma_commit(smem_addr(&bar_s[i & 1]));
+        hand_back(&v_free[st], i);
+        if (i + 2 < n_mine) issue_qk(i + 2);                       // its commit covers this P V as well
+        else umma_commit(smem_addr(&bar_s[sl][i & 1]));
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     const int any = __syncthreads_or(mma_failed);
     __syncthreads();                                             // (the softmax warps write the output between these two)
-    if (any && tid == 128) atomicExch(error_flag, 1);
+    if (any && (tid & 31) == 0) atomicExch(error_flag, 1);
     return;
   }
 
+  // ---- the softmax threads: thread r of slot sl owns row r of that query tile
+  const int sl = tid >> 7, row = tid & (UM - 1);
+  const int my_n = sl ? n_t1 : n_t0, my_rows = sl ? rows1 : rows0;
+  const int my_pos0 = pos0 + sl * UM;
+  const int my_kend = my_pos0 + my_rows;
+  const int my_kfirst = window > 0 ? max(0, my_pos0 - window + 1) : 0;
+  const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 lanes
+  const unsigned tm_base = tmem + sl * TM_SLOT + lane_base, tm_o = tm_base + TM_O;
   float mrow = -INFINITY, lrow = 0.0f;
   const float sl2 = scale * LOG2E_U;
-  const int p_row = pos0 + tid;                                   // this thread's query position
+  const int p_row = my_pos0 + row;                                // this thread's query position
   bool failed = false;
 
   // O accumulates in tensor memory over all key tiles.  The running maximum of a row is only moved when a
@@ -353,14 +381,14 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   // rescaling.  When it is moved, the thread multiplies its row of O in tensor memory by 2^(old - new).
   //
   // The scores of tile i + 1 are computed by the tensor core while the threads work on tile i (two buffers
-  // of scores).  MMAs issued in iteration i: P V of tile i, then the scores of tile i + 2, then a commit on
-  // the barrier of buffer i & 1; so that barrier's completion number i / 2 (parity (i >> 1) & 1) says that
-  // the scores of tile i are there, and with them P V up to tile i - 2.
+  // of scores per slot).  MMAs issued for a slot in iteration i: P V of tile i, then the scores of tile i + 2,
+  // then a commit on the barrier of buffer i & 1; so that barrier's completion number i / 2 (parity
+  // (i >> 1) & 1) says that the scores of tile i are there, and with them P V up to tile i - 2.
   constexpr float RESCALE_STEP = 8.0f;
-  for (int i = 0; i < n_t; ++i) {
-    const unsigned tm_s = tmem + TM_S + (i & 1) * UN + lane_base;  // scores of this tile; P goes over their first half
+  for (int i = 0; i < my_n; ++i) {
+    const unsigned tm_s = tm_base + TM_S + (i & 1) * UN;           // scores of this tile; P goes over their first half
     // the outcome of a wait is made the same for the whole warp, whose tensor-memory loads and stores are warp-wide
-    if (__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[i & 1]), (unsigned)((i >> 1) & 1)))) {
+    if (__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[sl][i & 1]), (unsigned)((i >> 1) & 1)))) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const int key0 = (t_begin + i) * UN;
       // this thread's row of scores
@@ -373,11 +401,11 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 #pragma unroll
         for (int c = 0; c < 32; ++c) { s[c] = __uint_as_float(r0[c]); s[32 + c] = __uint_as_float(r1[c]); }
       }
-      if (key0 + UN - 1 > pos0 || window > 0 || key0 < kfirst || key0 + UN > kend) {   // diagonal, window, edges
+      if (key0 + UN - 1 > my_pos0 || window > 0 || key0 < my_kfirst || key0 + UN > my_kend) {   // diagonal, window, edges
 #pragma unroll
         for (int c = 0; c < UN; ++c) {
           const int key = key0 + c;
-          const bool vis = key <= p_row && key < kend && (window <= 0 || key > p_row - window);
+          const bool vis = key <= p_row && key < my_kend && (window <= 0 || key > p_row - window);
           if (!vis) s[c] = -INFINITY;
         }
       }
@@ -425,7 +453,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       // it when any of its rows needs it.  O must then be complete up to tile i - 1: the commit of iteration
       // i - 1 (completion number (i - 1) / 2 + 1 of the other buffer's barrier) says so.
       if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-        if (!__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[(i + 1) & 1]), (unsigned)((((i - 1) >> 1) + 1) & 1)))) failed = true;
+        if (!__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[sl][(i + 1) & 1]), (unsigned)((((i - 1) >> 1) + 1) & 1)))) failed = true;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (!failed) {
 #pragma unroll
@@ -450,40 +478,45 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     }
     if (failed) break;                                             // the issuing warp's wait for P will run out too
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(&bar_p[i & 1])) : "memory");   // this row of P is written
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(&bar_p[sl][i & 1])) : "memory");   // this row of P is written
   }
-  // the commit of the last iteration (buffer (n_t - 1) & 1, completion number (n_t - 1) / 2 + 1) covers the last P V
-  if (!failed && !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[(n_t - 1) & 1]), (unsigned)((((n_t - 1) >> 1) + 1) & 1))))
+  // the slot's commit of its last iteration (buffer (n - 1) & 1, completion number (n - 1) / 2 + 1) covers its last P V
+  if (my_n > 0 && !failed &&
+      !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[sl][(my_n - 1) & 1]), (unsigned)((((my_n - 1) >> 1) + 1) & 1))))
     failed = true;
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const int any_failed = __syncthreads_or(failed);
+  const bool mine = row < my_rows;
   if (!any_failed && n_splits > 1) {
     // unnormalised O, and the row's maximum (in exponent units) and sum, for the merge kernel
-    float* po = part_o + (part_row0 + (tid < rows ? tid : 0)) * UD;
+    const size_t prow = part_row0 + sl * UM + (mine ? row : 0);
+    if (my_n > 0) {
+      float* po = part_o + prow * UD;
 #pragma unroll
-    for (int j = 0; j < UD / 32; ++j) {
-      unsigned r[32];
-      tmem_ld32_nowait(tm_o + j * 32, r);
-      tmem_ld_wait();
-      if (tid < rows) {
+      for (int j = 0; j < UD / 32; ++j) {
+        unsigned r[32];
+        tmem_ld32_nowait(tm_o + j * 32, r);
+        tmem_ld_wait();
+        if (mine) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(po + j * 32 + c * 4) = make_uint4(r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(po + j * 32 + c * 4) = make_uint4(r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
+        }
       }
     }
-    if (tid < rows) {
-      part_ml[(part_row0 + tid) * 2] = mrow == -INFINITY ? -INFINITY : mrow * sl2;
-      part_ml[(part_row0 + tid) * 2 + 1] = lrow;
+    if (mine) {
+      part_ml[prow * 2] = (my_n > 0 && mrow != -INFINITY) ? mrow * sl2 : -INFINITY;
+      part_ml[prow * 2 + 1] = my_n > 0 ? lrow : 0.0f;
     }
-  } else if (!any_failed) {
+  } else if (!any_failed && my_n > 0) {
     const float inv = lrow > 0.0f ? 1.0f / lrow : 0.0f;
-    bf16* dst = out + (size_t)(tok0 + (tid < rows ? tid : 0)) * out_stride + (size_t)head * UD;
+    bf16* dst = out + (size_t)(tok0 + sl * UM + (mine ? row : 0)) * out_stride + (size_t)head * UD;
 #pragma unroll
     for (int j = 0; j < UD / 32; ++j) {                            // warp-wide loads; rows beyond the portion are not stored
       unsigned r[32];
       tmem_ld32_nowait(tm_o + j * 32, r);
       tmem_ld_wait();
-      if (tid < rows) {
+      if (mine) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint4 v;
@@ -498,7 +531,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;\n" ::"r"(tmem) : "memory");
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
   if (any_failed && tid == 0) atomicExch(error_flag, 1);
 }
 
@@ -514,13 +547,13 @@ attn_prefill_umma_merge_kernel(const float* __restrict__ part_o, const float* __
   __shared__ float ml_s[MERGE_ROWS][MERGE_MAX_SPLITS][2];
   const int head = blockIdx.x, tile = blockIdx.y, r0 = blockIdx.z * MERGE_ROWS, d = threadIdx.x;
   const int e = tile_entry[tile], q0 = tile_q0[tile];
-  const int rows = min(UM, m.entry_q_len[e] - q0);
+  const int rows = min(2 * UM, m.entry_q_len[e] - q0);
   if (r0 >= rows) return;
   const int tok0 = m.entry_q_start[e] + q0;
-  const size_t base = ((size_t)tile * n_heads + head) * n_splits * UM;
+  const size_t base = ((size_t)tile * n_heads + head) * n_splits * (2 * UM);
   for (int i = threadIdx.x; i < MERGE_ROWS * n_splits; i += UD) {
     const int rr = i / n_splits, sp = i - rr * n_splits;
-    const float2 v = r0 + rr < rows ? *reinterpret_cast<const float2*>(part_ml + (base + (size_t)sp * UM + r0 + rr) * 2)
+    const float2 v = r0 + rr < rows ? *reinterpret_cast<const float2*>(part_ml + (base + (size_t)sp * (2 * UM) + r0 + rr) * 2)
                                     : make_float2(-INFINITY, 0.0f);
     ml_s[rr][sp][0] = v.x;
     ml_s[rr][sp][1] = v.y;
@@ -538,7 +571,7 @@ attn_prefill_umma_merge_kernel(const float* __restrict__ part_o, const float* __
       if (ms == -INFINITY) continue;                               // a part that saw nothing (its O was not written)
       const float f = ex2(ms - mm);
       l += ml_s[rr][sp][1] * f;
-      acc += part_o[(base + (size_t)sp * UM + r) * UD + d] * f;
+      acc += part_o[(base + (size_t)sp * (2 * UM) + r) * UD + d] * f;
     }
     out[(size_t)(tok0 + r) * out_stride + (size_t)head * UD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
   }
@@ -573,21 +606,12 @@ IFX_API int ifx_attn_prefill_umma_plan(int n_tiles, int n_heads, int max_key_til
   if (n_tiles < 1 || n_heads < 1) return 1;
   static int resident = 0;
   if (!resident) {
-    // Blocks per SM by shared memory and registers.  (The occupancy query answers 1 for this kernel, whose
-    // two blocks take an SM's shared memory to the byte, while two do run side by side.)
-    int dev = 0, sms = 0, smem_sm = 0, smem_reserved = 0, regs_sm = 0;
-    cudaFuncAttributes fa;
+    // one block per SM: a block takes all 512 columns of an SM's tensor memory
+    int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&smem_reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev) != cudaSuccess ||
-        cudaFuncGetAttributes(&fa, attn_prefill_umma_kernel) != cudaSuccess)
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       return 1;
-    const int by_smem = smem_sm / (SMEM_UMMA + (int)fa.sharedSizeBytes + smem_reserved);
-    const int by_regs = regs_sm / (fa.numRegs * U_THREADS > 0 ? fa.numRegs * U_THREADS : 1);
-    const int per_sm = by_smem < by_regs ? by_smem : by_regs;
-    resident = per_sm * sms > 0 ? per_sm * sms : sms;
+    resident = sms > 0 ? sms : 1;
   }
   const long long blocks = (long long)n_tiles * n_heads;
   int s = (int)(resident / blocks);
@@ -596,10 +620,10 @@ IFX_API int ifx_attn_prefill_umma_plan(int n_tiles, int n_heads, int max_key_til
   return s < 1 ? 1 : s;
 }
 
-// Prompt portions, head_dim 128, query tiles of 128 tokens of one entry (tile_entry / tile_q0).
+// Prompt portions, head_dim 128, query tiles of 256 tokens of one entry (tile_entry / tile_q0).
 // q rows, out rows, k_layer and v_layer 16-byte aligned.  error_flag: a device int set to 1 if a bounded
 // wait inside the kernel ran out (the output is then invalid).  n_splits > 1: scratch part_o float32
-// [n_tiles * n_heads * n_splits * 128 * 128] (16-byte aligned) and part_ml float32 [n_tiles * n_heads * n_splits * 128 * 2].
+// [n_tiles * n_heads * n_splits * 256 * 128] (16-byte aligned) and part_ml float32 [n_tiles * n_heads * n_splits * 256 * 2].
 IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, long long out_stride,
                                   void* k_layer, void* v_layer, long long page_stride, int page_size,
                                   const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_q0,
@@ -628,7 +652,7 @@ IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, 
                       tile_entry, tile_q0, n_heads, n_kv, scale, window, error_flag, part_o, part_ml, n_splits);
   if (!ifx_rc) ifx_rc = IFX_LAUNCH_CHECK();
   if (ifx_rc || n_splits == 1) return ifx_rc;
-  ifx_rc = launch_pdl(attn_prefill_umma_merge_kernel, dim3(n_heads, n_tiles, UM / MERGE_ROWS), dim3(UD), 0, stream, (const float*)part_o,
+  ifx_rc = launch_pdl(attn_prefill_umma_merge_kernel, dim3(n_heads, n_tiles, 2 * UM / MERGE_ROWS), dim3(UD), 0, stream, (const float*)part_o,
                       (const float*)part_ml, (bf16*)out, out_stride, m, tile_entry, tile_q0, n_heads, n_splits);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }

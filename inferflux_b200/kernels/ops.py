@@ -456,7 +456,7 @@ def attn_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
 
 
 UMMA_ATTENTION_HEAD_DIM = 128
-UMMA_TILE = 128
+UMMA_ATTENTION_TILE = 256          # tokens per query tile of attn_prefill_umma
 
 
 def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer: torch.Tensor,
@@ -466,7 +466,7 @@ def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
                       n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
                       n_splits: int = 1) -> torch.Tensor:
     """Attention of prompt portions with tcgen05.mma and tensor-memory
-    accumulators (bfloat16, head_dim 128); query tiles of 128 tokens listed by
+    accumulators (bfloat16, head_dim 128); query tiles of 256 tokens listed by
     tile_entry / tile_q0.  With ``n_splits`` > 1 the keys of every tile are cut
     into that many parts (see :func:`attn_prefill_umma_splits`), merged by a
     second kernel.  A bounded wait that runs out sets the device error flag
@@ -484,7 +484,7 @@ def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
     part_o = part_ml = None
     global launch_count
     if n_splits > 1:
-        rows = n_tiles * n_heads * n_splits * 128
+        rows = n_tiles * n_heads * n_splits * UMMA_ATTENTION_TILE
         part_o = torch.empty(rows * head_dim, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
         launch_count += 1          # the merge kernel

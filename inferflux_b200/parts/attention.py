@@ -32,7 +32,7 @@ from .linear import Linear
 
 QUERY_TILE = 16     # tokens per query tile of the generic attention kernel
 CHUNK_TILE = 64     # tokens per query tile of the mma.sync kernel for prompt portions
-UMMA_TILE = 128     # tokens per query tile of the tcgen05 kernel for prompt portions
+UMMA_TILE = ops.UMMA_ATTENTION_TILE   # tokens per query tile of the tcgen05 kernel for prompt portions (256)
 
 
 def contexts_skewed(lengths) -> bool:

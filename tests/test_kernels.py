@@ -289,7 +289,7 @@ def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, 
                                nh, nkv, hd, scale, window or 0)
     else:
         if ctiles and umma:
-            utiles = [(e, q0) for e, (c, ql) in enumerate(entries) if ql > 1 for q0 in range(0, ql, 128)]
+            utiles = [(e, q0) for e, (c, ql) in enumerate(entries) if ql > 1 for q0 in range(0, ql, ops.UMMA_ATTENTION_TILE)]
             te, tq = it([t[0] for t in utiles]).to(DEV), it([t[1] for t in utiles]).to(DEV)
             for splits in (1, 2, 5):                      # the keys of a query tile in one part and cut into parts
                 out_u = out.clone()
