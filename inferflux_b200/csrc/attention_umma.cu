@@ -151,6 +151,7 @@ constexpr int SMEM_UMMA = 2 * SQ_BYTES + (K_STAGES + V_STAGES) * SKV_BYTES;
 // Tensor memory, all 512 columns, per slot 256: S of even tiles 64 | S of odd tiles 64 | O 128.  P (64 packed
 // bfloat16 = 32 columns) is written over the first half of the scores it was made from.
 constexpr unsigned TM_SLOT = 256, TM_S = 0, TM_O = 128;
+constexpr int XCH_STRIDE = UD + 4;   // floats a row of the exchange between the two slots of one query tile (O, maximum, sum)
 
 // One TMA box of the paged cache into shared memory: 64 dims (one 128-byte panel row) x box_slots tokens of
 // one page and kv head, written in the 128-byte swizzle that the MMA descriptors expect (the swizzle goes by
@@ -215,8 +216,13 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   // second slot's first tiles may lie wholly before its rows' windows: they come out masked).  The first slot
   // stops where its last row's keys end, up to two tiles before the second; the second, when it has rows,
   // takes every tile, so it is always the last to read a stage.
-  const int n_t0 = max(0, min(n_t, (pos0 + rows0 - 1) / UN + 1 - t_begin));
-  const int n_t1 = rows1 > 0 ? n_t : 0;
+  //
+  // A block with one query tile only (a short portion, or a portion's last rows) deals its key tiles out to
+  // the two slots in turn instead: both hold the same rows, the first takes the even tiles and the second the
+  // odd ones, and their two results are put together at the end.
+  const bool narrow = rows1 == 0 && n_t >= 2;
+  const int n_t0 = narrow ? (n_t + 1) / 2 : max(0, min(n_t, (pos0 + rows0 - 1) / UN + 1 - t_begin));
+  const int n_t1 = narrow ? n_t / 2 : (rows1 > 0 ? n_t : 0);
 
   if (tid == 0) {
     auto init = [](unsigned long long* b, int count) {
@@ -298,6 +304,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     // only after the last MMA: nothing is in flight when this warp leaves.  (If a wait ran out, the two
     // barriers below still hold the block together and the error is recorded.)
     const int any = __syncthreads_or(copy_failed);
+    if (narrow) __syncthreads();                                 // (the two slots' results are put together here)
     __syncthreads();
     if (any && (tid & 31) == 0) atomicExch(error_flag, 1);
     return;
@@ -314,15 +321,17 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     if ((tid & 31) == 0) {
       const int sl = warp - U_SOFTMAX / 32;
       const int n_mine = sl ? n_t1 : n_t0, n_other = sl ? n_t0 : n_t1;
-      const unsigned tm = tmem + sl * TM_SLOT, sq = sq0 + sl * SQ_BYTES;
+      const unsigned tm = tmem + sl * TM_SLOT, sq = sq0 + (narrow ? 0 : sl) * SQ_BYTES;
+      // the slot's j-th tile among the block's
+      auto whole = [&](int j) { return narrow ? 2 * j + sl : j; };
       // a stage goes back to the copy warp after two arrivals: one from each slot, or both from the only
       // slot that reads the tile
       auto hand_back = [&](unsigned long long* bar, int t) {
         umma_commit(smem_addr(bar));
-        if (t >= n_other) umma_commit(smem_addr(bar));
+        if (narrow || t >= n_other) umma_commit(smem_addr(bar));
       };
-      auto issue_qk = [&](int t) {                                 // the slot's scores of tile t
-        const int st = t % K_STAGES;
+      auto issue_qk = [&](int j) {                                 // the scores of the slot's j-th tile
+        const int t = whole(j), st = t % K_STAGES;
         if (!mbar_wait_u(smem_addr(&k_full[st]), (unsigned)((t / K_STAGES) & 1))) { mma_failed = true; return; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const unsigned sk = sk0 + st * SKV_BYTES;
@@ -330,17 +339,17 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
         for (int k = 0; k < 8; ++k) {
           const unsigned long long da = umma_desc(sq + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
           const unsigned long long db = umma_desc(sk + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
-          umma_f16(tm + TM_S + (t & 1) * UN, da, db, IDESC_QK, k > 0);
+          umma_f16(tm + TM_S + (j & 1) * UN, da, db, IDESC_QK, k > 0);
         }
         hand_back(&k_free[st], t);
-        umma_commit(smem_addr(&bar_s[sl][t & 1]));
+        umma_commit(smem_addr(&bar_s[sl][j & 1]));
       };
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       for (int t = 0; t < 2 && t < n_mine && !mma_failed; ++t) issue_qk(t);
       for (int i = 0; i < n_mine && !mma_failed; ++i) {
         if (!mbar_wait_u(smem_addr(&bar_p[sl][i & 1]), (unsigned)((i >> 1) & 1))) { mma_failed = true; break; }
-        const int st = i % V_STAGES;
-        if (!mbar_wait_u(smem_addr(&v_full[st]), (unsigned)((i / V_STAGES) & 1))) { mma_failed = true; break; }
+        const int t = whole(i), st = t % V_STAGES;
+        if (!mbar_wait_u(smem_addr(&v_full[st]), (unsigned)((t / V_STAGES) & 1))) { mma_failed = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const unsigned sv = sv0 + st * SKV_BYTES;
 #pragma unroll
@@ -350,13 +359,14 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
           asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                        ::"r"(tm + TM_O), "r"(tm + TM_S + (i & 1) * UN + kk * 8), "l"(db), "r"(IDESC_PV), "r"(acc) : "memory");
         }
-        hand_back(&v_free[st], i);
+        hand_back(&v_free[st], t);
         if (i + 2 < n_mine) issue_qk(i + 2);                       // its commit covers this P V as well
         else umma_commit(smem_addr(&bar_s[sl][i & 1]));
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     const int any = __syncthreads_or(mma_failed);
+    if (narrow) __syncthreads();
     __syncthreads();                                             // (the softmax warps write the output between these two)
     if (any && (tid & 31) == 0) atomicExch(error_flag, 1);
     return;
@@ -364,8 +374,8 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 
   // ---- the softmax threads: thread r of slot sl owns row r of that query tile
   const int sl = tid >> 7, row = tid & (UM - 1);
-  const int my_n = sl ? n_t1 : n_t0, my_rows = sl ? rows1 : rows0;
-  const int my_pos0 = pos0 + sl * UM;
+  const int my_n = sl ? n_t1 : n_t0, my_rows = (sl && !narrow) ? rows1 : rows0;
+  const int my_pos0 = pos0 + (narrow ? 0 : sl * UM);
   const int my_kend = my_pos0 + my_rows;
   const int my_kfirst = window > 0 ? max(0, my_pos0 - window + 1) : 0;
   const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 lanes
@@ -390,7 +400,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     // the outcome of a wait is made the same for the whole warp, whose tensor-memory loads and stores are warp-wide
     if (__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[sl][i & 1]), (unsigned)((i >> 1) & 1)))) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const int key0 = (t_begin + i) * UN;
+      const int key0 = (t_begin + (narrow ? 2 * i + sl : i)) * UN;
       // this thread's row of scores
       float s[UN];
       {
@@ -486,8 +496,42 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     failed = true;
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const int any_failed = __syncthreads_or(failed);
-  const bool mine = row < my_rows;
-  if (!any_failed && n_splits > 1) {
+  // One query tile dealt out to two slots: the second slot hands its row of O, its maximum and its sum to the
+  // first through the key stages' shared memory (nothing reads or writes them any more), and the first puts
+  // the two together as the merge kernel would: O = O0 f0 + O1 f1 with f = 2^(own maximum - common maximum).
+  float f0 = 1.0f, f1 = 0.0f;
+  float m_out = (my_n > 0 && mrow != -INFINITY) ? mrow * sl2 : -INFINITY;       // in exponent units
+  const float4* other = nullptr;
+  if (narrow) {
+    float* xch = reinterpret_cast<float*>(smem_raw + 2 * SQ_BYTES);
+    float* xrow = xch + (size_t)row * XCH_STRIDE;
+    if (sl == 1 && !any_failed) {
+#pragma unroll
+      for (int j = 0; j < UD / 32; ++j) {
+        unsigned r[32];
+        tmem_ld32_nowait(tm_o + j * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(xrow + j * 32 + c * 4) = make_uint4(r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
+      }
+      xrow[UD] = m_out;
+      xrow[UD + 1] = lrow;
+    }
+    __syncthreads();
+    if (sl == 0) {
+      const float m1 = xrow[UD], l1 = xrow[UD + 1];
+      const float mm = fmaxf(m_out, m1);
+      f0 = m_out == -INFINITY ? 0.0f : ex2(m_out - mm);
+      f1 = m1 == -INFINITY ? 0.0f : ex2(m1 - mm);
+      lrow = lrow * f0 + l1 * f1;
+      m_out = mm;
+      other = reinterpret_cast<const float4*>(xrow);
+    }
+  }
+  const bool writer = !narrow || sl == 0;                          // (whole warps)
+  const bool mine = writer && row < my_rows;
+  if (!any_failed && writer && n_splits > 1) {
     // unnormalised O, and the row's maximum (in exponent units) and sum, for the merge kernel
     const size_t prow = part_row0 + sl * UM + (mine ? row : 0);
     if (my_n > 0) {
@@ -497,6 +541,16 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
         unsigned r[32];
         tmem_ld32_nowait(tm_o + j * 32, r);
         tmem_ld_wait();
+        if (narrow) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 o1 = other[j * 8 + c];
+            r[c * 4] = __float_as_uint(__uint_as_float(r[c * 4]) * f0 + o1.x * f1);
+            r[c * 4 + 1] = __float_as_uint(__uint_as_float(r[c * 4 + 1]) * f0 + o1.y * f1);
+            r[c * 4 + 2] = __float_as_uint(__uint_as_float(r[c * 4 + 2]) * f0 + o1.z * f1);
+            r[c * 4 + 3] = __float_as_uint(__uint_as_float(r[c * 4 + 3]) * f0 + o1.w * f1);
+          }
+        }
         if (mine) {
 #pragma unroll
           for (int c = 0; c < 8; ++c)
@@ -505,10 +559,10 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       }
     }
     if (mine) {
-      part_ml[prow * 2] = (my_n > 0 && mrow != -INFINITY) ? mrow * sl2 : -INFINITY;
+      part_ml[prow * 2] = m_out;
       part_ml[prow * 2 + 1] = my_n > 0 ? lrow : 0.0f;
     }
-  } else if (!any_failed && my_n > 0) {
+  } else if (!any_failed && writer && my_n > 0) {
     const float inv = lrow > 0.0f ? 1.0f / lrow : 0.0f;
     bf16* dst = out + (size_t)(tok0 + sl * UM + (mine ? row : 0)) * out_stride + (size_t)head * UD;
 #pragma unroll
@@ -516,6 +570,16 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       unsigned r[32];
       tmem_ld32_nowait(tm_o + j * 32, r);
       tmem_ld_wait();
+      if (narrow) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float4 o1 = other[j * 8 + c];
+          r[c * 4] = __float_as_uint(__uint_as_float(r[c * 4]) * f0 + o1.x * f1);
+          r[c * 4 + 1] = __float_as_uint(__uint_as_float(r[c * 4 + 1]) * f0 + o1.y * f1);
+          r[c * 4 + 2] = __float_as_uint(__uint_as_float(r[c * 4 + 2]) * f0 + o1.z * f1);
+          r[c * 4 + 3] = __float_as_uint(__uint_as_float(r[c * 4 + 3]) * f0 + o1.w * f1);
+        }
+      }
       if (mine) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -536,15 +600,20 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 }
 
 // The parts of a query tile's keys put together: block (head, tile, group of MERGE_ROWS rows), thread d takes
-// column d of the group's rows.  The (maximum, sum) pairs of the group go through shared memory, where every
-// thread finds each part's factor; the loads of O of different rows do not wait for one another.
-constexpr int MERGE_ROWS = 8, MERGE_MAX_SPLITS = 64;
+// column d of the group's rows.  The (maximum, sum) pairs of the group go through shared memory, where one
+// thread a row turns them into each part's factor 2^(its maximum - the common maximum) and the row's 1 / sum;
+// then every thread loads its column of eight parts at a time before it adds them up (in the order of the
+// parts, always), so that the loads do not wait for one another: with one load after the other the kernel
+// took longer than the attention it follows.
+constexpr int MERGE_ROWS = 8, MERGE_MAX_SPLITS = 64, MERGE_BATCH = 8;
 __global__ void __launch_bounds__(UD)
 attn_prefill_umma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                bf16* __restrict__ out, long long out_stride, UmmaMeta m,
                                const int* __restrict__ tile_entry, const int* __restrict__ tile_q0, int n_heads, int n_splits) {
   pdl_enter();
   __shared__ float ml_s[MERGE_ROWS][MERGE_MAX_SPLITS][2];
+  __shared__ float f_s[MERGE_ROWS][MERGE_MAX_SPLITS];
+  __shared__ float inv_s[MERGE_ROWS];
   const int head = blockIdx.x, tile = blockIdx.y, r0 = blockIdx.z * MERGE_ROWS, d = threadIdx.x;
   const int e = tile_entry[tile], q0 = tile_q0[tile];
   const int rows = min(2 * UM, m.entry_q_len[e] - q0);
@@ -559,21 +628,37 @@ attn_prefill_umma_merge_kernel(const float* __restrict__ part_o, const float* __
     ml_s[rr][sp][1] = v.y;
   }
   __syncthreads();
+  if (threadIdx.x < MERGE_ROWS) {
+    const int rr = threadIdx.x;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, ml_s[rr][sp][0]);
+    float l = 0.0f;
+    for (int sp = 0; sp < n_splits; ++sp) {                       // always in the order of the parts
+      const float ms = ml_s[rr][sp][0];
+      const float f = ms == -INFINITY ? 0.0f : ex2(ms - mm);       // a part that saw nothing: its O was not written
+      f_s[rr][sp] = f;
+      l += ml_s[rr][sp][1] * f;
+    }
+    inv_s[rr] = l > 0.0f ? 1.0f / l : 0.0f;
+  }
+  __syncthreads();
 #pragma unroll
   for (int rr = 0; rr < MERGE_ROWS; ++rr) {
     const int r = r0 + rr;
     if (r >= rows) continue;
-    float mm = -INFINITY;
-    for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, ml_s[rr][sp][0]);
-    float l = 0.0f, acc = 0.0f;
-    for (int sp = 0; sp < n_splits; ++sp) {                       // always in the order of the parts
-      const float ms = ml_s[rr][sp][0];
-      if (ms == -INFINITY) continue;                               // a part that saw nothing (its O was not written)
-      const float f = ex2(ms - mm);
-      l += ml_s[rr][sp][1] * f;
-      acc += part_o[(base + (size_t)sp * (2 * UM) + r) * UD + d] * f;
+    float acc = 0.0f;
+    for (int sp0 = 0; sp0 < n_splits; sp0 += MERGE_BATCH) {
+      float v[MERGE_BATCH], f[MERGE_BATCH];
+#pragma unroll
+      for (int k = 0; k < MERGE_BATCH; ++k) {
+        const int sp = sp0 + k;
+        f[k] = sp < n_splits ? f_s[rr][sp] : 0.0f;
+        v[k] = f[k] != 0.0f ? part_o[(base + (size_t)sp * (2 * UM) + r) * UD + d] : 0.0f;
+      }
+#pragma unroll
+      for (int k = 0; k < MERGE_BATCH; ++k) acc += v[k] * f[k];
     }
-    out[(size_t)(tok0 + r) * out_stride + (size_t)head * UD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    out[(size_t)(tok0 + r) * out_stride + (size_t)head * UD + d] = __float2bfloat16_rn(acc * inv_s[rr]);
   }
 }
 // One run's keys (or values) in the paged cache as a 4-D tensor for TMA: (dim, slot in the page, kv head, page),
