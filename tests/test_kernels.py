@@ -351,7 +351,7 @@ def test_attention_tensor_core(ops, nh, nkv, hd, ps, window, peaked):
 @pytest.mark.parametrize("peaked", [False, True])
 def test_attention_tcgen05_prompt_portions(ops, nh, nkv, ps, window, peaked):
     """The tcgen05 / tensor-memory kernel for prompt portions (head size 128), beside the decode kernel."""
-    entries = MIXED + [(0, 300), (200, 129), (5, 128)]
+    entries = MIXED + [(0, 300), (200, 129), (5, 128), (700, 260)]
     _attention_case(ops, torch.bfloat16, nh, nkv, 128, ps, window, entries, 23, peaked, fast=True, umma=True)
 
 
