@@ -13,6 +13,7 @@ through the scheduler, so several prompts share steps.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Union
 
@@ -277,11 +278,21 @@ class Engine:
             raise ValueError("one SamplingParams per prompt (or one for all)")
         rids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         guard = 0
-        while self.has_work():
-            self.step()
-            guard += 1
-            if guard > 10_000_000:
-                raise RuntimeError("generation made no progress")
+        # The collector of reference cycles is held off while the steps run: a step makes a few hundred small
+        # containers, which set it off again and again, and with the prompts' token lists alive a full
+        # collection takes tens of milliseconds, as long as ten decode steps.  (What a step makes is freed by
+        # its reference counts.)
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            while self.has_work():
+                self.step()
+                guard += 1
+                if guard > 10_000_000:
+                    raise RuntimeError("generation made no progress")
+        finally:
+            if collecting:
+                gc.enable()
         return [self._result(self._requests[rid]) for rid in rids]
 
     def run_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:

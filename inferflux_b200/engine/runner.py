@@ -62,6 +62,8 @@ class StepRunner:
         model.attach_states(self.state_storage)
         self.slab = MetadataSlab(1 << 16, self.device)
         self._graphs = {}
+        self._capture_stream = None
+        self._graph_pool = None
         self._graph_uses = {}
         self.graph_replays = 0
         self.steps = 0
@@ -291,11 +293,25 @@ class StepRunner:
             if device_tokens is not None:
                 ctx.token_ids.copy_(device_tokens[:r])
             logits = self.model.forward(ctx)                 # this step runs eagerly (and warms the libraries up)
-            torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             launches = ops.launch_count
-            with torch.cuda.graph(graph):                    # records the same launches; nothing runs
-                static_logits = self.model.forward(ctx)
+            # Recorded on a stream of its own between capture_begin and capture_end; nothing runs.  (The
+            # library's context manager would also hand every cached block back to the driver first, which
+            # the next prompt step then has to ask for again: several milliseconds each way.)
+            # All the graphs draw on one pool of memory: they replay one after the other on one stream, so what
+            # one needs between its kernels may lie where another's did, and a capture seldom has to ask the
+            # driver for memory.  What a graph hands out (its logits) stays its own while the record lives.
+            if self._capture_stream is None:
+                self._capture_stream = torch.cuda.Stream(device=self.device)
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            self._capture_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._capture_stream):
+                graph.capture_begin(pool=self._graph_pool)
+                try:
+                    static_logits = self.model.forward(ctx)
+                finally:
+                    graph.capture_end()
+            torch.cuda.current_stream().wait_stream(self._capture_stream)
             off = lambda t: int(t.storage_offset())
             self._graphs[key] = dict(slab=slab, graph=graph, logits=static_logits, used=slab._used,
                                      launches=ops.launch_count - launches,
