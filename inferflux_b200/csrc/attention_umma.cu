@@ -170,12 +170,16 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                          int page_size, int page_shift, UmmaMeta m, const int* __restrict__ tile_entry,
                          const int* __restrict__ tile_q0, int n_heads, int n_kv, float scale, int window,
                          int* __restrict__ error_flag, float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
-  pdl_enter();
+  // The kernel before this one (it rotates the queries and writes the new keys and values) is waited for only
+  // where its results are first read or the scratch of an earlier launch first written; until then the block
+  // reads the step's description, sets up its barriers and gets its tensor memory.
+  pdl_launch_dependents();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bar_s[2][2];       // per slot and buffer of scores: the tensor core is done
   __shared__ __align__(8) unsigned long long bar_p[2][2];       // per slot and buffer of scores: all 128 rows of P are written
   __shared__ __align__(8) unsigned long long k_full[K_STAGES], k_free[K_STAGES];   // a key stage has landed / was read
   __shared__ __align__(8) unsigned long long v_full[V_STAGES], v_free[V_STAGES];
+  __shared__ __align__(8) unsigned long long q_full;            // Q has landed (every softmax thread's copies)
   __shared__ unsigned tmem_slot;
   __shared__ int bt_s[BT_CACHE_U];
   const unsigned sbase = smem_addr(smem_raw);
@@ -206,6 +210,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int t_begin = t_all0 + split * per_split, n_t = min(per_split, n_all - split * per_split);
   const size_t part_row0 = (((size_t)tile * n_heads + head) * n_splits + split) * (2 * UM);
   if (n_t <= 0) {                                                // (block-uniform) nothing to do: a part that adds nothing
+    pdl_wait();
     if (tid < rows_all) {
       part_ml[(part_row0 + tid) * 2] = -INFINITY;
       part_ml[(part_row0 + tid) * 2 + 1] = 0.0f;
@@ -232,6 +237,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       for (int i = 0; i < 2; ++i) init(&bar_s[sl][i], 1), init(&bar_p[sl][i], UM);
     for (int i = 0; i < K_STAGES; ++i) init(&k_full[i], 1), init(&k_free[i], 2);
     for (int i = 0; i < V_STAGES; ++i) init(&v_full[i], 1), init(&v_free[i], 2);
+    init(&q_full, U_SOFTMAX);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
@@ -247,6 +253,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       bt_first = b0;
     }
   }
+  pdl_wait();
   // Q of both slots: row r (token tok0 + r), two panels of 64 dims per slot; rows beyond the portion are zero
   for (int idx = tid; idx < 2 * UM * 16 && tid < U_SOFTMAX; idx += U_SOFTMAX) {  // the softmax warps copy it, once
     const int r = idx >> 4, c = idx & 15, sl = r >> 7, rr = r & (UM - 1);
@@ -254,15 +261,18 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     const bf16* src = q + (size_t)(tok0 + (ok ? r : 0)) * q_stride + (size_t)head * UD + c * 8;
     cp_async16_u(sq0 + sl * SQ_BYTES + (unsigned)(c >> 3) * (UM * 128) + (unsigned)rr * 128u + (unsigned)(((c & 7) ^ (rr & 7)) << 4), src, ok);
   }
-  if (tid < U_SOFTMAX) {
-    asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); // Q is visible to the tensor core
-  }
+  if (tid < U_SOFTMAX) asm volatile("cp.async.commit_group;\n" ::);
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  __syncthreads();                                               // bt_s, barriers, tensor-memory address, Q
+  __syncthreads();                                               // bt_s, barriers, tensor-memory address
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem = tmem_slot;
+  // Q is waited for only now, and only by those who copy it: the first key and value tiles are on their way
+  // meanwhile.  The issuing threads wait on q_full before their first MMA.
+  if (tid < U_SOFTMAX) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); // Q is visible to the tensor core
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(&q_full)) : "memory");
+  }
 
   // ---- the last two warps copy the key tiles and the value tiles, up to four tiles ahead of their use.  A
   // stage is free once the MMAs of both slots that read it are done (each issuing thread commits onto k_free /
@@ -344,6 +354,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
         hand_back(&k_free[st], t);
         umma_commit(smem_addr(&bar_s[sl][j & 1]));
       };
+      if (!mbar_wait_u(smem_addr(&q_full), 0u)) mma_failed = true;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       for (int t = 0; t < 2 && t < n_mine && !mma_failed; ++t) issue_qk(t);
       for (int i = 0; i < n_mine && !mma_failed; ++i) {
@@ -495,14 +506,100 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       !__all_sync(0xffffffffu, mbar_wait_u(smem_addr(&bar_s[sl][(my_n - 1) & 1]), (unsigned)((((my_n - 1) >> 1) + 1) & 1))))
     failed = true;
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  const int any_failed = __syncthreads_or(failed);
-  // One query tile dealt out to two slots: the second slot hands its row of O, its maximum and its sum to the
-  // first through the key stages' shared memory (nothing reads or writes them any more), and the first puts
-  // the two together as the merge kernel would: O = O0 f0 + O1 f1 with f = 2^(own maximum - common maximum).
-  float f0 = 1.0f, f1 = 0.0f;
+  float f0 = 1.0f, f1 = 0.0f;                                     // (one query tile on two slots: see below)
   float m_out = (my_n > 0 && mrow != -INFINITY) ? mrow * sl2 : -INFINITY;       // in exponent units
   const float4* other = nullptr;
-  if (narrow) {
+  // A slot's result leaves the block: as unnormalised O with the row's maximum and sum for the merge kernel
+  // when the keys are cut into parts; else as bfloat16 rows of the output.  Both go through shared memory,
+  // the slot's own Q (read for the last time by the MMAs behind the wait above), so that a warp's stores are
+  // runs of 256 bytes of a row: a thread storing its own row 16 bytes at a time took three times as long.
+  const unsigned so = sq0 + (narrow ? 0 : sl) * SQ_BYTES;         // 128 rows of 256 bytes
+  const int lane = tid & 31;
+  // this thread's 32 columns j of O out of tensor memory (and, for a query tile on two slots, put together)
+  auto load_o = [&](int j, unsigned (&r)[32]) {
+    tmem_ld32_nowait(tm_o + j * 32, r);
+    tmem_ld_wait();
+    if (other) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float4 o1 = other[j * 8 + c];
+        r[c * 4] = __float_as_uint(__uint_as_float(r[c * 4]) * f0 + o1.x * f1);
+        r[c * 4 + 1] = __float_as_uint(__uint_as_float(r[c * 4 + 1]) * f0 + o1.y * f1);
+        r[c * 4 + 2] = __float_as_uint(__uint_as_float(r[c * 4 + 2]) * f0 + o1.z * f1);
+        r[c * 4 + 3] = __float_as_uint(__uint_as_float(r[c * 4 + 3]) * f0 + o1.w * f1);
+      }
+    }
+  };
+  // 16 bytes of this thread's row into the staging rows; piece p of row r lies at p ^ (r & 15)
+  auto stage = [&](int piece, unsigned a, unsigned b2, unsigned c, unsigned d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n"
+                 ::"r"(so + (unsigned)row * 256u + (unsigned)((piece ^ (row & 15)) << 4)), "r"(a), "r"(b2), "r"(c), "r"(d) : "memory");
+  };
+  // the warp stores the 32 staged rows that its own threads wrote, 256 bytes each, to dst + r * stride_bytes
+  auto store_rows = [&](unsigned char* dst, size_t stride_bytes) {
+    __syncwarp();
+    const int piece = lane & 15;
+#pragma unroll 4
+    for (int it = 0; it < 16; ++it) {
+      const int r = (warp & 3) * 32 + it * 2 + (lane >> 4);
+      if (r < my_rows) {
+        uint4 v;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                     : "r"(so + (unsigned)r * 256u + (unsigned)((piece ^ (r & 15)) << 4)));
+        *reinterpret_cast<uint4*>(dst + (size_t)r * stride_bytes + piece * 16) = v;
+      }
+    }
+    __syncwarp();
+  };
+  auto emit = [&]() {
+    if (n_splits > 1) {
+      const size_t prow0 = part_row0 + (narrow ? 0 : sl * UM);     // the slot's first row among the parts' rows
+      if (my_n > 0) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {                     // 64 float32 columns (256 bytes a row) at a time
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            unsigned r[32];
+            load_o(half * 2 + jj, r);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) stage(jj * 8 + c, r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
+          }
+          store_rows(reinterpret_cast<unsigned char*>(part_o + prow0 * UD + half * 64), UD * sizeof(float));
+        }
+      }
+      if (row < my_rows) {
+        part_ml[(prow0 + row) * 2] = m_out;
+        part_ml[(prow0 + row) * 2 + 1] = my_n > 0 ? lrow : 0.0f;
+      }
+      return;
+    }
+    if (my_n <= 0) return;
+    const float inv = lrow > 0.0f ? 1.0f / lrow : 0.0f;
+#pragma unroll
+    for (int j = 0; j < UD / 32; ++j) {
+      unsigned r[32];
+      load_o(j, r);
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        stage(j * 4 + c, pack2(__uint_as_float(r[c * 8]) * inv, __uint_as_float(r[c * 8 + 1]) * inv),
+              pack2(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv),
+              pack2(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv),
+              pack2(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv));
+    }
+    store_rows(reinterpret_cast<unsigned char*>(out + (size_t)(tok0 + (narrow ? 0 : sl * UM)) * out_stride + (size_t)head * UD),
+               (size_t)out_stride * sizeof(bf16));
+  };
+  int any_failed;
+  if (!narrow) {
+    // each slot writes as soon as it is done itself: the first, which ends up to two tiles before the second,
+    // does not wait for it
+    if (!failed) emit();
+    any_failed = __syncthreads_or(failed);
+  } else {
+    // One query tile dealt out to two slots: the second slot hands its row of O, its maximum and its sum to the
+    // first through the key stages' shared memory (nothing reads or writes them any more), and the first puts
+    // the two together as the merge kernel would: O = O0 f0 + O1 f1 with f = 2^(own maximum - common maximum).
+    any_failed = __syncthreads_or(failed);
     float* xch = reinterpret_cast<float*>(smem_raw + 2 * SQ_BYTES);
     float* xrow = xch + (size_t)row * XCH_STRIDE;
     if (sl == 1 && !any_failed) {
@@ -519,7 +616,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       xrow[UD + 1] = lrow;
     }
     __syncthreads();
-    if (sl == 0) {
+    if (sl == 0 && !any_failed) {
       const float m1 = xrow[UD], l1 = xrow[UD + 1];
       const float mm = fmaxf(m_out, m1);
       f0 = m_out == -INFINITY ? 0.0f : ex2(m_out - mm);
@@ -527,70 +624,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
       lrow = lrow * f0 + l1 * f1;
       m_out = mm;
       other = reinterpret_cast<const float4*>(xrow);
-    }
-  }
-  const bool writer = !narrow || sl == 0;                          // (whole warps)
-  const bool mine = writer && row < my_rows;
-  if (!any_failed && writer && n_splits > 1) {
-    // unnormalised O, and the row's maximum (in exponent units) and sum, for the merge kernel
-    const size_t prow = part_row0 + sl * UM + (mine ? row : 0);
-    if (my_n > 0) {
-      float* po = part_o + prow * UD;
-#pragma unroll
-      for (int j = 0; j < UD / 32; ++j) {
-        unsigned r[32];
-        tmem_ld32_nowait(tm_o + j * 32, r);
-        tmem_ld_wait();
-        if (narrow) {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const float4 o1 = other[j * 8 + c];
-            r[c * 4] = __float_as_uint(__uint_as_float(r[c * 4]) * f0 + o1.x * f1);
-            r[c * 4 + 1] = __float_as_uint(__uint_as_float(r[c * 4 + 1]) * f0 + o1.y * f1);
-            r[c * 4 + 2] = __float_as_uint(__uint_as_float(r[c * 4 + 2]) * f0 + o1.z * f1);
-            r[c * 4 + 3] = __float_as_uint(__uint_as_float(r[c * 4 + 3]) * f0 + o1.w * f1);
-          }
-        }
-        if (mine) {
-#pragma unroll
-          for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<uint4*>(po + j * 32 + c * 4) = make_uint4(r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
-        }
-      }
-    }
-    if (mine) {
-      part_ml[prow * 2] = m_out;
-      part_ml[prow * 2 + 1] = my_n > 0 ? lrow : 0.0f;
-    }
-  } else if (!any_failed && writer && my_n > 0) {
-    const float inv = lrow > 0.0f ? 1.0f / lrow : 0.0f;
-    bf16* dst = out + (size_t)(tok0 + sl * UM + (mine ? row : 0)) * out_stride + (size_t)head * UD;
-#pragma unroll
-    for (int j = 0; j < UD / 32; ++j) {                            // warp-wide loads; rows beyond the portion are not stored
-      unsigned r[32];
-      tmem_ld32_nowait(tm_o + j * 32, r);
-      tmem_ld_wait();
-      if (narrow) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float4 o1 = other[j * 8 + c];
-          r[c * 4] = __float_as_uint(__uint_as_float(r[c * 4]) * f0 + o1.x * f1);
-          r[c * 4 + 1] = __float_as_uint(__uint_as_float(r[c * 4 + 1]) * f0 + o1.y * f1);
-          r[c * 4 + 2] = __float_as_uint(__uint_as_float(r[c * 4 + 2]) * f0 + o1.z * f1);
-          r[c * 4 + 3] = __float_as_uint(__uint_as_float(r[c * 4 + 3]) * f0 + o1.w * f1);
-        }
-      }
-      if (mine) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint4 v;
-          v.x = pack2(__uint_as_float(r[c * 8]) * inv, __uint_as_float(r[c * 8 + 1]) * inv);
-          v.y = pack2(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv);
-          v.z = pack2(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv);
-          v.w = pack2(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + j * 32 + c * 8) = v;
-        }
-      }
+      emit();
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -610,15 +644,16 @@ __global__ void __launch_bounds__(UD)
 attn_prefill_umma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                bf16* __restrict__ out, long long out_stride, UmmaMeta m,
                                const int* __restrict__ tile_entry, const int* __restrict__ tile_q0, int n_heads, int n_splits) {
-  pdl_enter();
+  pdl_launch_dependents();
   __shared__ float ml_s[MERGE_ROWS][MERGE_MAX_SPLITS][2];
   __shared__ float f_s[MERGE_ROWS][MERGE_MAX_SPLITS];
   __shared__ float inv_s[MERGE_ROWS];
   const int head = blockIdx.x, tile = blockIdx.y, r0 = blockIdx.z * MERGE_ROWS, d = threadIdx.x;
-  const int e = tile_entry[tile], q0 = tile_q0[tile];
+  const int e = tile_entry[tile], q0 = tile_q0[tile];               // (the step's description: there before any kernel)
   const int rows = min(2 * UM, m.entry_q_len[e] - q0);
   if (r0 >= rows) return;
   const int tok0 = m.entry_q_start[e] + q0;
+  pdl_wait();                                                      // the parts are written
   const size_t base = ((size_t)tile * n_heads + head) * n_splits * (2 * UM);
   for (int i = threadIdx.x; i < MERGE_ROWS * n_splits; i += UD) {
     const int rr = i / n_splits, sp = i - rr * n_splits;
