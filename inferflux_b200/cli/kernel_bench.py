@@ -90,6 +90,20 @@ class Case:
                     if sw:
                         gu = torch.empty(rows, wrows, **bf)
                         self.extra.append(("library + swiglu", lambda i: ops.swiglu(torch.mm(x, ws[i].t(), out=gu), outg)))
+                    if name == "gemv_qkv" and hd == ops.QKV_EPILOGUE_HEAD_DIM:
+                        # the product with bias, rotation and cache write in its epilogue, beside library product + kernel
+                        ps = PAGE_SIZE
+                        pool = torch.zeros((rows + ps - 1) // ps, 1, 2, nkv, ps, hd, **bf)
+                        slots = torch.randperm(pool.shape[0] * ps, device=DEV)[:rows].to(torch.int32)
+                        bias = torch.randn(n, device=DEV)
+                        cos, sin = torch.randn(rows, hd // 2, device=DEV), torch.randn(rows, hd // 2, device=DEV)
+                        qo, qkv_lib = torch.empty(rows, nh * hd, **bf), torch.empty(rows, n, **bf)
+                        kv = (pool[0, 0, 0], pool[0, 0, 1], pool.stride(0), ps)
+                        self.extra.append(("tcgen05 with bias, rotation, cache write",
+                                           lambda i: ops.gemm_umma_qkv(x, ws[i], bias, qo, cos, sin, slots, *kv, nh, nkv)))
+                        self.extra.append(("library + bias, rotation, cache write",
+                                           lambda i: ops.qkv_rope_kv_write(torch.mm(x, ws[i].t(), out=qkv_lib), bias, cos, sin,
+                                                                           slots, *kv, nh, nkv, hd)))
             self.extra.append(("library", lambda i: torch.mm(x, ws[i].t())))
             if not sw and rows <= ops.SKINNY_MAX_ROWS:
                 sp = ops.gemm_umma_skinny_parts(n, k)

@@ -151,7 +151,21 @@ __device__ __forceinline__ void p_arrive_leader(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(bar & LEADER_MASK) : "memory");
 }
 
-// MODE 0: out = A W^T (+ bias); 1: SwiGLU of the two halves of W; 2: few rows of A.  In mode 2 the operands
+// What the epilogue of mode 3 needs: the product is the stacked q, k, v projection of head size 128, and the
+// epilogue adds the bias, rotates the query and key heads (rotate-half, the angles' cosines and sines per
+// token), writes the queries to out and the keys and values into the paged cache at each token's slot.
+struct QkvEpilogue {
+  const float* cos_t;       // [M, 64]
+  const float* sin_t;
+  const int* slot_map;      // [M]: page * page_size + offset; null or -1: nothing of that token is cached
+  bf16* k_cache;            // this layer's keys of page 0 / values of page 0
+  bf16* v_cache;
+  long long page_stride;    // elements between pages
+  int page_size, page_shift, n_heads, n_kv;
+};
+
+// MODE 0: out = A W^T (+ bias); 1: SwiGLU of the two halves of W; 2: few rows of A; 3: q, k, v with bias,
+// rotation and cache write (tiles of two heads of 128).  In mode 2 the operands
 // change places, so that the 256 rows of a tile are rows of the weights and its (few) columns the tokens: the
 // kernel is given the weights as map_a (M = their rows) and the activations as map_w (n_out = the tokens, all
 // in one tile), K is cut into k_parts parts that are tiles of their own, and the epilogue writes each part's
@@ -160,8 +174,8 @@ template <int MODE, typename TOut>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       TOut* __restrict__ out, long long ldo, const float* __restrict__ bias, int M, int n_out, int K,
-                      int tile_n, int* __restrict__ error_flag, int k_parts, long long part_stride) {
-  constexpr bool SWIGLU = MODE == 1, SKINNY = MODE == 2;
+                      int tile_n, int* __restrict__ error_flag, int k_parts, long long part_stride, QkvEpilogue qe) {
+  constexpr bool SWIGLU = MODE == 1, SKINNY = MODE == 2, QKV = MODE == 3;
   pdl_enter();
   extern __shared__ unsigned char g_smem_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * P_STAGES + 4];    // full[s], empty[s], acc_full[2], acc_empty[2]
@@ -280,6 +294,79 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             }
           }
         }
+      } else if (QKV) {
+        // The tile's 256 columns are two heads; this thread has one token's row of both.  Same operations, in
+        // the same order, as the kernel that does this after a library product (rope_math.cuh), on the float32
+        // sums themselves.
+        const int slot = (row < M && qe.slot_map) ? qe.slot_map[row] : -1;
+        const float* ct = qe.cos_t + (size_t)(row < M ? row : 0) * 64;
+        const float* st = qe.sin_t + (size_t)(row < M ? row : 0) * 64;
+        const size_t cache_at = slot >= 0 ? (size_t)(slot >> qe.page_shift) * qe.page_stride +
+                                                (size_t)(slot & (qe.page_size - 1)) * 128 : 0;
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+          const int head = n0 / 128 + hh;                          // among the nh + 2 nkv heads of the row
+          if (head >= qe.n_heads + 2 * qe.n_kv) break;             // (the same for the whole block)
+          const bool is_q = head < qe.n_heads, is_k = !is_q && head < qe.n_heads + qe.n_kv;
+          const int kvh = is_q ? 0 : head - qe.n_heads - (is_k ? 0 : qe.n_kv);
+          bf16* dst = is_q ? reinterpret_cast<bf16*>(out) + (size_t)(row < M ? row : 0) * ldo + (size_t)head * 128
+                           : (is_k ? qe.k_cache : qe.v_cache) + cache_at + (size_t)kvh * qe.page_size * 128;
+          const bool wanted = row < M && (is_q || slot >= 0);
+          const float* b = bias ? bias + (size_t)head * 128 : nullptr;
+          if (is_q || is_k) {
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {                 // pairs (i, i + 64), i in [32 half, 32 half + 32)
+              float lo[32], hi[32];
+              g_tmem_ld32(taddr + hh * 128 + half * 32, lo);
+              g_tmem_ld32(taddr + hh * 128 + 64 + half * 32, hi);
+              if (wanted) {
+                // 16 bytes a load: a thread reads 128 contiguous bytes of its token's cosines (a line of its own)
+                float cs[32], sn[32];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  *reinterpret_cast<float4*>(cs + 4 * i) = __ldg(reinterpret_cast<const float4*>(ct + half * 32) + i);
+                  *reinterpret_cast<float4*>(sn + 4 * i) = __ldg(reinterpret_cast<const float4*>(st + half * 32) + i);
+                }
+                if (b) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + half * 32) + i);
+                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(b + 64 + half * 32) + i);
+                    lo[4 * i] = __fadd_rn(lo[4 * i], b0.x); lo[4 * i + 1] = __fadd_rn(lo[4 * i + 1], b0.y);
+                    lo[4 * i + 2] = __fadd_rn(lo[4 * i + 2], b0.z); lo[4 * i + 3] = __fadd_rn(lo[4 * i + 3], b0.w);
+                    hi[4 * i] = __fadd_rn(hi[4 * i], b1.x); hi[4 * i + 1] = __fadd_rn(hi[4 * i + 1], b1.y);
+                    hi[4 * i + 2] = __fadd_rn(hi[4 * i + 2], b1.z); hi[4 * i + 3] = __fadd_rn(hi[4 * i + 3], b1.w);
+                  }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  const float x0 = lo[i], x1 = hi[i];
+                  lo[i] = __fmaf_rn(x0, cs[i], -__fmul_rn(x1, sn[i]));
+                  hi[i] = __fmaf_rn(x0, sn[i], __fmul_rn(x1, cs[i]));
+                }
+                store_row32<bf16>(dst + half * 32, lo, 32, true);
+                store_row32<bf16>(dst + 64 + half * 32, hi, 32, true);
+              }
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              float v[32];
+              g_tmem_ld32(taddr + hh * 128 + c * 32, v);
+              if (wanted) {
+                if (b) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + c * 32) + i);
+                    v[4 * i] = __fadd_rn(v[4 * i], b0.x); v[4 * i + 1] = __fadd_rn(v[4 * i + 1], b0.y);
+                    v[4 * i + 2] = __fadd_rn(v[4 * i + 2], b0.z); v[4 * i + 3] = __fadd_rn(v[4 * i + 3], b0.w);
+                  }
+                }
+                store_row32<bf16>(dst + c * 32, v, 32, true);
+              }
+            }
+          }
+        }
       } else if (SWIGLU) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -384,7 +471,7 @@ int launch_gemm_pair(const void* A, long long lda, const void* W, const float* b
   const int tiles = ((M + 255) / 256) * ((n_out + out_cols - 1) / out_cols);
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_a, map_w, (TOut*)out,
-                          ldo, bias, M, n_out, K, tile_n, error_flag, 1, 0ll);
+                          ldo, bias, M, n_out, K, tile_n, error_flag, 1, 0ll, QkvEpilogue{});
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 
@@ -411,6 +498,30 @@ int device_sms(int* sms) {
   return 0;
 }
 
+int launch_gemm_qkv(const void* A, long long lda, const void* W, const float* bias, bf16* q_out, long long ldo, int M, int K,
+                    const QkvEpilogue& qe, int* error_flag, cudaStream_t stream) {
+  auto kern = gemm_umma_pair_kernel<3, bf16>;
+  static bool ready = false;
+  if (!ready) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    ready = true;
+  }
+  int sms = 0;
+  int rc = device_sms(&sms);
+  if (rc) return rc;
+  const int n_out = (qe.n_heads + 2 * qe.n_kv) * 128, tile_n = 256;
+  CUtensorMap map_a, map_w;
+  rc = make_map(&map_a, A, M, K, lda, 128);
+  if (!rc) rc = make_map(&map_w, W, n_out, K, K, tile_n / 2);
+  if (rc) return rc;
+  const int tiles = ((M + 255) / 256) * ((n_out + tile_n - 1) / tile_n);
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_a, map_w, q_out,
+                          ldo, bias, M, n_out, K, tile_n, error_flag, 1, 0ll, qe);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
 int launch_gemm_skinny(const void* X, long long ldx, const void* W, float* out, long long ldo, int tokens, int n_out, int K,
                        int k_parts, long long part_stride, int* error_flag, cudaStream_t stream) {
   auto kern = gemm_umma_pair_kernel<2, float>;
@@ -431,7 +542,7 @@ int launch_gemm_skinny(const void* X, long long ldx, const void* W, float* out, 
   const int tiles = ((n_out + 255) / 256) * k_parts;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_w, map_x, out, ldo,
-                          (const float*)nullptr, n_out, tokens, K, tile_n, error_flag, k_parts, part_stride);
+                          (const float*)nullptr, n_out, tokens, K, tile_n, error_flag, k_parts, part_stride, QkvEpilogue{});
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 }  // namespace
@@ -476,4 +587,31 @@ IFX_API int ifx_gemm_umma_skinny_parts(int n_out, int K) {
   const int rc = device_sms(&sms);
   if (rc) return -rc;
   return skinny_parts(n_out, K, sms / 2);
+}
+
+// The stacked q, k, v projection of a step's tokens with everything that follows it before attention in its
+// epilogue: q_out[M, n_heads * 128] (rows ldo elements apart) receives the rotated queries, the paged cache the
+// rotated keys and the values at slot_map[token] (page * page_size + offset; -1: not cached).  Head size 128,
+// rotate-half over the whole head (cos_t, sin_t float32 [M, 64]), W [(n_heads + 2 n_kv) * 128, K] bfloat16,
+// bias float32 of that width or null.  A rows lda elements apart; K, lda, ldo and page_stride multiples of 8;
+// every pointer 16-byte aligned.
+IFX_API int ifx_gemm_umma_qkv(const void* A, long long lda, const void* W, const float* bias, void* q_out, long long ldo,
+                              const float* cos_t, const float* sin_t, const int* slot_map, void* k_layer, void* v_layer,
+                              long long page_stride, int page_size, int M, int K, int n_heads, int n_kv, int* error_flag,
+                              cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || (ldo & 7) || (page_stride & 7) || !error_flag || n_heads < 1 || n_kv < 0)
+    return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1)) || !cos_t || !sin_t) return IFX_ERR_UNSUPPORTED;
+  if (n_kv > 0 && (!slot_map || !k_layer || !v_layer)) return IFX_ERR_UNSUPPORTED;
+  if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)q_out | (uintptr_t)k_layer | (uintptr_t)v_layer | (uintptr_t)bias |
+       (uintptr_t)cos_t | (uintptr_t)sin_t) & 15)
+    return IFX_ERR_ALIGNMENT;
+  QkvEpilogue qe;
+  qe.cos_t = cos_t; qe.sin_t = sin_t; qe.slot_map = n_kv > 0 ? slot_map : nullptr;
+  qe.k_cache = (bf16*)k_layer; qe.v_cache = (bf16*)v_layer; qe.page_stride = page_stride;
+  qe.page_size = page_size; qe.page_shift = 0;
+  while ((1 << qe.page_shift) < page_size) ++qe.page_shift;
+  qe.n_heads = n_heads; qe.n_kv = n_kv;
+  return launch_gemm_qkv(A, lda, W, bias, (bf16*)q_out, ldo, M, K, qe, error_flag, stream);
 }

@@ -98,8 +98,8 @@ __global__ void qkv_rope_kv_write_kernel(T* __restrict__ qkv, const float* __res
 // Vector path (bfloat16, whole head rotated, head_dim a multiple of 16): a work item is 8
 // consecutive pairs (i .. i+7, i+half .. i+half+7) of one head: two 16-byte loads, two 16-byte stores
 // (rope_math.cuh).
-template <bool PART>
-__global__ void __launch_bounds__(PART ? 256 : 512) qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
+template <bool PART, int NB = 4>
+__global__ void __launch_bounds__(PART && NB > 1 ? 256 : 512) qkv_rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                 const int* __restrict__ slot_map, PagedKV kv,
                                                 int n_heads, int n_kv, int head_dim,
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(PART ? 256 : 512) qkv_rope_kv_write_bf16x8_ker
       const int h = w / hv, i = (w - h * hv) * 8;
       const int base = h * head_dim;
       uint4 p0, p1;
-      rope_pairs8<PART>(row, part, n_partials, part_stride, bias, ct, st, base + i, half, i, p0, p1);
+      rope_pairs8<PART, NB>(row, part, n_partials, part_stride, bias, ct, st, base + i, half, i, p0, p1);
       if (h < n_heads) {
         *reinterpret_cast<uint4*>(row + base + i) = p0;
         *reinterpret_cast<uint4*>(row + base + half + i) = p1;
@@ -139,19 +139,20 @@ __global__ void __launch_bounds__(PART ? 256 : 512) qkv_rope_kv_write_bf16x8_ker
     } else {
       const int e0 = (w - rot_items) * 8, h = e0 / head_dim, d = e0 - h * head_dim;
       *reinterpret_cast<uint4*>(vc + (size_t)h * kv.head_stride + d) =
-          biased8<PART>(row, part, n_partials, part_stride, bias, vbase + e0);
+          biased8<PART, NB>(row, part, n_partials, part_stride, bias, vbase + e0);
     }
   }
 }
 
-// The same for steps of many tokens (no partial sums): a block takes TOK consecutive tokens and a thread the same
-// 8-wide item of each of them, so that its loads of all TOK tokens are in flight together and it reads the bias
-// once.  The arithmetic per item is rope_pairs8 / biased8 as above.
-template <int TOK>
+// The same for steps of many tokens: a block takes TOK consecutive tokens and a thread the same 8-wide item of
+// each of them, so that its loads of all TOK tokens are in flight together and it reads the bias once.  The
+// arithmetic per item is rope_pairs8 / biased8 as above.  F32: the rows come as the product's float32 sums
+// (one slice, `sums`), and qkv only receives the rotated q.
+template <int TOK, bool F32>
 __global__ void __launch_bounds__(512) qkv_rope_kv_write_bf16x8_many_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                 const int* __restrict__ slot_map, PagedKV kv, int n_tokens,
-                                                int n_heads, int n_kv, int head_dim) {
+                                                int n_heads, int n_kv, int head_dim, const float* __restrict__ sums) {
   pdl_enter();
   const int t0 = blockIdx.x * TOK;
   const int half = head_dim / 2, hv = half / 8;
@@ -166,8 +167,8 @@ __global__ void __launch_bounds__(512) qkv_rope_kv_write_bf16x8_many_kernel(bf16
 #pragma unroll
       for (int k = 0; k < TOK; ++k) {
         const int t = min(t0 + k, n_tokens - 1);
-        rope_pairs8<false>(qkv + (size_t)t * width, nullptr, 0, 0, bias, cos_t + (size_t)t * half, sin_t + (size_t)t * half,
-                           base + i, half, i, p0[k], p1[k]);
+        rope_pairs8<F32, 1>(qkv + (size_t)t * width, F32 ? sums + (size_t)t * width : nullptr, 1, 0, bias,
+                            cos_t + (size_t)t * half, sin_t + (size_t)t * half, base + i, half, i, p0[k], p1[k]);
       }
 #pragma unroll
       for (int k = 0; k < TOK; ++k) {
@@ -193,7 +194,7 @@ __global__ void __launch_bounds__(512) qkv_rope_kv_write_bf16x8_many_kernel(bf16
 #pragma unroll
       for (int k = 0; k < TOK; ++k) {
         const int t = min(t0 + k, n_tokens - 1);
-        v[k] = biased8<false>(qkv + (size_t)t * width, nullptr, 0, 0, bias, vbase + e0);
+        v[k] = biased8<F32, 1>(qkv + (size_t)t * width, F32 ? sums + (size_t)t * width : nullptr, 1, 0, bias, vbase + e0);
       }
 #pragma unroll
       for (int k = 0; k < TOK; ++k) {
@@ -230,14 +231,21 @@ IFX_API int ifx_qkv_rope_kv_write(void* qkv, int dtype, const float* bias, const
   if (dtype == IFX_BF16 && rot_dim == head_dim && head_dim % 16 == 0 && aligned) {
     const int work8 = (n_heads + n_kv) * head_dim / 16 + n_kv * head_dim / 8;
     if (partials && (((uintptr_t)partials & 15) || n_partials < 1)) return IFX_ERR_ALIGNMENT;
-    const int th_max = partials ? 256 : 512;                    // the kernels' launch bounds
+    const int th_max = partials && n_partials > 1 ? 256 : 512;  // the kernels' launch bounds
     int th = 32;
     while (th < th_max && th < work8) th <<= 1;
     const long long part_stride = (long long)n_tokens * (n_heads + 2 * n_kv) * head_dim;
     constexpr int MANY_TOK = 4;
     if (!partials && n_kv > 0 && n_tokens >= 64 * MANY_TOK)
-      ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_many_kernel<MANY_TOK>, dim3((n_tokens + MANY_TOK - 1) / MANY_TOK), dim3(th), 0,
-                          stream, (bf16*)qkv, bias, cos_t, sin_t, slot_map, kv, n_tokens, n_heads, n_kv, head_dim);
+      ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_many_kernel<MANY_TOK, false>, dim3((n_tokens + MANY_TOK - 1) / MANY_TOK), dim3(th), 0,
+                          stream, (bf16*)qkv, bias, cos_t, sin_t, slot_map, kv, n_tokens, n_heads, n_kv, head_dim,
+                          (const float*)nullptr);
+    else if (partials && n_partials == 1 && n_kv > 0 && n_tokens >= 64 * MANY_TOK)
+      ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_many_kernel<MANY_TOK, true>, dim3((n_tokens + MANY_TOK - 1) / MANY_TOK), dim3(th), 0,
+                          stream, (bf16*)qkv, bias, cos_t, sin_t, slot_map, kv, n_tokens, n_heads, n_kv, head_dim, partials);
+    else if (partials && n_partials == 1)                         // one slice: no sums to batch, the wider block fits
+      ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel<true, 1>, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t,
+                          sin_t, slot_map, kv, n_heads, n_kv, head_dim, partials, n_partials, part_stride);
     else if (partials)
       ifx_rc = launch_pdl(qkv_rope_kv_write_bf16x8_kernel<true>, dim3(n_tokens), dim3(th), 0, stream, (bf16*)qkv, bias, cos_t, sin_t,
                           slot_map, kv, n_heads, n_kv, head_dim, partials, n_partials, part_stride);

@@ -76,6 +76,9 @@ def _lib():
         lib.ifx_gemm_umma_skinny.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int,
                                              c_void_p, c_void_p]
         lib.ifx_gemm_umma_skinny.restype = c_int
+        lib.ifx_gemm_umma_qkv.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.ifx_gemm_umma_qkv.restype = c_int
         lib.ifx_gemm_umma_skinny_parts.argtypes = [c_int, c_int]
         lib.ifx_gemm_umma_skinny_parts.restype = c_int
         lib.ifx_gemv_bf16_plan.argtypes = [c_int, c_int, c_int]
@@ -320,6 +323,44 @@ def gemm_umma(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     return out
 
 
+QKV_EPILOGUE_HEAD_DIM = 128     # the head size gemm_umma_qkv is written for
+
+
+def gemm_umma_qkv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                  cos: torch.Tensor, sin: torch.Tensor, slot_map: Optional[torch.Tensor],
+                  k_layer: Optional[torch.Tensor], v_layer: Optional[torch.Tensor], page_stride: int, page_size: int,
+                  n_heads: int, n_kv: int) -> torch.Tensor:
+    """The stacked q, k, v projection x[M, K] @ w[(nh + 2 nkv) * 128, K]^T of many
+    rows on the tcgen05 tensor cores, with what stands between it and attention
+    in its epilogue: bias, rotate-half rotation of the query and key heads
+    (``cos``, ``sin`` float32 [M, 64]), the queries as bfloat16 into the first
+    nh * 128 columns of ``q_out``'s rows, keys and values into the paged cache
+    at ``slot_map`` (page * page_size + offset).  Head size 128 only."""
+    m, k = x.shape
+    hd = QKV_EPILOGUE_HEAD_DIM
+    width = (n_heads + 2 * n_kv) * hd
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == (width, k),
+          "gemm_umma_qkv: bfloat16 x [M, K], w [(nh + 2 nkv) * 128, K]")
+    _need(q_out.dtype == torch.bfloat16 and q_out.dim() == 2 and q_out.shape[0] == m and q_out.shape[1] >= n_heads * hd
+          and q_out.stride(1) == 1 and q_out.stride(0) % 8 == 0, "gemm_umma_qkv: q_out bfloat16 [M, >= nh * 128]")
+    _need(k % 8 == 0 and x.stride(1) == 1 and (m == 1 or x.stride(0) % 8 == 0),
+          "gemm_umma_qkv: K and the row stride of x must be multiples of 8")
+    _need(tuple(cos.shape) == (m, hd // 2) and tuple(sin.shape) == (m, hd // 2) and cos.dtype == torch.float32
+          and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous(),
+          "gemm_umma_qkv: cos/sin float32 [M, 64]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == width, "gemm_umma_qkv: bias float32 [width]")
+    if n_kv:
+        _need(slot_map is not None and slot_map.dtype == torch.int32 and slot_map.numel() == m
+              and k_layer.dtype == torch.bfloat16 and v_layer.dtype == torch.bfloat16,
+              "gemm_umma_qkv: slot_map int32 [M], bfloat16 cache")
+    _check(_lib().ifx_gemm_umma_qkv(_ptr(x), x.stride(0) if m > 1 else k, _ptr(w), _ptr(bias), _ptr(q_out), q_out.stride(0),
+                                    _ptr(cos), _ptr(sin), _ptr(slot_map) if n_kv else None,
+                                    _ptr(k_layer) if n_kv else None, _ptr(v_layer) if n_kv else None, page_stride,
+                                    page_size, m, k, n_heads, n_kv, _ptr(error_flag(x.device)), _stream()), "gemm_umma_qkv")
+    return q_out
+
+
 SKINNY_MAX_ROWS = 256       # rows of x that gemm_umma_skinny takes
 
 
@@ -367,6 +408,17 @@ def gemv_k_splits(n: int, k: int, max_splits: int = 8) -> int:
             raise KernelError(f"gemv_k_splits: CUDA error {-s}")
         _gemv_plans[key] = s
     return _gemv_plans[key]
+
+
+_sm_counts = {}
+
+
+def sm_count(device) -> int:
+    """SMs of the device (where a kernel's plan is made on the host)."""
+    key = torch.device(device).index or 0
+    if key not in _sm_counts:
+        _sm_counts[key] = int(torch.cuda.get_device_properties(key).multi_processor_count)
+    return _sm_counts[key]
 
 
 _error_flags = {}

@@ -32,6 +32,7 @@ from .linear import Linear
 
 QUERY_TILE = 16     # tokens per query tile of the generic attention kernel
 CHUNK_TILE = 64     # tokens per query tile of the mma.sync kernel for prompt portions
+FUSED_QKV_MIN_ROWS = 2048   # from this many rows on q, k, v may come from the product with the fused epilogue
 UMMA_TILE = ops.UMMA_ATTENTION_TILE   # tokens per query tile of the tcgen05 kernel for prompt portions (256)
 
 
@@ -177,14 +178,27 @@ class GQAttention(Part):
             cos, sin = position
         else:
             cos = sin = torch.empty((n, 0), dtype=torch.float32, device=x.device)
+        g = run.kv_group
+        k_layer, v_layer, page_stride = ctx.kv.layer_views(g, run.kv_index)
+        if self._fused_qkv(x, n, cos):
+            # many rows: one kernel makes the product, adds the bias, rotates and writes the cache
+            q = torch.empty((n, self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
+            ops.gemm_umma_qkv(x, self.qkv.weight, self.qkv_bias, q, cos, sin, ctx.slot_maps[g] if nkv_w else None,
+                              k_layer if nkv_w else None, v_layer if nkv_w else None, page_stride, ctx.page_size,
+                              self.n_heads, nkv_w)
+            attn = torch.empty_like(q)
+            self.attend(q, attn, ctx, step, g, k_layer, v_layer, page_stride)
+            return self.o.forward(attn, out_dtype=x.dtype, allow_partials=True)
         # a few rows: the product may come as float32 partial sums, which the kernel below adds up
         partials = None
-        qkv = self.qkv.forward(x, allow_partials=2 * cos.shape[1] == self.head_dim and self.head_dim % 16 == 0)
+        # (q and k go on into the rotation and the scores: their product is taken as float32 sums wherever the
+        # kernel below can add such up; rounded to bfloat16 first, the logits behind 2,048 tokens were off by
+        # 2 % of the largest instead of 1.2 %)
+        sums = 2 * cos.shape[1] == self.head_dim and self.head_dim % 16 == 0
+        qkv = self.qkv.forward(x, allow_partials=sums, f32_sums=sums)
         if isinstance(qkv, PartialSums):
             partials = qkv.tensor
             qkv = torch.empty(partials.shape[1:], dtype=x.dtype, device=x.device)
-        g = run.kv_group
-        k_layer, v_layer, page_stride = ctx.kv.layer_views(g, run.kv_index)
         attn = torch.empty((n, self.n_heads * self.head_dim), dtype=qkv.dtype, device=x.device)
         if (step.n_decode == n and not step.n_chunk_tiles and nkv_w and qkv.dtype == torch.bfloat16
                 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and 2 * cos.shape[1] == self.head_dim
@@ -198,6 +212,27 @@ class GQAttention(Part):
                               ctx.page_size, self.n_heads, nkv_w, self.head_dim, partials)
         self.attend(qkv, attn, ctx, step, g, k_layer, v_layer, page_stride)
         return self.o.forward(attn, out_dtype=x.dtype, allow_partials=True)
+
+    def _fused_qkv(self, x: torch.Tensor, n: int, cos: torch.Tensor) -> bool:
+        """Whether the step's q, k, v come from the tcgen05 product with bias,
+        rotation and cache write in its epilogue: bfloat16, head size 128
+        rotated as a whole, and rows enough that it beats the library product
+        followed by the separate kernel.  It does when its tiles of 256 x 256
+        fill the rounds that the pairs of SMs make over them (measured, us,
+        fused against separate: 7B sizes 2,048 rows 49.7 / 58.0, 2,560 rows
+        67.3 / 78.5, 4,096 rows 91 / 106; 14B sizes 2,048 rows 111 / 120; 3B
+        sizes 4,096 rows 44 / 50) and not otherwise (7B 1,024 rows 32.7 / 30.5,
+        1,536 rows 49.2 / 43.2; 3B 2,048 rows, 80 tiles for 74 pairs, 31.0 /
+        27.5)."""
+        if not (n >= FUSED_QKV_MIN_ROWS and x.dtype == torch.bfloat16 and self.qkv.weight.dtype == torch.bfloat16
+                and self.qkv.bias is None and self.head_dim == ops.QKV_EPILOGUE_HEAD_DIM
+                and 2 * cos.shape[1] == self.head_dim and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                and self.qkv.in_features % 8 == 0):
+            return False
+        pairs = max(1, ops.sm_count(x.device) // 2)
+        tiles = ((n + 255) // 256) * ((self.qkv.out_features + 255) // 256)
+        filled = tiles / (((tiles + pairs - 1) // pairs) * pairs)
+        return filled >= 0.75 or (n >= 2 * FUSED_QKV_MIN_ROWS and filled >= 0.70)
 
     def attend(self, qkv, attn, ctx, step, g, k_layer, v_layer, page_stride) -> None:
         """bfloat16 with a head size the tensor-core kernels take: prompt

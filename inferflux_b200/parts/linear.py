@@ -34,11 +34,15 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         self.bias = None if bias is None else bias.to(torch.float32).contiguous()
 
-    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False):
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, allow_partials: bool = False,
+                f32_sums: bool = False):
         """x [M, in] -> [M, out] in ``out_dtype`` (default: x's type).  With
         ``allow_partials`` the result may be a :class:`PartialSums` (the
         weight-streaming kernel cuts K between blocks when a matrix has too few
-        rows to fill the GPU)."""
+        rows to fill the GPU).  With ``f32_sums`` on top of that, a bfloat16
+        product always comes as float32 sums (one slice from the library): for
+        a consumer that computes on with the sums, to which a rounding to
+        bfloat16 in between would only add error."""
         m = x.shape[0]
         out_dtype = out_dtype or x.dtype
         w = self.weight
@@ -59,6 +63,9 @@ class Linear:
             if splits > 1:
                 y = torch.empty((splits, m, self.out_features), dtype=torch.float32, device=x.device)
                 return PartialSums(ops.gemv_bf16(x, w, self.bias, y, k_splits=splits))
+            if allow_partials and f32_sums:
+                y = torch.empty((m, self.out_features), dtype=torch.float32, device=x.device)
+                return PartialSums(ops.gemv_bf16(x, w, self.bias, y).unsqueeze(0))
             y = torch.empty((m, self.out_features), dtype=out_dtype, device=x.device)
             return ops.gemv_bf16(x, w, self.bias, y)
         if (allow_partials and self.bias is None and m <= FEW_ROWS and self.in_features >= FEW_ROWS_MIN_K
@@ -66,6 +73,8 @@ class Linear:
             parts = ops.gemm_umma_skinny_parts(self.out_features, self.in_features)
             y = torch.empty((parts, m, self.out_features), dtype=torch.float32, device=x.device)
             return PartialSums(ops.gemm_umma_skinny(x, w, y))
+        if allow_partials and f32_sums and self.bias is None:
+            return PartialSums(ops.matmul_library(x, w, torch.float32).unsqueeze(0))
         y = ops.matmul_library(x, w, torch.float32 if (out_dtype == torch.float32 or self.bias is not None)
                                else torch.bfloat16)
         if self.bias is not None:

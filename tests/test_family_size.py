@@ -76,6 +76,7 @@ class Oracle:
         vocab = self.cfg["vocab_size"]
         self.seqs = {f"long{i}": random_tokens(vocab, n, 200 + i) for i, n in enumerate(LONG)}
         self.seqs.update({f"short{i}": random_tokens(vocab, 30, 300 + i) for i in range(N_SHORT)})
+        self.seqs["prompt2048"] = random_tokens(vocab, 2048 + 8, 400)
         self._hidden = {}
 
     def hidden(self, key):
@@ -262,6 +263,29 @@ def test_a_long_portion_beside_single_tokens(family, oracle):
             key, _, n = _short(oracle, int(e.rid[1:]))
             check.add(logits[row:row + 1], key, [n], "a single token beside the portion")
             row += 1
+    check.finish()
+
+
+def test_a_prompt_of_2048_tokens_in_one_step(family, oracle):
+    """2,048 tokens in one step and the next 8 one by one.  At the 7B sizes in
+    bfloat16 this is where q, k and v come from the tcgen05 product that adds
+    the bias, rotates and writes the cache in its epilogue (144 tiles for 74
+    pairs of SMs); the single tokens that follow read the keys and values it
+    wrote.  The same prompt in two steps of 1,024 takes the separate kernels."""
+    from inferflux_b200 import StepEntry
+    if oracle.cfg["hidden_size"] != 3584:
+        pytest.skip("the plain implementation follows one sequence of this length only, at the 7B sizes")
+    dtype, make = family
+    eng = make(4096 + 128)
+    check = Checker(oracle, dtype)
+    toks = oracle.seqs["prompt2048"]
+    want = [0, 1, 255, 256, 1023, 1024, 2047]
+    check.add(eng.run_step([StepEntry("a", toks[:2048], want)]), "prompt2048", want, "2,048 tokens in one step")
+    for p in range(8):
+        check.add(eng.run_step([StepEntry("a", [toks[2048 + p]], [0])]), "prompt2048", [2048 + p], "one by one behind them")
+    eng.run_step([StepEntry("b", toks[:1024], [])])
+    check.add(eng.run_step([StepEntry("b", toks[1024:2048], [1023])]), "prompt2048", [2047], "in two steps of 1,024")
+    check.add(eng.run_step([StepEntry("b", [toks[2048]], [0])]), "prompt2048", [2048], "one token behind two steps")
     check.finish()
 
 

@@ -43,6 +43,22 @@ def _check_greedy(cfg, w, prompt, tokens, dtype):
         seq.append(t)
 
 
+def _same_tokens(cfg, w, prompt, sp, want, got, dtype):
+    """The two runs gave the same tokens.  In bfloat16 two schedules round differently (a token's keys come
+    from another product when its request starts again), so a greedy request may part ways where the plain
+    implementation's two best logits, penalties applied, lie within the tolerance of each other: then both
+    tokens must be among those, and what follows is no longer compared."""
+    if want == got:
+        return
+    assert dtype == "bfloat16" and sp.temperature == 0.0, (want, got)
+    j = next(i for i, (a, b) in enumerate(zip(want, got)) if a != b)
+    seq = list(prompt) + list(want[:j])
+    logits = plain.apply_penalties(plain.forward(cfg, w, seq)[-1], seq[-sp.penalty_last_n:], sp.repetition_penalty,
+                                   sp.frequency_penalty, sp.presence_penalty)
+    for t in (want[j], got[j]):
+        assert float(logits.max() - logits[t]) <= 2 * TOL[dtype] * float(logits.abs().max()), (j, t)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "D", "E"])
 def test_greedy_generation_through_the_entry_point(folders, name, dtype):
@@ -374,8 +390,8 @@ def test_penalties_from_the_device_run_ahead_and_survive_preemption(folders, dty
     tight = _engine(folder, dtype, kv_cache_tokens=192)
     got = tight.generate(prompts, params)
     assert tight.stats["preemptions"] > 0
-    for a, b in zip(want, got):
-        assert a.tokens == b.tokens
+    for a, b, p, sp in zip(want, got, prompts, params):
+        _same_tokens(cfg, w, p, sp, a.tokens, b.tokens, dtype)
     # a window beyond the rings beside one within them
     long_window = [SamplingParams(temperature=0.0, max_tokens=30, repetition_penalty=1.3, penalty_last_n=1000, ignore_eos=True),
                    params[1]]

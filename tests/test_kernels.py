@@ -435,6 +435,59 @@ def test_decode_attention_prepares_its_own_qkv(ops, nh, nkv, hd, ps, window, n_p
             assert (got - v_new[:, :, None, :]).abs().max() < 0.05, "the output is not the token's own value"
 
 
+@pytest.mark.parametrize("m,nh,nkv,k,ps,with_bias", [(300, 3, 1, 200, 16, True), (513, 5, 2, 1096, 64, False),
+                                                     (2048, 28, 4, 3584, 16, True), (70, 2, 2, 64, 4, True)])
+def test_gemm_umma_qkv_epilogue(ops, m, nh, nkv, k, ps, with_bias):
+    """The tcgen05 product of the stacked q, k, v projection with bias, rotation and cache write in its
+    epilogue, against the product in float64 followed by the plain formulas; tokens with slot -1 leave the
+    cache alone; an odd number of heads leaves the last tile half empty."""
+    hd, g = 128, torch.Generator().manual_seed(90 + m)
+    width = (nh + 2 * nkv) * hd
+    x = (torch.randn((m, k), generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((width, k), generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn((width,), generator=g) * 0.5 if with_bias else None
+    ang = torch.randn((m, hd // 2), generator=g) * 3.0
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    pages = (m + ps - 1) // ps + 3
+    perm = torch.randperm(pages * ps, generator=g)[:m].to(torch.int32)
+    perm[5] = -1
+    perm[m - 1] = -1
+    pool = torch.full((pages, 1, 2, nkv, ps, hd), 7.0, dtype=torch.bfloat16)
+    # plain: float64 product, bias, rotate-half
+    prod = x.double() @ w.double().t()
+    if bias is not None:
+        prod = prod + bias.double()
+    heads = prod.view(m, nh + 2 * nkv, hd)
+    lo, hi = heads[:, :nh + nkv, :hd // 2], heads[:, :nh + nkv, hd // 2:]
+    c, s_ = cos.double()[:, None, :], sin.double()[:, None, :]
+    rot = torch.cat([lo * c - hi * s_, hi * c + lo * s_], dim=-1)
+    want_q, want_k, want_v = rot[:, :nh], rot[:, nh:], heads[:, nh + nkv:]
+    xd, wd, pd = x.to(DEV), w.to(DEV), pool.to(DEV)
+    q_out = torch.full((m, width), 3.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_umma_qkv(xd, wd, None if bias is None else bias.to(DEV), q_out, cos.to(DEV), sin.to(DEV), perm.to(DEV),
+                      pd[0, 0, 0], pd[0, 0, 1], pd.stride(0), ps, nh, nkv)
+    ops.check_device_errors(DEV)
+    _close(q_out[:, :nh * hd].float().cpu(), want_q.reshape(m, nh * hd).float(), 1.5e-2, "rotated queries")
+    assert torch.all(q_out[:, nh * hd:] == 3.0), "columns beyond the queries were written"
+    got = pd.float().cpu()
+    seen = torch.zeros((pages, ps), dtype=torch.bool)
+    for t in range(m):
+        sl = int(perm[t])
+        if sl < 0:
+            continue
+        seen[sl // ps, sl % ps] = True
+        _close(got[sl // ps, 0, 0, :, sl % ps], want_k[t].float(), 1.5e-2, f"key of token {t}")
+        _close(got[sl // ps, 0, 1, :, sl % ps], want_v[t].float(), 1.5e-2, f"value of token {t}")
+    untouched = got.permute(0, 4, 1, 2, 3, 5)[~seen]
+    assert torch.all(untouched == 7.0), "a slot that belongs to no token was written"
+    # beside the library product followed by the kernel that does the same on its bfloat16 rows
+    qkv = ops.matmul_library(xd, wd, torch.bfloat16)
+    pd2 = pool.to(DEV)
+    ops.qkv_rope_kv_write(qkv, None if bias is None else bias.to(DEV), cos.to(DEV), sin.to(DEV), perm.clamp(min=0).to(DEV),
+                          pd2[0, 0, 0], pd2[0, 0, 1], pd2.stride(0), ps, nh, nkv, hd)
+    _close(q_out[:, :nh * hd].float().cpu(), qkv[:, :nh * hd].float().cpu(), 3e-2, "beside the separate kernels")
+
+
 # --------------------------------------------------------------------- sampling
 def test_qkv_rope_from_partial_sums(ops):
     """The RoPE + cache-write kernel given float32 partial sums of the product
