@@ -359,6 +359,10 @@ def test_attention_long_context_far_key(ops):
     """4,000 cached keys; the query matches key 3 only: a fault in an early page shows."""
     for fast, umma in ((False, False), (True, False), (True, True)):
         _attention_case(ops, torch.bfloat16, 4, 1, 128, 16, None, [(4000, 1), (3990, 40)], 22, True, fast, umma)
+    # the tcgen05 kernel over 9,000 keys: two query tiles a block and one tile on both halves, 140 key tiles each;
+    # and a window of 1,000 keys over pages of 64 (the first pages given back)
+    _attention_case(ops, torch.bfloat16, 2, 1, 128, 16, None, [(9000, 1), (8700, 300)], 24, True, True, True)
+    _attention_case(ops, torch.bfloat16, 3, 3, 128, 64, 1000, [(5000, 290), (4990, 1)], 25, True, True, True)
 
 
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(28, 4, 128, 16, None), (5, 1, 64, 8, None), (40, 2, 128, 16, None),
