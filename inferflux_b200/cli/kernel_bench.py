@@ -17,6 +17,7 @@ Library kernels carry no stamp: their time counts toward the kernel before them.
 """
 from __future__ import annotations
 
+import os
 import argparse
 import sys
 
@@ -170,7 +171,11 @@ class Case:
                             qs, ql, cs, pos, pms, nh, nkv, hd, scale, 0, s)))
             else:
                 umma = name.endswith("umma")
-                tiles = [(0, q0) for q0 in range(0, q_len, ops.UMMA_ATTENTION_TILE if umma else 64)]
+                # the tile height as the attention part picks it: 128 where tiles of 256 would leave SMs idle
+                full = ops.UMMA_ATTENTION_TILE
+                utile = full // 2 if 2 * ((q_len + full - 1) // full) * nh <= ops.sm_count(DEV) else full
+                utile = int(os.environ.get("INFERFLUX_B200_BENCH_TILE_ROWS", utile))
+                tiles = [(0, q0) for q0 in range(0, q_len, utile if umma else 64)]
                 te, tq = it([t[0] for t in tiles]), it([t[1] for t in tiles])
                 kernel = ops.attn_prefill_umma if umma else ops.attn_prefill_bf16
                 # causal: query i sees ctx - q_len + i + 1 keys
@@ -179,8 +184,8 @@ class Case:
                 extra = ()
                 if umma:
                     splits = ops.attn_prefill_umma_splits(len(tiles), nh, ctx)
-                    self.note = f"splits={splits}"
-                    extra = (splits,)
+                    self.note = f"splits={splits} tiles of {utile}"
+                    extra = (splits, utile)
                 self.run = lambda i: kernel(q, q.stride(0), out, pools[i][0, 0, 0], pools[i][0, 0, 1],
                                                            pools[i].stride(0), ps, bt, te, tq, len(tiles), qs, ql, cs, nh,
                                                            nkv, hd, scale, 0, *extra)

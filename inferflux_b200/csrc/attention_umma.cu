@@ -169,7 +169,8 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                          const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          int page_size, int page_shift, UmmaMeta m, const int* __restrict__ tile_entry,
                          const int* __restrict__ tile_q0, int n_heads, int n_kv, float scale, int window,
-                         int* __restrict__ error_flag, float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
+                         int* __restrict__ error_flag, float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits,
+                         int tile_rows) {
   // The kernel before this one (it rotates the queries and writes the new keys and values) is waited for only
   // where its results are first read or the scratch of an earlier launch first written; until then the block
   // reads the step's description, sets up its barriers and gets its tensor memory.
@@ -192,7 +193,7 @@ attn_prefill_umma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   // tiles run last to first and heads fastest: the longest blocks (of every head) start first
   const int tile = gridDim.y - 1 - blockIdx.y;
   const int e = tile_entry[tile], q0 = tile_q0[tile], head = blockIdx.x;
-  const int rows_all = min(2 * UM, m.entry_q_len[e] - q0);
+  const int rows_all = min(tile_rows, m.entry_q_len[e] - q0);       // tile_rows: 256, or 128 (every tile on both slots)
   if (rows_all <= 0) return;
   const int tok0 = m.entry_q_start[e] + q0;
   const int pos0 = m.entry_ctx_start[e] + q0;
@@ -643,14 +644,15 @@ constexpr int MERGE_ROWS = 8, MERGE_MAX_SPLITS = 64, MERGE_BATCH = 8;
 __global__ void __launch_bounds__(UD)
 attn_prefill_umma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                bf16* __restrict__ out, long long out_stride, UmmaMeta m,
-                               const int* __restrict__ tile_entry, const int* __restrict__ tile_q0, int n_heads, int n_splits) {
+                               const int* __restrict__ tile_entry, const int* __restrict__ tile_q0, int n_heads, int n_splits,
+                               int tile_rows) {
   pdl_launch_dependents();
   __shared__ float ml_s[MERGE_ROWS][MERGE_MAX_SPLITS][2];
   __shared__ float f_s[MERGE_ROWS][MERGE_MAX_SPLITS];
   __shared__ float inv_s[MERGE_ROWS];
   const int head = blockIdx.x, tile = blockIdx.y, r0 = blockIdx.z * MERGE_ROWS, d = threadIdx.x;
   const int e = tile_entry[tile], q0 = tile_q0[tile];               // (the step's description: there before any kernel)
-  const int rows = min(2 * UM, m.entry_q_len[e] - q0);
+  const int rows = min(tile_rows, m.entry_q_len[e] - q0);
   if (r0 >= rows) return;
   const int tok0 = m.entry_q_start[e] + q0;
   pdl_wait();                                                      // the parts are written
@@ -740,7 +742,9 @@ IFX_API int ifx_attn_prefill_umma_plan(int n_tiles, int n_heads, int max_key_til
   return s < 1 ? 1 : s;
 }
 
-// Prompt portions, head_dim 128, query tiles of 256 tokens of one entry (tile_entry / tile_q0).
+// Prompt portions, head_dim 128, query tiles of tile_rows = 256 or 128 tokens of one entry (tile_entry / tile_q0;
+// with 128 every tile's key tiles are dealt out to both halves of its block: twice the blocks, for steps whose
+// tiles of 256 would leave SMs idle).
 // q rows, out rows, k_layer and v_layer 16-byte aligned.  error_flag: a device int set to 1 if a bounded
 // wait inside the kernel ran out (the output is then invalid).  n_splits > 1: scratch part_o float32
 // [n_tiles * n_heads * n_splits * 256 * 128] (16-byte aligned) and part_ml float32 [n_tiles * n_heads * n_splits * 256 * 2].
@@ -750,9 +754,10 @@ IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, 
                                   int n_tiles, const int* entry_q_start, const int* entry_q_len,
                                   const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
                                   int window, int* error_flag, float* part_o, float* part_ml, int n_splits,
-                                  int num_pages, cudaStream_t stream) {
+                                  int num_pages, int tile_rows, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (head_dim != UD || n_kv < 1 || n_heads % n_kv || n_tiles > 65535 || !error_flag) return IFX_ERR_UNSUPPORTED;
+  if (tile_rows != UM && tile_rows != 2 * UM) return IFX_ERR_UNSUPPORTED;
   if (n_splits < 1 || n_splits > MERGE_MAX_SPLITS || (n_splits > 1 && (!part_o || !part_ml))) return IFX_ERR_UNSUPPORTED;
   if (n_splits > 1 && ((uintptr_t)part_o & 15)) return IFX_ERR_ALIGNMENT;
   if (page_size <= 0 || (page_size & (page_size - 1)) || num_pages < 1) return IFX_ERR_UNSUPPORTED;
@@ -769,10 +774,10 @@ IFX_API int ifx_attn_prefill_umma(const void* q, long long q_stride, void* out, 
   if (e != cudaSuccess) return (int)e;
   ifx_rc = launch_pdl(attn_prefill_umma_kernel, dim3(n_heads, n_tiles, n_splits), dim3(U_THREADS), SMEM_UMMA, stream,
                       (const bf16*)q, q_stride, (bf16*)out, out_stride, map_k, map_v, page_size, page_shift, m,
-                      tile_entry, tile_q0, n_heads, n_kv, scale, window, error_flag, part_o, part_ml, n_splits);
+                      tile_entry, tile_q0, n_heads, n_kv, scale, window, error_flag, part_o, part_ml, n_splits, tile_rows);
   if (!ifx_rc) ifx_rc = IFX_LAUNCH_CHECK();
   if (ifx_rc || n_splits == 1) return ifx_rc;
-  ifx_rc = launch_pdl(attn_prefill_umma_merge_kernel, dim3(n_heads, n_tiles, 2 * UM / MERGE_ROWS), dim3(UD), 0, stream, (const float*)part_o,
-                      (const float*)part_ml, (bf16*)out, out_stride, m, tile_entry, tile_q0, n_heads, n_splits);
+  ifx_rc = launch_pdl(attn_prefill_umma_merge_kernel, dim3(n_heads, n_tiles, tile_rows / MERGE_ROWS), dim3(UD), 0, stream, (const float*)part_o,
+                      (const float*)part_ml, (bf16*)out, out_stride, m, tile_entry, tile_q0, n_heads, n_splits, tile_rows);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }

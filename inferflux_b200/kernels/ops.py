@@ -88,7 +88,7 @@ def _lib():
         lib.ifx_attn_prefill_umma.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                               c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-                                              c_void_p, c_int, c_int, c_void_p]
+                                              c_void_p, c_int, c_int, c_int, c_void_p]
         lib.ifx_attn_prefill_umma_plan.argtypes = [c_int, c_int, c_int]
         lib.ifx_attn_prefill_umma_plan.restype = c_int
         lib.ifx_argmax.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
@@ -516,10 +516,12 @@ def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
                       tile_entry: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
                       entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor,
                       n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
-                      n_splits: int = 1) -> torch.Tensor:
+                      n_splits: int = 1, tile_rows: int = 256) -> torch.Tensor:
     """Attention of prompt portions with tcgen05.mma and tensor-memory
-    accumulators (bfloat16, head_dim 128); query tiles of 256 tokens listed by
-    tile_entry / tile_q0.  With ``n_splits`` > 1 the keys of every tile are cut
+    accumulators (bfloat16, head_dim 128); query tiles of ``tile_rows`` = 256 or
+    128 tokens listed by tile_entry / tile_q0 (a block takes a tile and a head;
+    with 128 the tile's key tiles are dealt out to both halves of the block:
+    twice the blocks, for steps whose tiles of 256 would leave SMs idle).  With ``n_splits`` > 1 the keys of every tile are cut
     into that many parts (see :func:`attn_prefill_umma_splits`), merged by a
     second kernel.  A bounded wait that runs out sets the device error flag
     (see :func:`check_device_errors`)."""
@@ -545,7 +547,7 @@ def attn_prefill_umma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer
                                         _ptr(tile_entry), _ptr(tile_q0), n_tiles, _ptr(entry_q_start),
                                         _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, n_kv, head_dim,
                                         float(scale), int(window), _ptr(error_flag(q.device)), _ptr(part_o),
-                                        _ptr(part_ml), int(n_splits), int(num_pages), _stream()),
+                                        _ptr(part_ml), int(n_splits), int(num_pages), int(tile_rows), _stream()),
            "attn_prefill_umma")
     return out
 

@@ -62,9 +62,10 @@ class AttentionStep:
     chunk_tile_entry: torch.Tensor            # [Tc] tiles of CHUNK_TILE tokens over entries with more than one token
     chunk_tile_q0: torch.Tensor
     n_chunk_tiles: int
-    umma_tile_entry: torch.Tensor             # [Tu] tiles of UMMA_TILE tokens over the same entries
+    umma_tile_entry: torch.Tensor             # [Tu] tiles of umma_tile_rows tokens over the same entries
     umma_tile_q0: torch.Tensor
     n_umma_tiles: int
+    umma_tile_rows: int                       # UMMA_TILE, or half of it where tiles that high would leave SMs idle
     decode_entries: torch.Tensor              # [D] entries that bring exactly one token
     n_decode: int
     decode_skewed: bool                       # their contexts differ much in length (contexts_skewed)
@@ -86,6 +87,14 @@ class GQAttention(Part):
     # -- the step's description, once for all attention layers ------------
     def describe_step(self, layout, put) -> AttentionStep:
         tile_entry, tile_q0, ctile_entry, ctile_q0, utile_entry, utile_q0, dec = [], [], [], [], [], [], []
+        # The tcgen05 kernel gives a block (an SM) to a tile and head.  Tiles of 256 tokens share their key tiles
+        # between two query tiles; where they would take half the SMs or fewer, tiles of 128 make twice the
+        # blocks (measured, 7B shapes: 512 tokens at 2,048 of context 26.6 against 37.4 us, 512 alone 11.7 / 14.6;
+        # at 768 and 1,024 tokens, 84 and 112 blocks of 256, the higher tiles win by up to a tenth).
+        portions = [int(n) for n in layout.q_len[:layout.n_entries] if int(n) > 1]
+        blocks = sum((n + UMMA_TILE - 1) // UMMA_TILE for n in portions) * self.n_heads
+        on_gpu = torch.device(self.device).type == "cuda"
+        utile = UMMA_TILE // 2 if portions and on_gpu and 2 * blocks <= ops.sm_count(self.device) else UMMA_TILE
         for i in range(layout.n_entries):
             ln = int(layout.q_len[i])
             if ln == 1:
@@ -95,11 +104,11 @@ class GQAttention(Part):
                 tile_entry.append(i), tile_q0.append(q0)
             for q0 in range(0, ln, CHUNK_TILE):
                 ctile_entry.append(i), ctile_q0.append(q0)
-            for q0 in range(0, ln, UMMA_TILE):
+            for q0 in range(0, ln, utile):
                 utile_entry.append(i), utile_q0.append(q0)
         return AttentionStep(
             put(tile_entry), put(tile_q0), len(tile_entry), put(ctile_entry), put(ctile_q0), len(ctile_entry),
-            put(utile_entry), put(utile_q0), len(utile_entry), put(dec), len(dec),
+            put(utile_entry), put(utile_q0), len(utile_entry), utile, put(dec), len(dec),
             contexts_skewed([int(layout.ctx_start[i]) + 1 for i in dec]))
 
     def step_shape(self, layout) -> tuple:
@@ -250,7 +259,8 @@ class GQAttention(Part):
             splits = ops.attn_prefill_umma_splits(step.n_umma_tiles, self.n_heads, max_keys)
             ops.attn_prefill_umma(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
                                   ctx.block_tables[g], step.umma_tile_entry, step.umma_tile_q0, step.n_umma_tiles,
-                                  *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, splits)
+                                  *common, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, splits,
+                                  tile_rows=step.umma_tile_rows)
         elif step.n_chunk_tiles:
             ops.attn_prefill_bf16(qkv, qkv.stride(0), attn, k_layer, v_layer, page_stride, ctx.page_size,
                                   ctx.block_tables[g], step.chunk_tile_entry, step.chunk_tile_q0, step.n_chunk_tiles,

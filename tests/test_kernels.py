@@ -289,15 +289,16 @@ def _attention_case(ops, dtype, nh, nkv, hd, ps, window, entries, seed, peaked, 
                                nh, nkv, hd, scale, window or 0)
     else:
         if ctiles and umma:
-            utiles = [(e, q0) for e, (c, ql) in enumerate(entries) if ql > 1 for q0 in range(0, ql, ops.UMMA_ATTENTION_TILE)]
-            te, tq = it([t[0] for t in utiles]).to(DEV), it([t[1] for t in utiles]).to(DEV)
-            for splits in (1, 2, 5):                      # the keys of a query tile in one part and cut into parts
-                out_u = out.clone()
-                ops.attn_prefill_umma(qd, nh * hd, out_u, *args, te, tq, len(utiles), md["q_start"], md["q_len"],
-                                      md["ctx_start"], nh, nkv, hd, scale, window or 0, splits)
-                ops.check_device_errors(DEV)
-                rows = [r for e, (c, ql) in enumerate(entries) if ql > 1 for r in range(q_start[e], q_start[e] + ql)]
-                _close(out_u[rows], want[rows], 1.5e-2, f"prompt attention, keys in {splits} parts")
+            for tile_rows, parts in ((ops.UMMA_ATTENTION_TILE, (1, 2, 5)), (ops.UMMA_ATTENTION_TILE // 2, (1, 3))):
+                utiles = [(e, q0) for e, (c, ql) in enumerate(entries) if ql > 1 for q0 in range(0, ql, tile_rows)]
+                te, tq = it([t[0] for t in utiles]).to(DEV), it([t[1] for t in utiles]).to(DEV)
+                for splits in parts:                      # the keys of a query tile in one part and cut into parts
+                    out_u = out.clone()
+                    ops.attn_prefill_umma(qd, nh * hd, out_u, *args, te, tq, len(utiles), md["q_start"], md["q_len"],
+                                          md["ctx_start"], nh, nkv, hd, scale, window or 0, splits, tile_rows)
+                    ops.check_device_errors(DEV)
+                    rows = [r for e, (c, ql) in enumerate(entries) if ql > 1 for r in range(q_start[e], q_start[e] + ql)]
+                    _close(out_u[rows], want[rows], 1.5e-2, f"prompt attention, tiles of {tile_rows}, keys in {splits} parts")
             out = out_u
         elif ctiles:
             te, tq = it([t[0] for t in ctiles]).to(DEV), it([t[1] for t in ctiles]).to(DEV)
