@@ -457,15 +457,16 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       const float* st = prep.sin_t + (size_t)tok * HALF;
       const int slot = (prep.slot_map && ke == len) ? prep.slot_map[tok] : -1;   // ke == len: the token's own position is ours
       const int q_items = nrows * HV, k_items = slot >= 0 ? HV : 0, v_items = slot >= 0 ? HD / 8 : 0;
-      auto items = [&](auto part_tag) {
+      auto items = [&](auto part_tag, auto batch_tag) {
         constexpr bool PART = decltype(part_tag)::value;
+        constexpr int NB = decltype(batch_tag)::value;            // slices asked for together
         for (int w = tid; w < q_items + k_items + v_items; w += 128) {
           if (w < q_items + k_items) {
             const bool is_q = w < q_items;
             const int hl = is_q ? w / HV : 0, i = (is_q ? w - hl * HV : w - q_items) * 8;
             const int base = (is_q ? h0 + hl : n_heads + kvh) * HD;
             uint4 lo, hi;
-            rope_pairs8<PART>(row, part, prep.n_partials, prep.part_stride, prep.bias, ct, st, base + i, HALF, i, lo, hi);
+            rope_pairs8<PART, NB>(row, part, prep.n_partials, prep.part_stride, prep.bias, ct, st, base + i, HALF, i, lo, hi);
             bf16* dst = is_q ? q_s + hl * HD
                              : (bf16*)kv.k + (size_t)(slot >> kv.page_shift) * kv.page_stride + (size_t)kvh * kv.head_stride +
                                    (size_t)(slot & (kv.page_size - 1)) * HD;
@@ -476,11 +477,13 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
             bf16* dst = (bf16*)kv.v + (size_t)(slot >> kv.page_shift) * kv.page_stride + (size_t)kvh * kv.head_stride +
                         (size_t)(slot & (kv.page_size - 1)) * HD;
             *reinterpret_cast<uint4*>(dst + d) =
-                biased8<PART>(row, part, prep.n_partials, prep.part_stride, prep.bias, (n_heads + n_kv + kvh) * HD + d);
+                biased8<PART, NB>(row, part, prep.n_partials, prep.part_stride, prep.bias, (n_heads + n_kv + kvh) * HD + d);
           }
         }
       };
-      if (part) items(std::true_type{}); else items(std::false_type{});
+      if (!part) items(std::false_type{}, std::integral_constant<int, 1>{});
+      else if (prep.n_partials == 1) items(std::true_type{}, std::integral_constant<int, 1>{});   // (the library's float32 product)
+      else items(std::true_type{}, std::integral_constant<int, 4>{});
       if (slot >= 0) __threadfence();                           // the key and value are in memory before the tile that holds them is copied
       __syncthreads();
       const unsigned* pq = reinterpret_cast<const unsigned*>(q_s + (size_t)g * HD);

@@ -368,7 +368,7 @@ def test_attention_long_context_far_key(ops):
 
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(28, 4, 128, 16, None), (5, 1, 64, 8, None), (40, 2, 128, 16, None),
                                                  (14, 2, 128, 4, 129), (3, 3, 64, 32, 40)])
-@pytest.mark.parametrize("n_partials", [0, 3])
+@pytest.mark.parametrize("n_partials", [0, 1, 3])
 @pytest.mark.parametrize("own_key_stands_out", [False, True])
 def test_decode_attention_prepares_its_own_qkv(ops, nh, nkv, hd, ps, window, n_partials, own_key_stands_out):
     """A step of single tokens: the decode kernel that adds the bias, rotates and writes the cache itself gives
