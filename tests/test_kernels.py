@@ -472,7 +472,7 @@ def test_gemm_umma_qkv_epilogue(ops, m, nh, nkv, k, ps, with_bias):
     ops.gemm_umma_qkv(xd, wd, None if bias is None else bias.to(DEV), q_out, cos.to(DEV), sin.to(DEV), perm.to(DEV),
                       pd[0, 0, 0], pd[0, 0, 1], pd.stride(0), ps, nh, nkv)
     ops.check_device_errors(DEV)
-    _close(q_out[:, :nh * hd].float().cpu(), want_q.reshape(m, nh * hd).float(), 1.5e-2, "rotated queries")
+    _close(q_out[:, :nh * hd].float().cpu(), want_q.reshape(m, nh * hd).float(), 6e-3, "rotated queries")
     assert torch.all(q_out[:, nh * hd:] == 3.0), "columns beyond the queries were written"
     got = pd.float().cpu()
     seen = torch.zeros((pages, ps), dtype=torch.bool)
@@ -481,8 +481,8 @@ def test_gemm_umma_qkv_epilogue(ops, m, nh, nkv, k, ps, with_bias):
         if sl < 0:
             continue
         seen[sl // ps, sl % ps] = True
-        _close(got[sl // ps, 0, 0, :, sl % ps], want_k[t].float(), 1.5e-2, f"key of token {t}")
-        _close(got[sl // ps, 0, 1, :, sl % ps], want_v[t].float(), 1.5e-2, f"value of token {t}")
+        _close(got[sl // ps, 0, 0, :, sl % ps], want_k[t].float(), 6e-3, f"key of token {t}")
+        _close(got[sl // ps, 0, 1, :, sl % ps], want_v[t].float(), 6e-3, f"value of token {t}")
     untouched = got.permute(0, 4, 1, 2, 3, 5)[~seen]
     assert torch.all(untouched == 7.0), "a slot that belongs to no token was written"
     # beside the library product followed by the kernel that does the same on its bfloat16 rows
@@ -491,6 +491,23 @@ def test_gemm_umma_qkv_epilogue(ops, m, nh, nkv, k, ps, with_bias):
     ops.qkv_rope_kv_write(qkv, None if bias is None else bias.to(DEV), cos.to(DEV), sin.to(DEV), perm.clamp(min=0).to(DEV),
                           pd2[0, 0, 0], pd2[0, 0, 1], pd2.stride(0), ps, nh, nkv, hd)
     _close(q_out[:, :nh * hd].float().cpu(), qkv[:, :nh * hd].float().cpu(), 3e-2, "beside the separate kernels")
+
+
+def test_gemm_umma_qkv_epilogue_queries_only(ops):
+    """A layer that reads another layer's cache has only queries: no slot map, no cache."""
+    m, nh, k, hd, g = 260, 3, 136, 128, torch.Generator().manual_seed(95)
+    x = (torch.randn((m, k), generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((nh * hd, k), generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    bias = torch.randn((nh * hd,), generator=g) * 0.5
+    ang = torch.randn((m, hd // 2), generator=g) * 3.0
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    heads = (x.double() @ w.double().t() + bias.double()).view(m, nh, hd)
+    lo, hi, c, s_ = heads[..., :hd // 2], heads[..., hd // 2:], cos.double()[:, None, :], sin.double()[:, None, :]
+    want = torch.cat([lo * c - hi * s_, hi * c + lo * s_], dim=-1).reshape(m, nh * hd)
+    q_out = torch.empty((m, nh * hd), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_umma_qkv(x.to(DEV), w.to(DEV), bias.to(DEV), q_out, cos.to(DEV), sin.to(DEV), None, None, None, 0, 16, nh, 0)
+    ops.check_device_errors(DEV)
+    _close(q_out.float().cpu(), want.float(), 6e-3, "rotated queries")
 
 
 # --------------------------------------------------------------------- sampling
