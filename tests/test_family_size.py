@@ -276,7 +276,7 @@ def test_a_prompt_of_2048_tokens_in_one_step(family, oracle):
     if oracle.cfg["hidden_size"] != 3584:
         pytest.skip("the plain implementation follows one sequence of this length only, at the 7B sizes")
     dtype, make = family
-    eng = make(4096 + 128)
+    eng = make(4096 + 256, max_seqs=8)
     check = Checker(oracle, dtype)
     toks = oracle.seqs["prompt2048"]
     want = [0, 1, 255, 256, 1023, 1024, 2047]
@@ -286,6 +286,24 @@ def test_a_prompt_of_2048_tokens_in_one_step(family, oracle):
     eng.run_step([StepEntry("b", toks[:1024], [])])
     check.add(eng.run_step([StepEntry("b", toks[1024:2048], [1023])]), "prompt2048", [2047], "in two steps of 1,024")
     check.add(eng.run_step([StepEntry("b", [toks[2048]], [0])]), "prompt2048", [2048], "one token behind two steps")
+    eng.end_request("a"), eng.end_request("b")
+    # 2,048 rows again, of which three are single tokens of other requests: the same product makes their q, k and v
+    shorts = [_short(oracle, i) for i in range(3)]
+    eng.run_step([StepEntry(f"s{i}", seq[:n], []) for i, (_, seq, n) in enumerate(shorts)])
+    entries = [StepEntry(f"s{i}", [seq[n]], [0]) for i, (_, seq, n) in enumerate(shorts)]
+    entries.insert(1, StepEntry("c", toks[:2045], [2044]))
+    logits = eng.run_step(entries)
+    for row, e in enumerate(entries):
+        if e.rid == "c":
+            check.add(logits[row:row + 1], "prompt2048", [2044], "2,045 tokens beside three single ones")
+        else:
+            key, _, n = shorts[int(e.rid[1:])]
+            check.add(logits[row:row + 1], key, [n], "a single token beside 2,045")
+    logits = eng.run_step([StepEntry(f"s{i}", [seq[n + 1]], [0]) for i, (_, seq, n) in enumerate(shorts)]
+                          + [StepEntry("c", [toks[2045]], [0])])
+    for i, (key, _, n) in enumerate(shorts):
+        check.add(logits[i:i + 1], key, [n + 1], "the next single token")
+    check.add(logits[3:4], "prompt2048", [2045], "one token behind 2,045")
     check.finish()
 
 
