@@ -53,7 +53,7 @@ constexpr int UM = 128;          // query rows per slot; a block has two slots (
 constexpr int UN = 64;           // keys per tile
 constexpr int UD = 128;          // head size
 constexpr int WAIT_LIMIT = 1 << 20;   // tries of at most 2 microseconds each
-constexpr int BT_CACHE_U = 224;  // block-table entries a block keeps in shared memory (static shared memory stays under 1 KB)
+constexpr int BT_CACHE_U = 1024; // block-table entries a block keeps in shared memory (longer ranges are read where they lie)
 constexpr float LOG2E_U = 1.4426950408889634f;
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
