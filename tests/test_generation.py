@@ -77,6 +77,34 @@ def test_greedy_generation_through_the_entry_point(folders, name, dtype):
         assert eng.runner.graph_replays > 0          # decode-only steps ran as captured graphs
 
 
+def test_generate_leaves_the_collector_as_it_found_it(folders):
+    """Engine.generate holds the cycle collector off while it steps and puts it back, also when a step raises."""
+    import gc
+    from inferflux_b200 import SamplingParams
+    folder, cfg, _ = folders["A"]
+    eng = _engine(folder, "bfloat16")
+    seen = []
+    step = eng.step
+    eng.step = lambda: (seen.append(gc.isenabled()), step())[1]
+    assert gc.isenabled()
+    eng.generate([random_tokens(cfg["vocab_size"], 7, 3)], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    assert seen and not any(seen) and gc.isenabled()
+
+    def broken():
+        raise RuntimeError("a step that fails")
+    eng.step = broken
+    with pytest.raises(RuntimeError):
+        eng.generate([random_tokens(cfg["vocab_size"], 7, 4)], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    assert gc.isenabled()
+    gc.disable()
+    try:
+        eng.step = step
+        eng.generate([random_tokens(cfg["vocab_size"], 7, 5)], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+        assert not gc.isenabled()                            # it was off before: it stays off
+    finally:
+        gc.enable()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "D"])
 def test_long_decoding_token_by_token(folders, name, dtype):
