@@ -526,13 +526,18 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       const int key0 = (t_begin + i) * BK + warp * TK;          // this warp's 16 keys of the tile
       if (key0 >= ke || key0 + TK <= kb) continue;              // warp-uniform: nothing of ours in range
       const unsigned stage = ring_addr + (unsigned)((i % DSTAGES) * 2 * BK * HD * 2);
-      float s[4] = {0.f, 0.f, 0.f, 0.f};                        // (key g | g+8) x (head 2*t4 | 2*t4+1)
+      float s[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};   // (key g | g+8) x (head 2*t4 | 2*t4+1)
       {
         unsigned ka[KS][4];                                     // all key fragments first, then the MMAs
 #pragma unroll
         for (int k = 0; k < KS; ++k) ldmatrix_x4_at(ka[k], stage + koff[k]);
 #pragma unroll
-        for (int k = 0; k < KS; ++k) mma_bf16(s, ka[k], qb[k][0], qb[k][1]);
+        for (int k = 0; k < KS; k += 2) {                       // two chains of sums, so an MMA does not wait for the one before it
+          mma_bf16(s, ka[k], qb[k][0], qb[k][1]);
+          if (k + 1 < KS) mma_bf16(s1, ka[k + 1], qb[k + 1][0], qb[k + 1][1]);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[c] += s1[c];
       }
       const bool in0 = key0 + g >= kb && key0 + g < ke, in1 = key0 + g + 8 >= kb && key0 + g + 8 < ke;
       if (!in0) { s[0] = -INFINITY; s[1] = -INFINITY; }
@@ -849,13 +854,18 @@ attn_decode_even_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
     const int key0 = (cs.tile0 + cs.t) * BK + warp * TK;        // this warp's 16 keys of the tile
     if (key0 < ke && key0 + TK > kb) {                          // warp-uniform: something of ours is in range
       const unsigned stage = ring_addr + (unsigned)((i % DSTAGES) * 2 * BK * HD * 2);
-      float s[4] = {0.f, 0.f, 0.f, 0.f};                        // (key g | g+8) x (head 2*t4 | 2*t4+1)
+      float s[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};   // (key g | g+8) x (head 2*t4 | 2*t4+1)
       {
         unsigned ka[KS][4];                                     // all key fragments first, then the MMAs
 #pragma unroll
         for (int k = 0; k < KS; ++k) ldmatrix_x4_at(ka[k], stage + koff[k]);
 #pragma unroll
-        for (int k = 0; k < KS; ++k) mma_bf16(s, ka[k], qb[k][0], qb[k][1]);
+        for (int k = 0; k < KS; k += 2) {                       // two chains of sums, so an MMA does not wait for the one before it
+          mma_bf16(s, ka[k], qb[k][0], qb[k][1]);
+          if (k + 1 < KS) mma_bf16(s1, ka[k + 1], qb[k + 1][0], qb[k + 1][1]);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[c] += s1[c];
       }
       const bool in0 = key0 + g >= kb && key0 + g < ke, in1 = key0 + g + 8 >= kb && key0 + g + 8 < ke;
       if (!in0) { s[0] = -INFINITY; s[1] = -INFINITY; }
