@@ -366,6 +366,28 @@ def test_attention_long_context_far_key(ops):
     _attention_case(ops, torch.bfloat16, 3, 3, 128, 64, 1000, [(5000, 290), (4990, 1)], 25, True, True, True)
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_attention_tensor_core_random_steps(ops, seed):
+    """Ten steps drawn at random (heads, groups, page size, window, up to five entries of single tokens and
+    portions behind contexts of up to 2,500 tokens): the tcgen05 kernel at both tile heights and with the keys
+    in parts, and the decode kernels, against the reference."""
+    import random
+    rnd = random.Random(seed)
+    done = 0
+    while done < 10:
+        nkv, ratio = rnd.choice([1, 2, 3, 4]), rnd.choice([1, 2, 5, 7])
+        ps, window = rnd.choice([4, 8, 16, 32, 64, 128]), rnd.choice([None, None, 40, 129, 300, 1000])
+        entries = [(rnd.choice([0, 0, 1, 17, 63, 64, 100, 255, 256, 300, 700, 1500, 2500]),
+                    rnd.choice([1, 2, 5, 16, 65, 127, 128, 129, 200, 255, 256, 257, 300, 400, 513]))
+                   for _ in range(rnd.randint(1, 5))]
+        if sum(c + q for c, q in entries) > 5000:
+            continue
+        _attention_case(ops, torch.bfloat16, nkv * ratio, nkv, 128, ps, window, entries, rnd.randrange(10 ** 6),
+                        rnd.random() < 0.5, True, True)
+        ops.check_device_errors(DEV)
+        done += 1
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(28, 4, 128, 16, None), (5, 1, 64, 8, None), (40, 2, 128, 16, None),
                                                  (14, 2, 128, 4, 129), (3, 3, 64, 32, 40)])
 @pytest.mark.parametrize("n_partials", [0, 1, 3])
